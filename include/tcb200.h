@@ -1,0 +1,140 @@
+/*
+ * tcb200 — C ABI of the sm_100a kernel library behind the Tensor Comprehensions
+ * execution backend.
+ *
+ * This is the boundary a replacement for the reference's device runtime binds:
+ * where the reference JIT-compiles CUDA-C and launches it with cuLaunchKernel
+ * (tc/core/cuda/cuda_rtc.cc:299-387, reached from CudaTcExecutor::uncheckedRun,
+ * tc/core/cuda/cuda_tc_executor.cc:111-126), the new executor describes the
+ * pattern-matched comprehension as a tcb200_problem_t and calls into this
+ * library.  Plain C types, status codes, caller-owned memory, stream-ordered,
+ * re-entrant: no function here throws, aborts or calls exit().
+ *
+ * All tensor pointers are DEVICE pointers to dense row-major float32 data owned
+ * by the caller (the reference's layout: docs/source/semantics.rst:17-19).
+ */
+#ifndef TCB200_H_
+#define TCB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TCB200_ABI_VERSION 1
+
+/* Opaque CUDA stream handle; identical to cudaStream_t / CUstream. */
+typedef struct CUstream_st* tcb200_stream_t;
+
+/* Kernel families a comprehension can be matched to. */
+enum {
+  TCB200_FAMILY_CONTRACTION = 1, /* C(b,m,n) (+)= sum_k A(b,m,k) * B(b,n,k)  [+bias] [relu] */
+  TCB200_FAMILY_TENSORDOT = 2,   /* O(n,c1,c3,p) = sum_c2 I0(n,c1,c2,p) * I1(n,c2,c3,p), tiny C2,C3 */
+  TCB200_FAMILY_GROUP_CONV = 3   /* O(n,g,f,h,w) = sum_{c,kh,kw} I(n,g,c,h+kh,w+kw) * W(g,f,c,kh,kw) [+B(g,f)] */
+};
+
+/* Elementwise statements fused after the reduction (how the reference's TCs
+ * spell bias and ReLU: tc/library/fcrelu.h:24-26). */
+enum {
+  TCB200_EPI_NONE = 0,
+  TCB200_EPI_BIAS = 1,      /* O = O + bias             */
+  TCB200_EPI_BIAS_RELU = 2, /* O = fmax(O + bias, 0)    */
+  TCB200_EPI_RELU = 3       /* O = fmax(O, 0)           */
+};
+
+/* Kernel variants inside a family (the tile sweep behind ATenAutotuner::tune
+ * enumerates them; tc/aten/aten_autotuner.h:73-78 only promises "best first"). */
+enum {
+  TCB200_VARIANT_AUTO = 0,
+  TCB200_VARIANT_SIMT = 1,       /* fp32 FMA, shared-memory tiled                                */
+  TCB200_VARIANT_SIMT_SMALL = 2, /* fp32 FMA, one whole small matrix pair per CTA (batched)      */
+  TCB200_VARIANT_TCGEN05 = 3     /* tcgen05/TMEM tiles fed by TMA, TF32 with optional 3x split   */
+};
+
+/* Status codes (0 = success, negative = error). */
+enum {
+  TCB200_OK = 0,
+  TCB200_ERR_INVALID_ARGUMENT = -1,
+  TCB200_ERR_UNSUPPORTED = -2,   /* no kernel of the library covers this problem/tile: hard error, no fallback */
+  TCB200_ERR_CUDA = -3,          /* a CUDA runtime/driver call failed; tcb200_last_cuda_error() has the code   */
+  TCB200_ERR_ALIGNMENT = -4,     /* a pointer or leading dimension breaks the kernel's alignment rule          */
+  TCB200_ERR_DEVICE_TIMEOUT = -5,/* a bounded device-side wait gave up (reported through dev_status)           */
+  TCB200_ERR_NO_DEVICE = -6,
+  TCB200_ERR_TOO_LARGE = -7
+};
+
+typedef struct tcb200_problem {
+  int32_t family;
+  int32_t epilogue;
+  int32_t accumulate;  /* 0: "+=!" the output is overwritten; 1: "+=" added to what the output holds
+                          (test/cuda/test_compile_and_run.cc:181-200) */
+  int32_t a_k_major;   /* contraction: 1 if A's reduction index is innermost (A(m,k)), 0 if A(k,m) */
+  int32_t b_k_major;   /* contraction: 1 if B's reduction index is innermost (B(n,k)), 0 if B(k,n) */
+  int32_t bias_on_m;   /* contraction: 0 bias is indexed by n (columns), 1 by m (rows) */
+  int64_t batch, M, N, K;
+  int64_t lda, ldb, ldc;                /* leading dimensions, in elements */
+  int64_t stride_a, stride_b, stride_c; /* batch strides, in elements (0 = shared by all batches) */
+  int64_t conv[8];                      /* group conv: N, G, C, F, H, W, KH, KW (valid, unit stride) */
+  int64_t td[5];                        /* tensordot: N, C1, C2, C3, P (P = product of trailing shared dims) */
+} tcb200_problem_t;
+
+/* One point of a family's tile sweep.  Fields a variant does not use are 0. */
+typedef struct tcb200_tile {
+  int32_t variant;
+  int32_t bm, bn, bk;  /* CTA tile (contraction); bm = rows of C1 per CTA (tensordot) */
+  int32_t stages;      /* TMA pipeline depth (tcgen05) */
+  int32_t threads;     /* CTA size */
+  int32_t split_tf32;  /* tcgen05: 1 = one TF32 pass, 3 = 3xTF32 split keeping fp32 accuracy */
+} tcb200_tile_t;
+
+typedef struct tcb200_plan tcb200_plan_t;
+
+/* Library / device probes. */
+int tcb200_abi_version(void);
+const char* tcb200_strerror(int status);
+int tcb200_last_cuda_error(void); /* cudaError_t of the last TCB200_ERR_CUDA on this thread */
+int tcb200_device_count(int* count);
+
+/* Candidate tiles for a problem, preferred first.  Writes at most `max`
+ * entries to `out` and the number available to *n.  Replaces the search space
+ * of the reference's genetic autotuner (tc/autotuner/autotuner-inl.h:326-404). */
+int tcb200_query(const tcb200_problem_t* problem, tcb200_tile_t* out, int max, int* n);
+
+/* Validates problem+tile and records launch geometry for `device`.  tile may be
+ * NULL (family default).  No kernel is launched and no device memory is
+ * allocated.  Replaces CudaBackend::compileWithTcMapper + CudaRTCFunction::Compile
+ * (tc/core/cuda/cuda_tc_executor.cc:71-109, tc/core/cuda/cuda_rtc.cc:265-287). */
+int tcb200_plan_create(const tcb200_problem_t* problem, const tcb200_tile_t* tile,
+                       int device, tcb200_plan_t** plan);
+int tcb200_plan_destroy(tcb200_plan_t* plan);
+
+/* Grid / block the plan launches with (CudaTcExecutor::grid()/block(),
+ * tc/core/cuda/cuda_tc_executor.h:27-66) and a one-line human-readable
+ * description (what TcExecutor::compiledSource holds, tc/core/tc_executor.h:104-106). */
+int tcb200_plan_geometry(const tcb200_plan_t* plan, int64_t grid[3], int64_t block[3]);
+int tcb200_plan_describe(const tcb200_plan_t* plan, char* buf, size_t buflen);
+int tcb200_plan_tile(const tcb200_plan_t* plan, tcb200_tile_t* tile);
+
+/* Enqueues the plan on `stream` of the CURRENT device (which must be the plan's
+ * device) and returns without synchronising.  Replaces CudaRTCFunction::Launch
+ * (tc/core/cuda/cuda_rtc.cc:299-387).
+ *   inputs : contraction {A, B[, bias]}; tensordot {I0, I1}; group conv {I, W[, bias]}
+ *   outputs: {O}
+ *   dev_status: optional device int; a kernel whose bounded wait gives up stores a
+ *               nonzero code there instead of spinning (NULL: not reported).
+ * The plan is immutable: it may be launched concurrently from several host threads
+ * and streams. */
+int tcb200_launch(const tcb200_plan_t* plan, const void* const* inputs, int n_inputs,
+                  void* const* outputs, int n_outputs, tcb200_stream_t stream,
+                  int* dev_status);
+
+/* Writes `bytes` of a rotating pattern to `buf` on `stream`: the bench uses it to
+ * evict L2 between timed launches of the small problems. */
+int tcb200_l2_flush(void* buf, size_t bytes, tcb200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TCB200_H_ */

@@ -1,0 +1,252 @@
+// extern "C" surface of the tcb200 kernel library (declared in include/tcb200.h).
+// Validates arguments, owns the immutable plan objects and dispatches to the
+// kernel families.  Nothing here throws or aborts; every failure is a status code.
+#include <stdio.h>
+#include <string.h>
+
+#include <new>
+
+#include "common.cuh"
+
+namespace tcb200 {
+
+static thread_local cudaError_t g_last_cuda_error = cudaSuccess;
+void set_last_cuda_error(cudaError_t e) { g_last_cuda_error = e; }
+
+namespace {
+
+__global__ void l2_flush_kernel(float4* buf, size_t n4, float v) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4;
+       i += (size_t)gridDim.x * blockDim.x)
+    buf[i] = make_float4(v, v, v, v);
+}
+
+int n_inputs_expected(const tcb200_problem_t& p) {
+  const bool has_bias = p.epilogue == TCB200_EPI_BIAS || p.epilogue == TCB200_EPI_BIAS_RELU;
+  return 2 + (has_bias ? 1 : 0);
+}
+
+const char* variant_name(int v) {
+  switch (v) {
+    case TCB200_VARIANT_SIMT: return "simt";
+    case TCB200_VARIANT_SIMT_SMALL: return "simt_small";
+    case TCB200_VARIANT_TCGEN05: return "tcgen05";
+    default: return "auto";
+  }
+}
+
+const char* epilogue_name(int e) {
+  switch (e) {
+    case TCB200_EPI_BIAS: return "+bias";
+    case TCB200_EPI_BIAS_RELU: return "+bias,relu";
+    case TCB200_EPI_RELU: return "relu";
+    default: return "none";
+  }
+}
+
+}  // namespace
+}  // namespace tcb200
+
+using namespace tcb200;
+
+struct tcb200_plan {
+  Plan impl;
+};
+
+extern "C" {
+
+int tcb200_abi_version(void) { return TCB200_ABI_VERSION; }
+
+const char* tcb200_strerror(int status) {
+  switch (status) {
+    case TCB200_OK: return "success";
+    case TCB200_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case TCB200_ERR_UNSUPPORTED: return "no kernel of this library covers the requested problem/tile";
+    case TCB200_ERR_CUDA: return "a CUDA call failed (see tcb200_last_cuda_error)";
+    case TCB200_ERR_ALIGNMENT: return "pointer or leading dimension violates the kernel's alignment rule";
+    case TCB200_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+    case TCB200_ERR_NO_DEVICE: return "no usable CUDA device";
+    case TCB200_ERR_TOO_LARGE: return "problem exceeds the kernel's size limits";
+    default: return "unknown tcb200 status";
+  }
+}
+
+int tcb200_last_cuda_error(void) { return (int)g_last_cuda_error; }
+
+int tcb200_device_count(int* count) {
+  if (!count) return TCB200_ERR_INVALID_ARGUMENT;
+  int c = 0;
+  cudaError_t e = cudaGetDeviceCount(&c);
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e);
+    (void)cudaGetLastError();
+    *count = 0;
+    return TCB200_ERR_NO_DEVICE;
+  }
+  *count = c;
+  return TCB200_OK;
+}
+
+int tcb200_query(const tcb200_problem_t* problem, tcb200_tile_t* out, int max, int* n) {
+  if (!problem || !n || max < 0 || (max > 0 && !out)) return TCB200_ERR_INVALID_ARGUMENT;
+  *n = 0;
+  switch (problem->family) {
+    case TCB200_FAMILY_TENSORDOT:
+      return tensordot_query(*problem, out, max, n);
+    case TCB200_FAMILY_GROUP_CONV:
+      return group_conv_query(*problem, out, max, n);
+    case TCB200_FAMILY_CONTRACTION: {
+      // tensor-core tiles first (when the contraction is large enough), then the SIMT ones.
+      int n_tc = 0, n_simt = 0;
+      int st = contraction_tc_query(*problem, out, max, &n_tc);
+      if (st != TCB200_OK) return st;
+      const int used = n_tc < max ? n_tc : max;
+      st = contraction_simt_query(*problem, out ? out + used : nullptr, max - used, &n_simt);
+      if (st != TCB200_OK) return st;
+      *n = n_tc + n_simt;
+      return TCB200_OK;
+    }
+    default:
+      return TCB200_ERR_INVALID_ARGUMENT;
+  }
+}
+
+int tcb200_plan_create(const tcb200_problem_t* problem, const tcb200_tile_t* tile, int device,
+                       tcb200_plan_t** plan) {
+  if (!problem || !plan || device < 0) return TCB200_ERR_INVALID_ARGUMENT;
+  *plan = nullptr;
+  tcb200_plan_t* pl = new (std::nothrow) tcb200_plan_t();
+  if (!pl) return TCB200_ERR_INVALID_ARGUMENT;
+  Plan& P = pl->impl;
+  P.p = *problem;
+  if (tile) P.tile = *tile; else memset(&P.tile, 0, sizeof(P.tile));
+  P.device = device;
+  P.kernel_id = 0;
+  int st = TCB200_ERR_INVALID_ARGUMENT;
+  switch (problem->family) {
+    case TCB200_FAMILY_TENSORDOT:
+      st = tensordot_plan(P);
+      break;
+    case TCB200_FAMILY_GROUP_CONV:
+      st = group_conv_plan(P);
+      break;
+    case TCB200_FAMILY_CONTRACTION:
+      if (P.tile.variant == TCB200_VARIANT_AUTO) {
+        // Family default = first candidate of the sweep.
+        tcb200_tile_t first;
+        int n = 0;
+        st = tcb200_query(problem, &first, 1, &n);
+        if (st != TCB200_OK) break;
+        if (n == 0) { st = TCB200_ERR_UNSUPPORTED; break; }
+        P.tile = first;
+      }
+      if (P.tile.variant == TCB200_VARIANT_TCGEN05) st = contraction_tc_plan(P);
+      else st = contraction_simt_plan(P);
+      break;
+    default:
+      break;
+  }
+  if (st != TCB200_OK) {
+    delete pl;
+    return st;
+  }
+  *plan = pl;
+  return TCB200_OK;
+}
+
+int tcb200_plan_destroy(tcb200_plan_t* plan) {
+  delete plan;
+  return TCB200_OK;
+}
+
+int tcb200_plan_geometry(const tcb200_plan_t* plan, int64_t grid[3], int64_t block[3]) {
+  if (!plan || !grid || !block) return TCB200_ERR_INVALID_ARGUMENT;
+  const Launch& l = plan->impl.launch;
+  grid[0] = l.grid.x; grid[1] = l.grid.y; grid[2] = l.grid.z;
+  block[0] = l.block.x; block[1] = l.block.y; block[2] = l.block.z;
+  return TCB200_OK;
+}
+
+int tcb200_plan_tile(const tcb200_plan_t* plan, tcb200_tile_t* tile) {
+  if (!plan || !tile) return TCB200_ERR_INVALID_ARGUMENT;
+  *tile = plan->impl.tile;
+  return TCB200_OK;
+}
+
+int tcb200_plan_describe(const tcb200_plan_t* plan, char* buf, size_t buflen) {
+  if (!plan || !buf || buflen == 0) return TCB200_ERR_INVALID_ARGUMENT;
+  const Plan& P = plan->impl;
+  const tcb200_problem_t& p = P.p;
+  const tcb200_tile_t& t = P.tile;
+  const Launch& l = P.launch;
+  char head[256];
+  switch (p.family) {
+    case TCB200_FAMILY_TENSORDOT:
+      snprintf(head, sizeof(head), "tcb200::tensordot N=%lld C1=%lld C2=%lld C3=%lld P=%lld",
+               (long long)p.td[0], (long long)p.td[1], (long long)p.td[2], (long long)p.td[3],
+               (long long)p.td[4]);
+      break;
+    case TCB200_FAMILY_GROUP_CONV:
+      snprintf(head, sizeof(head),
+               "tcb200::group_conv N=%lld G=%lld C=%lld F=%lld H=%lld W=%lld KH=%lld KW=%lld epilogue=%s",
+               (long long)p.conv[0], (long long)p.conv[1], (long long)p.conv[2],
+               (long long)p.conv[3], (long long)p.conv[4], (long long)p.conv[5],
+               (long long)p.conv[6], (long long)p.conv[7], epilogue_name(p.epilogue));
+      break;
+    default:
+      snprintf(head, sizeof(head),
+               "tcb200::contraction batch=%lld M=%lld N=%lld K=%lld A=%s B=%s epilogue=%s%s",
+               (long long)p.batch, (long long)p.M, (long long)p.N, (long long)p.K,
+               p.a_k_major ? "k-major" : "m-major", p.b_k_major ? "k-major" : "n-major",
+               epilogue_name(p.epilogue), p.accumulate ? " accumulate" : "");
+      break;
+  }
+  snprintf(buf, buflen,
+           "%s | variant=%s tile=%dx%dx%d stages=%d threads=%d split_tf32=%d | grid=(%u,%u,%u) "
+           "block=(%u,%u,%u) smem=%zu",
+           head, variant_name(t.variant), t.bm, t.bn, t.bk, t.stages, t.threads, t.split_tf32,
+           l.grid.x, l.grid.y, l.grid.z, l.block.x, l.block.y, l.block.z, l.smem);
+  return TCB200_OK;
+}
+
+int tcb200_launch(const tcb200_plan_t* plan, const void* const* inputs, int n_inputs,
+                  void* const* outputs, int n_outputs, tcb200_stream_t stream, int* dev_status) {
+  if (!plan || !inputs || !outputs) return TCB200_ERR_INVALID_ARGUMENT;
+  const Plan& P = plan->impl;
+  if (n_inputs != n_inputs_expected(P.p) || n_outputs != 1) return TCB200_ERR_INVALID_ARGUMENT;
+  for (int i = 0; i < n_inputs; ++i)
+    if (!inputs[i]) return TCB200_ERR_INVALID_ARGUMENT;
+  if (!outputs[0]) return TCB200_ERR_INVALID_ARGUMENT;
+  int cur = -1;
+  TCB200_CUDA_TRY(cudaGetDevice(&cur));
+  if (cur != P.device) return TCB200_ERR_INVALID_ARGUMENT;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const float* in0 = static_cast<const float*>(inputs[0]);
+  const float* in1 = static_cast<const float*>(inputs[1]);
+  const float* bias = n_inputs > 2 ? static_cast<const float*>(inputs[2]) : nullptr;
+  float* out = static_cast<float*>(outputs[0]);
+  switch (P.p.family) {
+    case TCB200_FAMILY_TENSORDOT:
+      return tensordot_launch(P, in0, in1, out, s);
+    case TCB200_FAMILY_GROUP_CONV:
+      return group_conv_launch(P, in0, in1, bias, out, s);
+    case TCB200_FAMILY_CONTRACTION:
+      if (P.tile.variant == TCB200_VARIANT_TCGEN05)
+        return contraction_tc_launch(P, in0, in1, bias, out, s, dev_status);
+      return contraction_simt_launch(P, in0, in1, bias, out, s);
+    default:
+      return TCB200_ERR_INVALID_ARGUMENT;
+  }
+}
+
+int tcb200_l2_flush(void* buf, size_t bytes, tcb200_stream_t stream) {
+  if (!buf || bytes < 16 || ((uintptr_t)buf & 15)) return TCB200_ERR_INVALID_ARGUMENT;
+  static unsigned counter = 0;
+  const float v = (float)(++counter & 1023);
+  l2_flush_kernel<<<kNumSMs * 4, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<float4*>(buf), bytes / 16, v);
+  TCB200_CUDA_TRY(cudaGetLastError());
+  return TCB200_OK;
+}
+
+}  // extern "C"

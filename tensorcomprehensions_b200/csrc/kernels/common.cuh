@@ -1,0 +1,100 @@
+// Shared declarations of the tcb200 kernel library (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <algorithm>
+
+#include "tcb200.h"
+
+namespace tcb200 {
+
+constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs; grids are sized in multiples of this
+
+// Launch geometry + resolved tile of one plan.
+struct Launch {
+  dim3 grid{1, 1, 1};
+  dim3 block{1, 1, 1};
+  size_t smem = 0;
+};
+
+struct Plan {
+  tcb200_problem_t p;
+  tcb200_tile_t tile;
+  int device;
+  Launch launch;
+  int kernel_id;  // family-private selector of the instantiated kernel
+};
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+inline int64_t round_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
+
+// Thread-local record of the last failing CUDA call.
+void set_last_cuda_error(cudaError_t e);
+
+#define TCB200_CUDA_TRY(expr)                 \
+  do {                                        \
+    cudaError_t _e = (expr);                  \
+    if (_e != cudaSuccess) {                  \
+      ::tcb200::set_last_cuda_error(_e);      \
+      return TCB200_ERR_CUDA;                 \
+    }                                         \
+  } while (0)
+
+// ---- family entry points (each in its own .cu) ----------------------------------------
+// *_query: append candidate tiles (preferred first); *_plan: validate + fill Launch;
+// *_launch: enqueue.
+
+int tensordot_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n);
+int tensordot_plan(Plan& plan);
+int tensordot_launch(const Plan& plan, const float* I0, const float* I1, float* O, cudaStream_t s);
+
+int contraction_simt_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n);
+int contraction_simt_plan(Plan& plan);
+int contraction_simt_launch(const Plan& plan, const float* A, const float* B, const float* bias,
+                            float* C, cudaStream_t s);
+
+int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n);
+int contraction_tc_plan(Plan& plan);
+int contraction_tc_launch(const Plan& plan, const float* A, const float* B, const float* bias,
+                          float* C, cudaStream_t s, int* dev_status);
+
+int group_conv_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n);
+int group_conv_plan(Plan& plan);
+int group_conv_launch(const Plan& plan, const float* I, const float* W, const float* bias,
+                      float* O, cudaStream_t s);
+
+// ---- small device helpers ---------------------------------------------------------------
+
+__device__ __forceinline__ float4 ldg_stream4(const float4* p) {
+  // Read-once data: bypass L1 allocation so the streamed operand does not evict the reused one.
+  float4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void stg_stream4(float4* p, const float4& v) {
+  asm volatile("st.global.cs.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z),
+               "f"(v.w)
+               : "memory");
+}
+
+template <int EPI>
+__device__ __forceinline__ float apply_epilogue(float acc, float bias) {
+  if (EPI == TCB200_EPI_BIAS) return acc + bias;
+  if (EPI == TCB200_EPI_BIAS_RELU) return fmaxf(acc + bias, 0.0f);
+  if (EPI == TCB200_EPI_RELU) return fmaxf(acc, 0.0f);
+  return acc;
+}
+
+__device__ __forceinline__ float apply_epilogue_rt(int epi, float acc, float bias) {
+  if (epi == TCB200_EPI_BIAS) return acc + bias;
+  if (epi == TCB200_EPI_BIAS_RELU) return fmaxf(acc + bias, 0.0f);
+  if (epi == TCB200_EPI_RELU) return fmaxf(acc, 0.0f);
+  return acc;
+}
+
+}  // namespace tcb200

@@ -1,0 +1,273 @@
+// K1 (SIMT variants) — strided-batched contraction in plain fp32 FMA:
+//   C(b,m,n) (+)= sum_k A(b,m,k) * B(b,n,k)   [+ bias] [relu]
+//
+// Two kernels:
+//   * simt_small: one whole (A_b, B_b) pair per CTA in shared memory.  This is the path
+//     for the reference's batchmatmul benchmark (tc/benchmarks/batchmatmul.cc:80-84:
+//     500 x [26x72]·[72x26]) where each matrix is far below one tensor-core tile and
+//     the problem is bound by HBM and launch latency, not by math.
+//   * simt_tiled: 64x64x16 shared-memory tiles, 4x4 register blocking, any operand
+//     major-ness, any size.  Exact-fp32 path for contractions the tcgen05 kernel does
+//     not take (reduction too short, K not a multiple of 4, "+=" accumulation into
+//     unaligned outputs) and one point of the tile sweep.
+// Both follow the loop nest's semantics (test/test_core.cc:93-127): zero-initialised
+// accumulator, reduction in increasing k.
+#include "common.cuh"
+
+namespace tcb200 {
+namespace {
+
+struct GemmArgs {
+  const float* A;
+  const float* B;
+  const float* bias;
+  float* C;
+  int M, N, K;
+  int64_t lda, ldb, ldc, sa, sb, sc;
+  int epi, bias_on_m, accumulate;
+};
+
+__device__ __forceinline__ void store_out(const GemmArgs& g, float* Cb, int m, int n, float acc) {
+  float bias = 0.f;
+  if (g.epi == TCB200_EPI_BIAS || g.epi == TCB200_EPI_BIAS_RELU)
+    bias = __ldg(g.bias + (g.bias_on_m ? m : n));
+  float* c = Cb + (int64_t)m * g.ldc + n;
+  if (g.accumulate) acc += *c;
+  *c = apply_epilogue_rt(g.epi, acc, bias);
+}
+
+// ------------------------------------------------------------------------------------
+// simt_tiled
+// ------------------------------------------------------------------------------------
+constexpr int BM = 64, BN = 64, BK = 16, PAD = 4;
+
+// Loads a (64 rows of the free index) x (16 of k) tile into smem as T[k][row].
+// `kmaj`: the operand's k is its innermost (contiguous) index.
+template <bool KMAJ>
+__device__ __forceinline__ void load_tile(const float* __restrict__ base, int64_t ld, int rows,
+                                          int K, int row0, int k0, bool vec_ok,
+                                          float (*T)[BM + PAD], int tid) {
+  if (KMAJ) {
+    const int r = tid >> 2, kk = (tid & 3) << 2;
+    const int row = row0 + r, k = k0 + kk;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (row < rows) {
+      const float* src = base + (int64_t)row * ld + k;
+      if (vec_ok && k + 3 < K) {
+        float4 q = __ldg(reinterpret_cast<const float4*>(src));
+        v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (k + i < K) v[i] = __ldg(src + i);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) T[kk + i][r] = v[i];
+  } else {
+    const int kk = tid >> 4, r = (tid & 15) << 2;
+    const int row = row0 + r, k = k0 + kk;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (k < K) {
+      const float* src = base + (int64_t)k * ld + row;
+      if (vec_ok && row + 3 < rows) {
+        float4 q = __ldg(reinterpret_cast<const float4*>(src));
+        v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (row + i < rows) v[i] = __ldg(src + i);
+      }
+    }
+    *reinterpret_cast<float4*>(&T[kk][r]) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+}
+
+template <bool AK, bool BKM>
+__global__ void __launch_bounds__(256) simt_tiled_kernel(GemmArgs g, int a_vec, int b_vec) {
+  __shared__ __align__(16) float As[BK][BM + PAD];
+  __shared__ __align__(16) float Bs[BK][BN + PAD];
+  const int tid = threadIdx.x;
+  const int tx = tid & 15, ty = tid >> 4;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int64_t b = blockIdx.z;
+  const float* A = g.A + b * g.sa;
+  const float* B = g.B + b * g.sb;
+  float* C = g.C + b * g.sc;
+
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+  for (int k0 = 0; k0 < g.K; k0 += BK) {
+    load_tile<AK>(A, g.lda, g.M, g.K, m0, k0, a_vec, As, tid);
+    load_tile<BKM>(B, g.ldb, g.N, g.K, n0, k0, b_vec, Bs, tid);
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+      const float4 a = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
+      const float4 bq = *reinterpret_cast<const float4*>(&Bs[k][tx * 4]);
+      const float av[4] = {a.x, a.y, a.z, a.w};
+      const float bv[4] = {bq.x, bq.y, bq.z, bq.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= g.M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < g.N) store_out(g, C, m, n, acc[i][j]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// simt_small: whole matrices of one batch entry in shared memory; 2x2 outputs per thread.
+// smem: As[M][K+1] (row-major, padded), Bs[K][N + (N odd ? 0 : 1)] (k-major).
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) simt_small_kernel(GemmArgs g, int ldbs) {
+  extern __shared__ __align__(16) float smem[];
+  const int M = g.M, N = g.N, K = g.K;
+  const int ldas = K + 1;
+  float* As = smem;
+  float* Bs = smem + (size_t)M * ldas;
+  const int64_t b = blockIdx.x;
+  const float* A = g.A + b * g.sa;
+  const float* B = g.B + b * g.sb;
+  float* C = g.C + b * g.sc;
+  const int tid = threadIdx.x, nt = blockDim.x;
+
+  // Only the A(m,k) / B(k,n) row-major form reaches this kernel (checked by the plan), so
+  // consecutive threads read consecutive addresses of both operands.
+  for (int i = tid; i < M * K; i += nt) {
+    const int m = i / K, k = i - m * K;
+    As[m * ldas + k] = __ldg(A + (int64_t)m * g.lda + k);
+  }
+  for (int i = tid; i < K * N; i += nt) {
+    const int k = i / N, n = i - k * N;
+    Bs[k * ldbs + n] = __ldg(B + (int64_t)k * g.ldb + n);
+  }
+  __syncthreads();
+
+  const int tm = (M + 1) >> 1, tn = (N + 1) >> 1;
+  for (int t = tid; t < tm * tn; t += nt) {
+    const int mi = (t / tn) * 2, ni = (t % tn) * 2;
+    const bool m1 = mi + 1 < M, n1 = ni + 1 < N;
+    const float* a0 = As + mi * ldas;
+    const float* a1 = As + (m1 ? mi + 1 : mi) * ldas;
+    const float* b0 = Bs + ni;
+    const int nj = n1 ? 1 : 0;
+    float c00 = 0.f, c01 = 0.f, c10 = 0.f, c11 = 0.f;
+#pragma unroll 8
+    for (int k = 0; k < K; ++k) {
+      const float x0 = a0[k], x1 = a1[k];
+      const float y0 = b0[k * ldbs], y1 = b0[k * ldbs + nj];
+      c00 = fmaf(x0, y0, c00);
+      c01 = fmaf(x0, y1, c01);
+      c10 = fmaf(x1, y0, c10);
+      c11 = fmaf(x1, y1, c11);
+    }
+    store_out(g, C, mi, ni, c00);
+    if (n1) store_out(g, C, mi, ni + 1, c01);
+    if (m1) store_out(g, C, mi + 1, ni, c10);
+    if (m1 && n1) store_out(g, C, mi + 1, ni + 1, c11);
+  }
+}
+
+bool valid(const tcb200_problem_t& p) {
+  return p.batch > 0 && p.M > 0 && p.N > 0 && p.K > 0 && p.M < (1ll << 31) &&
+         p.N < (1ll << 31) && p.K < (1ll << 31) && p.batch <= 0x7fffffffll && p.lda > 0 &&
+         p.ldb > 0 && p.ldc >= p.N && p.stride_a >= 0 && p.stride_b >= 0 && p.stride_c >= 0;
+}
+
+size_t small_smem_bytes(const tcb200_problem_t& p, int* ldbs) {
+  const int l = (int)p.N | 1;  // odd row pitch keeps the k-strided column reads off one bank
+  if (ldbs) *ldbs = l;
+  return sizeof(float) * ((size_t)p.M * (p.K + 1) + (size_t)p.K * l);
+}
+
+// simt_small reads A as (m,k) row-major and B as (k,n) row-major: the batchmatmul form.
+bool small_ok(const tcb200_problem_t& p) {
+  return p.a_k_major && !p.b_k_major && small_smem_bytes(p, nullptr) <= 48 * 1024 &&
+         p.M * p.N <= 4096;
+}
+
+}  // namespace
+
+int contraction_simt_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n) {
+  if (!valid(p)) return TCB200_ERR_INVALID_ARGUMENT;
+  int cnt = 0;
+  auto push = [&](int variant, int bm, int bn, int bk, int threads) {
+    if (cnt < max && out) out[cnt] = tcb200_tile_t{variant, bm, bn, bk, 0, threads, 0};
+    ++cnt;
+  };
+  if (small_ok(p)) {
+    push(TCB200_VARIANT_SIMT_SMALL, (int)p.M, (int)p.N, (int)p.K, 192);
+    push(TCB200_VARIANT_SIMT_SMALL, (int)p.M, (int)p.N, (int)p.K, 128);
+    push(TCB200_VARIANT_SIMT_SMALL, (int)p.M, (int)p.N, (int)p.K, 256);
+  }
+  push(TCB200_VARIANT_SIMT, BM, BN, BK, 256);
+  *n = cnt;
+  return TCB200_OK;
+}
+
+int contraction_simt_plan(Plan& plan) {
+  const tcb200_problem_t& p = plan.p;
+  if (!valid(p)) return TCB200_ERR_INVALID_ARGUMENT;
+  tcb200_tile_t& t = plan.tile;
+  if (t.variant == TCB200_VARIANT_SIMT_SMALL) {
+    if (!small_ok(p)) return TCB200_ERR_UNSUPPORTED;
+    if (t.threads <= 0) t.threads = 192;
+    if (t.threads > 256 || t.threads % 32) return TCB200_ERR_INVALID_ARGUMENT;
+    t.bm = (int)p.M; t.bn = (int)p.N; t.bk = (int)p.K;
+    plan.launch.grid = dim3((unsigned)p.batch, 1, 1);
+    plan.launch.block = dim3(t.threads, 1, 1);
+    plan.launch.smem = small_smem_bytes(p, nullptr);
+    plan.kernel_id = 10;
+    return TCB200_OK;
+  }
+  if (t.variant != TCB200_VARIANT_SIMT) return TCB200_ERR_UNSUPPORTED;
+  t.bm = BM; t.bn = BN; t.bk = BK; t.threads = 256;
+  if (p.batch > 65535) return TCB200_ERR_TOO_LARGE;
+  if (ceil_div(p.M, BM) > 65535) return TCB200_ERR_TOO_LARGE;
+  plan.launch.grid = dim3((unsigned)ceil_div(p.N, BN), (unsigned)ceil_div(p.M, BM), (unsigned)p.batch);
+  plan.launch.block = dim3(256, 1, 1);
+  plan.launch.smem = 0;
+  plan.kernel_id = (p.a_k_major ? 1 : 0) | (p.b_k_major ? 2 : 0);
+  return TCB200_OK;
+}
+
+int contraction_simt_launch(const Plan& plan, const float* A, const float* B, const float* bias,
+                            float* C, cudaStream_t s) {
+  const tcb200_problem_t& p = plan.p;
+  GemmArgs g{A, B, bias, C, (int)p.M, (int)p.N, (int)p.K, p.lda, p.ldb, p.ldc,
+             p.stride_a, p.stride_b, p.stride_c, p.epilogue, p.bias_on_m, p.accumulate};
+  if (plan.kernel_id == 10) {
+    int ldbs = 0;
+    const size_t smem = small_smem_bytes(p, &ldbs);
+    simt_small_kernel<<<plan.launch.grid, plan.launch.block, smem, s>>>(g, ldbs);
+  } else {
+    // 128-bit loads need a 16-byte aligned base, leading dimension and batch stride.
+    const int a_vec = ((uintptr_t)A % 16 == 0) && p.lda % 4 == 0 && p.stride_a % 4 == 0;
+    const int b_vec = ((uintptr_t)B % 16 == 0) && p.ldb % 4 == 0 && p.stride_b % 4 == 0;
+    switch (plan.kernel_id) {
+      case 0: simt_tiled_kernel<false, false><<<plan.launch.grid, plan.launch.block, 0, s>>>(g, a_vec, b_vec); break;
+      case 1: simt_tiled_kernel<true, false><<<plan.launch.grid, plan.launch.block, 0, s>>>(g, a_vec, b_vec); break;
+      case 2: simt_tiled_kernel<false, true><<<plan.launch.grid, plan.launch.block, 0, s>>>(g, a_vec, b_vec); break;
+      default: simt_tiled_kernel<true, true><<<plan.launch.grid, plan.launch.block, 0, s>>>(g, a_vec, b_vec); break;
+    }
+  }
+  TCB200_CUDA_TRY(cudaGetLastError());
+  return TCB200_OK;
+}
+
+}  // namespace tcb200

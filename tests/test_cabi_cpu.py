@@ -1,0 +1,62 @@
+"""The C-ABI library loads without a GPU and exports every symbol its header declares."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from tensorcomprehensions_b200 import cabi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "tcb200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(tcb200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_exports_every_declared_symbol():
+    L = cabi.lib()
+    names = declared_symbols()
+    assert len(names) >= 12
+    for n in names:
+        assert hasattr(L, n), "libtcb200.so does not export " + n
+    assert set(cabi.SYMBOLS) <= set(names)
+    assert L.tcb200_abi_version() == 1
+
+
+def test_strerror_and_argument_checks():
+    L = cabi.lib()
+    assert cabi.strerror(0) == "success"
+    assert "no kernel" in cabi.strerror(-2)
+    n = ctypes.c_int(0)
+    assert L.tcb200_query(None, None, 0, ctypes.byref(n)) == -1
+    bad = cabi.Problem()
+    bad.family = 99
+    assert L.tcb200_query(ctypes.byref(bad), None, 0, ctypes.byref(n)) == -1
+    h = ctypes.c_void_p()
+    assert L.tcb200_plan_create(ctypes.byref(bad), None, 0, ctypes.byref(h)) == -1 and not h
+
+
+def test_query_and_plan_without_gpu():
+    p = cabi.tensordot_problem(32, 512, 8, 2, 784)
+    tiles = cabi.query(p)
+    assert tiles and tiles[0].variant == cabi.VARIANT_SIMT and tiles[0].bm > 0
+    plan = cabi.Plan(p, tiles[0])
+    grid, block = plan.geometry()
+    assert grid[2] == 32 and block[0] * block[1] <= 256
+    assert "tensordot" in plan.describe()
+    # tensordot with an epilogue is not a kernel of the library: hard error, no fallback
+    p.epilogue = cabi.EPI_BIAS
+    with pytest.raises(cabi.Tcb200Error) as e:
+        cabi.Plan(p)
+    assert e.value.status == -2
+
+    q = cabi.contraction_problem(500, 26, 26, 72, a_k_major=True, b_k_major=False)
+    variants = [t.variant for t in cabi.query(q)]
+    assert cabi.VARIANT_SIMT_SMALL in variants and cabi.VARIANT_SIMT in variants
+    c = cabi.group_conv_problem(32, 32, 16, 16, 16, 16, 3, 3)
+    plan = cabi.Plan(c)
+    grid, _ = plan.geometry()
+    assert grid[0] == 32 * 32
