@@ -150,11 +150,15 @@ class Plan:
         self.device = device
 
     def close(self):
-        if self._h:
-            lib().tcb200_plan_destroy(self._h)
-            self._h = ctypes.c_void_p()
+        if self._h and _lib is not None:
+            _lib.tcb200_plan_destroy(self._h)
+        self._h = ctypes.c_void_p()
 
-    __del__ = close
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # interpreter shutdown: module globals may already be gone
+            pass
 
     def geometry(self):
         g, b = (ctypes.c_int64 * 3)(), (ctypes.c_int64 * 3)()

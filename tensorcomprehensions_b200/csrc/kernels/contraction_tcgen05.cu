@@ -1,6 +1,504 @@
+// K1 (tensor-core variant) — C(b,m,n) (+)= sum_k A(b,m,k) * B(b,n,k) [+bias][relu], both operands
+// k-major ("NT" form: the reference's transposed matmul tc/benchmarks/tmm.cc:79-83 and the
+// fully-connected layers of tc/library/fcrelu.h:22-28, tc/benchmarks/MLP_model.cc:547-560).
+//
+// Blackwell execution model, one 128 x BN output tile per CTA:
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of the fp32 A (128x32) and B (BNx32)
+//               k-blocks into 128B-swizzled shared memory, completion on an mbarrier (no multicast)
+//   warps 2-5   3xTF32 split (when split_tf32 == 3): every fp32 value v of the stage is rewritten
+//               in place as hi = tf32(v) and lo = tf32(v - hi) goes to a second buffer with the
+//               same (swizzled) layout, then the stage is handed to the MMA warp; afterwards the
+//               same warps run the epilogue
+//   warp 1      one elected thread issues tcgen05.mma.kind::tf32 (M=128, N=BN, K=8) with the
+//               accumulator in TMEM: per k-slice  lo*hi, hi*lo, hi*hi  (small terms first), and
+//               tcgen05.commit releases the stage back to the producer
+//   epilogue    tcgen05.ld of the fp32 accumulator (lane = row), + bias, ReLU, 128-bit stores
+//
+// Why the split: kind::tf32 keeps 10 mantissa bits of each operand.  With v = hi + lo
+// (hi, lo both exactly representable in TF32 up to 2^-21 |v|) the three products recover
+// fp32-level accuracy (the dropped lo*lo term is 2^-22 relative) at 3x the tensor work.
+//
+// Every wait on an mbarrier is bounded: when it gives up the thread records a code in
+// *dev_status, stops issuing work and falls through to the common exit, where TMEM is freed.
+#include <cuda.h>
+
+#include <atomic>
+#include <mutex>
+
 #include "common.cuh"
+
 namespace tcb200 {
-int contraction_tc_query(const tcb200_problem_t&, tcb200_tile_t*, int, int* n) { *n = 0; return TCB200_OK; }
-int contraction_tc_plan(Plan&) { return TCB200_ERR_UNSUPPORTED; }
-int contraction_tc_launch(const Plan&, const float*, const float*, const float*, float*, cudaStream_t, int*) { return TCB200_ERR_UNSUPPORTED; }
+namespace {
+
+constexpr int BM = 128;       // UMMA M (cta_group::1)
+constexpr int BK = 32;        // fp32 elements per 128-byte swizzle row
+constexpr int UMMA_K = 8;     // kind::tf32
+constexpr int kThreads = 192;
+constexpr int kSmemBudget = 200 * 1024;
+
+__host__ __device__ constexpr int raw_bytes(int bn) { return (BM + bn) * BK * 4; }
+__host__ __device__ constexpr int stage_bytes(int bn, int split) {
+  return raw_bytes(bn) * (split == 3 ? 2 : 1);
 }
+__host__ __device__ constexpr int num_stages(int bn, int split) {
+  return (kSmemBudget / stage_bytes(bn, split)) > 8 ? 8 : (kSmemBudget / stage_bytes(bn, split));
+}
+constexpr int kBarrierBytes = 512;
+__host__ __device__ constexpr int smem_bytes(int bn, int split) {
+  return num_stages(bn, split) * stage_bytes(bn, split) + kBarrierBytes + 1024 /*alignment slack*/;
+}
+
+struct TcArgs {
+  float* C;
+  const float* bias;
+  int M, N, K;
+  int64_t ldc, stride_c;
+  int epi, bias_on_m, accumulate;
+  int a_batched, b_batched;  // 0: operand shared by all batch entries
+  int c_vec;                 // 128-bit stores allowed
+  int* dev_status;
+};
+
+// ---------------------------------------------------------------------------------- PTX
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: gives up after ~2 s of wall time, records `code` and returns false.
+__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int code,
+                                            int* dev_status, volatile int* abort_flag) {
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (globaltimer_ns() - t0 > 2000000000ull) {
+      *abort_flag = code;
+      if (dev_status) atomicCAS(dev_status, 0, code);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code,
+                                          int* dev_status, volatile int* abort_flag) {
+  for (int i = 0; i < 64; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, code, dev_status, abort_flag);
+}
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* tm, int x, int y, int z,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, "
+      "%3, %4}], [%5];" ::"r"(smem_u32(dst)),
+      "l"(tm), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(slot)),
+               "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+// Shared-memory matrix descriptor: k-major operand, 128-byte swizzle, rows of 128 B, groups of
+// 8 rows 1024 B apart (SBO); LBO is unused for swizzled k-major; descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);   // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                    // leading byte offset (ignored)
+  d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset
+  d |= (uint64_t)1 << 46;                    // version
+  d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: D=f32, A=B=tf32, both k-major, M=128, N=BN.
+__host__ __device__ constexpr uint32_t make_idesc(int bn) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(bn >> 3) << 17) |
+         ((uint32_t)(BM >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------------- kernel
+template <int BN, int SPLIT>
+__global__ void __launch_bounds__(kThreads, 1)
+contraction_tc_kernel(const __grid_constant__ CUtensorMap tmA,
+                      const __grid_constant__ CUtensorMap tmB, TcArgs a) {
+  constexpr int STAGES = num_stages(BN, SPLIT);
+  constexpr int RAW = raw_bytes(BN);
+  constexpr int STAGE = stage_bytes(BN, SPLIT);
+  constexpr int A_BYTES = BM * BK * 4;
+  constexpr uint32_t IDESC = make_idesc(BN);
+  static_assert(STAGES >= 2, "pipeline needs two stages");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE);
+  uint64_t* ready = full + STAGES;
+  uint64_t* empty = ready + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM, batch = blockIdx.z;
+  const int num_kb = (a.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&ready[s], 128);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, BN);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_d = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const int za = a.a_batched ? batch : 0, zb = a.b_batched ? batch : 0;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1, 1, a.dev_status, abort_flag)) break;
+        uint8_t* st = smem + s * STAGE;
+        mbar_expect_tx(&full[s], RAW);
+        tma_load_3d(st, &tmA, kb * BK, m0, za, &full[s]);
+        tma_load_3d(st + A_BYTES, &tmB, kb * BK, n0, zb, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t accumulate = 0;
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1;
+        ok = mbar_wait(SPLIT == 3 ? &ready[s] : &full[s], ph, 2, a.dev_status, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + s * STAGE);
+        const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+          const uint32_t koff = ks * UMMA_K * 4;
+          const uint64_t a_hi = make_desc(sa + koff), b_hi = make_desc(sb + koff);
+          if (SPLIT == 3) {
+            const uint64_t a_lo = make_desc(sa + RAW + koff), b_lo = make_desc(sb + RAW + koff);
+            umma_tf32(tmem_d, a_lo, b_hi, IDESC, accumulate);
+            umma_tf32(tmem_d, a_hi, b_lo, IDESC, 1);
+            umma_tf32(tmem_d, a_hi, b_hi, IDESC, 1);
+          } else {
+            umma_tf32(tmem_d, a_hi, b_hi, IDESC, accumulate);
+          }
+          accumulate = 1;
+        }
+        umma_commit(&empty[s]);  // frees the stage once the MMAs above have read it
+      }
+      if (ok) umma_commit(acc_full);
+    }
+  } else {
+    // ------------------------------------------------ 3xTF32 split, then epilogue
+    const int t = threadIdx.x - 64;  // 0..127
+    bool ok = true;
+    if (SPLIT == 3) {
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1;
+        ok = mbar_wait(&full[s], ph, 3, a.dev_status, abort_flag);
+        if (!ok) break;
+        float4* hi = reinterpret_cast<float4*>(smem + s * STAGE);
+        float4* lo = reinterpret_cast<float4*>(smem + s * STAGE + RAW);
+#pragma unroll 4
+        for (int i = t; i < RAW / 16; i += 128) {
+          const float4 v = hi[i];
+          float4 h, l;
+          h.x = to_tf32(v.x); h.y = to_tf32(v.y); h.z = to_tf32(v.z); h.w = to_tf32(v.w);
+          l.x = to_tf32(v.x - h.x); l.y = to_tf32(v.y - h.y);
+          l.z = to_tf32(v.z - h.z); l.w = to_tf32(v.w - h.w);
+          hi[i] = h;
+          lo[i] = l;
+        }
+        // make the generic-proxy writes visible to the tensor core (async proxy)
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(&ready[s]);
+      }
+    }
+    if (ok) ok = mbar_wait(acc_full, 0, 4, a.dev_status, abort_flag);
+    if (ok) {
+      tc_fence_after();
+      const int q = warp & 3;  // TMEM lane quarter this warp may access
+      const int row = m0 + q * 32 + lane;
+      float* crow = a.C + (int64_t)batch * a.stride_c + (int64_t)row * a.ldc;
+      const bool has_bias = a.epi == TCB200_EPI_BIAS || a.epi == TCB200_EPI_BIAS_RELU;
+      const float bias_m = (has_bias && a.bias_on_m && row < a.M) ? __ldg(a.bias + row) : 0.f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        float v[32];
+        tmem_ld32(tmem_d + ((uint32_t)(q * 32) << 16) + c0, v);
+        const int nb = n0 + c0;
+        if (row < a.M && nb < a.N) {
+          if (a.c_vec && nb + 32 <= a.N) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 b4 = make_float4(bias_m, bias_m, bias_m, bias_m);
+              if (has_bias && !a.bias_on_m) b4 = __ldg(reinterpret_cast<const float4*>(a.bias + nb + j));
+              float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              float4* dst = reinterpret_cast<float4*>(crow + nb + j);
+              if (a.accumulate) {
+                const float4 old = *dst;
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              o.x = apply_epilogue_rt(a.epi, o.x, b4.x);
+              o.y = apply_epilogue_rt(a.epi, o.y, b4.y);
+              o.z = apply_epilogue_rt(a.epi, o.z, b4.z);
+              o.w = apply_epilogue_rt(a.epi, o.w, b4.w);
+              *dst = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int n = nb + j;
+              if (n < a.N) {
+                float o = v[j];
+                if (a.accumulate) o += crow[n];
+                const float b = has_bias ? (a.bias_on_m ? bias_m : __ldg(a.bias + n)) : 0.f;
+                crow[n] = apply_epilogue_rt(a.epi, o, b);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_d, BN);
+  }
+}
+
+// ---------------------------------------------------------------------------------- host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static std::mutex mu;
+  static EncodeTiledFn fn = nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    else
+      (void)cudaGetLastError();
+  }
+  return fn;
+}
+
+// {k, rows, batch} fp32 tensor, box {32, box_rows, 1}, 128-byte swizzle, zero fill out of bounds.
+int make_operand_map(CUtensorMap* tm, const float* base, int64_t K, int64_t rows, int64_t ld,
+                     int64_t batch, int64_t stride, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return TCB200_ERR_CUDA;
+  const bool batched = batch > 1 && stride > 0;
+  cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)(batched ? batch : 1)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 4, (cuuint64_t)(batched ? stride : rows * ld) * 4};
+  cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? TCB200_OK : TCB200_ERR_CUDA;
+}
+
+bool shape_ok(const tcb200_problem_t& p) {
+  return p.a_k_major && p.b_k_major && p.batch > 0 && p.batch <= 65535 && p.M > 0 && p.N > 0 &&
+         p.K > 0 && p.M < (1ll << 31) && p.N < (1ll << 31) && p.K < (1ll << 31) &&
+         p.lda % 4 == 0 && p.ldb % 4 == 0 && p.lda >= p.K && p.ldb >= p.K && p.ldc >= p.N &&
+         p.stride_a % 4 == 0 && p.stride_b % 4 == 0 && p.stride_a >= 0 && p.stride_b >= 0 &&
+         ceil_div(p.M, BM) <= 65535;
+}
+
+// "Large enough to be a real dense contraction": at least four 32-wide k-blocks and one full tile
+// of rows; everything smaller is bandwidth/latency bound and stays on the SIMT kernels.
+bool worth_it(const tcb200_problem_t& p) { return p.K >= 128 && p.M >= 64 && p.N >= 64; }
+
+template <int BN, int SPLIT>
+int launch_inst(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const TcArgs& args,
+                cudaStream_t s) {
+  static std::atomic<uint64_t> configured{0};  // bit per device
+  const uint64_t bit = 1ull << (plan.device & 63);
+  if (!(configured.load(std::memory_order_acquire) & bit)) {
+    TCB200_CUDA_TRY(cudaFuncSetAttribute(contraction_tc_kernel<BN, SPLIT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         smem_bytes(BN, SPLIT)));
+    configured.fetch_or(bit, std::memory_order_release);
+  }
+  contraction_tc_kernel<BN, SPLIT>
+      <<<plan.launch.grid, plan.launch.block, smem_bytes(BN, SPLIT), s>>>(ta, tb, args);
+  TCB200_CUDA_TRY(cudaGetLastError());
+  return TCB200_OK;
+}
+
+}  // namespace
+
+// Tensor-core tiles are listed first (= family default) only when this is set; the SIMT tiles
+// always follow.
+#ifndef TCB200_TCGEN05_DEFAULT
+#define TCB200_TCGEN05_DEFAULT 0
+#endif
+
+int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n) {
+  *n = 0;
+  if (!TCB200_TCGEN05_DEFAULT) return TCB200_OK;
+  if (!shape_ok(p) || !worth_it(p)) return TCB200_OK;
+  int cnt = 0;
+  auto push = [&](int bn, int split) {
+    if (cnt < max && out)
+      out[cnt] = tcb200_tile_t{TCB200_VARIANT_TCGEN05, BM, bn, BK, num_stages(bn, split), kThreads, split};
+    ++cnt;
+  };
+  const int bns[] = {128, 256, 64};
+  for (int bn : bns)
+    if (p.N >= bn) push(bn, 3);
+  *n = cnt;
+  return TCB200_OK;
+}
+
+int contraction_tc_plan(Plan& plan) {
+  const tcb200_problem_t& p = plan.p;
+  if (!shape_ok(p)) return TCB200_ERR_UNSUPPORTED;
+  tcb200_tile_t& t = plan.tile;
+  if (t.bn == 0) t.bn = 128;
+  if (t.split_tf32 == 0) t.split_tf32 = 3;
+  if (t.bn != 64 && t.bn != 128 && t.bn != 256) return TCB200_ERR_UNSUPPORTED;
+  if (t.split_tf32 != 1 && t.split_tf32 != 3) return TCB200_ERR_UNSUPPORTED;
+  t.bm = BM;
+  t.bk = BK;
+  t.threads = kThreads;
+  t.stages = num_stages(t.bn, t.split_tf32);
+  plan.launch.grid = dim3((unsigned)ceil_div(p.N, t.bn), (unsigned)ceil_div(p.M, BM), (unsigned)p.batch);
+  plan.launch.block = dim3(kThreads, 1, 1);
+  plan.launch.smem = smem_bytes(t.bn, t.split_tf32);
+  plan.kernel_id = t.bn * 10 + t.split_tf32;
+  return TCB200_OK;
+}
+
+int contraction_tc_launch(const Plan& plan, const float* A, const float* B, const float* bias,
+                          float* C, cudaStream_t s, int* dev_status) {
+  const tcb200_problem_t& p = plan.p;
+  if (((uintptr_t)A | (uintptr_t)B) & 15) return TCB200_ERR_ALIGNMENT;
+  CUtensorMap ta, tb;
+  int st = make_operand_map(&ta, A, p.K, p.M, p.lda, p.batch, p.stride_a, BM);
+  if (st != TCB200_OK) return st;
+  st = make_operand_map(&tb, B, p.K, p.N, p.ldb, p.batch, p.stride_b, plan.tile.bn);
+  if (st != TCB200_OK) return st;
+  TcArgs a;
+  a.C = C; a.bias = bias;
+  a.M = (int)p.M; a.N = (int)p.N; a.K = (int)p.K;
+  a.ldc = p.ldc; a.stride_c = p.stride_c;
+  a.epi = p.epilogue; a.bias_on_m = p.bias_on_m; a.accumulate = p.accumulate;
+  a.a_batched = p.batch > 1 && p.stride_a > 0;
+  a.b_batched = p.batch > 1 && p.stride_b > 0;
+  const bool bias_vec = !bias || p.bias_on_m || ((uintptr_t)bias & 15) == 0;
+  a.c_vec = ((uintptr_t)C & 15) == 0 && p.ldc % 4 == 0 && p.stride_c % 4 == 0 && bias_vec;
+  a.dev_status = dev_status;
+  switch (plan.kernel_id) {
+    case 643: return launch_inst<64, 3>(plan, ta, tb, a, s);
+    case 641: return launch_inst<64, 1>(plan, ta, tb, a, s);
+    case 1283: return launch_inst<128, 3>(plan, ta, tb, a, s);
+    case 1281: return launch_inst<128, 1>(plan, ta, tb, a, s);
+    case 2563: return launch_inst<256, 3>(plan, ta, tb, a, s);
+    case 2561: return launch_inst<256, 1>(plan, ta, tb, a, s);
+    default: return TCB200_ERR_UNSUPPORTED;
+  }
+}
+
+}  // namespace tcb200

@@ -1,0 +1,102 @@
+"""The tcgen05/TMEM contraction kernel (explicit tiles) against the CPU checker.  Needs a B200."""
+import pytest
+import torch
+
+from oracle import oracle as orc
+from tensorcomprehensions_b200 import cabi
+from tensorcomprehensions_b200 import workloads as wl
+
+from helpers import STRICT, assert_close, run_plan
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(shape, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(shape, generator=g, dtype=torch.float32)
+
+
+def tc_tile(bn, split):
+    t = cabi.Tile()
+    t.variant, t.bn, t.split_tf32 = cabi.VARIANT_TCGEN05, bn, split
+    return t
+
+
+def ref64(A, B):
+    return torch.matmul(A.double(), B.double().transpose(-1, -2)).float()
+
+
+@pytest.mark.parametrize("bn", [128, 64, 256])
+@pytest.mark.parametrize("split", [1, 3])
+@pytest.mark.parametrize("shape", [(1, 128, 256, 128), (1, 256, 384, 512), (1, 70, 200, 132), (3, 130, 96, 256)])
+def test_tcgen05_tiles(cuda, bn, split, shape):
+    b, M, N, K = shape
+    A, B = _rand((b, M, K), 21), _rand((b, N, K), 22)
+    ref = ref64(A, B)
+    p = cabi.contraction_problem(b, M, N, K, True, True)
+    out, plan = run_plan(p, [A.to(cuda), B.to(cuda)], (b, M, N), tc_tile(bn, split))
+    # one TF32 pass keeps 10 mantissa bits per operand: only the benchmark criterion applies;
+    # the 3xTF32 split must also meet the reference's own checkRtol at 3e-7.
+    assert_close(out, ref, K, [A, B], 3e-7 if split == 3 else None, plan.describe())
+
+
+@pytest.mark.parametrize("epi", [cabi.EPI_NONE, cabi.EPI_BIAS, cabi.EPI_BIAS_RELU, cabi.EPI_RELU])
+@pytest.mark.parametrize("N", [384, 100])  # 100: ragged columns -> scalar stores
+def test_tcgen05_epilogues(cuda, epi, N):
+    M, K = 200, 320
+    I, W, b = _rand((M, K), 23), _rand((N, K), 24), _rand((N,), 25)
+    has_bias = epi in (cabi.EPI_BIAS, cabi.EPI_BIAS_RELU)
+    ref = orc.loop_fcrelu(I, W, b if has_bias else None, relu=epi in (cabi.EPI_BIAS_RELU, cabi.EPI_RELU),
+                          double=True)
+    p = cabi.contraction_problem(1, M, N, K, True, True, epilogue=epi)
+    ins = [I.to(cuda), W.to(cuda)] + ([b.to(cuda)] if has_bias else [])
+    out, plan = run_plan(p, ins, (M, N), tc_tile(128, 3))
+    assert_close(out, ref, K, [I, W], 3e-7, plan.describe())
+    if epi == cabi.EPI_NONE:
+        p2 = cabi.contraction_problem(1, M, N, K, True, True, accumulate=True)
+        init = _rand((M, N), 26).to(cuda)
+        out2, _ = run_plan(p2, ins, (M, N), tc_tile(128, 3), out_init=init)
+        assert_close(out2, ref + init.cpu().numpy(), K, what="accumulate")
+
+
+def test_tcgen05_shared_operand(cuda):
+    b, M, N, K = 4, 128, 128, 128
+    A, B = _rand((b, M, K), 27), _rand((N, K), 28)
+    ref = ref64(A, B)
+    p = cabi.contraction_problem(b, M, N, K, True, True, stride_b=0)
+    out, plan = run_plan(p, [A.to(cuda), B.to(cuda)], (b, M, N), tc_tile(128, 3))
+    assert_close(out, ref, K, [A, B], 3e-7, plan.describe())
+
+
+def test_tcgen05_rejects_what_it_cannot_take(cuda):
+    # K not a multiple of 4 breaks the 16-byte row pitch TMA needs: the plan is refused
+    p = cabi.contraction_problem(1, 128, 128, 130, True, True)
+    with pytest.raises(cabi.Tcb200Error) as e:
+        cabi.Plan(p, tc_tile(128, 3))
+    assert e.value.status == -2
+    p = cabi.contraction_problem(1, 128, 128, 128, True, False)
+    with pytest.raises(cabi.Tcb200Error):
+        cabi.Plan(p, tc_tile(128, 3))
+
+
+@pytest.mark.parametrize("bn,split", [(128, 3), (256, 3), (128, 1)])
+def test_tmm_full_size_tcgen05(cuda, bn, split):
+    w = wl.tmm()
+    A, B = wl.make_inputs(w)
+    p = cabi.contraction_problem(1, 128, 16384, 4096, True, True)
+    out, plan = run_plan(p, [A.to(cuda), B.to(cuda)], (128, 16384), tc_tile(bn, split))
+    assert_close(out, orc.aten_tmm(A, B), 4096, [A, B], STRICT["tmm"] if split == 3 else None, plan.describe())
+
+
+def test_mlp3_full_size_tcgen05(cuda):
+    w = wl.mlp3()
+    ins = wl.make_inputs(w)
+    I, W2, B2, W3, B3, W4, B4 = [t.to(cuda) for t in ins]
+    refs = orc.aten_mlp3(*ins)
+    x = I
+    for (Wt, Bt, L), ref in zip(((W2, B2, 2048), (W3, B3, 1024), (W4, B4, 512)), refs):
+        p = cabi.contraction_problem(1, x.shape[0], Wt.shape[0], x.shape[1], True, True,
+                                     epilogue=cabi.EPI_BIAS_RELU)
+        out, plan = run_plan(p, [x, Wt, Bt], (x.shape[0], Wt.shape[0]), tc_tile(128, 3))
+        assert_close(out, ref, L, ins, STRICT["mlp3"], plan.describe())
+        x = out
