@@ -227,7 +227,7 @@ int tcb200_launch(const tcb200_plan_t* plan, const void* const* inputs, int n_in
   float* out = static_cast<float*>(outputs[0]);
   switch (P.p.family) {
     case TCB200_FAMILY_TENSORDOT:
-      return tensordot_launch(P, in0, in1, out, s);
+      return tensordot_launch(P, in0, in1, out, s, dev_status);
     case TCB200_FAMILY_GROUP_CONV:
       return group_conv_launch(P, in0, in1, bias, out, s);
     case TCB200_FAMILY_CONTRACTION:

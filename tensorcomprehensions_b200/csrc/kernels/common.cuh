@@ -48,7 +48,8 @@ void set_last_cuda_error(cudaError_t e);
 
 int tensordot_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n);
 int tensordot_plan(Plan& plan);
-int tensordot_launch(const Plan& plan, const float* I0, const float* I1, float* O, cudaStream_t s);
+int tensordot_launch(const Plan& plan, const float* I0, const float* I1, float* O, cudaStream_t s,
+                     int* dev_status);
 
 int contraction_simt_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n);
 int contraction_simt_plan(Plan& plan);

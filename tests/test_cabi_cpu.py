@@ -43,8 +43,12 @@ def test_query_and_plan_without_gpu():
     p = cabi.tensordot_problem(32, 512, 8, 2, 784)
     tiles = cabi.query(p)
     assert tiles and tiles[0].variant == cabi.VARIANT_SIMT and tiles[0].bm > 0
+    assert tiles[0].stages >= 2                      # persistent bulk-copy kernel first
     plan = cabi.Plan(p, tiles[0])
     grid, block = plan.geometry()
+    assert grid == (148, 1, 1) and block == (256, 1, 1)
+    direct = [t for t in tiles if t.stages == 0 and t.bm > 0][0]
+    grid, block = cabi.Plan(p, direct).geometry()
     assert grid[2] == 32 and block[0] * block[1] <= 256
     assert "tensordot" in plan.describe()
     # tensordot with an epilogue is not a kernel of the library: hard error, no fallback
