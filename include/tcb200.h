@@ -130,6 +130,24 @@ int tcb200_launch(const tcb200_plan_t* plan, const void* const* inputs, int n_in
                   void* const* outputs, int n_outputs, tcb200_stream_t stream,
                   int* dev_status);
 
+/* Device plumbing for hosts that do not link the CUDA runtime themselves (the C++ host library
+ * reaches CUDA only through this ABI).  tcb200_set_device / tcb200_get_device wrap the calling
+ * thread's current device (the reference's WithCudaDevice, tc/core/cuda/cuda.h:79-96);
+ * tcb200_device_name is the device string tuned configurations are keyed by
+ * (CudaGPUInfo::getCudaDeviceStr, tc/core/cuda/cuda.h:98-118). */
+int tcb200_get_device(int* device);
+int tcb200_set_device(int device);
+int tcb200_device_name(int device, char* buf, size_t buflen);
+int tcb200_stream_synchronize(tcb200_stream_t stream);
+
+/* Event timer around any number of launches on `stream`: start records an event, stop records a
+ * second one, waits for it and returns the elapsed device time in microseconds (what
+ * CudaRTCFunction::Launch does when profiling, tc/core/cuda/cuda_rtc.cc:373-386, without
+ * truncating to whole microseconds).  stop destroys the timer. */
+typedef struct tcb200_timer tcb200_timer_t;
+int tcb200_timer_start(tcb200_stream_t stream, tcb200_timer_t** timer);
+int tcb200_timer_stop(tcb200_timer_t* timer, tcb200_stream_t stream, float* elapsed_us);
+
 /* Writes `bytes` of a rotating pattern to `buf` on `stream`: the bench uses it to
  * evict L2 between timed launches of the small problems. */
 int tcb200_l2_flush(void* buf, size_t bytes, tcb200_stream_t stream);

@@ -1,0 +1,239 @@
+"""Python face of the backend: the subset of the reference's `tensor_comprehensions` package that
+sits on the hot path (tensor_comprehensions/__init__.py:47-71,123-143,145-218,329-403):
+
+    import tensorcomprehensions_b200 as tc
+    T = tc.define(TC_TEXT, tc.make_naive_options_factory())
+    out = T.tensordot(I0, I1)                       # compiles lazily per input shapes, then runs
+    exe = tc.compile(TC_TEXT, "tensordot", "naive", I0, I1); out = exe(I0, I1)
+    best = tc.autotune(TC_TEXT, "tensordot", I0, I1, starting_options="naive")
+    tc.assert_almost_equal(out, expected, I0, I1, operations=8)
+
+Everything runs through the C++ host (tclib -> tc::aten::compile / run / ATenAutotuner::tune) and
+the sm_100a kernel library; there is no eager or CPU fallback: a comprehension that matches no
+kernel family raises tclib.ErrorReport from compile.
+"""
+import time
+from typing import Callable, Iterable, List, Optional, Tuple, Union
+
+import torch
+
+from . import tclib  # noqa: F401  (hard import: the native extension is the only path)
+from .tclib import MappingOptions
+
+SILENT = True
+
+
+def assert_almost_equal(actual, expected, *inputs, operations: int = 1, precision: float = 1e-7):
+    """max|actual - expected| <= operations * precision * max over inputs of max|input|
+    (the reference's Python twin of checkRtol, tensor_comprehensions/__init__.py:47-71)."""
+    diff = actual - expected
+    max_value = 0.0
+    for inp in inputs:
+        max_value = max(float(inp.abs().max()), max_value)
+    max_diff = float(diff.abs().max())
+    assert max_diff <= operations * precision * max_value, (
+        "error at relative precision: {}, #operations: {}, max_value: {}, max_diff: {}".format(
+            precision, operations, max_value, max_diff))
+
+
+def _as_options(o) -> MappingOptions:
+    if isinstance(o, MappingOptions):
+        return o
+    if o is None:
+        return MappingOptions("naive")
+    return MappingOptions(o)
+
+
+def _stream(inputs):
+    for t in inputs:
+        if t.is_cuda:
+            return torch.cuda.current_stream(t.device).cuda_stream
+    return None
+
+
+class Executor(object):
+    """Callable result of compiling one TC def for fixed input sizes."""
+
+    def __init__(self, executor):
+        self.executor = executor
+
+    def __call__(self, *inputs, outputs: Optional[Tuple[torch.Tensor]] = None, unchecked: bool = False):
+        inputs = list(inputs)
+        if outputs is None:
+            outs = self.executor.run(inputs, [], _stream(inputs))
+        elif unchecked:
+            outs = self.executor.unchecked_run(inputs, list(outputs), _stream(inputs))
+        else:
+            outs = self.executor.run(inputs, list(outputs), _stream(inputs))
+        return outs[0] if len(outs) == 1 else tuple(outs)
+
+    def run(self, inputs, outputs):
+        """List in, list out, no allocation: the form the benchmark loop uses."""
+        return self.executor.unchecked_run(list(inputs), list(outputs), _stream(inputs))
+
+    def profile(self, *inputs, outputs=None):
+        return self.executor.profile(list(inputs), list(outputs) if outputs is not None else [])
+
+    @property
+    def compiled_source(self):
+        return self.executor.compiled_source
+
+    def __getattr__(self, name):
+        return getattr(self.executor, name)
+
+
+def compile(tc: str, entry_point: str, mapping_options: Union[str, MappingOptions], *inputs) -> Executor:
+    """Compiles `entry_point` of `tc` for the shapes of `inputs` (tensor_comprehensions/__init__.py:123-143)."""
+    return Executor(tclib.compile(tc, entry_point, list(inputs), _as_options(mapping_options)))
+
+
+class TunerConfig(object):
+    """Knobs of the tile sweep.  The reference's generations / population / threads settings have no
+    meaning for an exhaustive sweep and are accepted and ignored."""
+
+    def __init__(self, profile_iterations: int = 10, **ignored):
+        self.profile_iterations = profile_iterations
+
+    def generations(self, n):
+        return self
+
+    def pop_size(self, n):
+        return self
+
+    def number_elites(self, n):
+        return self
+
+    def threads(self, n):
+        return self
+
+
+class MappingOptionsCache(object):
+    """Line-oriented text cache of tuned options keyed by (entry point, input sizes)
+    (the role of the reference's MappingOptionsCache, tensor_comprehensions/__init__.py:186-218)."""
+
+    def __init__(self, filename: str):
+        self.filename = filename
+
+    @staticmethod
+    def _key(entry_point, inputs):
+        return entry_point + "|" + ";".join(",".join(str(s) for s in t.shape) for t in inputs)
+
+    def load(self, tc: str, entry_point: str, inputs, count: int = 1) -> List[MappingOptions]:
+        found = []
+        try:
+            with open(self.filename) as f:
+                for line in f:
+                    parts = line.rstrip("\n").split("\t")
+                    if len(parts) == 2 and parts[0] == self._key(entry_point, inputs):
+                        found.append(MappingOptions(parts[1]))
+        except FileNotFoundError:
+            pass
+        return found[-count:][::-1]
+
+    def store(self, entry_point: str, inputs, options: MappingOptions):
+        with open(self.filename, "a") as f:
+            f.write(self._key(entry_point, inputs) + "\t" + options.serialize() + "\n")
+
+
+def autotune(tc: str, entry_point: str, *inputs, starting_options=None, tuner_config: TunerConfig = None,
+             cache_filename: Optional[str] = None, load_from_cache: bool = False,
+             store_to_cache: bool = False) -> MappingOptions:
+    """Times every candidate tile of the matched kernel families on the inputs' device and returns the
+    fastest as a MappingOptions (tensor_comprehensions/__init__.py:145-218)."""
+    inputs = list(inputs)
+    if cache_filename is not None and load_from_cache:
+        cached = MappingOptionsCache(cache_filename).load(tc, entry_point, inputs, 1)
+        if cached:
+            return cached[0]
+    base = _as_options(starting_options)
+    if tuner_config is not None:
+        tclib.set_flag("tuner_profile_iterations", str(tuner_config.profile_iterations))
+    best = tclib.tune(tc, entry_point, inputs, base, 1)
+    result = best[0] if best else base
+    if cache_filename is not None and store_to_cache:
+        MappingOptionsCache(cache_filename).store(entry_point, inputs, result)
+    return result
+
+
+def autotune_and_compile(tc: str, entry_point: str, *inputs, starting_options=None, tuner_config=None,
+                         cache_filename=None, load_from_cache=False, store_to_cache=False) -> Executor:
+    best = autotune(tc, entry_point, *inputs, starting_options=starting_options, tuner_config=tuner_config,
+                    cache_filename=cache_filename, load_from_cache=load_from_cache, store_to_cache=store_to_cache)
+    return compile(tc, entry_point, best, *inputs)
+
+
+class Tuner(object):
+    """tc.Tuner(tc_text, cache_file).tune(entry_point, inputs, base_options, config)."""
+
+    def __init__(self, tc: str, cache_filename: Optional[str] = None):
+        self.tc, self.cache_filename = tc, cache_filename
+
+    def tune(self, entry_point: str, inputs, base_options: MappingOptions = None, config: TunerConfig = None):
+        return autotune(self.tc, entry_point, *inputs, starting_options=base_options, tuner_config=config,
+                        cache_filename=self.cache_filename, store_to_cache=self.cache_filename is not None)
+
+
+def make_naive_options_factory() -> Callable:
+    def generate(tc: str, entry_point: str, *inputs) -> MappingOptions:
+        return MappingOptions("naive")
+    return generate
+
+
+def make_load_from_cache_options_factory(cache_filename: str) -> Callable:
+    def generate(tc: str, entry_point: str, *inputs) -> MappingOptions:
+        loaded = MappingOptionsCache(cache_filename).load(tc, entry_point, list(inputs), 1)
+        return loaded[0] if loaded else None
+    return generate
+
+
+def make_autotuned_options_factory(starting_options=None, tuner_config=None, cache_filename=None,
+                                   load_from_cache=False, store_to_cache=False) -> Callable:
+    def generate(tc: str, entry_point: str, *inputs) -> MappingOptions:
+        return autotune(tc, entry_point, *inputs, starting_options=starting_options, tuner_config=tuner_config,
+                        cache_filename=cache_filename, load_from_cache=load_from_cache,
+                        store_to_cache=store_to_cache)
+    return generate
+
+
+class TC(object):
+    """Every def of the TC text is a method; calling it compiles lazily for the input sizes (through
+    the options factory) and runs (tensor_comprehensions/__init__.py:329-403)."""
+
+    def __init__(self, tc: str, mapping_options_factory: Callable):
+        self.tc = tc
+        self.mapping_options_factory = mapping_options_factory
+        self._executors = {}
+        import re
+        for name in re.findall(r"\bdef\s+([A-Za-z_][A-Za-z0-9_]*)\s*\(", tc):
+            setattr(self, name, self._make_closure(name))
+
+    def _make_closure(self, name):
+        def fun(*inputs, outputs=None, unchecked=False):
+            return self(name, *inputs, outputs=outputs, unchecked=unchecked)
+        return fun
+
+    @staticmethod
+    def _key(entry_point, inputs):
+        return (entry_point,) + tuple((tuple(t.shape), tuple(t.stride()), t.dtype, str(t.device)) for t in inputs)
+
+    def __call__(self, entry_point: str, *inputs, outputs=None, unchecked=False):
+        key = self._key(entry_point, inputs)
+        exe = self._executors.get(key)
+        if exe is None:
+            if not SILENT:
+                print('TC "{}" was not explicitly compiled for inputs of sizes:\n  {}\n....Generate implicit '
+                      'MappingOptions'.format(entry_point, " ".join(str(tuple(i.size())) for i in inputs)))
+            options = self.mapping_options_factory(self.tc, entry_point, *inputs)
+            assert options is not None, "No options found for TC {} with inputs of sizes:\n  {}\n".format(
+                entry_point, " ".join(str(tuple(i.size())) for i in inputs))
+            start = time.perf_counter()
+            exe = compile(self.tc, entry_point, options, *inputs)
+            self._executors[key] = exe
+            if not SILENT:
+                print('Done compiling TC "{}" (compile time: {}ms)'.format(
+                    entry_point, int((time.perf_counter() - start) * 1e3)))
+        return exe(*inputs, outputs=outputs, unchecked=unchecked)
+
+
+def define(tc: str, mapping_options_factory: Callable) -> TC:
+    return TC(tc, mapping_options_factory)

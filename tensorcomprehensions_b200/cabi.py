@@ -21,6 +21,8 @@ SYMBOLS = [
     "tcb200_abi_version", "tcb200_strerror", "tcb200_last_cuda_error", "tcb200_device_count",
     "tcb200_query", "tcb200_plan_create", "tcb200_plan_destroy", "tcb200_plan_geometry",
     "tcb200_plan_describe", "tcb200_plan_tile", "tcb200_launch", "tcb200_l2_flush",
+    "tcb200_get_device", "tcb200_set_device", "tcb200_device_name", "tcb200_stream_synchronize",
+    "tcb200_timer_start", "tcb200_timer_stop",
 ]
 
 

@@ -1,0 +1,472 @@
+// Statements of an analysed def -> launches of the tcb200 kernel families (see kernel_matcher.h).
+#include "tc/core/kernel_matcher.h"
+
+#include <algorithm>
+#include <cstring>
+#include <map>
+#include <set>
+
+#include "tc/lang/error_report.h"
+
+namespace tc {
+
+using lang::ErrorReport;
+using lang::TreeRef;
+
+std::string MatchedLaunch::family() const {
+  switch (problem.family) {
+    case TCB200_FAMILY_CONTRACTION: return "contraction";
+    case TCB200_FAMILY_TENSORDOT: return "tensordot";
+    case TCB200_FAMILY_GROUP_CONV: return "group_conv";
+    default: return "?";
+  }
+}
+
+namespace {
+
+[[noreturn]] void unmatched(const StatementAnalysis& st, const std::string& why) {
+  throw ErrorReport(st.tree)
+      << "no kernel family of the B200 backend matches this comprehension (" << why
+      << "); supported: batched/transposed contractions O +=! A * B, tensordot with shared "
+         "trailing indices, grouped convolution, each optionally followed by + bias and fmax(., 0)";
+}
+
+struct Operand {
+  std::string tensor;
+  std::vector<std::string> vars;  // one index variable per dimension
+  std::vector<int64_t> shape, strides;
+  int value = -1;  // position in [inputs..., outputs...]
+};
+
+int valueIndex(const DefAnalysis& def, const std::string& tensor) {
+  for (size_t i = 0; i < def.inputs.size(); ++i)
+    if (def.inputs[i].name == tensor) return (int)i;
+  for (size_t i = 0; i < def.outputs.size(); ++i)
+    if (def.outputs[i].name == tensor) return (int)(def.inputs.size() + i);
+  return -1;
+}
+
+const TreeRef& stripParens(const TreeRef& t) { return t; }
+
+bool isFloat32(const TensorSymbol* t) {
+  return t && (t->scalarKind == lang::TK_FLOAT || t->scalarKind == lang::TK_FLOAT32);
+}
+
+// Every index of the access is a plain variable, no variable twice.
+bool plainOperand(const DefAnalysis& def, const TensorAccess& a, Operand* op) {
+  const TensorSymbol* sym = def.find(a.tensor);
+  if (!sym || sym->shape.size() != a.indices.size()) return false;
+  op->tensor = a.tensor;
+  op->shape = sym->shape;
+  op->strides = makeStridesFromSizes(sym->shape);
+  op->value = valueIndex(def, a.tensor);
+  std::set<std::string> seen;
+  for (const auto& idx : a.indices) {
+    std::string v;
+    if (!idx.isSingleVar(&v) || !seen.insert(v).second) return false;
+    op->vars.push_back(v);
+  }
+  return true;
+}
+
+int posOf(const std::vector<std::string>& vars, const std::string& v) {
+  auto it = std::find(vars.begin(), vars.end(), v);
+  return it == vars.end() ? -1 : (int)(it - vars.begin());
+}
+
+// Flattens `group` (given in the order it appears in `op`) to one strided dimension of `op`:
+// consecutive positions, row-major.  Returns false if the variables are not adjacent.
+bool flatten(const Operand& op, const std::vector<std::string>& group, int64_t* extent,
+             int64_t* stride) {
+  *extent = 1;
+  *stride = 0;
+  if (group.empty()) return true;
+  std::vector<int> pos;
+  for (const auto& v : group) {
+    int p = posOf(op.vars, v);
+    if (p < 0) return false;
+    pos.push_back(p);
+  }
+  for (size_t i = 1; i < pos.size(); ++i)
+    if (pos[i] != pos[i - 1] + 1) return false;
+  for (int p : pos) *extent *= op.shape[p];
+  *stride = op.strides[pos.back()];
+  return true;
+}
+
+// The variables of `group` ordered as they appear in `op`.
+std::vector<std::string> orderedIn(const Operand& op, const std::set<std::string>& group) {
+  std::vector<std::string> r;
+  for (const auto& v : op.vars)
+    if (group.count(v)) r.push_back(v);
+  return r;
+}
+
+bool sameOrder(const std::vector<std::string>& a, const std::vector<std::string>& b) { return a == b; }
+
+// ----------------------------------------------------------------------------------------------
+// reduction statement: tensordot / contraction
+// ----------------------------------------------------------------------------------------------
+bool matchProduct(const DefAnalysis& def, const StatementAnalysis& st, MatchedLaunch* out,
+                  std::string* why) {
+  const TreeRef rhs = stripParens(lang::Comprehension(st.tree).rhs());
+  if (rhs->kind() != '*' || rhs->trees().size() != 2 || rhs->tree(0)->kind() != lang::TK_ACCESS ||
+      rhs->tree(1)->kind() != lang::TK_ACCESS || st.reads.size() != 2) {
+    *why = "the right-hand side is not a product of two tensor accesses";
+    return false;
+  }
+  Operand A, B, O;
+  if (!plainOperand(def, st.reads[0], &A) || !plainOperand(def, st.reads[1], &B)) {
+    *why = "an operand index is not a plain index variable";
+    return false;
+  }
+  const TensorSymbol* osym = def.find(st.lhs);
+  O.tensor = st.lhs;
+  O.vars = st.lhsIndices;
+  O.shape = osym->shape;
+  O.strides = makeStridesFromSizes(O.shape);
+  O.value = valueIndex(def, st.lhs);
+  {
+    std::set<std::string> seen(O.vars.begin(), O.vars.end());
+    if (seen.size() != O.vars.size()) {
+      *why = "an output index is repeated";
+      return false;
+    }
+  }
+  if (!isFloat32(def.find(A.tensor)) || !isFloat32(def.find(B.tensor)) || !isFloat32(osym)) {
+    *why = "only float32 tensors are supported";
+    return false;
+  }
+  // every index must start at 0 and span the tensors' full extents (no where-clause windows)
+  for (const auto& kv : st.ranges)
+    if (kv.second.min != 0) {
+      *why = "index " + kv.first + " does not start at 0";
+      return false;
+    }
+  auto fullExtent = [&](const Operand& op) {
+    for (size_t d = 0; d < op.vars.size(); ++d)
+      if (st.ranges.at(op.vars[d]).extent() != op.shape[d]) return false;
+    return true;
+  };
+  if (!fullExtent(A) || !fullExtent(B)) {
+    *why = "an index covers only part of an operand dimension";
+    return false;
+  }
+
+  std::set<std::string> batch, mset, nset, kset;
+  for (const auto& v : O.vars) {
+    const bool a = posOf(A.vars, v) >= 0, b = posOf(B.vars, v) >= 0;
+    if (a && b) batch.insert(v);
+    else if (a) mset.insert(v);
+    else if (b) nset.insert(v);
+    else { *why = "output index " + v + " appears in no operand"; return false; }
+  }
+  for (const auto& v : st.reductionVars) {
+    if (posOf(A.vars, v) >= 0 && posOf(B.vars, v) >= 0) kset.insert(v);
+    else { *why = "reduction index " + v + " does not appear in both operands"; return false; }
+  }
+  if (kset.empty()) { *why = "no reduction index"; return false; }
+  for (const auto& v : A.vars)
+    if (!batch.count(v) && !mset.count(v) && !kset.count(v)) { *why = "unclassified index"; return false; }
+  for (const auto& v : B.vars)
+    if (!batch.count(v) && !nset.count(v) && !kset.count(v)) { *why = "unclassified index"; return false; }
+
+  // The group that is outer in O plays "M" and its operand plays "A" (multiplication commutes).
+  if (!mset.empty() && !nset.empty()) {
+    const int firstM = posOf(O.vars, *orderedIn(O, mset).begin());
+    const int firstN = posOf(O.vars, *orderedIn(O, nset).begin());
+    if (firstN < firstM) {
+      std::swap(A, B);
+      std::swap(mset, nset);
+    }
+  }
+
+  tcb200_problem_t& p = out->problem;
+  memset(&p, 0, sizeof(p));
+  p.accumulate = st.assignment == lang::TK_PLUS_EQ ? 1 : 0;
+  out->output = O.value;
+
+  // ---- tensordot: trailing batch indices innermost in all three tensors -----------------------
+  std::vector<std::string> inner;
+  for (int i = (int)O.vars.size() - 1; i >= 0 && batch.count(O.vars[i]); --i)
+    inner.insert(inner.begin(), O.vars[i]);
+  if (!inner.empty()) {
+    auto tail = [&](const Operand& op) {
+      if (op.vars.size() < inner.size()) return false;
+      return std::equal(inner.begin(), inner.end(), op.vars.end() - inner.size());
+    };
+    std::set<std::string> innerSet(inner.begin(), inner.end()), outer;
+    for (const auto& v : batch)
+      if (!innerSet.count(v)) outer.insert(v);
+    // layouts: O = [outer, M, N, inner]  A = [outer, M, K, inner]  B = [outer, K, N, inner]
+    auto layout = [&](const Operand& op, const std::set<std::string>& g1,
+                      const std::set<std::string>& g2) {
+      std::vector<std::string> expect = orderedIn(O, outer);
+      if (!sameOrder(orderedIn(op, outer), expect)) return false;
+      std::vector<std::string> a = orderedIn(op, g1), b = orderedIn(op, g2);
+      expect.insert(expect.end(), a.begin(), a.end());
+      expect.insert(expect.end(), b.begin(), b.end());
+      expect.insert(expect.end(), inner.begin(), inner.end());
+      return op.vars == expect;
+    };
+    if (tail(A) && tail(B) && layout(O, mset, nset) && layout(A, mset, kset) && layout(B, kset, nset) &&
+        sameOrder(orderedIn(A, mset), orderedIn(O, mset)) &&
+        sameOrder(orderedIn(B, nset), orderedIn(O, nset)) &&
+        sameOrder(orderedIn(A, kset), orderedIn(B, kset))) {
+      auto prod = [&](const std::set<std::string>& g) {
+        int64_t e = 1;
+        for (const auto& v : g) e *= st.ranges.at(v).extent();
+        return e;
+      };
+      if (!p.accumulate) {
+        p.family = TCB200_FAMILY_TENSORDOT;
+        p.td[0] = prod(outer);
+        p.td[1] = prod(mset);
+        p.td[2] = prod(kset);
+        p.td[3] = prod(nset);
+        p.td[4] = prod(innerSet);
+        out->inputs = {A.value, B.value};
+        return true;
+      }
+    }
+    // not the tensordot layout: fall through and try to see it as a batched contraction
+  }
+
+  // ---- strided-batched contraction ----------------------------------------------------------------
+  int64_t eB, eM, eN, eK, sBo, sBa, sBb, sMo, sMa, sNo, sNb, sKa, sKb;
+  std::vector<std::string> bo = orderedIn(O, batch), mo = orderedIn(O, mset), no = orderedIn(O, nset),
+                           ko = orderedIn(A, kset);
+  if (!sameOrder(orderedIn(A, batch), bo) || !sameOrder(orderedIn(B, batch), bo) ||
+      !sameOrder(orderedIn(A, mset), mo) || !sameOrder(orderedIn(B, nset), no) ||
+      !sameOrder(orderedIn(B, kset), ko)) {
+    *why = "index groups are ordered differently in the operands";
+    return false;
+  }
+  int64_t e2;
+  if (!flatten(O, bo, &eB, &sBo) || !flatten(A, bo, &e2, &sBa) || !flatten(B, bo, &e2, &sBb) ||
+      !flatten(O, mo, &eM, &sMo) || !flatten(A, mo, &e2, &sMa) || !flatten(O, no, &eN, &sNo) ||
+      !flatten(B, no, &e2, &sNb) || !flatten(A, ko, &eK, &sKa) || !flatten(B, ko, &e2, &sKb)) {
+    *why = "an index group is not contiguous in a tensor, so it does not flatten to one dimension";
+    return false;
+  }
+  // batch indices must be the leading dimensions (uniform batch stride)
+  for (size_t i = 0; i < bo.size(); ++i)
+    if (O.vars[i] != bo[i] || A.vars[i] != bo[i] || B.vars[i] != bo[i]) {
+      *why = "batch indices are not the leading dimensions of all three tensors";
+      return false;
+    }
+  // C: n innermost (or absent), m next
+  if (!no.empty() && sNo != 1) { *why = "output columns are not contiguous"; return false; }
+  if (no.empty() && !mo.empty() && sMo != 1) { *why = "output is not dense"; return false; }
+  p.family = TCB200_FAMILY_CONTRACTION;
+  p.batch = eB; p.M = eM; p.N = eN; p.K = eK;
+  p.stride_a = bo.empty() ? 0 : sBa;
+  p.stride_b = bo.empty() ? 0 : sBb;
+  p.stride_c = bo.empty() ? 0 : sBo;
+  p.ldc = no.empty() ? 1 : (mo.empty() ? eN : sMo);
+  // A: k innermost -> k-major with row pitch = stride of m; else m innermost with pitch = stride of k
+  if (sKa == 1) { p.a_k_major = 1; p.lda = mo.empty() ? eK : sMa; }
+  else if (mo.empty() || sMa == 1) { p.a_k_major = 0; p.lda = sKa; }
+  else { *why = "neither index group of the first operand is contiguous"; return false; }
+  if (sKb == 1) { p.b_k_major = 1; p.ldb = no.empty() ? eK : sNb; }
+  else if (no.empty() || sNb == 1) { p.b_k_major = 0; p.ldb = sKb; }
+  else { *why = "neither index group of the second operand is contiguous"; return false; }
+  out->inputs = {A.value, B.value};
+  return true;
+}
+
+// ----------------------------------------------------------------------------------------------
+// reduction statement: (grouped) convolution
+// ----------------------------------------------------------------------------------------------
+bool matchConv(const DefAnalysis& def, const StatementAnalysis& st, MatchedLaunch* out) {
+  const TreeRef rhs = lang::Comprehension(st.tree).rhs();
+  if (rhs->kind() != '*' || rhs->trees().size() != 2 || st.reads.size() != 2) return false;
+  if (rhs->tree(0)->kind() != lang::TK_ACCESS || rhs->tree(1)->kind() != lang::TK_ACCESS) return false;
+  for (int swap = 0; swap < 2; ++swap) {
+    const TensorAccess& I = st.reads[swap], &W = st.reads[1 - swap];
+    const TensorSymbol* isym = def.find(I.tensor), *wsym = def.find(W.tensor), *osym = def.find(st.lhs);
+    if (!isym || !wsym || !isFloat32(isym) || !isFloat32(wsym) || !isFloat32(osym)) continue;
+    const size_t r = st.lhsIndices.size();
+    const bool grouped = r == 5;
+    if (!(r == 5 || r == 4) || I.indices.size() != r || W.indices.size() != r) continue;
+    const int g = grouped ? 1 : 0;  // extra leading index
+    // O = (n, [g,] f, h, w)   I = (n, [g,] c, h+kh, w+kw)   W = ([g,] f, c, kh, kw)
+    const std::string &n = st.lhsIndices[0], &f = st.lhsIndices[1 + g], &h = st.lhsIndices[2 + g],
+                      &w = st.lhsIndices[3 + g];
+    std::string v, c, kh, kw;
+    auto single = [&](const AffineIndex& a, const std::string& want) {
+      return a.isSingleVar(&v) && v == want;
+    };
+    auto sumOf = [&](const AffineIndex& a, const std::string& x, std::string* other) {
+      if (!a.affine || a.constant != 0 || a.coeff.size() != 2) return false;
+      auto it = a.coeff.find(x);
+      if (it == a.coeff.end() || it->second != 1) return false;
+      for (const auto& kv : a.coeff)
+        if (kv.first != x) {
+          if (kv.second != 1) return false;
+          *other = kv.first;
+        }
+      return true;
+    };
+    if (!single(I.indices[0], n)) continue;
+    if (grouped && (!single(I.indices[1], st.lhsIndices[1]) || !single(W.indices[0], st.lhsIndices[1]))) continue;
+    if (!I.indices[1 + g].isSingleVar(&c)) continue;
+    if (!sumOf(I.indices[2 + g], h, &kh) || !sumOf(I.indices[3 + g], w, &kw)) continue;
+    if (!single(W.indices[0 + g], f) || !single(W.indices[1 + g], c) || !single(W.indices[2 + g], kh) ||
+        !single(W.indices[3 + g], kw))
+      continue;
+    std::set<std::string> red(st.reductionVars.begin(), st.reductionVars.end());
+    if (red != std::set<std::string>{c, kh, kw}) continue;
+    bool zeroBased = true;
+    for (const auto& kv : st.ranges) zeroBased = zeroBased && kv.second.min == 0;
+    if (!zeroBased) continue;
+    tcb200_problem_t& p = out->problem;
+    memset(&p, 0, sizeof(p));
+    p.family = TCB200_FAMILY_GROUP_CONV;
+    p.accumulate = st.assignment == lang::TK_PLUS_EQ ? 1 : 0;
+    p.conv[0] = isym->shape[0];
+    p.conv[1] = grouped ? isym->shape[1] : 1;
+    p.conv[2] = isym->shape[1 + g];
+    p.conv[3] = wsym->shape[0 + g];
+    p.conv[4] = isym->shape[2 + g];
+    p.conv[5] = isym->shape[3 + g];
+    p.conv[6] = wsym->shape[2 + g];
+    p.conv[7] = wsym->shape[3 + g];
+    // output must be the full valid window
+    if (st.ranges.at(h).extent() != p.conv[4] - p.conv[6] + 1 ||
+        st.ranges.at(w).extent() != p.conv[5] - p.conv[7] + 1 || st.ranges.at(c).extent() != p.conv[2])
+      continue;
+    out->inputs = {valueIndex(def, I.tensor), valueIndex(def, W.tensor)};
+    out->output = valueIndex(def, st.lhs);
+    return true;
+  }
+  return false;
+}
+
+// ----------------------------------------------------------------------------------------------
+// elementwise follow-ups on the tensor just produced
+// ----------------------------------------------------------------------------------------------
+// O(idx) = O(idx) [+ Bias(sub)]: returns the access that is NOT the self access, or null.
+bool isSelfAccess(const StatementAnalysis& st, const TensorAccess& a) {
+  if (a.tensor != st.lhs || a.indices.size() != st.lhsIndices.size()) return false;
+  for (size_t i = 0; i < a.indices.size(); ++i) {
+    std::string v;
+    if (!a.indices[i].isSingleVar(&v) || v != st.lhsIndices[i]) return false;
+  }
+  return true;
+}
+
+// Positions (in the left-hand side) of the variables a bias access is indexed by; empty = no match.
+std::vector<int> biasPositions(const StatementAnalysis& st, const TensorAccess& b) {
+  std::vector<int> pos;
+  for (const auto& idx : b.indices) {
+    std::string v;
+    if (!idx.isSingleVar(&v)) return {};
+    int p = posOf(st.lhsIndices, v);
+    if (p < 0) return {};
+    pos.push_back(p);
+  }
+  return pos;
+}
+
+bool matchBias(const DefAnalysis& def, const StatementAnalysis& st, MatchedLaunch* launch) {
+  if (st.assignment != '=' || !st.reductionVars.empty() || st.reads.size() != 2) return false;
+  const TreeRef rhs = lang::Comprehension(st.tree).rhs();
+  if (rhs->kind() != '+' || rhs->trees().size() != 2) return false;
+  if (rhs->tree(0)->kind() != lang::TK_ACCESS || rhs->tree(1)->kind() != lang::TK_ACCESS) return false;
+  const int self = isSelfAccess(st, st.reads[0]) ? 0 : (isSelfAccess(st, st.reads[1]) ? 1 : -1);
+  if (self < 0) return false;
+  const TensorAccess& bias = st.reads[1 - self];
+  const TensorSymbol* bsym = def.find(bias.tensor);
+  if (!bsym || !bsym->isInput || !isFloat32(bsym)) return false;
+  std::vector<int> pos = biasPositions(st, bias);
+  if (pos.empty()) return false;
+  tcb200_problem_t& p = launch->problem;
+  if (p.epilogue != TCB200_EPI_NONE) return false;
+  const int rank = (int)st.lhsIndices.size();
+  if (p.family == TCB200_FAMILY_GROUP_CONV) {
+    // B(g, f) on O(n, g, f, h, w); B(f) on O(n, f, h, w)
+    const bool grouped = rank == 5;
+    if (grouped ? (pos != std::vector<int>{1, 2}) : (pos != std::vector<int>{1})) return false;
+  } else if (p.family == TCB200_FAMILY_CONTRACTION) {
+    // bias over exactly the column group (trailing dims of O) or exactly the row group
+    // (the dims between the batch dims and the column group); count dims from the launch's sizes
+    int64_t cols = 1, rows = 1;
+    int nColDims = 0;
+    const TensorSymbol* osym = def.find(st.lhs);
+    for (int d = rank - 1; d >= 0 && cols < p.N; --d) { cols *= osym->shape[d]; ++nColDims; }
+    if (cols != p.N) return false;
+    int nRowDims = 0;
+    for (int d = rank - 1 - nColDims; d >= 0 && rows < p.M; --d) { rows *= osym->shape[d]; ++nRowDims; }
+    std::vector<int> colPos, rowPos;
+    for (int d = rank - nColDims; d < rank; ++d) colPos.push_back(d);
+    for (int d = rank - nColDims - nRowDims; d < rank - nColDims; ++d) rowPos.push_back(d);
+    if (pos == colPos && p.N > 1) p.bias_on_m = 0;
+    else if (pos == rowPos && rows == p.M && p.batch == 1) p.bias_on_m = 1;
+    else return false;
+  } else {
+    return false;
+  }
+  p.epilogue = TCB200_EPI_BIAS;
+  launch->inputs.push_back(valueIndex(def, bias.tensor));
+  return true;
+}
+
+bool matchRelu(const StatementAnalysis& st, MatchedLaunch* launch) {
+  if (st.assignment != '=' || !st.reductionVars.empty() || st.reads.size() != 1) return false;
+  const TreeRef rhs = lang::Comprehension(st.tree).rhs();
+  if (rhs->kind() != lang::TK_BUILT_IN) return false;
+  lang::BuiltIn b(rhs);
+  if (b.name() != "fmax" || b.arguments().size() != 2) return false;
+  int selfArg = -1;
+  for (int i = 0; i < 2; ++i)
+    if (b.arguments()[i]->kind() == lang::TK_ACCESS) selfArg = i;
+  if (selfArg < 0 || !isSelfAccess(st, st.reads[0])) return false;
+  const TreeRef zero = b.arguments()[1 - selfArg];
+  if (zero->kind() != lang::TK_CONST || lang::Const(zero).value() != 0.0) return false;
+  tcb200_problem_t& p = launch->problem;
+  if (p.family == TCB200_FAMILY_TENSORDOT) return false;
+  if (p.epilogue == TCB200_EPI_NONE && p.family == TCB200_FAMILY_CONTRACTION) p.epilogue = TCB200_EPI_RELU;
+  else if (p.epilogue == TCB200_EPI_BIAS) p.epilogue = TCB200_EPI_BIAS_RELU;
+  else return false;
+  return true;
+}
+
+}  // namespace
+
+std::vector<MatchedLaunch> matchKernels(const DefAnalysis& def) {
+  std::vector<MatchedLaunch> launches;
+  for (size_t s = 0; s < def.statements.size(); ++s) {
+    const StatementAnalysis& st = def.statements[s];
+    const bool reduction = !st.reductionVars.empty();
+    if (reduction) {
+      if (st.assignment != lang::TK_PLUS_EQ_B && st.assignment != lang::TK_PLUS_EQ)
+        unmatched(st, "only sum reductions (+=, +=!) map to a kernel family");
+      MatchedLaunch l;
+      std::string why;
+      if (!matchConv(def, st, &l) && !matchProduct(def, st, &l, &why)) unmatched(st, why);
+      l.statements.push_back((int)s);
+      launches.push_back(std::move(l));
+      continue;
+    }
+    // elementwise statement: must extend the launch that produced the same tensor just before
+    if (launches.empty() || def.outputs.empty() ||
+        launches.back().output != valueIndex(def, st.lhs))
+      unmatched(st, "an elementwise statement is only supported as the epilogue of the reduction "
+                    "that produced the same tensor");
+    MatchedLaunch& l = launches.back();
+    const StatementAnalysis& producer = def.statements[l.statements.front()];
+    if (producer.lhsIndices.size() != st.lhsIndices.size())
+      unmatched(st, "epilogue rank differs from its producer");
+    for (const auto& v : st.lhsIndices)
+      if (st.ranges.at(v).min != 0) unmatched(st, "epilogue covers only part of the tensor");
+    if (!matchBias(def, st, &l) && !matchRelu(st, &l))
+      unmatched(st, "not a '+ bias' or 'fmax(., 0)' epilogue");
+    l.statements.push_back((int)s);
+  }
+  if (launches.empty() && !def.statements.empty())
+    unmatched(def.statements.front(), "no reduction statement");
+  return launches;
+}
+
+}  // namespace tc

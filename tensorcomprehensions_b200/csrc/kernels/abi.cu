@@ -53,6 +53,10 @@ struct tcb200_plan {
   Plan impl;
 };
 
+struct tcb200_timer {
+  cudaEvent_t start = nullptr, stop = nullptr;
+};
+
 extern "C" {
 
 int tcb200_abi_version(void) { return TCB200_ABI_VERSION; }
@@ -237,6 +241,66 @@ int tcb200_launch(const tcb200_plan_t* plan, const void* const* inputs, int n_in
     default:
       return TCB200_ERR_INVALID_ARGUMENT;
   }
+}
+
+int tcb200_get_device(int* device) {
+  if (!device) return TCB200_ERR_INVALID_ARGUMENT;
+  TCB200_CUDA_TRY(cudaGetDevice(device));
+  return TCB200_OK;
+}
+
+int tcb200_set_device(int device) {
+  TCB200_CUDA_TRY(cudaSetDevice(device));
+  return TCB200_OK;
+}
+
+int tcb200_device_name(int device, char* buf, size_t buflen) {
+  if (!buf || buflen == 0) return TCB200_ERR_INVALID_ARGUMENT;
+  cudaDeviceProp prop;
+  TCB200_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+  snprintf(buf, buflen, "%s", prop.name);
+  return TCB200_OK;
+}
+
+int tcb200_stream_synchronize(tcb200_stream_t stream) {
+  TCB200_CUDA_TRY(cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)));
+  return TCB200_OK;
+}
+
+int tcb200_timer_start(tcb200_stream_t stream, tcb200_timer_t** timer) {
+  if (!timer) return TCB200_ERR_INVALID_ARGUMENT;
+  *timer = nullptr;
+  tcb200_timer_t* t = new (std::nothrow) tcb200_timer_t();
+  if (!t) return TCB200_ERR_INVALID_ARGUMENT;
+  cudaError_t e = cudaEventCreate(&t->start);
+  if (e == cudaSuccess) e = cudaEventCreate(&t->stop);
+  if (e == cudaSuccess) e = cudaEventRecord(t->start, reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e);
+    if (t->start) cudaEventDestroy(t->start);
+    if (t->stop) cudaEventDestroy(t->stop);
+    delete t;
+    return TCB200_ERR_CUDA;
+  }
+  *timer = t;
+  return TCB200_OK;
+}
+
+int tcb200_timer_stop(tcb200_timer_t* timer, tcb200_stream_t stream, float* elapsed_us) {
+  if (!timer || !elapsed_us) return TCB200_ERR_INVALID_ARGUMENT;
+  float ms = 0.f;
+  cudaError_t e = cudaEventRecord(timer->stop, reinterpret_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess) e = cudaEventSynchronize(timer->stop);
+  if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, timer->start, timer->stop);
+  cudaEventDestroy(timer->start);
+  cudaEventDestroy(timer->stop);
+  delete timer;
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e);
+    return TCB200_ERR_CUDA;
+  }
+  *elapsed_us = ms * 1000.f;
+  return TCB200_OK;
 }
 
 int tcb200_l2_flush(void* buf, size_t bytes, tcb200_stream_t stream) {

@@ -1,0 +1,116 @@
+"""The public API end to end on a B200: tc.compile / tc.define / autotune -> C++ host -> kernels,
+checked against the CPU checker.  Mirrors how the reference's tests drive it
+(test/cuda/test_tc_mapper.cc, python/tests/test_tc.py)."""
+import pytest
+import torch
+
+import tensorcomprehensions_b200 as tc
+from oracle import oracle as orc
+from tensorcomprehensions_b200 import tclib
+from tensorcomprehensions_b200 import workloads as wl
+
+from helpers import STRICT, assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("name", list(wl.ALL))
+def test_small_instances_through_define(cuda, name):
+    w = wl.ALL[name](**wl.SMALL[name])
+    ins = wl.make_inputs(w)
+    T = tc.define(w.tc, tc.make_naive_options_factory())
+    outs = getattr(T, w.entry)(*[t.to(cuda) for t in ins])
+    outs = list(outs) if isinstance(outs, tuple) else [outs]
+    refs = orc.as_list(orc.LOOP[name](*ins))
+    assert len(outs) == len(refs)
+    for o, r, L in zip(outs, refs, w.reduction):
+        assert_close(o, r, L, ins, STRICT[name], name, strict_is_gate=False)
+    # second call hits the per-shape executor cache and gives the same bits
+    outs2 = getattr(T, w.entry)(*[t.to(cuda) for t in ins])
+    outs2 = list(outs2) if isinstance(outs2, tuple) else [outs2]
+    for a, b in zip(outs, outs2):
+        assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("name", list(wl.ALL))
+def test_full_size_through_compile(cuda, name):
+    w = wl.ALL[name]()
+    ins = wl.make_inputs(w)
+    dev_ins = [t.to(cuda) for t in ins]
+    exe = tc.compile(w.tc, w.entry, "naive", *dev_ins)
+    outs = [torch.full(s, float("nan"), device=cuda) for s in exe.output_shapes()]
+    res = exe(*dev_ins, outputs=tuple(outs))
+    torch.cuda.synchronize()
+    refs = orc.as_list(orc.ATEN[name](*ins))
+    for o, r, L in zip(outs, refs, w.reduction):
+        assert_close(o, r, L, ins, STRICT[name], exe.compiled_source, strict_is_gate=False)
+    prof = exe.profile(*dev_ins, outputs=outs)
+    assert prof["kernel_runtime_us"] > 0
+
+
+def test_tensordot_example_flow(cuda):
+    """tc/examples/tensordot.cc:41-69: tune from naive options, compile with the best, run, reuse the
+    options on two other sizes."""
+    tcs = wl.TENSORDOT_TC
+    I0, I1 = torch.rand(16, 8, 16, 17, 25, device=cuda), torch.rand(16, 16, 2, 17, 25, device=cuda)
+    best = tc.autotune(tcs, "tensordot", I0, I1, starting_options="naive")
+    assert isinstance(best, tc.MappingOptions) and best.to_tile() is not None
+    exe = tc.compile(tcs, "tensordot", best, I0, I1)
+    out = exe(I0, I1)
+    assert_close(out, orc.loop_tensordot(I0.cpu(), I1.cpu()), 16, what=exe.compiled_source)
+    for s0, s1 in (((4, 9, 7, 16, 14), (4, 7, 3, 16, 14)), ((8, 5, 11, 10, 10), (8, 11, 16, 10, 10))):
+        A, B = torch.rand(s0, device=cuda), torch.rand(s1, device=cuda)
+        exe = tc.compile(tcs, "tensordot", best, A, B)
+        assert_close(exe(A, B), orc.loop_tensordot(A.cpu(), B.cpu()), s0[2], what=exe.compiled_source)
+
+
+def test_tune_returns_best_first_and_every_option_compiles(cuda):
+    w = wl.batchmatmul()
+    X, Y = [t.to(cuda) for t in wl.make_inputs(w)]
+    ranked = tclib.tune_report(w.tc, w.entry, [X, Y])
+    assert len(ranked) >= 2
+    times = [r[1] for r in ranked]
+    assert times == sorted(times)
+    ref = orc.loop_batchmatmul(X.cpu(), Y.cpu())
+    for options, us, desc in ranked:
+        exe = tc.compile(w.tc, w.entry, options, X, Y)
+        assert exe.tiles()[0] == options.to_tile()
+        assert_close(exe(X, Y), ref, 72, what=desc)
+
+
+def test_accumulating_reduction_keeps_output(cuda):
+    """'+=' without '!' adds to what the output holds (test/cuda/test_compile_and_run.cc:181-200)."""
+    tcs = "def mm(float(M,K) A, float(K,N) B) -> (C) { C(m,n) += A(m,k) * B(k,n) }"
+    A, B = torch.randn(33, 20, device=cuda), torch.randn(20, 17, device=cuda)
+    exe = tc.compile(tcs, "mm", "naive", A, B)
+    C = torch.ones(33, 17, device=cuda)
+    exe(A, B, outputs=(C,))
+    assert_close(C, (A.double() @ B.double()).float().cpu() + 1, 20, what="+=")
+
+
+def test_run_checks_shapes_and_types(cuda):
+    w = wl.tmm(M=64, N=64, K=64)
+    A, B = [t.to(cuda) for t in wl.make_inputs(w)]
+    exe = tc.compile(w.tc, w.entry, "naive", A, B)
+    with pytest.raises(tclib.ErrorReport, match="expected size"):
+        exe(A[:32].contiguous(), B)
+    with pytest.raises(tclib.ErrorReport, match="expected 2 "):
+        exe(A)
+    with pytest.raises(tclib.ErrorReport, match="float"):
+        exe(A.double(), B)
+    # the unchecked path takes raw pointers
+    C = torch.empty(64, 64, device=cuda)
+    exe(A, B, outputs=(C,), unchecked=True)
+    assert_close(C, (A.double() @ B.double().t()).float().cpu(), 64)
+
+
+def test_runs_on_the_callers_stream(cuda):
+    w = wl.tmm(M=128, N=256, K=128)
+    A, B = [t.to(cuda) for t in wl.make_inputs(w)]
+    exe = tc.compile(w.tc, w.entry, "naive", A, B)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        C = exe(A, B)
+    s.synchronize()
+    assert_close(C, (A.double() @ B.double().t()).float().cpu(), 128)
