@@ -5,10 +5,10 @@
 // Blackwell execution model, one 128 x BN output tile per CTA:
 //   warp 0      TMA producer: cp.async.bulk.tensor loads of the fp32 A (128x32) and B (BNx32)
 //               k-blocks into 128B-swizzled shared memory, completion on an mbarrier (no multicast)
-//   warps 2-5   3xTF32 split (when split_tf32 == 3): every fp32 value v of the stage is rewritten
-//               in place as hi = tf32(v) and lo = tf32(v - hi) goes to a second buffer with the
-//               same (swizzled) layout, then the stage is handed to the MMA warp; afterwards the
-//               same warps run the epilogue
+//   warps 2-5   3xTF32 split (when split_tf32 == 3): for every fp32 value v of the stage,
+//               lo = tf32(v - trunc_tf32(v)) goes to a second buffer with the same (swizzled)
+//               layout; the raw tile serves as hi because the tensor core truncates fp32 words to
+//               TF32 itself; then the stage is handed to the MMA warp
 //   warp 1      one elected thread issues tcgen05.mma.kind::tf32 (M=128, N=BN, K=8) with the
 //               accumulator in TMEM: per k-slice  lo*hi, hi*lo, hi*hi  (small terms first), and
 //               tcgen05.commit releases the stage back to the producer
@@ -34,7 +34,6 @@ namespace {
 constexpr int BM = 128;       // UMMA M (cta_group::1)
 constexpr int BK = 32;        // fp32 elements per 128-byte swizzle row
 constexpr int UMMA_K = 8;     // kind::tf32
-constexpr int kThreads = 192;
 constexpr int kSmemBudget = 200 * 1024;
 
 __host__ __device__ constexpr int raw_bytes(int bn) { return (BM + bn) * BK * 4; }
@@ -52,7 +51,7 @@ __host__ __device__ constexpr int smem_bytes(int bn, int split) {
 struct TcArgs {
   float* C;
   const float* bias;
-  int M, N, K;
+  int M, N, K, batch;
   int64_t ldc, stride_c;
   int epi, bias_on_m, accumulate;
   int a_batched, b_batched;  // 0: operand shared by all batch entries
@@ -96,6 +95,32 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint6
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// A operand read from tensor memory (lane = row, one fp32 per column), B from shared memory.
+__device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// 32 lanes x 32 columns of 32-bit: thread t of the warp writes columns [c, c+32) of lane base+t.
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+  const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+      "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+      "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                    smem_u32(bar))
@@ -122,6 +147,10 @@ __device__ __forceinline__ float to_tf32(float x) {
   return __uint_as_float(r);
 }
 
+__device__ __forceinline__ float tf32_trunc(float x) {
+  return __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+}
+
 // Shared-memory matrix descriptor: k-major operand, 128-byte swizzle, rows of 128 B, groups of
 // 8 rows 1024 B apart (SBO); LBO is unused for swizzled k-major; descriptor version 1 (sm_100).
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
@@ -140,8 +169,21 @@ __host__ __device__ constexpr uint32_t make_idesc(int bn) {
 }
 
 // ---------------------------------------------------------------------------------- kernel
+// Warp roles.  With the 3xTF32 split: 0 = TMA, 1 = MMA, 2-5 = split, 6-13 = drain/epilogue (448
+// threads); with a single TF32 pass the split warps do not exist (320 threads).  The eight drain
+// warps have warp%4 = {2,3,0,1,2,3,0,1} in both cases: two per TMEM lane quarter, each taking one
+// half of the tile's columns.
+template <int SPLIT>
+__host__ __device__ constexpr int num_threads() { return SPLIT == 3 ? 448 : 320; }
+
+// K elements accumulated inside TMEM before the partial sum is drained into fp32 registers.
+// The tensor core adds into its fp32 accumulator with truncation, so a long chain of accumulations
+// drifts towards zero by up to half an ulp per MMA; draining every 256 K elements and summing the
+// chunks with round-to-nearest FADDs keeps the result at SIMT-fp32 accuracy.
+constexpr int kChunkKB = 8;  // k-blocks of 32
+
 template <int BN, int SPLIT>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(num_threads<SPLIT>(), 1)
 contraction_tc_kernel(const __grid_constant__ CUtensorMap tmA,
                       const __grid_constant__ CUtensorMap tmB, TcArgs a) {
   constexpr int STAGES = num_stages(BN, SPLIT);
@@ -149,6 +191,10 @@ contraction_tc_kernel(const __grid_constant__ CUtensorMap tmA,
   constexpr int STAGE = stage_bytes(BN, SPLIT);
   constexpr int A_BYTES = BM * BK * 4;
   constexpr uint32_t IDESC = make_idesc(BN);
+  constexpr bool CHUNKED = BN <= 128;  // register budget of the drain warps: BN fp32 per thread
+  constexpr int SPLIT_WARPS = SPLIT == 3 ? 4 : 0;
+  constexpr int DRAIN_WARP0 = 2 + SPLIT_WARPS;
+  constexpr uint32_t TMEM_COLS = 2 * BN;  // two accumulators: MMA fills one while the other drains
   static_assert(STAGES >= 2, "pipeline needs two stages");
 
   extern __shared__ uint8_t smem_raw[];
@@ -156,13 +202,17 @@ contraction_tc_kernel(const __grid_constant__ CUtensorMap tmA,
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE);
   uint64_t* ready = full + STAGES;
   uint64_t* empty = ready + STAGES;
-  uint64_t* acc_full = empty + STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  uint64_t* acc_full = empty + STAGES;   // [2]
+  uint64_t* acc_empty = acc_full + 2;    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM, batch = blockIdx.z;
   const int num_kb = (a.K + BK - 1) / BK;
+  const int chunk_kb = CHUNKED ? kChunkKB : num_kb;
+  const int num_chunks = (num_kb + chunk_kb - 1) / chunk_kb;
+  const int tiles_n = (a.N + BN - 1) / BN, tiles_m = (a.M + BM - 1) / BM;
+  const int64_t num_tiles = (int64_t)tiles_n * tiles_m * a.batch;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -170,81 +220,112 @@ contraction_tc_kernel(const __grid_constant__ CUtensorMap tmA,
       mbar_init(&ready[s], 128);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(acc_full, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 256);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(tmem_slot, BN);
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_d = *tmem_slot;
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Static persistent schedule: tile t -> (batch, m-tile, n-tile) with n fastest, so the CTAs that
+  // run at the same time share rows of A (L2 hits) while B tiles differ.
+  auto tile_coords = [&](int64_t t, int* m0, int* n0, int* bz) {
+    *n0 = (int)(t % tiles_n) * BN;
+    *m0 = (int)((t / tiles_n) % tiles_m) * BM;
+    *bz = (int)(t / ((int64_t)tiles_n * tiles_m));
+  };
 
   if (warp == 0) {
     // ------------------------------------------------ TMA producer
     if (lane == 0) {
-      const int za = a.a_batched ? batch : 0, zb = a.b_batched ? batch : 0;
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        if (!mbar_wait(&empty[s], ph ^ 1, 1, a.dev_status, abort_flag)) break;
-        uint8_t* st = smem + s * STAGE;
-        mbar_expect_tx(&full[s], RAW);
-        tma_load_3d(st, &tmA, kb * BK, m0, za, &full[s]);
-        tma_load_3d(st + A_BYTES, &tmB, kb * BK, n0, zb, &full[s]);
+      uint32_t it = 0;
+      for (int64_t t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        int m0, n0, bz;
+        tile_coords(t, &m0, &n0, &bz);
+        const int za = a.a_batched ? bz : 0, zb = a.b_batched ? bz : 0;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(&empty[s], ph ^ 1, 1, a.dev_status, abort_flag);
+          if (!ok) break;
+          uint8_t* st = smem + s * STAGE;
+          mbar_expect_tx(&full[s], RAW);
+          tma_load_3d(st, &tmA, kb * BK, m0, za, &full[s]);
+          tma_load_3d(st + A_BYTES, &tmB, kb * BK, n0, zb, &full[s]);
+        }
+        if (!ok) break;
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------ MMA issuer
     if (lane == 0) {
-      uint32_t accumulate = 0;
+      uint32_t it = 0, cc = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        ok = mbar_wait(SPLIT == 3 ? &ready[s] : &full[s], ph, 2, a.dev_status, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t sa = smem_u32(smem + s * STAGE);
-        const uint32_t sb = sa + A_BYTES;
+      for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        for (int c = 0; c < num_chunks && ok; ++c, ++cc) {
+          const uint32_t buf = cc & 1;
+          ok = mbar_wait(&acc_empty[buf], ((cc >> 1) & 1) ^ 1, 5, a.dev_status, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t tmem_d = tmem_base + buf * BN;
+          uint32_t accumulate = 0;
+          const int kb_end = min(num_kb, (c + 1) * chunk_kb);
+          for (int kb = c * chunk_kb; kb < kb_end; ++kb, ++it) {
+            const int s = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1;
+            ok = mbar_wait(SPLIT == 3 ? &ready[s] : &full[s], ph, 2, a.dev_status, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t sa = smem_u32(smem + s * STAGE);
+            const uint32_t sb = sa + A_BYTES;
 #pragma unroll
-        for (int ks = 0; ks < BK / UMMA_K; ++ks) {
-          const uint32_t koff = ks * UMMA_K * 4;
-          const uint64_t a_hi = make_desc(sa + koff), b_hi = make_desc(sb + koff);
-          if (SPLIT == 3) {
-            const uint64_t a_lo = make_desc(sa + RAW + koff), b_lo = make_desc(sb + RAW + koff);
-            umma_tf32(tmem_d, a_lo, b_hi, IDESC, accumulate);
-            umma_tf32(tmem_d, a_hi, b_lo, IDESC, 1);
-            umma_tf32(tmem_d, a_hi, b_hi, IDESC, 1);
-          } else {
-            umma_tf32(tmem_d, a_hi, b_hi, IDESC, accumulate);
+            for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+              const uint32_t koff = ks * UMMA_K * 4;
+              const uint64_t a_hi = make_desc(sa + koff), b_hi = make_desc(sb + koff);
+              if (SPLIT == 3) {
+                const uint64_t a_lo = make_desc(sa + RAW + koff), b_lo = make_desc(sb + RAW + koff);
+                umma_tf32(tmem_d, a_lo, b_hi, IDESC, accumulate);
+                umma_tf32(tmem_d, a_hi, b_lo, IDESC, 1);
+                umma_tf32(tmem_d, a_hi, b_hi, IDESC, 1);
+              } else {
+                umma_tf32(tmem_d, a_hi, b_hi, IDESC, accumulate);
+              }
+              accumulate = 1;
+            }
+            umma_commit(&empty[s]);  // frees the stage once the MMAs above have read it
           }
-          accumulate = 1;
+          if (ok) umma_commit(&acc_full[buf]);
         }
-        umma_commit(&empty[s]);  // frees the stage once the MMAs above have read it
       }
-      if (ok) umma_commit(acc_full);
     }
-  } else {
-    // ------------------------------------------------ 3xTF32 split, then epilogue
-    const int t = threadIdx.x - 64;  // 0..127
+  } else if (warp < DRAIN_WARP0) {
+    // ------------------------------------------------ 3xTF32 split (exists only when SPLIT == 3)
+    const int tt = threadIdx.x - 64;  // 0..127
+    uint32_t it = 0;
     bool ok = true;
-    if (SPLIT == 3) {
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
+    for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
         ok = mbar_wait(&full[s], ph, 3, a.dev_status, abort_flag);
         if (!ok) break;
         float4* hi = reinterpret_cast<float4*>(smem + s * STAGE);
         float4* lo = reinterpret_cast<float4*>(smem + s * STAGE + RAW);
 #pragma unroll 4
-        for (int i = t; i < RAW / 16; i += 128) {
+        for (int i = tt; i < RAW / 16; i += 128) {
+          // kind::tf32 reads an fp32 word by dropping its 13 low mantissa bits (truncation, measured),
+          // so the raw tile already IS the hi operand; only lo = v - trunc(v) has to be written.
           const float4 v = hi[i];
-          float4 h, l;
-          h.x = to_tf32(v.x); h.y = to_tf32(v.y); h.z = to_tf32(v.z); h.w = to_tf32(v.w);
-          l.x = to_tf32(v.x - h.x); l.y = to_tf32(v.y - h.y);
-          l.z = to_tf32(v.z - h.z); l.w = to_tf32(v.w - h.w);
-          hi[i] = h;
+          float4 l;
+          l.x = to_tf32(v.x - tf32_trunc(v.x)); l.y = to_tf32(v.y - tf32_trunc(v.y));
+          l.z = to_tf32(v.z - tf32_trunc(v.z)); l.w = to_tf32(v.w - tf32_trunc(v.w));
           lo[i] = l;
         }
         // make the generic-proxy writes visible to the tensor core (async proxy)
@@ -252,50 +333,95 @@ contraction_tc_kernel(const __grid_constant__ CUtensorMap tmA,
         mbar_arrive(&ready[s]);
       }
     }
-    if (ok) ok = mbar_wait(acc_full, 0, 4, a.dev_status, abort_flag);
-    if (ok) {
-      tc_fence_after();
-      const int q = warp & 3;  // TMEM lane quarter this warp may access
+  } else {
+    // ------------------------------------------------ drain + epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+    constexpr int HALF = BN / 2;                       // columns this warp drains
+    const int col0 = ((warp - DRAIN_WARP0) >> 2) * HALF;
+    const bool has_bias = a.epi == TCB200_EPI_BIAS || a.epi == TCB200_EPI_BIAS_RELU;
+    uint32_t cc = 0;
+    bool ok = true;
+    for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      int m0, n0, bz;
+      tile_coords(t, &m0, &n0, &bz);
       const int row = m0 + q * 32 + lane;
-      float* crow = a.C + (int64_t)batch * a.stride_c + (int64_t)row * a.ldc;
-      const bool has_bias = a.epi == TCB200_EPI_BIAS || a.epi == TCB200_EPI_BIAS_RELU;
+      float* crow = a.C + (int64_t)bz * a.stride_c + (int64_t)row * a.ldc;
       const float bias_m = (has_bias && a.bias_on_m && row < a.M) ? __ldg(a.bias + row) : 0.f;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        float v[32];
-        tmem_ld32(tmem_d + ((uint32_t)(q * 32) << 16) + c0, v);
+
+      auto store32 = [&](const float* v, int c0) {
         const int nb = n0 + c0;
-        if (row < a.M && nb < a.N) {
-          if (a.c_vec && nb + 32 <= a.N) {
+        if (row >= a.M || nb >= a.N) return;
+        if (a.c_vec && nb + 32 <= a.N) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 b4 = make_float4(bias_m, bias_m, bias_m, bias_m);
-              if (has_bias && !a.bias_on_m) b4 = __ldg(reinterpret_cast<const float4*>(a.bias + nb + j));
-              float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-              float4* dst = reinterpret_cast<float4*>(crow + nb + j);
-              if (a.accumulate) {
-                const float4 old = *dst;
-                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-              }
-              o.x = apply_epilogue_rt(a.epi, o.x, b4.x);
-              o.y = apply_epilogue_rt(a.epi, o.y, b4.y);
-              o.z = apply_epilogue_rt(a.epi, o.z, b4.z);
-              o.w = apply_epilogue_rt(a.epi, o.w, b4.w);
-              *dst = o;
+          for (int j = 0; j < 32; j += 4) {
+            float4 b4 = make_float4(bias_m, bias_m, bias_m, bias_m);
+            if (has_bias && !a.bias_on_m) b4 = __ldg(reinterpret_cast<const float4*>(a.bias + nb + j));
+            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            float4* dst = reinterpret_cast<float4*>(crow + nb + j);
+            if (a.accumulate) {
+              const float4 old = *dst;
+              o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
             }
-          } else {
+            o.x = apply_epilogue_rt(a.epi, o.x, b4.x);
+            o.y = apply_epilogue_rt(a.epi, o.y, b4.y);
+            o.z = apply_epilogue_rt(a.epi, o.z, b4.z);
+            o.w = apply_epilogue_rt(a.epi, o.w, b4.w);
+            *dst = o;
+          }
+        } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int n = nb + j;
-              if (n < a.N) {
-                float o = v[j];
-                if (a.accumulate) o += crow[n];
-                const float b = has_bias ? (a.bias_on_m ? bias_m : __ldg(a.bias + n)) : 0.f;
-                crow[n] = apply_epilogue_rt(a.epi, o, b);
-              }
+          for (int j = 0; j < 32; ++j) {
+            const int n = nb + j;
+            if (n < a.N) {
+              float o = v[j];
+              if (a.accumulate) o += crow[n];
+              const float bb = has_bias ? (a.bias_on_m ? bias_m : __ldg(a.bias + n)) : 0.f;
+              crow[n] = apply_epilogue_rt(a.epi, o, bb);
             }
           }
         }
+      };
+
+      if (CHUNKED) {
+        constexpr int G = CHUNKED ? HALF / 32 : 1;
+        float acc[G][32];
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[g][j] = 0.f;
+        for (int c = 0; c < num_chunks; ++c, ++cc) {
+          const uint32_t buf = cc & 1;
+          ok = mbar_wait(&acc_full[buf], (cc >> 1) & 1, 4, a.dev_status, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            float v[32];
+            tmem_ld32(tmem_base + buf * BN + lane_base + col0 + g * 32, v);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[g][j] += v[j];
+          }
+          tc_fence_before();
+          mbar_arrive(&acc_empty[buf]);  // the MMA warp may overwrite this accumulator
+        }
+        if (!ok) break;
+#pragma unroll
+        for (int g = 0; g < G; ++g) store32(acc[g], col0 + g * 32);
+      } else {
+        const uint32_t buf = cc & 1;
+        ok = mbar_wait(&acc_full[buf], (cc >> 1) & 1, 4, a.dev_status, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll 1
+        for (int c0 = col0; c0 < col0 + HALF; c0 += 32) {
+          float v[32];
+          tmem_ld32(tmem_base + buf * BN + lane_base + c0, v);
+          store32(v, c0);
+        }
+        tc_fence_before();
+        mbar_arrive(&acc_empty[buf]);
+        ++cc;
       }
     }
   }
@@ -304,7 +430,292 @@ contraction_tc_kernel(const __grid_constant__ CUtensorMap tmA,
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_d, BN);
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------- kernel (TS)
+// Same pipeline with the A operand staged in TENSOR MEMORY instead of shared memory (3xTF32 only).
+// Shared-memory bandwidth, not the tensor pipe, bounds the all-shared-memory kernel: per k-block
+// the tensor core re-reads both operands for each of the three MMAs.  Here the split warps write
+// A's hi and lo halves into TMEM columns (tcgen05.st, lane = row) and the MMAs read A from there,
+// so shared memory only carries B: its traffic per k-block drops from 192 KB to 128 KB (BN = 128)
+// and a stage shrinks to 48 KB (A raw + B raw + B lo), which doubles the pipeline depth.
+// TMEM columns: [0, 2*BN) two accumulators, [256, 512) ring of 4 x (A hi: 32, A lo: 32).
+__host__ __device__ constexpr int ts_stage_bytes(int bn) { return BM * BK * 4 + 2 * bn * BK * 4; }
+constexpr int kTsStages = 4;
+__host__ __device__ constexpr int ts_smem_bytes(int bn) {
+  return kTsStages * ts_stage_bytes(bn) + kBarrierBytes + 1024;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(448, 1)
+contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
+                      const __grid_constant__ CUtensorMap tmB, TcArgs a) {
+  constexpr int SPLIT = 3;
+  constexpr int STAGES = kTsStages;
+  constexpr int A_BYTES = BM * BK * 4;
+  constexpr int B_BYTES = BN * BK * 4;
+  constexpr int RAW = A_BYTES + B_BYTES;   // bytes one k-block brings in through TMA
+  constexpr int STAGE = ts_stage_bytes(BN);  // [A raw][B raw = hi][B lo]
+  constexpr uint32_t A_RING = 256;         // first TMEM column of the A ring
+  static_assert(BN <= 128, "two accumulators and the A ring share 512 TMEM columns");
+  constexpr uint32_t IDESC = make_idesc(BN);
+  constexpr bool CHUNKED = BN <= 128;  // register budget of the drain warps: BN fp32 per thread
+  constexpr int SPLIT_WARPS = SPLIT == 3 ? 4 : 0;
+  constexpr int DRAIN_WARP0 = 2 + SPLIT_WARPS;
+  constexpr uint32_t TMEM_COLS = 512;
+  static_assert(STAGES >= 2, "pipeline needs two stages");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE);
+  uint64_t* ready = full + STAGES;
+  uint64_t* empty = ready + STAGES;
+  uint64_t* acc_full = empty + STAGES;   // [2]
+  uint64_t* acc_empty = acc_full + 2;    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_kb = (a.K + BK - 1) / BK;
+  const int chunk_kb = CHUNKED ? kChunkKB : num_kb;
+  const int num_chunks = (num_kb + chunk_kb - 1) / chunk_kb;
+  const int tiles_n = (a.N + BN - 1) / BN, tiles_m = (a.M + BM - 1) / BM;
+  const int64_t num_tiles = (int64_t)tiles_n * tiles_m * a.batch;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&ready[s], 128);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 256);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Static persistent schedule: tile t -> (batch, m-tile, n-tile) with n fastest, so the CTAs that
+  // run at the same time share rows of A (L2 hits) while B tiles differ.
+  auto tile_coords = [&](int64_t t, int* m0, int* n0, int* bz) {
+    *n0 = (int)(t % tiles_n) * BN;
+    *m0 = (int)((t / tiles_n) % tiles_m) * BM;
+    *bz = (int)(t / ((int64_t)tiles_n * tiles_m));
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int64_t t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        int m0, n0, bz;
+        tile_coords(t, &m0, &n0, &bz);
+        const int za = a.a_batched ? bz : 0, zb = a.b_batched ? bz : 0;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(&empty[s], ph ^ 1, 1, a.dev_status, abort_flag);
+          if (!ok) break;
+          uint8_t* st = smem + s * STAGE;
+          mbar_expect_tx(&full[s], RAW);
+          tma_load_3d(st, &tmA, kb * BK, m0, za, &full[s]);
+          tma_load_3d(st + A_BYTES, &tmB, kb * BK, n0, zb, &full[s]);
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0, cc = 0;
+      bool ok = true;
+      for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        for (int c = 0; c < num_chunks && ok; ++c, ++cc) {
+          const uint32_t buf = cc & 1;
+          ok = mbar_wait(&acc_empty[buf], ((cc >> 1) & 1) ^ 1, 5, a.dev_status, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t tmem_d = tmem_base + buf * BN;
+          uint32_t accumulate = 0;
+          const int kb_end = min(num_kb, (c + 1) * chunk_kb);
+          for (int kb = c * chunk_kb; kb < kb_end; ++kb, ++it) {
+            const int s = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1;
+            ok = mbar_wait(&ready[s], ph, 2, a.dev_status, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t sb = smem_u32(smem + s * STAGE) + A_BYTES;
+            const uint32_t ta_hi = tmem_base + A_RING + s * 64, ta_lo = ta_hi + 32;
+#pragma unroll
+            for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+              const uint32_t koff = ks * UMMA_K * 4;
+              const uint64_t b_hi = make_desc(sb + koff), b_lo = make_desc(sb + B_BYTES + koff);
+              umma_tf32_ts(tmem_d, ta_lo + ks * UMMA_K, b_hi, IDESC, accumulate);
+              umma_tf32_ts(tmem_d, ta_hi + ks * UMMA_K, b_lo, IDESC, 1);
+              umma_tf32_ts(tmem_d, ta_hi + ks * UMMA_K, b_hi, IDESC, 1);
+              accumulate = 1;
+            }
+            umma_commit(&empty[s]);  // frees the stage once the MMAs above have read it
+          }
+          if (ok) umma_commit(&acc_full[buf]);
+        }
+      }
+    }
+  } else if (warp < DRAIN_WARP0) {
+    // ------------------------------------------------ 3xTF32 split: A -> TMEM, B lo -> smem
+    const int tt = threadIdx.x - 64;  // 0..127
+    const int arow = (warp & 3) * 32 + lane;  // TMEM lane quarter of this warp
+    uint32_t it = 0;
+    bool ok = true;
+    for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        ok = mbar_wait(&full[s], ph, 3, a.dev_status, abort_flag);
+        if (!ok) break;
+        // A: this thread owns row `arow` of the 128 x 32 tile (TMEM lane = row).  The tile sits in
+        // shared memory with the 128-byte swizzle: 16-byte chunk c of row r is stored at c ^ (r & 7).
+        {
+          const float4* arow_p = reinterpret_cast<const float4*>(smem + s * STAGE + arow * 128);
+          float hi[32], lo[32];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const float4 v = arow_p[c ^ (arow & 7)];
+            hi[4 * c + 0] = v.x; hi[4 * c + 1] = v.y; hi[4 * c + 2] = v.z; hi[4 * c + 3] = v.w;
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) lo[j] = to_tf32(hi[j] - tf32_trunc(hi[j]));
+          const uint32_t ta = tmem_base + A_RING + s * 64 + ((uint32_t)(arow & ~31) << 16);
+          tmem_st32(ta, hi);        // the tensor core truncates the fp32 words itself
+          tmem_st32(ta + 32, lo);
+        }
+        // B: lo = tf32(v - trunc(v)) into the second buffer, same (swizzled) layout; raw B is hi.
+        {
+          const float4* bh = reinterpret_cast<const float4*>(smem + s * STAGE + A_BYTES);
+          float4* bl = reinterpret_cast<float4*>(smem + s * STAGE + A_BYTES + B_BYTES);
+#pragma unroll 4
+          for (int i = tt; i < B_BYTES / 16; i += 128) {
+            const float4 v = bh[i];
+            float4 l;
+            l.x = to_tf32(v.x - tf32_trunc(v.x)); l.y = to_tf32(v.y - tf32_trunc(v.y));
+            l.z = to_tf32(v.z - tf32_trunc(v.z)); l.w = to_tf32(v.w - tf32_trunc(v.w));
+            bl[i] = l;
+          }
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        // make the generic-proxy writes visible to the tensor core (async proxy)
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(&ready[s]);
+      }
+    }
+  } else {
+    // ------------------------------------------------ drain + epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+    constexpr int HALF = BN / 2;                       // columns this warp drains
+    const int col0 = ((warp - DRAIN_WARP0) >> 2) * HALF;
+    const bool has_bias = a.epi == TCB200_EPI_BIAS || a.epi == TCB200_EPI_BIAS_RELU;
+    uint32_t cc = 0;
+    bool ok = true;
+    for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      int m0, n0, bz;
+      tile_coords(t, &m0, &n0, &bz);
+      const int row = m0 + q * 32 + lane;
+      float* crow = a.C + (int64_t)bz * a.stride_c + (int64_t)row * a.ldc;
+      const float bias_m = (has_bias && a.bias_on_m && row < a.M) ? __ldg(a.bias + row) : 0.f;
+
+      auto store32 = [&](const float* v, int c0) {
+        const int nb = n0 + c0;
+        if (row >= a.M || nb >= a.N) return;
+        if (a.c_vec && nb + 32 <= a.N) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            float4 b4 = make_float4(bias_m, bias_m, bias_m, bias_m);
+            if (has_bias && !a.bias_on_m) b4 = __ldg(reinterpret_cast<const float4*>(a.bias + nb + j));
+            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            float4* dst = reinterpret_cast<float4*>(crow + nb + j);
+            if (a.accumulate) {
+              const float4 old = *dst;
+              o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+            }
+            o.x = apply_epilogue_rt(a.epi, o.x, b4.x);
+            o.y = apply_epilogue_rt(a.epi, o.y, b4.y);
+            o.z = apply_epilogue_rt(a.epi, o.z, b4.z);
+            o.w = apply_epilogue_rt(a.epi, o.w, b4.w);
+            *dst = o;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int n = nb + j;
+            if (n < a.N) {
+              float o = v[j];
+              if (a.accumulate) o += crow[n];
+              const float bb = has_bias ? (a.bias_on_m ? bias_m : __ldg(a.bias + n)) : 0.f;
+              crow[n] = apply_epilogue_rt(a.epi, o, bb);
+            }
+          }
+        }
+      };
+
+      if (CHUNKED) {
+        constexpr int G = CHUNKED ? HALF / 32 : 1;
+        float acc[G][32];
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[g][j] = 0.f;
+        for (int c = 0; c < num_chunks; ++c, ++cc) {
+          const uint32_t buf = cc & 1;
+          ok = mbar_wait(&acc_full[buf], (cc >> 1) & 1, 4, a.dev_status, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            float v[32];
+            tmem_ld32(tmem_base + buf * BN + lane_base + col0 + g * 32, v);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[g][j] += v[j];
+          }
+          tc_fence_before();
+          mbar_arrive(&acc_empty[buf]);  // the MMA warp may overwrite this accumulator
+        }
+        if (!ok) break;
+#pragma unroll
+        for (int g = 0; g < G; ++g) store32(acc[g], col0 + g * 32);
+      } else {
+        const uint32_t buf = cc & 1;
+        ok = mbar_wait(&acc_full[buf], (cc >> 1) & 1, 4, a.dev_status, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll 1
+        for (int c0 = col0; c0 < col0 + HALF; c0 += 32) {
+          float v[32];
+          tmem_ld32(tmem_base + buf * BN + lane_base + c0, v);
+          store32(v, c0);
+        }
+        tc_fence_before();
+        mbar_arrive(&acc_empty[buf]);
+        ++cc;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -376,6 +787,22 @@ int launch_inst(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, 
   return TCB200_OK;
 }
 
+template <int BN>
+int launch_ts(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const TcArgs& args,
+              cudaStream_t s) {
+  static std::atomic<uint64_t> configured{0};  // bit per device
+  const uint64_t bit = 1ull << (plan.device & 63);
+  if (!(configured.load(std::memory_order_acquire) & bit)) {
+    TCB200_CUDA_TRY(cudaFuncSetAttribute(contraction_ts_kernel<BN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         ts_smem_bytes(BN)));
+    configured.fetch_or(bit, std::memory_order_release);
+  }
+  contraction_ts_kernel<BN><<<plan.launch.grid, plan.launch.block, ts_smem_bytes(BN), s>>>(ta, tb, args);
+  TCB200_CUDA_TRY(cudaGetLastError());
+  return TCB200_OK;
+}
+
 }  // namespace
 
 int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n) {
@@ -384,12 +811,19 @@ int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max,
   int cnt = 0;
   auto push = [&](int bn, int split) {
     if (cnt < max && out)
-      out[cnt] = tcb200_tile_t{TCB200_VARIANT_TCGEN05, BM, bn, BK, num_stages(bn, split), kThreads, split};
+      out[cnt] = tcb200_tile_t{TCB200_VARIANT_TCGEN05, BM, bn, BK, num_stages(bn, split), split == 3 ? 448 : 320, split};
     ++cnt;
   };
+  auto push_ts = [&](int bn) {
+    if (cnt < max && out)
+      out[cnt] = tcb200_tile_t{TCB200_VARIANT_TCGEN05_TS, BM, bn, BK, kTsStages, 448, 3};
+    ++cnt;
+  };
+  if (p.N >= 128) push_ts(128);
   const int bns[] = {128, 256, 64};
   for (int bn : bns)
     if (p.N >= bn) push(bn, 3);
+  if (p.N >= 64 && p.N < 128) push_ts(64);
   *n = cnt;
   return TCB200_OK;
 }
@@ -404,12 +838,16 @@ int contraction_tc_plan(Plan& plan) {
   if (t.split_tf32 != 1 && t.split_tf32 != 3) return TCB200_ERR_UNSUPPORTED;
   t.bm = BM;
   t.bk = BK;
-  t.threads = kThreads;
-  t.stages = num_stages(t.bn, t.split_tf32);
-  plan.launch.grid = dim3((unsigned)ceil_div(p.N, t.bn), (unsigned)ceil_div(p.M, BM), (unsigned)p.batch);
-  plan.launch.block = dim3(kThreads, 1, 1);
-  plan.launch.smem = smem_bytes(t.bn, t.split_tf32);
-  plan.kernel_id = t.bn * 10 + t.split_tf32;
+  t.threads = t.split_tf32 == 3 ? 448 : 320;
+  const bool ts_mode = t.variant == TCB200_VARIANT_TCGEN05_TS;
+  if (ts_mode && (t.bn > 128 || t.split_tf32 != 3)) return TCB200_ERR_UNSUPPORTED;
+  t.stages = ts_mode ? kTsStages : num_stages(t.bn, t.split_tf32);
+  // persistent CTAs, one per SM, walking the tiles with a static stride
+  const int64_t tiles = ceil_div(p.N, t.bn) * ceil_div(p.M, BM) * p.batch;
+  plan.launch.grid = dim3((unsigned)std::min<int64_t>(tiles, kNumSMs), 1, 1);
+  plan.launch.block = dim3(t.threads, 1, 1);
+  plan.launch.smem = ts_mode ? ts_smem_bytes(t.bn) : smem_bytes(t.bn, t.split_tf32);
+  plan.kernel_id = t.bn * 10 + t.split_tf32 + (ts_mode ? 100000 : 0);
   return TCB200_OK;
 }
 
@@ -424,7 +862,7 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
   if (st != TCB200_OK) return st;
   TcArgs a;
   a.C = C; a.bias = bias;
-  a.M = (int)p.M; a.N = (int)p.N; a.K = (int)p.K;
+  a.M = (int)p.M; a.N = (int)p.N; a.K = (int)p.K; a.batch = (int)p.batch;
   a.ldc = p.ldc; a.stride_c = p.stride_c;
   a.epi = p.epilogue; a.bias_on_m = p.bias_on_m; a.accumulate = p.accumulate;
   a.a_batched = p.batch > 1 && p.stride_a > 0;
@@ -433,6 +871,8 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
   a.c_vec = ((uintptr_t)C & 15) == 0 && p.ldc % 4 == 0 && p.stride_c % 4 == 0 && bias_vec;
   a.dev_status = dev_status;
   switch (plan.kernel_id) {
+    case 100643: return launch_ts<64>(plan, ta, tb, a, s);
+    case 101283: return launch_ts<128>(plan, ta, tb, a, s);
     case 643: return launch_inst<64, 3>(plan, ta, tb, a, s);
     case 641: return launch_inst<64, 1>(plan, ta, tb, a, s);
     case 1283: return launch_inst<128, 3>(plan, ta, tb, a, s);

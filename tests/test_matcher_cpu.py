@@ -95,7 +95,7 @@ def test_compile_without_a_device_and_compiled_source():
     src = exe.compiled_source
     assert "tcb200::contraction" in src and "variant=tcgen05" in src and exe.num_launches == 1
     assert exe.output_shapes() == [[128, 16384]]
-    assert exe.grid == [128, 1, 1] and exe.block == [192, 1, 1]
+    assert exe.grid == [128, 1, 1] and exe.block == [448, 1, 1]
     w = wl.mlp3()
     assert tc.compile(w.tc, w.entry, "mlp", *[torch.empty(s) for s in w.shapes]).num_launches == 3
 
@@ -124,7 +124,7 @@ def test_mapping_options_roundtrip_and_tile_encoding():
     # a tuned tile is honoured where a launch accepts it and ignored elsewhere
     w = wl.tmm()
     exe = tc.compile(w.tc, w.entry, o, *[torch.empty(s) for s in w.shapes])
-    assert exe.tiles() == [(3, 128, 256, 32, 2, 192, 3)]
+    assert exe.tiles() == [(3, 128, 256, 32, 2, 448, 3)]
     w = wl.tensordot()
     exe = tc.compile(w.tc, w.entry, o, *[torch.empty(s) for s in w.shapes])
     assert exe.tiles()[0][0] == 1  # tensordot has no tcgen05 variant: family default

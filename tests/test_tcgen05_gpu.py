@@ -16,9 +16,9 @@ def _rand(shape, seed):
     return torch.randn(shape, generator=g, dtype=torch.float32)
 
 
-def tc_tile(bn, split):
+def tc_tile(bn, split, ts=False):
     t = cabi.Tile()
-    t.variant, t.bn, t.split_tf32 = cabi.VARIANT_TCGEN05, bn, split
+    t.variant, t.bn, t.split_tf32 = (cabi.VARIANT_TCGEN05_TS if ts else cabi.VARIANT_TCGEN05), bn, split
     return t
 
 
@@ -38,6 +38,19 @@ def test_tcgen05_tiles(cuda, bn, split, shape):
     # one TF32 pass keeps 10 mantissa bits per operand: only the benchmark criterion applies;
     # the 3xTF32 split must also meet the reference's own checkRtol at 3e-7.
     assert_close(out, ref, K, [A, B], 3e-7 if split == 3 else None, plan.describe())
+
+
+@pytest.mark.parametrize("bn", [128, 64])
+@pytest.mark.parametrize("shape", [(1, 128, 256, 128), (1, 256, 384, 512), (1, 70, 200, 132), (3, 130, 96, 256),
+                                   (1, 300, 128, 4096)])
+def test_tcgen05_ts_tiles(cuda, bn, shape):
+    """A operand staged in tensor memory: must meet the reference's own checkRtol too."""
+    b, M, N, K = shape
+    A, B = _rand((b, M, K), 31), _rand((b, N, K), 32)
+    p = cabi.contraction_problem(b, M, N, K, True, True)
+    out, plan = run_plan(p, [A.to(cuda), B.to(cuda)], (b, M, N), tc_tile(bn, 3, ts=True))
+    assert "tcgen05_ts" in plan.describe()
+    assert_close(out, ref64(A, B), K, [A, B], 3e-7, plan.describe())
 
 
 @pytest.mark.parametrize("epi", [cabi.EPI_NONE, cabi.EPI_BIAS, cabi.EPI_BIAS_RELU, cabi.EPI_RELU])
@@ -79,12 +92,12 @@ def test_tcgen05_rejects_what_it_cannot_take(cuda):
         cabi.Plan(p, tc_tile(128, 3))
 
 
-@pytest.mark.parametrize("bn,split", [(128, 3), (256, 3), (128, 1)])
-def test_tmm_full_size_tcgen05(cuda, bn, split):
+@pytest.mark.parametrize("bn,split,ts", [(128, 3, True), (128, 3, False), (256, 3, False), (128, 1, False)])
+def test_tmm_full_size_tcgen05(cuda, bn, split, ts):
     w = wl.tmm()
     A, B = wl.make_inputs(w)
     p = cabi.contraction_problem(1, 128, 16384, 4096, True, True)
-    out, plan = run_plan(p, [A.to(cuda), B.to(cuda)], (128, 16384), tc_tile(bn, split))
+    out, plan = run_plan(p, [A.to(cuda), B.to(cuda)], (128, 16384), tc_tile(bn, split, ts))
     assert_close(out, orc.aten_tmm(A, B), 4096, [A, B], STRICT["tmm"] if split == 3 else None, plan.describe(),
                  strict_is_gate=False)
 
