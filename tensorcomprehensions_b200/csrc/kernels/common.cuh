@@ -83,6 +83,24 @@ __device__ __forceinline__ void stg_stream4(float4* p, const float4& v) {
                : "memory");
 }
 
+// Asynchronous global -> shared copies (LDGSTS): the data never passes through registers, so a
+// thread can have many in flight instead of stalling on each load's first use.
+__device__ __forceinline__ void cp_async_4(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(
+                   (uint32_t)__cvta_generic_to_shared(smem_dst)),
+               "l"(gmem_src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                   (uint32_t)__cvta_generic_to_shared(smem_dst)),
+               "l"(gmem_src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.wait_all;" ::: "memory");
+}
+
 template <int EPI>
 __device__ __forceinline__ float apply_epilogue(float acc, float bias) {
   if (EPI == TCB200_EPI_BIAS) return acc + bias;

@@ -132,12 +132,24 @@ __global__ void __launch_bounds__(256) simt_tiled_kernel(GemmArgs g, int a_vec, 
 
 // ------------------------------------------------------------------------------------
 // simt_small: whole matrices of one batch entry in shared memory; 2x2 outputs per thread.
-// smem: As[M][K+1] (row-major, padded), Bs[K][N + (N odd ? 0 : 1)] (k-major).
+// The kernel is instruction-bound (profiled: 2.5 IPC, integer index math and scalar shared loads
+// dominated), so the FAST form avoids divisions (one warp stages one row at a time, a lane per
+// 16-byte / 8-byte chunk), stages with asynchronous copies, and consumes four k per step with
+// 128-bit loads of A and 64-bit loads of B: 6 shared loads per 16 FMAs.
+//   FAST needs: K % 4 == 0, lda % 4 == 0, 16-byte aligned A slabs; ldb % 2 == 0, 8-byte aligned B slabs.
+// smem: As[M][lda_s], Bs[K][ldb_s];  FAST: lda_s = K + 4, ldb_s = even(N) + 2;  else K + 1, N | 1.
 // ------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) simt_small_kernel(GemmArgs g, int ldbs) {
+__device__ __forceinline__ void cp_async_8(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(
+                   (uint32_t)__cvta_generic_to_shared(smem_dst)),
+               "l"(gmem_src)
+               : "memory");
+}
+
+template <bool FAST>
+__global__ void __launch_bounds__(256) simt_small_kernel(GemmArgs g, int ldas, int ldbs) {
   extern __shared__ __align__(16) float smem[];
   const int M = g.M, N = g.N, K = g.K;
-  const int ldas = K + 1;
   float* As = smem;
   float* Bs = smem + (size_t)M * ldas;
   const int64_t b = blockIdx.x;
@@ -146,16 +158,29 @@ __global__ void __launch_bounds__(256) simt_small_kernel(GemmArgs g, int ldbs) {
   float* C = g.C + b * g.sc;
   const int tid = threadIdx.x, nt = blockDim.x;
 
-  // Only the A(m,k) / B(k,n) row-major form reaches this kernel (checked by the plan), so
-  // consecutive threads read consecutive addresses of both operands.
-  for (int i = tid; i < M * K; i += nt) {
-    const int m = i / K, k = i - m * K;
-    As[m * ldas + k] = __ldg(A + (int64_t)m * g.lda + k);
+  // Only the A(m,k) / B(k,n) row-major form reaches this kernel (checked by the plan).
+  if (FAST) {
+    const int warp = tid >> 5, lane = tid & 31, nw = nt >> 5;
+    const int ka = K >> 2, nb = (N + 1) >> 1;
+    for (int m = warp; m < M; m += nw)
+      for (int q = lane; q < ka; q += 32)
+        cp_async_16(As + m * ldas + 4 * q, A + (int64_t)m * g.lda + 4 * q);
+    for (int k = warp; k < K; k += nw)
+      for (int q = lane; q < nb; q += 32) {
+        if (2 * q + 1 < N) cp_async_8(Bs + k * ldbs + 2 * q, B + (int64_t)k * g.ldb + 2 * q);
+        else cp_async_4(Bs + k * ldbs + 2 * q, B + (int64_t)k * g.ldb + 2 * q);
+      }
+  } else {
+    for (int i = tid; i < M * K; i += nt) {
+      const int m = i / K, k = i - m * K;
+      cp_async_4(As + m * ldas + k, A + (int64_t)m * g.lda + k);
+    }
+    for (int i = tid; i < K * N; i += nt) {
+      const int k = i / N, n = i - k * N;
+      cp_async_4(Bs + k * ldbs + n, B + (int64_t)k * g.ldb + n);
+    }
   }
-  for (int i = tid; i < K * N; i += nt) {
-    const int k = i / N, n = i - k * N;
-    Bs[k * ldbs + n] = __ldg(B + (int64_t)k * g.ldb + n);
-  }
+  cp_async_wait_all();
   __syncthreads();
 
   const int tm = (M + 1) >> 1, tn = (N + 1) >> 1;
@@ -165,16 +190,38 @@ __global__ void __launch_bounds__(256) simt_small_kernel(GemmArgs g, int ldbs) {
     const float* a0 = As + mi * ldas;
     const float* a1 = As + (m1 ? mi + 1 : mi) * ldas;
     const float* b0 = Bs + ni;
-    const int nj = n1 ? 1 : 0;
     float c00 = 0.f, c01 = 0.f, c10 = 0.f, c11 = 0.f;
+    if (FAST) {
+      // b0 + 1 may be the padding column when N is odd: its products only reach c01/c11, which are
+      // not stored then.
+#pragma unroll 2
+      for (int k = 0; k < K; k += 4) {
+        const float4 x0 = *reinterpret_cast<const float4*>(a0 + k);
+        const float4 x1 = *reinterpret_cast<const float4*>(a1 + k);
+        const float2 y0 = *reinterpret_cast<const float2*>(b0 + (k + 0) * ldbs);
+        const float2 y1 = *reinterpret_cast<const float2*>(b0 + (k + 1) * ldbs);
+        const float2 y2 = *reinterpret_cast<const float2*>(b0 + (k + 2) * ldbs);
+        const float2 y3 = *reinterpret_cast<const float2*>(b0 + (k + 3) * ldbs);
+        c00 = fmaf(x0.x, y0.x, c00); c01 = fmaf(x0.x, y0.y, c01);
+        c10 = fmaf(x1.x, y0.x, c10); c11 = fmaf(x1.x, y0.y, c11);
+        c00 = fmaf(x0.y, y1.x, c00); c01 = fmaf(x0.y, y1.y, c01);
+        c10 = fmaf(x1.y, y1.x, c10); c11 = fmaf(x1.y, y1.y, c11);
+        c00 = fmaf(x0.z, y2.x, c00); c01 = fmaf(x0.z, y2.y, c01);
+        c10 = fmaf(x1.z, y2.x, c10); c11 = fmaf(x1.z, y2.y, c11);
+        c00 = fmaf(x0.w, y3.x, c00); c01 = fmaf(x0.w, y3.y, c01);
+        c10 = fmaf(x1.w, y3.x, c10); c11 = fmaf(x1.w, y3.y, c11);
+      }
+    } else {
+      const int nj = n1 ? 1 : 0;
 #pragma unroll 8
-    for (int k = 0; k < K; ++k) {
-      const float x0 = a0[k], x1 = a1[k];
-      const float y0 = b0[k * ldbs], y1 = b0[k * ldbs + nj];
-      c00 = fmaf(x0, y0, c00);
-      c01 = fmaf(x0, y1, c01);
-      c10 = fmaf(x1, y0, c10);
-      c11 = fmaf(x1, y1, c11);
+      for (int k = 0; k < K; ++k) {
+        const float x0 = a0[k], x1 = a1[k];
+        const float y0 = b0[k * ldbs], y1 = b0[k * ldbs + nj];
+        c00 = fmaf(x0, y0, c00);
+        c01 = fmaf(x0, y1, c01);
+        c10 = fmaf(x1, y0, c10);
+        c11 = fmaf(x1, y1, c11);
+      }
     }
     store_out(g, C, mi, ni, c00);
     if (n1) store_out(g, C, mi, ni + 1, c01);
@@ -189,15 +236,22 @@ bool valid(const tcb200_problem_t& p) {
          p.ldb > 0 && p.ldc >= p.N && p.stride_a >= 0 && p.stride_b >= 0 && p.stride_c >= 0;
 }
 
-size_t small_smem_bytes(const tcb200_problem_t& p, int* ldbs) {
-  const int l = (int)p.N | 1;  // odd row pitch keeps the k-strided column reads off one bank
-  if (ldbs) *ldbs = l;
-  return sizeof(float) * ((size_t)p.M * (p.K + 1) + (size_t)p.K * l);
+// Shape part of the FAST conditions (pointer alignment is checked at launch).
+bool small_fast_shape(const tcb200_problem_t& p) {
+  return p.K % 4 == 0 && p.lda % 4 == 0 && p.stride_a % 4 == 0 && p.ldb % 2 == 0 && p.stride_b % 2 == 0;
+}
+// Shared-memory pitches: the larger (FAST) ones are always reserved so the launch can pick either form.
+void small_pitches(const tcb200_problem_t& p, bool fast, int* ldas, int* ldbs) {
+  *ldas = fast ? (int)p.K + 4 : (int)p.K + 1;
+  *ldbs = fast ? (int)((p.N + 1) / 2 * 2 + 2) : ((int)p.N | 1);  // odd pitch keeps k-strided reads off one bank
+}
+size_t small_smem_bytes(const tcb200_problem_t& p) {
+  return sizeof(float) * ((size_t)p.M * (p.K + 4) + (size_t)p.K * ((p.N + 1) / 2 * 2 + 2));
 }
 
 // simt_small reads A as (m,k) row-major and B as (k,n) row-major: the batchmatmul form.
 bool small_ok(const tcb200_problem_t& p) {
-  return p.a_k_major && !p.b_k_major && small_smem_bytes(p, nullptr) <= 48 * 1024 &&
+  return p.a_k_major && !p.b_k_major && small_smem_bytes(p) <= 48 * 1024 &&
          p.M * p.N <= 4096;
 }
 
@@ -211,9 +265,9 @@ int contraction_simt_query(const tcb200_problem_t& p, tcb200_tile_t* out, int ma
     ++cnt;
   };
   if (small_ok(p)) {
+    push(TCB200_VARIANT_SIMT_SMALL, (int)p.M, (int)p.N, (int)p.K, 256);
     push(TCB200_VARIANT_SIMT_SMALL, (int)p.M, (int)p.N, (int)p.K, 192);
     push(TCB200_VARIANT_SIMT_SMALL, (int)p.M, (int)p.N, (int)p.K, 128);
-    push(TCB200_VARIANT_SIMT_SMALL, (int)p.M, (int)p.N, (int)p.K, 256);
   }
   push(TCB200_VARIANT_SIMT, BM, BN, BK, 256);
   *n = cnt;
@@ -226,12 +280,12 @@ int contraction_simt_plan(Plan& plan) {
   tcb200_tile_t& t = plan.tile;
   if (t.variant == TCB200_VARIANT_SIMT_SMALL) {
     if (!small_ok(p)) return TCB200_ERR_UNSUPPORTED;
-    if (t.threads <= 0) t.threads = 192;
+    if (t.threads <= 0) t.threads = 256;
     if (t.threads > 256 || t.threads % 32) return TCB200_ERR_INVALID_ARGUMENT;
     t.bm = (int)p.M; t.bn = (int)p.N; t.bk = (int)p.K;
     plan.launch.grid = dim3((unsigned)p.batch, 1, 1);
     plan.launch.block = dim3(t.threads, 1, 1);
-    plan.launch.smem = small_smem_bytes(p, nullptr);
+    plan.launch.smem = small_smem_bytes(p);
     plan.kernel_id = 10;
     return TCB200_OK;
   }
@@ -252,9 +306,13 @@ int contraction_simt_launch(const Plan& plan, const float* A, const float* B, co
   GemmArgs g{A, B, bias, C, (int)p.M, (int)p.N, (int)p.K, p.lda, p.ldb, p.ldc,
              p.stride_a, p.stride_b, p.stride_c, p.epilogue, p.bias_on_m, p.accumulate};
   if (plan.kernel_id == 10) {
-    int ldbs = 0;
-    const size_t smem = small_smem_bytes(p, &ldbs);
-    simt_small_kernel<<<plan.launch.grid, plan.launch.block, smem, s>>>(g, ldbs);
+    const bool fast = small_fast_shape(p) && ((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 8 == 0);
+    int ldas = 0, ldbs = 0;
+    small_pitches(p, fast, &ldas, &ldbs);
+    if (fast)
+      simt_small_kernel<true><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(g, ldas, ldbs);
+    else
+      simt_small_kernel<false><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(g, ldas, ldbs);
   } else {
     // 128-bit loads need a 16-byte aligned base, leading dimension and batch stride.
     const int a_vec = ((uintptr_t)A % 16 == 0) && p.lda % 4 == 0 && p.stride_a % 4 == 0;

@@ -4,7 +4,16 @@
 // Replaces the kernel the reference generates for tc/benchmarks/group_convolution.cc:124-132
 // (library twin tc/library/group_convolution.h:26-44 with stride 1).
 //
-// SIMT variant: one CTA per (n, g, band of output rows).  The band's input halo
+// Two SIMT kernels:
+//  * rows kernel (default when W <= 16 and F % 4 == 0): one CTA per (g, pair of n).  A thread owns
+//    one output row h of four output channels: 4 x OW accumulators in registers.  Per (c, kh) it
+//    reads one input row (four 128-bit shared loads, row pitch padded to 20 floats so the eight
+//    rows a quarter-warp touches fall into distinct banks) and three 128-bit filter vectors, and
+//    issues 4 * OW * KW FMAs: ~24 FMAs per shared load, so the kernel is bound by the fp32 pipe,
+//    not by shared memory.
+//  * band kernel (any size): one CTA per (n, g, band of output rows), one pixel x four channels
+//    per thread.
+// Band kernel: one CTA per (n, g, band of output rows).  The band's input halo
 // (C x (rows+KH-1) x W) and the group's filters are staged in shared memory once; the
 // filters are re-laid out as Ws[c][kh][kw][f] so one 128-bit shared load feeds four
 // output channels.  Consecutive threads take consecutive output pixels, so the halo
@@ -97,6 +106,128 @@ __global__ void __launch_bounds__(256) group_conv_simt_kernel(ConvArgs a) {
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// rows kernel
+// ------------------------------------------------------------------------------------------------
+constexpr int kRowsMaxW = 16;   // input width held in registers
+constexpr int kRowsPitch = 20;  // shared-memory row pitch in floats (80 B)
+
+__global__ void __launch_bounds__(256) group_conv_rows_kernel(ConvArgs a, int n_per_cta, int N) {
+  extern __shared__ __align__(16) float smem[];
+  const int g = blockIdx.x;
+  const int n0 = blockIdx.y * n_per_cta;
+  const int nn = min(n_per_cta, N - n0);
+  const int taps = a.C * a.KH * a.KW;
+  const int Fp = a.F;  // multiple of 4 (checked by the plan)
+  float* Ws = smem;                        // [taps][F]
+  float* Is = smem + (size_t)taps * Fp;    // [nn][C][H][kRowsPitch]
+  const int tid = threadIdx.x, nt = blockDim.x;
+
+  // Staging uses asynchronous copies so every thread has all of its loads in flight at once.
+  // Filters: read in global order (f, tap) and scattered to the transposed layout [tap][f].
+  const float* Wg = a.W + (size_t)g * a.F * taps;
+  for (int i = tid; i < taps * Fp; i += nt) {
+    const int f = i / taps, t = i - f * taps;
+    cp_async_4(Ws + (size_t)t * Fp + f, Wg + i);
+  }
+  const int plane = a.C * a.H;  // rows per n
+  const float* Ig = a.I + ((size_t)n0 * a.G + g) * plane * a.Wd;
+  const size_t n_stride = (size_t)a.G * plane * a.Wd;
+  if ((a.Wd & 3) == 0 && (((uintptr_t)a.I) & 15) == 0) {
+    const int w4 = a.Wd >> 2;
+    for (int i = tid; i < nn * plane * w4; i += nt) {
+      const int q = i % w4, r = i / w4;  // r = ni * plane + c * H + h
+      const int ni = r / plane, ch = r - ni * plane;
+      cp_async_16(Is + (size_t)r * kRowsPitch + 4 * q, Ig + ni * n_stride + (size_t)ch * a.Wd + 4 * q);
+    }
+  } else {
+    for (int i = tid; i < nn * plane * a.Wd; i += nt) {
+      const int w = i % a.Wd, r = i / a.Wd;
+      const int ni = r / plane, ch = r - ni * plane;
+      cp_async_4(Is + (size_t)r * kRowsPitch + w, Ig + ni * n_stride + (size_t)ch * a.Wd + w);
+    }
+  }
+  cp_async_wait_all();
+  __syncthreads();
+
+  const int FQ = a.F / 4;
+  const int per_n = FQ * a.OH;
+  if (tid >= nn * per_n) return;
+  const int ni = tid / per_n, rem = tid - ni * per_n;
+  const int fq = rem / a.OH, h = rem - fq * a.OH;
+
+  float acc[4][kRowsMaxW];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int w = 0; w < kRowsMaxW; ++w) acc[j][w] = 0.f;
+
+  const float* in = Is + (size_t)ni * plane * kRowsPitch;
+  for (int c = 0; c < a.C; ++c) {
+    for (int kh = 0; kh < a.KH; ++kh) {
+      const float4* row = reinterpret_cast<const float4*>(in + (size_t)(c * a.H + h + kh) * kRowsPitch);
+      float x[kRowsMaxW + 4];
+#pragma unroll
+      for (int q = 0; q < kRowsMaxW / 4; ++q) {
+        const float4 v = row[q];
+        x[4 * q] = v.x; x[4 * q + 1] = v.y; x[4 * q + 2] = v.z; x[4 * q + 3] = v.w;
+      }
+#pragma unroll
+      for (int q = kRowsMaxW; q < kRowsMaxW + 4; ++q) x[q] = 0.f;
+      const float* wrow = Ws + (size_t)((c * a.KH + kh) * a.KW) * Fp + fq * 4;
+#pragma unroll
+      for (int kw = 0; kw < 4; ++kw) {  // KW <= 4 (checked by the plan)
+        if (kw < a.KW) {
+          const float4 wv = *reinterpret_cast<const float4*>(wrow + (size_t)kw * Fp);
+#pragma unroll
+          for (int w = 0; w < kRowsMaxW; ++w) {
+            const float xv = x[w + kw];
+            acc[0][w] = fmaf(xv, wv.x, acc[0][w]);
+            acc[1][w] = fmaf(xv, wv.y, acc[1][w]);
+            acc[2][w] = fmaf(xv, wv.z, acc[2][w]);
+            acc[3][w] = fmaf(xv, wv.w, acc[3][w]);
+          }
+        }
+      }
+    }
+  }
+  const bool has_bias = a.epi == TCB200_EPI_BIAS || a.epi == TCB200_EPI_BIAS_RELU;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int f = fq * 4 + j;
+    const float bias = has_bias ? __ldg(a.bias + g * a.F + f) : 0.f;
+    float* o = a.O + ((((size_t)(n0 + ni) * a.G + g) * a.F + f) * a.OH + h) * a.OW;
+#pragma unroll
+    for (int w = 0; w < kRowsMaxW; ++w) {
+      if (w < a.OW) {
+        float v = acc[j][w];
+        if (a.accumulate) v += o[w];
+        o[w] = apply_epilogue_rt(a.epi, v, bias);
+      }
+    }
+  }
+}
+
+bool rows_ok(const tcb200_problem_t& p) {
+  const int64_t C = p.conv[2], F = p.conv[3], H = p.conv[4], W = p.conv[5], KH = p.conv[6], KW = p.conv[7];
+  const int64_t OH = H - KH + 1;
+  return W <= kRowsMaxW && KW <= 4 && F % 4 == 0 && (F / 4) * OH <= 256 &&
+         sizeof(float) * (size_t)(C * KH * KW * F + C * H * kRowsPitch) <= 96 * 1024;
+}
+
+// n per CTA: as many as fit 256 threads and the shared-memory budget
+int rows_n_per_cta(const tcb200_problem_t& p, int want, size_t* bytes) {
+  const int64_t C = p.conv[2], F = p.conv[3], H = p.conv[4], KH = p.conv[6], KW = p.conv[7];
+  const int64_t per_n = (F / 4) * (H - KH + 1);
+  int64_t n = want > 0 ? want : 2;
+  n = std::max<int64_t>(1, std::min<int64_t>(n, std::min<int64_t>(256 / per_n, p.conv[0])));
+  auto need = [&](int64_t k) { return sizeof(float) * (size_t)(C * KH * KW * F + k * C * H * kRowsPitch); };
+  while (n > 1 && need(n) > 96 * 1024) --n;
+  if (bytes) *bytes = need(n);
+  return (int)n;
+}
+
 bool valid(const tcb200_problem_t& p) {
   for (int i = 0; i < 8; ++i)
     if (p.conv[i] <= 0 || p.conv[i] > (1 << 24)) return false;
@@ -128,6 +259,15 @@ int pick_band(const tcb200_problem_t& p, int ft, size_t* bytes) {
 int group_conv_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n) {
   if (!valid(p)) return TCB200_ERR_INVALID_ARGUMENT;
   int cnt = 0;
+  if (rows_ok(p)) {
+    // bk = n per CTA of the rows kernel
+    const int ns[] = {2, 1, 4};
+    for (int k : ns) {
+      if (k > p.conv[0] || k * (p.conv[3] / 4) * (p.conv[4] - p.conv[6] + 1) > 256) continue;
+      if (cnt < max && out) out[cnt] = tcb200_tile_t{TCB200_VARIANT_SIMT, 0, 0, k, 0, 0, 0};
+      ++cnt;
+    }
+  }
   const int threads[] = {256, 224, 128};
   for (int t : threads) {
     if (cnt < max && out) out[cnt] = tcb200_tile_t{TCB200_VARIANT_SIMT, 0, 0, 0, 0, t, 0};
@@ -145,8 +285,24 @@ int group_conv_plan(Plan& plan) {
   if (t.variant == TCB200_VARIANT_AUTO) {
     t.variant = TCB200_VARIANT_SIMT;
     t.threads = 256;
+    t.bk = rows_ok(p) ? 2 : 0;
   }
   if (t.variant != TCB200_VARIANT_SIMT) return TCB200_ERR_UNSUPPORTED;
+  if (t.bk > 0) {  // rows kernel
+    if (!rows_ok(p)) return TCB200_ERR_UNSUPPORTED;
+    size_t bytes = 0;
+    const int npc = rows_n_per_cta(p, t.bk, &bytes);
+    const int per_n = (int)((p.conv[3] / 4) * (p.conv[4] - p.conv[6] + 1));
+    t.bk = npc;
+    t.bm = 0; t.bn = 4;
+    t.threads = (int)round_up((int64_t)npc * per_n, 32);
+    if (ceil_div(p.conv[0], npc) > 65535) return TCB200_ERR_TOO_LARGE;
+    plan.launch.grid = dim3((unsigned)p.conv[1], (unsigned)ceil_div(p.conv[0], npc), 1);
+    plan.launch.block = dim3(t.threads, 1, 1);
+    plan.launch.smem = bytes;
+    plan.kernel_id = 100;
+    return TCB200_OK;
+  }
   if (t.threads <= 0) t.threads = 256;
   if (t.threads > 256 || t.threads % 32) return TCB200_ERR_INVALID_ARGUMENT;
   const int ft = p.conv[3] % 4 == 0 ? 4 : 1;
@@ -174,6 +330,15 @@ int group_conv_launch(const Plan& plan, const float* I, const float* W, const fl
   a.OH = a.H - a.KH + 1; a.OW = a.Wd - a.KW + 1;
   a.band = plan.tile.bm;
   a.epi = p.epilogue; a.accumulate = p.accumulate;
+  if (plan.kernel_id == 100) {
+    if (plan.launch.smem > 48 * 1024)
+      TCB200_CUDA_TRY(cudaFuncSetAttribute(group_conv_rows_kernel,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+    group_conv_rows_kernel<<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(
+        a, plan.tile.bk, (int)p.conv[0]);
+    TCB200_CUDA_TRY(cudaGetLastError());
+    return TCB200_OK;
+  }
   auto fn = plan.kernel_id == 4 ? group_conv_simt_kernel<4> : group_conv_simt_kernel<1>;
   if (plan.launch.smem > 48 * 1024)
     TCB200_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
