@@ -63,4 +63,6 @@ def test_query_and_plan_without_gpu():
     c = cabi.group_conv_problem(32, 32, 16, 16, 16, 16, 3, 3)
     plan = cabi.Plan(c)
     grid, _ = plan.geometry()
-    assert grid[0] == 32 * 32
+    assert grid[:2] == (32, 16)                       # rows kernel: one CTA per (g, pair of n)
+    band = [t for t in cabi.query(c) if t.bk == 0][0]
+    assert cabi.Plan(c, band).geometry()[0][0] == 32 * 32
