@@ -32,8 +32,11 @@ METRIC = "tc5_suite_throughput"
 UNIT = "TFLOP/s"
 
 # DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from the
-# ncu capture summarised under profiles/), keyed by workload; None until captured.
-NCU_TRAFFIC_BYTES = {}
+# ncu captures summarised under profiles/), keyed by workload.  mlp3: the first (largest) of its three
+# launches, [16384x2048]x[1024x2048]; algorithmic bytes of that launch are 209.7 MB, the 67 MB output
+# is only partly written back to DRAM before the kernel ends (it stays in the 126 MB L2).
+NCU_TRAFFIC_BYTES = {"mlp3": 142714368 + 41280256, "tmm": 270605312 + 3933696,
+                     "tensordot": 413891584 + 84587008}
 
 
 def load_peaks():
@@ -104,13 +107,13 @@ class ClockSampler:
 class Program:
     """One comprehension compiled for its shapes: device buffers, plans, launch."""
 
-    def __init__(self, w, dev, seed, rotate_bytes):
+    def __init__(self, w, dev, seed, rotate_bytes, tune=False):
         import torch
         from tensorcomprehensions_b200 import workloads as wl
         from tensorcomprehensions_b200 import runtime
         self.w, self.dev = w, dev
         self.host_inputs = [t.pin_memory() for t in wl.make_inputs(w, seed=seed)]
-        self.exe = runtime.compile_workload(w, dev)
+        self.exe = runtime.compile_workload(w, dev, tune=tune)
         # rotating sets: a small problem is timed over enough copies of its buffers to exceed L2
         per_set = w.bytes
         self.sets = max(1, -(-rotate_bytes // per_set)) if per_set < rotate_bytes else 1
@@ -165,7 +168,7 @@ def run_product(args):
 
     names = list(wl.ALL) if args.workload == "suite" else [args.workload]
     progs = [Program(wl.ALL[n](), dev, seed=20240 + wl.ALL[n]().index + 1000 * rank,
-                     rotate_bytes=192 << 20) for n in names]
+                     rotate_bytes=192 << 20, tune=args.tune) for n in names]
     launches_per_step = sum(p.launches_per_run for p in progs)
 
     def barrier():
@@ -181,12 +184,12 @@ def run_product(args):
         return float(t.item())
 
     # ---- timed region 1: device-resident inputs ----------------------------------------------
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()   # sampled from the warm-up to the end of the host-buffer region
     for _ in range(args.warmup):
         for p in progs:
             p.run()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(progs) + 1)] for _ in range(args.steps)]
     barrier()
     for s in range(args.steps):
@@ -259,7 +262,8 @@ def run_product(args):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
         "config": {"workload": "tc5_suite" if args.workload == "suite" else args.workload,
-                   "configs": names, "shard": "one full-size instance of every comprehension per GPU",
+                   "configs": names, "tiles": "autotuned" if args.tune else "family default",
+                   "shard": "one full-size instance of every comprehension per GPU",
                    "l2": "inputs larger than L2 (suite streams 1.2 GB per step; small problems rotate over "
                          ">=192 MB of buffer sets)"},
         "e2e": {"value": round(flops_step / (e2e_ms * 1e-3) / 1e12, 3), "unit": UNIT,
@@ -342,13 +346,15 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="suite",
                     choices=["suite", "tensordot", "batchmatmul", "tmm", "group_conv", "mlp3"])
     ap.add_argument("--cpu-seconds", type=float, default=20.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--tune", action="store_true",
+                    help="pick each comprehension's tile with the autotuner's sweep instead of the family default")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

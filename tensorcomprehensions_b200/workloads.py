@@ -50,7 +50,9 @@ def mlp3(float(B, N) I, float(O, N) W2, float(O) B2, float(P, O) W3, float(P) B3
 }
 """
 
-Workload = namedtuple("Workload", "name index tc entry shapes dist shard_inputs reduction bytes flops bound")
+# shard_inputs: per input, the dimension that is split across GPUs (None = replicated);
+# shard_outputs: per output, the dimension the shards concatenate along.
+Workload = namedtuple("Workload", "name index tc entry shapes dist shard_inputs shard_outputs reduction bytes flops bound")
 
 
 def _prod(s):
@@ -63,14 +65,14 @@ def _prod(s):
 def tensordot(N=32, C1=512, C2=8, C3=2, H=28, W=28):
     shapes = [(N, C1, C2, H, W), (N, C2, C3, H, W)]
     out = N * C1 * C3 * H * W
-    return Workload("tensordot", 1, TENSORDOT_TC, "tensordot", shapes, ["uniform", "uniform"], [0, 0], [C2],
+    return Workload("tensordot", 1, TENSORDOT_TC, "tensordot", shapes, ["uniform", "uniform"], [0, 0], [0], [C2],
                     4 * (_prod(shapes[0]) + _prod(shapes[1]) + out), 2 * out * C2, "hbm")
 
 
 def batchmatmul(B=500, N=26, M=72, K=26):
     shapes = [(B, N, M), (B, M, K)]
     out = B * N * K
-    return Workload("batchmatmul", 2, BATCHMATMUL_TC, "batch_matmul", shapes, ["normal", "normal"], [0, 0], [M],
+    return Workload("batchmatmul", 2, BATCHMATMUL_TC, "batch_matmul", shapes, ["normal", "normal"], [0, 0], [0], [M],
                     4 * (_prod(shapes[0]) + _prod(shapes[1]) + out), 2 * out * M, "hbm")
 
 
@@ -78,7 +80,7 @@ def tmm(M=128, N=16384, K=4096):
     shapes = [(M, K), (N, K)]
     out = M * N
     # N is the sharded index: B's rows are sharded (dim 0), A is replicated (None)
-    return Workload("tmm", 3, TMM_TC, "tmm", shapes, ["normal", "normal"], [None, 0], [K],
+    return Workload("tmm", 3, TMM_TC, "tmm", shapes, ["normal", "normal"], [None, 0], [1], [K],
                     4 * (_prod(shapes[0]) + _prod(shapes[1]) + out), 2 * out * K, "tensor")
 
 
@@ -86,7 +88,7 @@ def group_conv(N=32, G=32, C=16, F=16, H=16, W=16, KH=3, KW=3):
     shapes = [(N, G, C, H, W), (G, F, C, KH, KW), (G, F)]
     out = N * G * F * (H - KH + 1) * (W - KW + 1)
     return Workload("group_conv", 4, GROUP_CONV_TC, "group_convolution", shapes,
-                    ["uniform", "uniform", "uniform"], [0, None, None], [C * KH * KW],
+                    ["uniform", "uniform", "uniform"], [0, None, None], [0], [C * KH * KW],
                     4 * (sum(_prod(s) for s in shapes) + out), 2 * out * C * KH * KW + out, "hbm")
 
 
@@ -96,7 +98,7 @@ def mlp3(B=16384, N=2048, O=1024, P=512, Q=256):
             ("normal", 1 / math.sqrt(O)), ("normal", 1 / math.sqrt(O)),
             ("normal", 1 / math.sqrt(P)), ("normal", 1 / math.sqrt(P))]
     outs = B * (O + P + Q)
-    return Workload("mlp3", 5, MLP3_TC, "mlp3", shapes, dist, [0, None, None, None, None, None, None],
+    return Workload("mlp3", 5, MLP3_TC, "mlp3", shapes, dist, [0, None, None, None, None, None, None], [0, 0, 0],
                     [N, O, P], 4 * (sum(_prod(s) for s in shapes) + outs),
                     2 * B * (N * O + O * P + P * Q), "tensor")
 
