@@ -141,6 +141,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
       : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ float to_tf32(float x) {
   uint32_t r;
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
@@ -448,8 +460,12 @@ __host__ __device__ constexpr int ts_smem_bytes(int bn) {
   return kTsStages * ts_stage_bytes(bn) + kBarrierBytes + 1024;
 }
 
+// Warps: 0 = TMA, 1 = MMA, 2-9 = split (two sets of four that alternate k-blocks, so one set's
+// shared-load / tcgen05.st latencies overlap the other set's work), 10-17 = drain/epilogue.
+constexpr int kTsThreads = 576;
+
 template <int BN>
-__global__ void __launch_bounds__(448, 1)
+__global__ void __launch_bounds__(kTsThreads, 1)
 contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
                       const __grid_constant__ CUtensorMap tmB, TcArgs a) {
   constexpr int SPLIT = 3;
@@ -462,8 +478,8 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
   static_assert(BN <= 128, "two accumulators and the A ring share 512 TMEM columns");
   constexpr uint32_t IDESC = make_idesc(BN);
   constexpr bool CHUNKED = BN <= 128;  // register budget of the drain warps: BN fp32 per thread
-  constexpr int SPLIT_WARPS = SPLIT == 3 ? 4 : 0;
-  constexpr int DRAIN_WARP0 = 2 + SPLIT_WARPS;
+  constexpr int SPLIT_WARPS = 8;
+  constexpr int DRAIN_WARP0 = 2 + SPLIT_WARPS;  // warp 10: 10 % 4 == 2, the drain quarters stay {2,3,0,1,...}
   constexpr uint32_t TMEM_COLS = 512;
   static_assert(STAGES >= 2, "pipeline needs two stages");
 
@@ -572,12 +588,14 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
     }
   } else if (warp < DRAIN_WARP0) {
     // ------------------------------------------------ 3xTF32 split: A -> TMEM, B lo -> smem
-    const int tt = threadIdx.x - 64;  // 0..127
-    const int arow = (warp & 3) * 32 + lane;  // TMEM lane quarter of this warp
+    const int set = (warp - 2) >> 2;                  // which of the two alternating sets
+    const int tt = (threadIdx.x - 64) & 127;          // 0..127 within the set
+    const int arow = (warp & 3) * 32 + lane;          // TMEM lane quarter of this warp
     uint32_t it = 0;
     bool ok = true;
     for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        if ((int)(it & 1) != set) continue;
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
         ok = mbar_wait(&full[s], ph, 3, a.dev_status, abort_flag);
@@ -682,10 +700,13 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
           tc_fence_after();
 #pragma unroll
           for (int g = 0; g < G; ++g) {
-            float v[32];
-            tmem_ld32(tmem_base + buf * BN + lane_base + col0 + g * 32, v);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) acc[g][j] += v[j];
+            for (int h = 0; h < 2; ++h) {  // 16 columns at a time keeps the staging registers low
+              float v[16];
+              tmem_ld16(tmem_base + buf * BN + lane_base + col0 + g * 32 + h * 16, v);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) acc[g][h * 16 + j] += v[j];
+            }
           }
           tc_fence_before();
           mbar_arrive(&acc_empty[buf]);  // the MMA warp may overwrite this accumulator
@@ -798,7 +819,7 @@ int launch_ts(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, co
                                          ts_smem_bytes(BN)));
     configured.fetch_or(bit, std::memory_order_release);
   }
-  contraction_ts_kernel<BN><<<plan.launch.grid, plan.launch.block, ts_smem_bytes(BN), s>>>(ta, tb, args);
+  contraction_ts_kernel<BN><<<plan.launch.grid, dim3(kTsThreads, 1, 1), ts_smem_bytes(BN), s>>>(ta, tb, args);
   TCB200_CUDA_TRY(cudaGetLastError());
   return TCB200_OK;
 }
@@ -816,7 +837,7 @@ int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max,
   };
   auto push_ts = [&](int bn) {
     if (cnt < max && out)
-      out[cnt] = tcb200_tile_t{TCB200_VARIANT_TCGEN05_TS, BM, bn, BK, kTsStages, 448, 3};
+      out[cnt] = tcb200_tile_t{TCB200_VARIANT_TCGEN05_TS, BM, bn, BK, kTsStages, kTsThreads, 3};
     ++cnt;
   };
   if (p.N >= 128) push_ts(128);
@@ -838,10 +859,10 @@ int contraction_tc_plan(Plan& plan) {
   if (t.split_tf32 != 1 && t.split_tf32 != 3) return TCB200_ERR_UNSUPPORTED;
   t.bm = BM;
   t.bk = BK;
-  t.threads = t.split_tf32 == 3 ? 448 : 320;
   const bool ts_mode = t.variant == TCB200_VARIANT_TCGEN05_TS;
   if (ts_mode && (t.bn > 128 || t.split_tf32 != 3)) return TCB200_ERR_UNSUPPORTED;
   t.stages = ts_mode ? kTsStages : num_stages(t.bn, t.split_tf32);
+  t.threads = ts_mode ? kTsThreads : (t.split_tf32 == 3 ? 448 : 320);
   // persistent CTAs, one per SM, walking the tiles with a static stride
   const int64_t tiles = ceil_div(p.N, t.bn) * ceil_div(p.M, BM) * p.batch;
   plan.launch.grid = dim3((unsigned)std::min<int64_t>(tiles, kNumSMs), 1, 1);
