@@ -235,7 +235,7 @@ int tcb200_launch(const tcb200_plan_t* plan, const void* const* inputs, int n_in
     case TCB200_FAMILY_TENSORDOT:
       return tensordot_launch(P, in0, in1, out, s, dev_status);
     case TCB200_FAMILY_GROUP_CONV:
-      return group_conv_launch(P, in0, in1, bias, out, s);
+      return group_conv_launch(P, in0, in1, bias, out, s, dev_status);
     case TCB200_FAMILY_CONTRACTION:
       if (P.tile.variant == TCB200_VARIANT_TCGEN05 || P.tile.variant == TCB200_VARIANT_TCGEN05_TS)
         return contraction_tc_launch(P, in0, in1, bias, out, s, dev_status);

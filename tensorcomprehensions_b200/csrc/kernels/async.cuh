@@ -1,5 +1,5 @@
 // mbarrier / bulk-copy PTX helpers shared by the kernels that stage data with the async proxy.
-// Every wait is bounded: after ~2 s of wall time it records a code in *dev_status (and in a
+// Every wait is bounded: after about two seconds it records a code in *dev_status (and in a
 // CTA-wide abort flag so the other roles stop too) and returns false instead of spinning.
 #pragma once
 
@@ -22,6 +22,13 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One arrival per warp instead of 32: every lane's prior writes are ordered before the elected
+// lane's (releasing) arrive by the warp barrier.  128 arrivals on one mbarrier are 128 serialised
+// shared-memory atomics, which is what bounds pipelines with little work per hand-off.
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -33,20 +40,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ uint64_t globaltimer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait: gives up after ~2 s of wall time, records `code` and returns false.
+// Bounded wait: gives up after ~4e9 SM cycles (about two seconds), records `code` and returns false.
+// The SM cycle counter is used because it is cheap to read; a wait that succeeds within the first
+// few thousand polls (every wait of a healthy pipeline) never reads a timer at all.
 static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int code,
-                                            int* dev_status, volatile int* abort_flag) {
-  const uint64_t t0 = globaltimer_ns();
+                                                   int* dev_status, volatile int* abort_flag) {
+  const long long t0 = clock64();
   for (;;) {
-    for (int i = 0; i < 256; ++i)
+    for (int i = 0; i < 1024; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > 2000000000ull) {
+    if (clock64() - t0 > 4000000000ll) {
       *abort_flag = code;
       if (dev_status) atomicCAS(dev_status, 0, code);
       return false;
@@ -55,11 +59,10 @@ static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parit
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code,
                                           int* dev_status, volatile int* abort_flag) {
-  for (int i = 0; i < 64; ++i)
+  for (int i = 0; i < 4096; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, code, dev_status, abort_flag);
 }
-
 
 // 1-D bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completion counted
 // in bytes on an mbarrier.  No multicast.

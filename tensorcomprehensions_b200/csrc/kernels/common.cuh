@@ -5,6 +5,7 @@
 #include <stdint.h>
 
 #include <algorithm>
+#include <atomic>
 
 #include "tcb200.h"
 
@@ -29,6 +30,17 @@ struct Plan {
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline int64_t round_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device): the call costs tens of
+// microseconds, more than the small kernels themselves.  `flags` is a per-kernel static bit set.
+template <typename Fn>
+inline cudaError_t ensure_dynamic_smem(Fn fn, int bytes, int device, std::atomic<uint64_t>& flags) {
+  const uint64_t bit = 1ull << (device & 63);
+  if (flags.load(std::memory_order_acquire) & bit) return cudaSuccess;
+  cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) flags.fetch_or(bit, std::memory_order_release);
+  return e;
+}
 
 // Thread-local record of the last failing CUDA call.
 void set_last_cuda_error(cudaError_t e);
@@ -64,7 +76,12 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
 int group_conv_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n);
 int group_conv_plan(Plan& plan);
 int group_conv_launch(const Plan& plan, const float* I, const float* W, const float* bias,
-                      float* O, cudaStream_t s);
+                      float* O, cudaStream_t s, int* dev_status);
+// tensor-core variant (group_conv_tcgen05.cu)
+bool group_conv_tc_ok(const tcb200_problem_t& p);
+int group_conv_tc_plan(Plan& plan);
+int group_conv_tc_launch(const Plan& plan, const float* I, const float* W, const float* bias,
+                         float* O, cudaStream_t s, int* dev_status);
 
 // ---- small device helpers ---------------------------------------------------------------
 

@@ -4,7 +4,7 @@
 // Replaces the kernel the reference generates for tc/benchmarks/group_convolution.cc:124-132
 // (library twin tc/library/group_convolution.h:26-44 with stride 1).
 //
-// Two SIMT kernels:
+// SIMT kernels (a tensor-core implicit-GEMM variant lives in group_conv_tcgen05.cu):
 //  * rows kernel (default when W <= 16 and F % 4 == 0): one CTA per (g, pair of n).  A thread owns
 //    one output row h of four output channels: 4 x OW accumulators in registers.  Per (c, kh) it
 //    reads one input row (four 128-bit shared loads, row pitch padded to 20 floats so the eight
@@ -268,6 +268,13 @@ int group_conv_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int
       ++cnt;
     }
   }
+  // tensor-core implicit GEMM: correct and fp32-accurate, but hand-off latency bound on small
+  // problems (see group_conv_tcgen05.cu); the sweep can still pick it where it wins
+  if (group_conv_tc_ok(p)) {
+    if (cnt < max && out)
+      out[cnt] = tcb200_tile_t{TCB200_VARIANT_TCGEN05_TS, 128, (int)p.conv[3], 8, 4, 448, 3};
+    ++cnt;
+  }
   const int threads[] = {256, 224, 128};
   for (int t : threads) {
     if (cnt < max && out) out[cnt] = tcb200_tile_t{TCB200_VARIANT_SIMT, 0, 0, 0, 0, t, 0};
@@ -282,6 +289,8 @@ int group_conv_plan(Plan& plan) {
   if (!valid(p)) return TCB200_ERR_INVALID_ARGUMENT;
   if (p.epilogue == TCB200_EPI_RELU) return TCB200_ERR_UNSUPPORTED;
   tcb200_tile_t& t = plan.tile;
+  if (t.variant == TCB200_VARIANT_AUTO && !rows_ok(p) && group_conv_tc_ok(p)) t.variant = TCB200_VARIANT_TCGEN05_TS;
+  if (t.variant == TCB200_VARIANT_TCGEN05_TS) return group_conv_tc_plan(plan);
   if (t.variant == TCB200_VARIANT_AUTO) {
     t.variant = TCB200_VARIANT_SIMT;
     t.threads = 256;
@@ -321,7 +330,8 @@ int group_conv_plan(Plan& plan) {
 }
 
 int group_conv_launch(const Plan& plan, const float* I, const float* W, const float* bias,
-                      float* O, cudaStream_t s) {
+                      float* O, cudaStream_t s, int* dev_status) {
+  if (plan.kernel_id == 200) return group_conv_tc_launch(plan, I, W, bias, O, s, dev_status);
   const tcb200_problem_t& p = plan.p;
   ConvArgs a;
   a.I = I; a.W = W; a.bias = bias; a.O = O;
@@ -331,18 +341,16 @@ int group_conv_launch(const Plan& plan, const float* I, const float* W, const fl
   a.band = plan.tile.bm;
   a.epi = p.epilogue; a.accumulate = p.accumulate;
   if (plan.kernel_id == 100) {
-    if (plan.launch.smem > 48 * 1024)
-      TCB200_CUDA_TRY(cudaFuncSetAttribute(group_conv_rows_kernel,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+    static std::atomic<uint64_t> rows_configured{0};
+    TCB200_CUDA_TRY(ensure_dynamic_smem(group_conv_rows_kernel, (int)kSmemBudget, plan.device, rows_configured));
     group_conv_rows_kernel<<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(
         a, plan.tile.bk, (int)p.conv[0]);
     TCB200_CUDA_TRY(cudaGetLastError());
     return TCB200_OK;
   }
   auto fn = plan.kernel_id == 4 ? group_conv_simt_kernel<4> : group_conv_simt_kernel<1>;
-  if (plan.launch.smem > 48 * 1024)
-    TCB200_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)kSmemBudget));
+  static std::atomic<uint64_t> band_configured[2];
+  TCB200_CUDA_TRY(ensure_dynamic_smem(fn, (int)kSmemBudget, plan.device, band_configured[plan.kernel_id == 4]));
   fn<<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(a);
   TCB200_CUDA_TRY(cudaGetLastError());
   return TCB200_OK;

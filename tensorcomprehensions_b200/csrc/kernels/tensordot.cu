@@ -346,8 +346,9 @@ int tensordot_launch(const Plan& plan, const float* I0, const float* I1, float* 
     a.R = plan.tile.bm; a.RY = plan.tile.bn; a.stages = plan.tile.stages;
     a.stage_bytes = (uint32_t)round_up((int64_t)a.R * p.td[2] * a.P4 * 16, 128);
     a.dev_status = dev_status;
-    TCB200_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)plan.launch.smem));
+    static std::atomic<uint64_t> configured[17][5];  // one flag word per (C2 <= 16, C3 <= 4) instantiation
+    TCB200_CUDA_TRY(ensure_dynamic_smem(fn, (int)kBulkSmemBudget + 1024, plan.device,
+                                        configured[p.td[2]][p.td[3]]));
     fn<<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(a);
   } else if (plan.kernel_id >= 1 && aligned) {
     vec4_fn fn = pick_vec4((int)p.td[2], (int)p.td[3]);

@@ -62,7 +62,10 @@ def test_query_and_plan_without_gpu():
     assert cabi.VARIANT_SIMT_SMALL in variants and cabi.VARIANT_SIMT in variants
     c = cabi.group_conv_problem(32, 32, 16, 16, 16, 16, 3, 3)
     plan = cabi.Plan(c)
-    grid, _ = plan.geometry()
-    assert grid[:2] == (32, 16)                       # rows kernel: one CTA per (g, pair of n)
-    band = [t for t in cabi.query(c) if t.bk == 0][0]
+    grid, block = plan.geometry()
+    assert grid[:2] == (32, 16)                        # rows kernel: one CTA per (g, pair of n)
+    tcv = [t for t in cabi.query(c) if t.variant == cabi.VARIANT_TCGEN05_TS][0]
+    pt = cabi.Plan(c, tcv)
+    assert pt.geometry() == ((148, 1, 1), (448, 1, 1)) and "tcgen05_ts" in pt.describe()  # implicit GEMM
+    band = [t for t in cabi.query(c) if t.variant == cabi.VARIANT_SIMT and t.bk == 0][0]
     assert cabi.Plan(c, band).geometry()[0][0] == 32 * 32

@@ -154,6 +154,10 @@ def test_contraction_shared_operand_and_padded_ld(cuda):
     (1, 1, 1, 1, 3, 3, 3, 3),       # single output pixel
     (2, 2, 8, 4, 6, 6, 1, 1),       # 1x1 filter
     (1, 2, 4, 8, 8, 10, 5, 2),      # non-square filter
+    (3, 2, 8, 16, 12, 20, 3, 3),    # tensor-core form: C=8, wide rows
+    (2, 2, 16, 32, 10, 8, 5, 2),    # tensor-core form: F=32, non-square filter
+    (5, 3, 16, 16, 9, 12, 1, 1),    # tensor-core form: 1x1 filter, odd item count
+    (1, 1, 16, 16, 24, 20, 3, 3),   # tensor-core form: four pixel tiles
 ])
 @pytest.mark.parametrize("bias", [True, False])
 def test_group_conv_small(cuda, dims, bias):
