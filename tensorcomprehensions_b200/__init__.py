@@ -10,7 +10,7 @@ __all__ = ["cabi", "workloads"]
 
 def __getattr__(name):
     # Python API (needs the tclib extension) is resolved on first use.
-    if name in ("define", "compile", "autotune", "autotune_and_compile", "MappingOptions", "TC",
+    if name in ("define", "compile", "autotune", "autotune_and_compile", "MappingOptions", "TC", "HostStagedExecutor",
                 "Tuner", "TunerConfig", "Executor", "assert_almost_equal", "make_naive_options_factory",
                 "make_load_from_cache_options_factory", "make_autotuned_options_factory",
                 "MappingOptionsCache", "tclib", "sharding"):

@@ -82,6 +82,65 @@ class Executor(object):
         return getattr(self.executor, name)
 
 
+class HostStagedExecutor(object):
+    """Runs a compiled TC from HOST buffers: pinned inputs are copied in on one stream, the kernels
+    run on a second, outputs are copied back on a third, with `depth` sets of device buffers so the
+    copies of consecutive calls overlap each other and the compute (PCIe is full duplex).
+
+        staged = tc.HostStagedExecutor(exe, depth=2)
+        for batch in batches: staged.submit(batch.inputs, batch.outputs)   # pinned CPU tensors
+        staged.synchronize()
+
+    Every call still moves all of its inputs to the device and all of its outputs back."""
+
+    def __init__(self, executor: Executor, device, depth: int = 2):
+        self.exe, self.device, self.depth = executor, torch.device(device), depth
+        self.out_shapes = executor.output_shapes()
+        self.h2d, self.compute, self.d2h = (torch.cuda.Stream(self.device) for _ in range(3))
+        self.dev_in = [None] * depth
+        self.dev_out = [[torch.empty(s, dtype=torch.float32, device=self.device) for s in self.out_shapes]
+                        for _ in range(depth)]
+        self.ev_in = [torch.cuda.Event() for _ in range(depth)]
+        self.ev_done = [torch.cuda.Event() for _ in range(depth)]
+        self.ev_out = [torch.cuda.Event() for _ in range(depth)]
+        self.calls = 0
+
+    def submit(self, host_inputs, host_outputs):
+        k, slot = self.calls, self.calls % self.depth
+        self.calls += 1
+        if self.dev_in[slot] is None:
+            self.dev_in[slot] = [torch.empty(t.shape, dtype=t.dtype, device=self.device) for t in host_inputs]
+        with torch.cuda.stream(self.h2d):
+            if k >= self.depth:
+                self.h2d.wait_event(self.ev_done[slot])  # the kernels that read this input set are done
+            for d, h in zip(self.dev_in[slot], host_inputs):
+                d.copy_(h, non_blocking=True)
+            self.ev_in[slot].record(self.h2d)
+        with torch.cuda.stream(self.compute):
+            self.compute.wait_event(self.ev_in[slot])
+            if k >= self.depth:
+                self.compute.wait_event(self.ev_out[slot])  # the previous results of this set were copied out
+            self.exe.run(self.dev_in[slot], self.dev_out[slot])
+            self.ev_done[slot].record(self.compute)
+        with torch.cuda.stream(self.d2h):
+            self.d2h.wait_event(self.ev_done[slot])
+            for h, d in zip(host_outputs, self.dev_out[slot]):
+                h.copy_(d, non_blocking=True)
+            self.ev_out[slot].record(self.d2h)
+
+    def join(self, stream=None):
+        """Makes `stream` (default: the current one) wait for everything submitted so far."""
+        stream = stream or torch.cuda.current_stream(self.device)
+        for s in (self.h2d, self.compute, self.d2h):
+            ev = torch.cuda.Event()
+            ev.record(s)
+            stream.wait_event(ev)
+
+    def synchronize(self):
+        for s in (self.h2d, self.compute, self.d2h):
+            s.synchronize()
+
+
 def compile(tc: str, entry_point: str, mapping_options: Union[str, MappingOptions], *inputs) -> Executor:
     """Compiles `entry_point` of `tc` for the shapes of `inputs` (tensor_comprehensions/__init__.py:123-143)."""
     return Executor(tclib.compile(tc, entry_point, list(inputs), _as_options(mapping_options)))

@@ -23,6 +23,9 @@ class CompiledWorkload:
     def run(self, inputs, outputs):
         self.exe.run(inputs, outputs)
 
+    def host_staged(self, depth=2):
+        return api.HostStagedExecutor(self.exe, self.dev, depth)
+
     def describe(self):
         return " ; ".join(l for l in self.exe.compiled_source.strip().split("\n") if not l.startswith("//"))
 
