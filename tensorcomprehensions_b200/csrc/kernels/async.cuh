@@ -63,6 +63,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int co
     if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, code, dev_status, abort_flag);
 }
+// Same contract, for a role that waits long and can afford to react late: sleeps `ns` nanoseconds
+// between polls so that its polling does not queue ahead of the shared-memory accesses of the
+// warps that are on the critical path.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, unsigned ns, int code,
+                                                  int* dev_status, volatile int* abort_flag) {
+  for (int i = 0; i < 4096; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(ns);
+  }
+  return mbar_wait_slow(bar, parity, code, dev_status, abort_flag);
+}
 
 // 1-D bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completion counted
 // in bytes on an mbarrier.  No multicast.

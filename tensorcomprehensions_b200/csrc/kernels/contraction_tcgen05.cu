@@ -233,8 +233,8 @@ contraction_tc_kernel(const __grid_constant__ CUtensorMap tmA,
           // so the raw tile already IS the hi operand; only lo = v - trunc(v) has to be written.
           const float4 v = hi[i];
           float4 l;
-          l.x = to_tf32(v.x - tf32_trunc(v.x)); l.y = to_tf32(v.y - tf32_trunc(v.y));
-          l.z = to_tf32(v.z - tf32_trunc(v.z)); l.w = to_tf32(v.w - tf32_trunc(v.w));
+          l.x = tf32_lo(v.x); l.y = tf32_lo(v.y);
+          l.z = tf32_lo(v.z); l.w = tf32_lo(v.w);
           lo[i] = l;
         }
         // make the generic-proxy writes visible to the tensor core (async proxy)
@@ -357,26 +357,38 @@ __host__ __device__ constexpr int ts_smem_bytes(int bn) {
   return kTsStages * ts_stage_bytes(bn) + kBarrierBytes + 1024;
 }
 
-// Warps: 0 = TMA, 1 = MMA, 2-9 = split (two sets of four that alternate k-blocks, so one set's
-// shared-load / tcgen05.st latencies overlap the other set's work), 10-17 = drain/epilogue.
-constexpr int kTsThreads = 576;
+// Warps: 0 = TMA, 1-2 = MMA issuers, 3-10 = split (two sets of four that alternate k-blocks, so one
+// set's shared-load / tcgen05.st latencies overlap the other set's work), 11-18 = drain/epilogue.
+//
+// Two MMA issuers: measured on B200, a thread that has just issued tcgen05.mma instructions pays
+// about 230 cycles for its next mbarrier wait (and ~100 for any other instruction) while the tensor
+// pipe holds at most one or two MMAs in its queue, so a single issuer that waits once per k-block
+// leaves the pipe idle a quarter of the time (1030 cycles per 12 MMAs of 128x128x8 instead of 768).
+// Two issuers in different warps that alternate k-blocks hide each other's waits (769 cycles per
+// 12 MMAs in the same microbenchmark).  Their MMAs reach the pipe in no fixed order, so every MMA
+// accumulates (none overwrites) and the drain warps zero an accumulator after reading it; the order
+// of the fp32 additions inside the tensor core can therefore differ between two runs.
+constexpr int kTsThreads = 608;
 
 template <int BN>
 __global__ void __launch_bounds__(kTsThreads, 1)
 contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
                       const __grid_constant__ CUtensorMap tmB, TcArgs a) {
-  constexpr int SPLIT = 3;
   constexpr int STAGES = kTsStages;
   constexpr int A_BYTES = BM * BK * 4;
   constexpr int B_BYTES = BN * BK * 4;
   constexpr int RAW = A_BYTES + B_BYTES;   // bytes one k-block brings in through TMA
   constexpr int STAGE = ts_stage_bytes(BN);  // [A raw][B raw = hi][B lo]
   constexpr uint32_t A_RING = 256;         // first TMEM column of the A ring
-  static_assert(BN <= 128, "two accumulators and the A ring share 512 TMEM columns");
+  constexpr uint32_t ACC_STRIDE = 128;     // TMEM columns between the two accumulators
+  static_assert(BN <= 128 && BN % 16 == 0, "two accumulators and the A ring share 512 TMEM columns");
   constexpr uint32_t IDESC = make_idesc(BN);
-  constexpr bool CHUNKED = BN <= 128;  // register budget of the drain warps: BN fp32 per thread
+  constexpr int MMA_WARPS = 2;
+  constexpr int SPLIT_WARP0 = 1 + MMA_WARPS;
   constexpr int SPLIT_WARPS = 8;
-  constexpr int DRAIN_WARP0 = 2 + SPLIT_WARPS;  // warp 10: 10 % 4 == 2, the drain quarters stay {2,3,0,1,...}
+  constexpr int DRAIN_WARP0 = SPLIT_WARP0 + SPLIT_WARPS;  // 8 warps from here cover every TMEM lane quarter twice
+  constexpr int FIRST = ((BN / 2 + 15) / 16) * 16;         // columns of the first drain warp of a quarter
+  constexpr int PIECES = FIRST / 16;
   constexpr uint32_t TMEM_COLS = 512;
   static_assert(STAGES >= 2, "pipeline needs two stages");
 
@@ -392,7 +404,7 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (a.K + BK - 1) / BK;
-  const int chunk_kb = CHUNKED ? kChunkKB : num_kb;
+  const int chunk_kb = kChunkKB;
   const int num_chunks = (num_kb + chunk_kb - 1) / chunk_kb;
   const int tiles_n = (a.N + BN - 1) / BN, tiles_m = (a.M + BM - 1) / BM;
   const int64_t num_tiles = (int64_t)tiles_n * tiles_m * a.batch;
@@ -404,7 +416,7 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
       mbar_init(&empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_full[b], MMA_WARPS);
       mbar_init(&acc_empty[b], 256);
     }
     *abort_flag = 0;
@@ -415,6 +427,21 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const bool second_half = warp >= DRAIN_WARP0 + 4;  // drain warps: which column range of the quarter
+  float zeros[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) zeros[j] = 0.f;
+  if (warp >= DRAIN_WARP0) {
+    // both accumulators start at zero
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    for (int buf = 0; buf < 2; ++buf)
+      for (int c = second_half ? FIRST : 0; c < (second_half ? BN : FIRST); c += 16)
+        tmem_st16(tmem_base + buf * ACC_STRIDE + lane_base + c, zeros);
+    tmem_wait_st();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
 
   // Static persistent schedule: tile t -> (batch, m-tile, n-tile) with n fastest, so the CTAs that
   // run at the same time share rows of A (L2 hits) while B tiles differ.
@@ -446,8 +473,9 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
         if (!ok) break;
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------ MMA issuer
+  } else if (warp < SPLIT_WARP0) {
+    // ------------------------------------------------ MMA issuers (k-block it belongs to issuer it & 1)
+    const int issuer = warp - 1;
     if (lane == 0) {
       uint32_t it = 0, cc = 0;
       bool ok = true;
@@ -457,10 +485,10 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
           ok = mbar_wait(&acc_empty[buf], ((cc >> 1) & 1) ^ 1, 5, a.dev_status, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t tmem_d = tmem_base + buf * BN;
-          uint32_t accumulate = 0;
+          const uint32_t tmem_d = tmem_base + buf * ACC_STRIDE;
           const int kb_end = min(num_kb, (c + 1) * chunk_kb);
           for (int kb = c * chunk_kb; kb < kb_end; ++kb, ++it) {
+            if ((int)(it & 1) != issuer) continue;
             const int s = it % STAGES;
             const uint32_t ph = (it / STAGES) & 1;
             ok = mbar_wait(&ready[s], ph, 2, a.dev_status, abort_flag);
@@ -472,10 +500,9 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
             for (int ks = 0; ks < BK / UMMA_K; ++ks) {
               const uint32_t koff = ks * UMMA_K * 4;
               const uint64_t b_hi = make_desc(sb + koff), b_lo = make_desc(sb + B_BYTES + koff);
-              umma_tf32_ts(tmem_d, ta_lo + ks * UMMA_K, b_hi, IDESC, accumulate);
+              umma_tf32_ts(tmem_d, ta_lo + ks * UMMA_K, b_hi, IDESC, 1);
               umma_tf32_ts(tmem_d, ta_hi + ks * UMMA_K, b_lo, IDESC, 1);
               umma_tf32_ts(tmem_d, ta_hi + ks * UMMA_K, b_hi, IDESC, 1);
-              accumulate = 1;
             }
             umma_commit(&empty[s]);  // frees the stage once the MMAs above have read it
           }
@@ -485,8 +512,8 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
     }
   } else if (warp < DRAIN_WARP0) {
     // ------------------------------------------------ 3xTF32 split: A -> TMEM, B lo -> smem
-    const int set = (warp - 2) >> 2;                  // which of the two alternating sets
-    const int tt = (threadIdx.x - 64) & 127;          // 0..127 within the set
+    const int set = (warp - SPLIT_WARP0) >> 2;             // which of the two alternating sets
+    const int tt = (threadIdx.x - SPLIT_WARP0 * 32) & 127;  // 0..127 within the set
     const int arow = (warp & 3) * 32 + lane;          // TMEM lane quarter of this warp
     uint32_t it = 0;
     bool ok = true;
@@ -508,7 +535,7 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
             hi[4 * c + 0] = v.x; hi[4 * c + 1] = v.y; hi[4 * c + 2] = v.z; hi[4 * c + 3] = v.w;
           }
 #pragma unroll
-          for (int j = 0; j < 32; ++j) lo[j] = to_tf32(hi[j] - tf32_trunc(hi[j]));
+          for (int j = 0; j < 32; ++j) lo[j] = tf32_lo(hi[j]);
           const uint32_t ta = tmem_base + A_RING + s * 64 + ((uint32_t)(arow & ~31) << 16);
           tmem_st32(ta, hi);        // the tensor core truncates the fp32 words itself
           tmem_st32(ta + 32, lo);
@@ -521,8 +548,8 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
           for (int i = tt; i < B_BYTES / 16; i += 128) {
             const float4 v = bh[i];
             float4 l;
-            l.x = to_tf32(v.x - tf32_trunc(v.x)); l.y = to_tf32(v.y - tf32_trunc(v.y));
-            l.z = to_tf32(v.z - tf32_trunc(v.z)); l.w = to_tf32(v.w - tf32_trunc(v.w));
+            l.x = tf32_lo(v.x); l.y = tf32_lo(v.y);
+            l.z = tf32_lo(v.z); l.w = tf32_lo(v.w);
             bl[i] = l;
           }
         }
@@ -535,10 +562,13 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
     }
   } else {
     // ------------------------------------------------ drain + epilogue
+    // Two warps per TMEM lane quarter: the first takes columns [0, FIRST), the second [FIRST, BN),
+    // both in pieces of 16 columns (FIRST is a multiple of 16, so BN = 112 splits into 64 + 48).
+    // A piece is zeroed right after it has been read: both MMA issuers always accumulate.
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     const uint32_t lane_base = (uint32_t)(q * 32) << 16;
-    constexpr int HALF = BN / 2;                       // columns this warp drains
-    const int col0 = ((warp - DRAIN_WARP0) >> 2) * HALF;
+    const int col0 = second_half ? FIRST : 0;
+    const int mycols = second_half ? BN - FIRST : FIRST;
     const bool has_bias = a.epi == TCB200_EPI_BIAS || a.epi == TCB200_EPI_BIAS_RELU;
     uint32_t cc = 0;
     bool ok = true;
@@ -549,12 +579,12 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
       float* crow = a.C + (int64_t)bz * a.stride_c + (int64_t)row * a.ldc;
       const float bias_m = (has_bias && a.bias_on_m && row < a.M) ? __ldg(a.bias + row) : 0.f;
 
-      auto store32 = [&](const float* v, int c0) {
+      auto store16 = [&](const float* v, int c0) {
         const int nb = n0 + c0;
         if (row >= a.M || nb >= a.N) return;
-        if (a.c_vec && nb + 32 <= a.N) {
+        if (a.c_vec && nb + 16 <= a.N) {
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
+          for (int j = 0; j < 16; j += 4) {
             float4 b4 = make_float4(bias_m, bias_m, bias_m, bias_m);
             if (has_bias && !a.bias_on_m) b4 = __ldg(reinterpret_cast<const float4*>(a.bias + nb + j));
             float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
@@ -571,7 +601,7 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
+          for (int j = 0; j < 16; ++j) {
             const int n = nb + j;
             if (n < a.N) {
               float o = v[j];
@@ -583,49 +613,35 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
         }
       };
 
-      if (CHUNKED) {
-        constexpr int G = CHUNKED ? HALF / 32 : 1;
-        float acc[G][32];
+      float acc[PIECES][16];
 #pragma unroll
-        for (int g = 0; g < G; ++g)
+      for (int g = 0; g < PIECES; ++g)
 #pragma unroll
-          for (int j = 0; j < 32; ++j) acc[g][j] = 0.f;
-        for (int c = 0; c < num_chunks; ++c, ++cc) {
-          const uint32_t buf = cc & 1;
-          ok = mbar_wait(&acc_full[buf], (cc >> 1) & 1, 4, a.dev_status, abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-#pragma unroll
-          for (int g = 0; g < G; ++g) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {  // 16 columns at a time keeps the staging registers low
-              float v[16];
-              tmem_ld16(tmem_base + buf * BN + lane_base + col0 + g * 32 + h * 16, v);
-#pragma unroll
-              for (int j = 0; j < 16; ++j) acc[g][h * 16 + j] += v[j];
-            }
-          }
-          tc_fence_before();
-          mbar_arrive(&acc_empty[buf]);  // the MMA warp may overwrite this accumulator
-        }
-        if (!ok) break;
-#pragma unroll
-        for (int g = 0; g < G; ++g) store32(acc[g], col0 + g * 32);
-      } else {
+        for (int j = 0; j < 16; ++j) acc[g][j] = 0.f;
+      for (int c = 0; c < num_chunks; ++c, ++cc) {
         const uint32_t buf = cc & 1;
         ok = mbar_wait(&acc_full[buf], (cc >> 1) & 1, 4, a.dev_status, abort_flag);
         if (!ok) break;
         tc_fence_after();
-#pragma unroll 1
-        for (int c0 = col0; c0 < col0 + HALF; c0 += 32) {
-          float v[32];
-          tmem_ld32(tmem_base + buf * BN + lane_base + c0, v);
-          store32(v, c0);
+#pragma unroll
+        for (int g = 0; g < PIECES; ++g) {
+          if (g * 16 < mycols) {  // the same for the whole warp
+            const uint32_t taddr = tmem_base + buf * ACC_STRIDE + lane_base + col0 + g * 16;
+            float v[16];
+            tmem_ld16(taddr, v);
+            tmem_st16(taddr, zeros);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[g][j] += v[j];
+          }
         }
+        tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(&acc_empty[buf]);
-        ++cc;
+        mbar_arrive(&acc_empty[buf]);  // zeroed: the MMA warps may accumulate into it again
       }
+      if (!ok) break;
+#pragma unroll
+      for (int g = 0; g < PIECES; ++g)
+        if (g * 16 < mycols) store16(acc[g], col0 + g * 16);
     }
   }
 
@@ -738,6 +754,7 @@ int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max,
     ++cnt;
   };
   if (p.N >= 128) push_ts(128);
+  if (p.N >= 112) push_ts(112);
   const int bns[] = {128, 256, 64};
   for (int bn : bns)
     if (p.N >= bn) push(bn, 3);
@@ -752,7 +769,8 @@ int contraction_tc_plan(Plan& plan) {
   tcb200_tile_t& t = plan.tile;
   if (t.bn == 0) t.bn = 128;
   if (t.split_tf32 == 0) t.split_tf32 = 3;
-  if (t.bn != 64 && t.bn != 128 && t.bn != 256) return TCB200_ERR_UNSUPPORTED;
+  if (t.bn != 64 && t.bn != 128 && t.bn != 256 && !(t.bn == 112 && t.variant == TCB200_VARIANT_TCGEN05_TS))
+    return TCB200_ERR_UNSUPPORTED;
   if (t.split_tf32 != 1 && t.split_tf32 != 3) return TCB200_ERR_UNSUPPORTED;
   t.bm = BM;
   t.bk = BK;
@@ -791,6 +809,7 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
   switch (plan.kernel_id) {
     case 100643: return launch_ts<64>(plan, ta, tb, a, s);
     case 101283: return launch_ts<128>(plan, ta, tb, a, s);
+    case 101123: return launch_ts<112>(plan, ta, tb, a, s);
     case 643: return launch_inst<64, 3>(plan, ta, tb, a, s);
     case 641: return launch_inst<64, 1>(plan, ta, tb, a, s);
     case 1283: return launch_inst<128, 3>(plan, ta, tb, a, s);

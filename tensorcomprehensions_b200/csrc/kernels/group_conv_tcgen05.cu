@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tc_kernel(ConvTcArgs a
           const float v = raw[e];
           const uint32_t off = s * shift_bytes + (c >> 2) * lbo + (f >> 3) * 128 + (f & 7) * 16 + (c & 3) * 4;
           *reinterpret_cast<float*>(chi + off) = v;
-          *reinterpret_cast<float*>(clo + off) = to_tf32(v - tf32_trunc(v));
+          *reinterpret_cast<float*>(clo + off) = tf32_lo(v);
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         mbar_arrive_warp(&w_ready[buf]);
@@ -221,7 +221,7 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tc_kernel(ConvTcArgs a
 #pragma unroll
             for (int c = 0; c < C; ++c) hi[c] = src[(size_t)c * PL];
 #pragma unroll
-            for (int c = 0; c < C; ++c) lo[c] = to_tf32(hi[c] - tf32_trunc(hi[c]));
+            for (int c = 0; c < C; ++c) lo[c] = tf32_lo(hi[c]);
             const uint32_t ta = tmem_base + kAccCols + slot * (2 * C) + lane_addr;
             if (C == 16) {
               tmem_st16(ta, hi);

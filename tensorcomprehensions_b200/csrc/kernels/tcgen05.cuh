@@ -126,6 +126,14 @@ __device__ __forceinline__ float to_tf32(float x) {
 __device__ __forceinline__ float tf32_trunc(float x) {
   return __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
 }
+// Low half of the 3xTF32 split, for a consumer that truncates its operands to tf32 (the tensor core
+// does): v - trunc(v) is exact in fp32, and adding half a tf32 ulp to its bit pattern turns the
+// consumer's truncation into round-to-nearest (ties away from zero), which is what cvt.rna.tf32
+// would give.  Three full-rate integer/float instructions per element instead of a conversion.
+__device__ __forceinline__ float tf32_lo(float v) {
+  const float r = v - tf32_trunc(v);
+  return __uint_as_float(__float_as_uint(r) + 0x1000u);
+}
 
 
 // 8- and 16-column stores of 32-bit words: thread t writes columns [c, c+N) of lane base+t.

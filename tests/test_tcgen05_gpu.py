@@ -40,7 +40,7 @@ def test_tcgen05_tiles(cuda, bn, split, shape):
     assert_close(out, ref, K, [A, B], 3e-7 if split == 3 else None, plan.describe())
 
 
-@pytest.mark.parametrize("bn", [128, 64])
+@pytest.mark.parametrize("bn", [128, 112, 64])
 @pytest.mark.parametrize("shape", [(1, 128, 256, 128), (1, 256, 384, 512), (1, 70, 200, 132), (3, 130, 96, 256),
                                    (1, 300, 128, 4096)])
 def test_tcgen05_ts_tiles(cuda, bn, shape):
@@ -92,7 +92,7 @@ def test_tcgen05_rejects_what_it_cannot_take(cuda):
         cabi.Plan(p, tc_tile(128, 3))
 
 
-@pytest.mark.parametrize("bn,split,ts", [(128, 3, True), (128, 3, False), (256, 3, False), (128, 1, False)])
+@pytest.mark.parametrize("bn,split,ts", [(128, 3, True), (112, 3, True), (128, 3, False), (256, 3, False), (128, 1, False)])
 def test_tmm_full_size_tcgen05(cuda, bn, split, ts):
     w = wl.tmm()
     A, B = wl.make_inputs(w)
