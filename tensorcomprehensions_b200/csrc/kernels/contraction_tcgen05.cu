@@ -350,11 +350,31 @@ contraction_tc_kernel(const __grid_constant__ CUtensorMap tmA,
 // A's hi and lo halves into TMEM columns (tcgen05.st, lane = row) and the MMAs read A from there,
 // so shared memory only carries B: its traffic per k-block drops from 192 KB to 128 KB (BN = 128)
 // and a stage shrinks to 48 KB (A raw + B raw + B lo), which doubles the pipeline depth.
-// TMEM columns: [0, 2*BN) two accumulators, [256, 512) ring of 4 x (A hi: 32, A lo: 32).
-__host__ __device__ constexpr int ts_stage_bytes(int bn) { return BM * BK * 4 + 2 * bn * BK * 4; }
-constexpr int kTsStages = 4;
+// TMEM columns: [0, 128) and [128, 256) two accumulators, [256, 512) ring of 4 x (A hi: 32, A lo: 32).
+//
+// Three rings, each as deep as its storage allows, because a buffer's life differs per operand:
+// raw A lives in shared memory only from its TMA load to the split (2 slots of 16 KB), A hi/lo in
+// TMEM from the split to the last MMA that reads them (4 slots of 64 columns), and B raw + B lo in
+// shared memory from the TMA load to the last MMA (the rest of shared memory: 6 slots at BN = 128).
+// Measured life of a B slot is ~4100 cycles (TMA ~1000, split ~1050, hand-offs ~850, MMAs of two
+// interleaved k-blocks ~1200), so the slot count sets the k-block rate until the tensor pipe does.
+//
+// Every ring has an EVEN number of slots.  Even and odd k-blocks are handled by different warps
+// (split sets, MMA issuers) that can drift apart by more than a ring; with an even ring a slot
+// always belongs to the same set, which therefore sees its barrier phases one by one.  With an
+// odd ring a set could test a parity that the other set's phase has not yet flipped and take a
+// stale "complete" for its own.
+constexpr int kTsTmemSlots = 4;
+constexpr int kTsBarrierBytes = 512;
+constexpr int kTsSmemLimit = 227 * 1024;
+__host__ __device__ constexpr int ts_a_slots(int bn) { return bn <= 64 ? 4 : 2; }
+__host__ __device__ constexpr int ts_b_slot_bytes(int bn) { return 2 * bn * BK * 4; }
+__host__ __device__ constexpr int ts_b_slots(int bn) {
+  const int n = (kTsSmemLimit - kTsBarrierBytes - 1024 - ts_a_slots(bn) * BM * BK * 4) / ts_b_slot_bytes(bn);
+  return n >= 8 ? 8 : (n & ~1);
+}
 __host__ __device__ constexpr int ts_smem_bytes(int bn) {
-  return kTsStages * ts_stage_bytes(bn) + kBarrierBytes + 1024;
+  return ts_a_slots(bn) * BM * BK * 4 + ts_b_slots(bn) * ts_b_slot_bytes(bn) + kTsBarrierBytes + 1024;
 }
 
 // Warps: 0 = TMA, 1-2 = MMA issuers, 3-10 = split (two sets of four that alternate k-blocks, so one
@@ -374,11 +394,11 @@ template <int BN>
 __global__ void __launch_bounds__(kTsThreads, 1)
 contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
                       const __grid_constant__ CUtensorMap tmB, TcArgs a) {
-  constexpr int STAGES = kTsStages;
+  constexpr int A_SLOTS = ts_a_slots(BN), T_SLOTS = kTsTmemSlots, B_SLOTS = ts_b_slots(BN);
   constexpr int A_BYTES = BM * BK * 4;
   constexpr int B_BYTES = BN * BK * 4;
-  constexpr int RAW = A_BYTES + B_BYTES;   // bytes one k-block brings in through TMA
-  constexpr int STAGE = ts_stage_bytes(BN);  // [A raw][B raw = hi][B lo]
+  constexpr int B_SLOT = ts_b_slot_bytes(BN);  // [B raw = hi][B lo]
+  constexpr int B_RING = A_SLOTS * A_BYTES;    // byte offset of the B ring
   constexpr uint32_t A_RING = 256;         // first TMEM column of the A ring
   constexpr uint32_t ACC_STRIDE = 128;     // TMEM columns between the two accumulators
   static_assert(BN <= 128 && BN % 16 == 0, "two accumulators and the A ring share 512 TMEM columns");
@@ -390,14 +410,19 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
   constexpr int FIRST = ((BN / 2 + 15) / 16) * 16;         // columns of the first drain warp of a quarter
   constexpr int PIECES = FIRST / 16;
   constexpr uint32_t TMEM_COLS = 512;
-  static_assert(STAGES >= 2, "pipeline needs two stages");
+  static_assert(B_SLOTS >= 2 && B_SLOTS <= 8 && A_SLOTS <= 4, "barrier arrays are sized for 4 / 8 slots");
+  static_assert(A_SLOTS % 2 == 0 && B_SLOTS % 2 == 0 && T_SLOTS % 2 == 0, "a slot must stay with one set");
+  static_assert(B_BYTES % 1024 == 0, "128-byte swizzle atoms must stay 1024-byte aligned");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE);
-  uint64_t* ready = full + STAGES;
-  uint64_t* empty = ready + STAGES;
-  uint64_t* acc_full = empty + STAGES;   // [2]
+  uint64_t* full_a = reinterpret_cast<uint64_t*>(smem + B_RING + B_SLOTS * B_SLOT);  // [4]
+  uint64_t* empty_a = full_a + 4;        // [4] raw A slot read by the split warps
+  uint64_t* tfree = empty_a + 4;         // [4] TMEM A slot read by its MMAs
+  uint64_t* full_b = tfree + 4;          // [8]
+  uint64_t* ready = full_b + 8;          // [8] A hi/lo in TMEM and B lo in shared memory are in place
+  uint64_t* empty_b = ready + 8;         // [8] B slot read by its MMAs
+  uint64_t* acc_full = empty_b + 8;      // [2]
   uint64_t* acc_empty = acc_full + 2;    // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -410,10 +435,15 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
   const int64_t num_tiles = (int64_t)tiles_n * tiles_m * a.batch;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&ready[s], 128);
-      mbar_init(&empty[s], 1);
+    for (int s = 0; s < 4; ++s) {
+      mbar_init(&full_a[s], 1);
+      mbar_init(&empty_a[s], 4);  // one elected arrival per warp of the split set
+      mbar_init(&tfree[s], 1);
+    }
+    for (int s = 0; s < 8; ++s) {
+      mbar_init(&full_b[s], 1);
+      mbar_init(&ready[s], 4);
+      mbar_init(&empty_b[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], MMA_WARPS);
@@ -461,14 +491,15 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
         const int za = a.a_batched ? bz : 0, zb = a.b_batched ? bz : 0;
         bool ok = true;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          ok = mbar_wait(&empty[s], ph ^ 1, 1, a.dev_status, abort_flag);
+          const int sa = it % A_SLOTS, sb = it % B_SLOTS;
+          ok = mbar_wait(&empty_a[sa], ((it / A_SLOTS) & 1) ^ 1, 1, a.dev_status, abort_flag);
           if (!ok) break;
-          uint8_t* st = smem + s * STAGE;
-          mbar_expect_tx(&full[s], RAW);
-          tma_load_3d(st, &tmA, kb * BK, m0, za, &full[s]);
-          tma_load_3d(st + A_BYTES, &tmB, kb * BK, n0, zb, &full[s]);
+          mbar_expect_tx(&full_a[sa], A_BYTES);
+          tma_load_3d(smem + sa * A_BYTES, &tmA, kb * BK, m0, za, &full_a[sa]);
+          ok = mbar_wait(&empty_b[sb], ((it / B_SLOTS) & 1) ^ 1, 1, a.dev_status, abort_flag);
+          if (!ok) break;
+          mbar_expect_tx(&full_b[sb], B_BYTES);
+          tma_load_3d(smem + B_RING + sb * B_SLOT, &tmB, kb * BK, n0, zb, &full_b[sb]);
         }
         if (!ok) break;
       }
@@ -489,13 +520,12 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
           const int kb_end = min(num_kb, (c + 1) * chunk_kb);
           for (int kb = c * chunk_kb; kb < kb_end; ++kb, ++it) {
             if ((int)(it & 1) != issuer) continue;
-            const int s = it % STAGES;
-            const uint32_t ph = (it / STAGES) & 1;
-            ok = mbar_wait(&ready[s], ph, 2, a.dev_status, abort_flag);
+            const int s = it % B_SLOTS, st = it % T_SLOTS;
+            ok = mbar_wait(&ready[s], (it / B_SLOTS) & 1, 2, a.dev_status, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t sb = smem_u32(smem + s * STAGE) + A_BYTES;
-            const uint32_t ta_hi = tmem_base + A_RING + s * 64, ta_lo = ta_hi + 32;
+            const uint32_t sb = smem_u32(smem + B_RING + s * B_SLOT);
+            const uint32_t ta_hi = tmem_base + A_RING + st * 64, ta_lo = ta_hi + 32;
 #pragma unroll
             for (int ks = 0; ks < BK / UMMA_K; ++ks) {
               const uint32_t koff = ks * UMMA_K * 4;
@@ -504,7 +534,8 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
               umma_tf32_ts(tmem_d, ta_hi + ks * UMMA_K, b_lo, IDESC, 1);
               umma_tf32_ts(tmem_d, ta_hi + ks * UMMA_K, b_hi, IDESC, 1);
             }
-            umma_commit(&empty[s]);  // frees the stage once the MMAs above have read it
+            umma_commit(&empty_b[s]);  // both fire once the MMAs above have read their operands
+            umma_commit(&tfree[st]);
           }
           if (ok) umma_commit(&acc_full[buf]);
         }
@@ -520,14 +551,15 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
     for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         if ((int)(it & 1) != set) continue;
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
-        ok = mbar_wait(&full[s], ph, 3, a.dev_status, abort_flag);
+        const int sa = it % A_SLOTS, st = it % T_SLOTS, s = it % B_SLOTS;
+        ok = mbar_wait(&tfree[st], ((it / T_SLOTS) & 1) ^ 1, 6, a.dev_status, abort_flag) &&
+             mbar_wait(&full_a[sa], (it / A_SLOTS) & 1, 3, a.dev_status, abort_flag);
         if (!ok) break;
+        tc_fence_after();
         // A: this thread owns row `arow` of the 128 x 32 tile (TMEM lane = row).  The tile sits in
         // shared memory with the 128-byte swizzle: 16-byte chunk c of row r is stored at c ^ (r & 7).
         {
-          const float4* arow_p = reinterpret_cast<const float4*>(smem + s * STAGE + arow * 128);
+          const float4* arow_p = reinterpret_cast<const float4*>(smem + sa * A_BYTES + arow * 128);
           float hi[32], lo[32];
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
@@ -536,14 +568,21 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
           }
 #pragma unroll
           for (int j = 0; j < 32; ++j) lo[j] = tf32_lo(hi[j]);
-          const uint32_t ta = tmem_base + A_RING + s * 64 + ((uint32_t)(arow & ~31) << 16);
+          const uint32_t ta = tmem_base + A_RING + st * 64 + ((uint32_t)(arow & ~31) << 16);
           tmem_st32(ta, hi);        // the tensor core truncates the fp32 words itself
           tmem_st32(ta + 32, lo);
+          // Free the raw A slot only once the stores have consumed the registers the shared-memory
+          // loads filled.  Arriving right after the loads were issued was measured to be too early:
+          // with two slots the refill landed while loads were still queued (wrong results).
+          tmem_wait_st();
+          mbar_arrive_warp(&empty_a[sa]);
         }
+        ok = mbar_wait(&full_b[s], (it / B_SLOTS) & 1, 7, a.dev_status, abort_flag);
+        if (!ok) break;
         // B: lo = tf32(v - trunc(v)) into the second buffer, same (swizzled) layout; raw B is hi.
         {
-          const float4* bh = reinterpret_cast<const float4*>(smem + s * STAGE + A_BYTES);
-          float4* bl = reinterpret_cast<float4*>(smem + s * STAGE + A_BYTES + B_BYTES);
+          const float4* bh = reinterpret_cast<const float4*>(smem + B_RING + s * B_SLOT);
+          float4* bl = reinterpret_cast<float4*>(smem + B_RING + s * B_SLOT + B_BYTES);
 #pragma unroll 4
           for (int i = tt; i < B_BYTES / 16; i += 128) {
             const float4 v = bh[i];
@@ -557,7 +596,7 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
         tc_fence_before();
         // make the generic-proxy writes visible to the tensor core (async proxy)
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive(&ready[s]);
+        mbar_arrive_warp(&ready[s]);
       }
     }
   } else {
@@ -750,7 +789,7 @@ int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max,
   };
   auto push_ts = [&](int bn) {
     if (cnt < max && out)
-      out[cnt] = tcb200_tile_t{TCB200_VARIANT_TCGEN05_TS, BM, bn, BK, kTsStages, kTsThreads, 3};
+      out[cnt] = tcb200_tile_t{TCB200_VARIANT_TCGEN05_TS, BM, bn, BK, ts_b_slots(bn), kTsThreads, 3};
     ++cnt;
   };
   if (p.N >= 128) push_ts(128);
@@ -776,7 +815,7 @@ int contraction_tc_plan(Plan& plan) {
   t.bk = BK;
   const bool ts_mode = t.variant == TCB200_VARIANT_TCGEN05_TS;
   if (ts_mode && (t.bn > 128 || t.split_tf32 != 3)) return TCB200_ERR_UNSUPPORTED;
-  t.stages = ts_mode ? kTsStages : num_stages(t.bn, t.split_tf32);
+  t.stages = ts_mode ? ts_b_slots(t.bn) : num_stages(t.bn, t.split_tf32);
   t.threads = ts_mode ? kTsThreads : (t.split_tf32 == 3 ? 448 : 320);
   // persistent CTAs, one per SM, walking the tiles with a static stride
   const int64_t tiles = ceil_div(p.N, t.bn) * ceil_div(p.M, BM) * p.batch;
