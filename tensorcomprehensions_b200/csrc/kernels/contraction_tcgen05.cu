@@ -352,29 +352,31 @@ contraction_tc_kernel(const __grid_constant__ CUtensorMap tmA,
 // and a stage shrinks to 48 KB (A raw + B raw + B lo), which doubles the pipeline depth.
 // TMEM columns: [0, 128) and [128, 256) two accumulators, [256, 512) ring of 4 x (A hi: 32, A lo: 32).
 //
-// Three rings, each as deep as its storage allows, because a buffer's life differs per operand:
-// raw A lives in shared memory only from its TMA load to the split (2 slots of 16 KB), A hi/lo in
-// TMEM from the split to the last MMA that reads them (4 slots of 64 columns), and B raw + B lo in
-// shared memory from the TMA load to the last MMA (the rest of shared memory: 6 slots at BN = 128).
-// Measured life of a B slot is ~4100 cycles (TMA ~1000, split ~1050, hand-offs ~850, MMAs of two
-// interleaved k-blocks ~1200), so the slot count sets the k-block rate until the tensor pipe does.
+// Three rings in shared memory plus one in TMEM, each as deep as its buffer's life needs:
+//   raw A     4 x 16 KB   TMA load -> read by the split (~1600 cycles)
+//   raw B     6 x BN*128  TMA load -> last MMA that reads it as "B hi" (~4000 cycles)
+//   B lo      4 x BN*128  written by the split -> last MMA (~2400 cycles)
+//   A hi/lo   4 x 64 TMEM columns, same life and same slot index as B lo ("processed" slot)
+// 224 KB at BN = 128.  One ring of whole stages (A raw + B raw + B lo = 48 KB) fits only four
+// times.
 //
 // Every ring has an EVEN number of slots.  Even and odd k-blocks are handled by different warps
 // (split sets, MMA issuers) that can drift apart by more than a ring; with an even ring a slot
 // always belongs to the same set, which therefore sees its barrier phases one by one.  With an
 // odd ring a set could test a parity that the other set's phase has not yet flipped and take a
 // stale "complete" for its own.
-constexpr int kTsTmemSlots = 4;
+constexpr int kTsASlots = 4;
+constexpr int kTsPSlots = 4;      // processed slots: A hi/lo in TMEM + B lo in shared memory
 constexpr int kTsBarrierBytes = 512;
 constexpr int kTsSmemLimit = 227 * 1024;
-__host__ __device__ constexpr int ts_a_slots(int bn) { return bn <= 64 ? 4 : 2; }
-__host__ __device__ constexpr int ts_b_slot_bytes(int bn) { return 2 * bn * BK * 4; }
+__host__ __device__ constexpr int ts_b_bytes(int bn) { return bn * BK * 4; }
 __host__ __device__ constexpr int ts_b_slots(int bn) {
-  const int n = (kTsSmemLimit - kTsBarrierBytes - 1024 - ts_a_slots(bn) * BM * BK * 4) / ts_b_slot_bytes(bn);
+  const int n = (kTsSmemLimit - kTsBarrierBytes - 1024 - kTsASlots * BM * BK * 4 - kTsPSlots * ts_b_bytes(bn)) /
+                ts_b_bytes(bn);
   return n >= 8 ? 8 : (n & ~1);
 }
 __host__ __device__ constexpr int ts_smem_bytes(int bn) {
-  return ts_a_slots(bn) * BM * BK * 4 + ts_b_slots(bn) * ts_b_slot_bytes(bn) + kTsBarrierBytes + 1024;
+  return kTsASlots * BM * BK * 4 + (ts_b_slots(bn) + kTsPSlots) * ts_b_bytes(bn) + kTsBarrierBytes + 1024;
 }
 
 // Warps: 0 = TMA, 1-2 = MMA issuers, 3-10 = split (two sets of four that alternate k-blocks, so one
@@ -394,11 +396,11 @@ template <int BN>
 __global__ void __launch_bounds__(kTsThreads, 1)
 contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
                       const __grid_constant__ CUtensorMap tmB, TcArgs a) {
-  constexpr int A_SLOTS = ts_a_slots(BN), T_SLOTS = kTsTmemSlots, B_SLOTS = ts_b_slots(BN);
+  constexpr int A_SLOTS = kTsASlots, P_SLOTS = kTsPSlots, B_SLOTS = ts_b_slots(BN);
   constexpr int A_BYTES = BM * BK * 4;
   constexpr int B_BYTES = BN * BK * 4;
-  constexpr int B_SLOT = ts_b_slot_bytes(BN);  // [B raw = hi][B lo]
-  constexpr int B_RING = A_SLOTS * A_BYTES;    // byte offset of the B ring
+  constexpr int B_RING = A_SLOTS * A_BYTES;          // byte offset of the raw B ring
+  constexpr int LO_RING = B_RING + B_SLOTS * B_BYTES;  // byte offset of the B lo ring
   constexpr uint32_t A_RING = 256;         // first TMEM column of the A ring
   constexpr uint32_t ACC_STRIDE = 128;     // TMEM columns between the two accumulators
   static_assert(BN <= 128 && BN % 16 == 0, "two accumulators and the A ring share 512 TMEM columns");
@@ -410,18 +412,18 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
   constexpr int FIRST = ((BN / 2 + 15) / 16) * 16;         // columns of the first drain warp of a quarter
   constexpr int PIECES = FIRST / 16;
   constexpr uint32_t TMEM_COLS = 512;
-  static_assert(B_SLOTS >= 2 && B_SLOTS <= 8 && A_SLOTS <= 4, "barrier arrays are sized for 4 / 8 slots");
-  static_assert(A_SLOTS % 2 == 0 && B_SLOTS % 2 == 0 && T_SLOTS % 2 == 0, "a slot must stay with one set");
+  static_assert(B_SLOTS >= 2 && B_SLOTS <= 8 && A_SLOTS <= 4 && P_SLOTS == 4, "barrier arrays / TMEM ring sizes");
+  static_assert(A_SLOTS % 2 == 0 && B_SLOTS % 2 == 0 && P_SLOTS % 2 == 0, "a slot must stay with one set");
   static_assert(B_BYTES % 1024 == 0, "128-byte swizzle atoms must stay 1024-byte aligned");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* full_a = reinterpret_cast<uint64_t*>(smem + B_RING + B_SLOTS * B_SLOT);  // [4]
+  uint64_t* full_a = reinterpret_cast<uint64_t*>(smem + LO_RING + P_SLOTS * B_BYTES);  // [4]
   uint64_t* empty_a = full_a + 4;        // [4] raw A slot read by the split warps
-  uint64_t* tfree = empty_a + 4;         // [4] TMEM A slot read by its MMAs
-  uint64_t* full_b = tfree + 4;          // [8]
-  uint64_t* ready = full_b + 8;          // [8] A hi/lo in TMEM and B lo in shared memory are in place
-  uint64_t* empty_b = ready + 8;         // [8] B slot read by its MMAs
+  uint64_t* pfree = empty_a + 4;         // [4] processed slot (A hi/lo, B lo) read by its MMAs
+  uint64_t* ready = pfree + 4;           // [4] processed slot filled
+  uint64_t* full_b = ready + 4;          // [8]
+  uint64_t* empty_b = full_b + 8;        // [8] raw B slot read by its MMAs
   uint64_t* acc_full = empty_b + 8;      // [2]
   uint64_t* acc_empty = acc_full + 2;    // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
@@ -438,11 +440,11 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
     for (int s = 0; s < 4; ++s) {
       mbar_init(&full_a[s], 1);
       mbar_init(&empty_a[s], 4);  // one elected arrival per warp of the split set
-      mbar_init(&tfree[s], 1);
+      mbar_init(&pfree[s], 1);
+      mbar_init(&ready[s], 4);
     }
     for (int s = 0; s < 8; ++s) {
       mbar_init(&full_b[s], 1);
-      mbar_init(&ready[s], 4);
       mbar_init(&empty_b[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -499,7 +501,7 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
           ok = mbar_wait(&empty_b[sb], ((it / B_SLOTS) & 1) ^ 1, 1, a.dev_status, abort_flag);
           if (!ok) break;
           mbar_expect_tx(&full_b[sb], B_BYTES);
-          tma_load_3d(smem + B_RING + sb * B_SLOT, &tmB, kb * BK, n0, zb, &full_b[sb]);
+          tma_load_3d(smem + B_RING + sb * B_BYTES, &tmB, kb * BK, n0, zb, &full_b[sb]);
         }
         if (!ok) break;
       }
@@ -520,22 +522,23 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
           const int kb_end = min(num_kb, (c + 1) * chunk_kb);
           for (int kb = c * chunk_kb; kb < kb_end; ++kb, ++it) {
             if ((int)(it & 1) != issuer) continue;
-            const int s = it % B_SLOTS, st = it % T_SLOTS;
-            ok = mbar_wait(&ready[s], (it / B_SLOTS) & 1, 2, a.dev_status, abort_flag);
+            const int s = it % B_SLOTS, sp = it % P_SLOTS;
+            ok = mbar_wait(&ready[sp], (it / P_SLOTS) & 1, 2, a.dev_status, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t sb = smem_u32(smem + B_RING + s * B_SLOT);
-            const uint32_t ta_hi = tmem_base + A_RING + st * 64, ta_lo = ta_hi + 32;
+            const uint32_t sb = smem_u32(smem + B_RING + s * B_BYTES);
+            const uint32_t sl = smem_u32(smem + LO_RING + sp * B_BYTES);
+            const uint32_t ta_hi = tmem_base + A_RING + sp * 64, ta_lo = ta_hi + 32;
 #pragma unroll
             for (int ks = 0; ks < BK / UMMA_K; ++ks) {
               const uint32_t koff = ks * UMMA_K * 4;
-              const uint64_t b_hi = make_desc(sb + koff), b_lo = make_desc(sb + B_BYTES + koff);
+              const uint64_t b_hi = make_desc(sb + koff), b_lo = make_desc(sl + koff);
               umma_tf32_ts(tmem_d, ta_lo + ks * UMMA_K, b_hi, IDESC, 1);
               umma_tf32_ts(tmem_d, ta_hi + ks * UMMA_K, b_lo, IDESC, 1);
               umma_tf32_ts(tmem_d, ta_hi + ks * UMMA_K, b_hi, IDESC, 1);
             }
             umma_commit(&empty_b[s]);  // both fire once the MMAs above have read their operands
-            umma_commit(&tfree[st]);
+            umma_commit(&pfree[sp]);
           }
           if (ok) umma_commit(&acc_full[buf]);
         }
@@ -551,8 +554,8 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
     for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         if ((int)(it & 1) != set) continue;
-        const int sa = it % A_SLOTS, st = it % T_SLOTS, s = it % B_SLOTS;
-        ok = mbar_wait(&tfree[st], ((it / T_SLOTS) & 1) ^ 1, 6, a.dev_status, abort_flag) &&
+        const int sa = it % A_SLOTS, sp = it % P_SLOTS, s = it % B_SLOTS;
+        ok = mbar_wait(&pfree[sp], ((it / P_SLOTS) & 1) ^ 1, 6, a.dev_status, abort_flag) &&
              mbar_wait(&full_a[sa], (it / A_SLOTS) & 1, 3, a.dev_status, abort_flag);
         if (!ok) break;
         tc_fence_after();
@@ -568,7 +571,7 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
           }
 #pragma unroll
           for (int j = 0; j < 32; ++j) lo[j] = tf32_lo(hi[j]);
-          const uint32_t ta = tmem_base + A_RING + st * 64 + ((uint32_t)(arow & ~31) << 16);
+          const uint32_t ta = tmem_base + A_RING + sp * 64 + ((uint32_t)(arow & ~31) << 16);
           tmem_st32(ta, hi);        // the tensor core truncates the fp32 words itself
           tmem_st32(ta + 32, lo);
           // Free the raw A slot only once the stores have consumed the registers the shared-memory
@@ -581,8 +584,8 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
         if (!ok) break;
         // B: lo = tf32(v - trunc(v)) into the second buffer, same (swizzled) layout; raw B is hi.
         {
-          const float4* bh = reinterpret_cast<const float4*>(smem + B_RING + s * B_SLOT);
-          float4* bl = reinterpret_cast<float4*>(smem + B_RING + s * B_SLOT + B_BYTES);
+          const float4* bh = reinterpret_cast<const float4*>(smem + B_RING + s * B_BYTES);
+          float4* bl = reinterpret_cast<float4*>(smem + LO_RING + sp * B_BYTES);
 #pragma unroll 4
           for (int i = tt; i < B_BYTES / 16; i += 128) {
             const float4 v = bh[i];
@@ -596,7 +599,7 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
         tc_fence_before();
         // make the generic-proxy writes visible to the tensor core (async proxy)
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive_warp(&ready[s]);
+        mbar_arrive_warp(&ready[sp]);
       }
     }
   } else {
