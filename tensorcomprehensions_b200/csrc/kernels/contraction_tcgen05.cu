@@ -795,12 +795,26 @@ int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max,
       out[cnt] = tcb200_tile_t{TCB200_VARIANT_TCGEN05_TS, BM, bn, BK, ts_b_slots(bn), kTsThreads, 3};
     ++cnt;
   };
-  if (p.N >= 128) push_ts(128);
-  if (p.N >= 112) push_ts(112);
+  // Preferred tile first: fewest waves of the persistent grid, weighted by the measured time of a
+  // tile of each width relative to a 128-wide one (the tensor pipe does not run a narrower MMA
+  // proportionally faster).  N = 16384 with M = 128 gives 128 tiles at BN = 128 but 147 at BN = 112,
+  // which fills 147 of the 148 SMs in the same single wave.
+  const int ts_bn[3] = {128, 112, 64};
+  const double ts_cost[3] = {1.0, 0.97, 0.65};
+  int order[3] = {0, 1, 2};
+  double cost[3];
+  for (int i = 0; i < 3; ++i) {
+    const int64_t tiles = ceil_div(p.N, ts_bn[i]) * ceil_div(p.M, BM) * p.batch;
+    cost[i] = (double)ceil_div(tiles, kNumSMs) * ts_cost[i];
+  }
+  for (int i = 0; i < 3; ++i)
+    for (int j = i + 1; j < 3; ++j)
+      if (cost[order[j]] < cost[order[i]]) { const int t = order[i]; order[i] = order[j]; order[j] = t; }
+  for (int i = 0; i < 3; ++i)
+    if (p.N >= ts_bn[order[i]]) push_ts(ts_bn[order[i]]);
   const int bns[] = {128, 256, 64};
   for (int bn : bns)
     if (p.N >= bn) push(bn, 3);
-  if (p.N >= 64 && p.N < 128) push_ts(64);
   *n = cnt;
   return TCB200_OK;
 }
