@@ -387,9 +387,12 @@ __host__ __device__ constexpr int ts_smem_bytes(int bn) {
 // pipe holds at most one or two MMAs in its queue, so a single issuer that waits once per k-block
 // leaves the pipe idle a quarter of the time (1030 cycles per 12 MMAs of 128x128x8 instead of 768).
 // Two issuers in different warps that alternate k-blocks hide each other's waits (769 cycles per
-// 12 MMAs in the same microbenchmark).  Their MMAs reach the pipe in no fixed order, so every MMA
-// accumulates (none overwrites) and the drain warps zero an accumulator after reading it; the order
-// of the fp32 additions inside the tensor core can therefore differ between two runs.
+// 12 MMAs in the same microbenchmark).  Their MMAs reach the pipe in no fixed order, so each issuer
+// owns one TMEM accumulator: the additions inside an accumulator keep their order and the result is
+// the same bits on every run.  An accumulator is drained into fp32 registers every kChunkKB of its
+// issuer's k-blocks (the tensor core's own fp32 accumulation truncates); the second issuer's chunk
+// boundaries are shifted by half a chunk so that while one issuer waits for its drain the other
+// keeps the tensor pipe busy.
 constexpr int kTsThreads = 608;
 
 template <int BN>
@@ -405,8 +408,7 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
   constexpr uint32_t ACC_STRIDE = 128;     // TMEM columns between the two accumulators
   static_assert(BN <= 128 && BN % 16 == 0, "two accumulators and the A ring share 512 TMEM columns");
   constexpr uint32_t IDESC = make_idesc(BN);
-  constexpr int MMA_WARPS = 2;
-  constexpr int SPLIT_WARP0 = 1 + MMA_WARPS;
+  constexpr int SPLIT_WARP0 = 3;  // after the TMA warp and the two MMA issuer warps
   constexpr int SPLIT_WARPS = 8;
   constexpr int DRAIN_WARP0 = SPLIT_WARP0 + SPLIT_WARPS;  // 8 warps from here cover every TMEM lane quarter twice
   constexpr int FIRST = ((BN / 2 + 15) / 16) * 16;         // columns of the first drain warp of a quarter
@@ -431,8 +433,6 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (a.K + BK - 1) / BK;
-  const int chunk_kb = kChunkKB;
-  const int num_chunks = (num_kb + chunk_kb - 1) / chunk_kb;
   const int tiles_n = (a.N + BN - 1) / BN, tiles_m = (a.M + BM - 1) / BM;
   const int64_t num_tiles = (int64_t)tiles_n * tiles_m * a.batch;
 
@@ -448,7 +448,7 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
       mbar_init(&empty_b[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&acc_full[b], MMA_WARPS);
+      mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 256);
     }
     *abort_flag = 0;
@@ -460,20 +460,19 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const bool second_half = warp >= DRAIN_WARP0 + 4;  // drain warps: which column range of the quarter
-  float zeros[16];
-#pragma unroll
-  for (int j = 0; j < 16; ++j) zeros[j] = 0.f;
-  if (warp >= DRAIN_WARP0) {
-    // both accumulators start at zero
-    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    for (int buf = 0; buf < 2; ++buf)
-      for (int c = second_half ? FIRST : 0; c < (second_half ? BN : FIRST); c += 16)
-        tmem_st16(tmem_base + buf * ACC_STRIDE + lane_base + c, zeros);
-    tmem_wait_st();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
+
+  // Issuer i takes the k-blocks whose running number (counted over all tiles of this CTA) has
+  // parity i.  Within a tile that starts at running number it0 these are kb = first + 2j,
+  // j = 0 .. count-1; own k-block j closes a chunk when (j + 1 + skew) % kChunkKB == 0 (skew 0 for
+  // issuer 0, kChunkKB / 2 for issuer 1) or when it is the issuer's last k-block of the tile.
+  auto own_first = [](uint32_t it0, int i) { return (int)((it0 ^ (uint32_t)i) & 1u); };
+  auto own_count = [&](uint32_t it0, int i) {
+    const int f = own_first(it0, i);
+    return num_kb > f ? (num_kb - f + 1) / 2 : 0;
+  };
+  auto closes_chunk = [](int j, int count, int i) {
+    return j == count - 1 || (j + 1 + (i ? kChunkKB / 2 : 0)) % kChunkKB == 0;
+  };
 
   // Static persistent schedule: tile t -> (batch, m-tile, n-tile) with n fastest, so the CTAs that
   // run at the same time share rows of A (L2 hits) while B tiles differ.
@@ -507,40 +506,47 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
       }
     }
   } else if (warp < SPLIT_WARP0) {
-    // ------------------------------------------------ MMA issuers (k-block it belongs to issuer it & 1)
+    // ------------------------------------------------ MMA issuers
     const int issuer = warp - 1;
     if (lane == 0) {
-      uint32_t it = 0, cc = 0;
+      uint32_t it0 = 0, cc = 0;  // running k-block number at the start of the tile; chunks of this issuer
       bool ok = true;
-      for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        for (int c = 0; c < num_chunks && ok; ++c, ++cc) {
-          const uint32_t buf = cc & 1;
-          ok = mbar_wait(&acc_empty[buf], ((cc >> 1) & 1) ^ 1, 5, a.dev_status, abort_flag);
+      const uint32_t tmem_d = tmem_base + issuer * ACC_STRIDE;
+      for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, it0 += (uint32_t)num_kb) {
+        const int first = own_first(it0, issuer), count = own_count(it0, issuer);
+        bool opens = true;
+        for (int j = 0; j < count; ++j) {
+          const uint32_t it = it0 + (uint32_t)(first + 2 * j);
+          uint32_t accumulate = 1;
+          if (opens) {  // the drain warps have read the previous chunk out of this accumulator
+            ok = mbar_wait(&acc_empty[issuer], (cc & 1) ^ 1, 5, a.dev_status, abort_flag);
+            if (!ok) break;
+            accumulate = 0;
+            opens = false;
+          }
+          const int s = it % B_SLOTS, sp = it % P_SLOTS;
+          ok = mbar_wait(&ready[sp], (it / P_SLOTS) & 1, 2, a.dev_status, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t tmem_d = tmem_base + buf * ACC_STRIDE;
-          const int kb_end = min(num_kb, (c + 1) * chunk_kb);
-          for (int kb = c * chunk_kb; kb < kb_end; ++kb, ++it) {
-            if ((int)(it & 1) != issuer) continue;
-            const int s = it % B_SLOTS, sp = it % P_SLOTS;
-            ok = mbar_wait(&ready[sp], (it / P_SLOTS) & 1, 2, a.dev_status, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t sb = smem_u32(smem + B_RING + s * B_BYTES);
-            const uint32_t sl = smem_u32(smem + LO_RING + sp * B_BYTES);
-            const uint32_t ta_hi = tmem_base + A_RING + sp * 64, ta_lo = ta_hi + 32;
+          const uint32_t sb = smem_u32(smem + B_RING + s * B_BYTES);
+          const uint32_t sl = smem_u32(smem + LO_RING + sp * B_BYTES);
+          const uint32_t ta_hi = tmem_base + A_RING + sp * 64, ta_lo = ta_hi + 32;
 #pragma unroll
-            for (int ks = 0; ks < BK / UMMA_K; ++ks) {
-              const uint32_t koff = ks * UMMA_K * 4;
-              const uint64_t b_hi = make_desc(sb + koff), b_lo = make_desc(sl + koff);
-              umma_tf32_ts(tmem_d, ta_lo + ks * UMMA_K, b_hi, IDESC, 1);
-              umma_tf32_ts(tmem_d, ta_hi + ks * UMMA_K, b_lo, IDESC, 1);
-              umma_tf32_ts(tmem_d, ta_hi + ks * UMMA_K, b_hi, IDESC, 1);
-            }
-            umma_commit(&empty_b[s]);  // both fire once the MMAs above have read their operands
-            umma_commit(&pfree[sp]);
+          for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+            const uint32_t koff = ks * UMMA_K * 4;
+            const uint64_t b_hi = make_desc(sb + koff), b_lo = make_desc(sl + koff);
+            umma_tf32_ts(tmem_d, ta_lo + ks * UMMA_K, b_hi, IDESC, accumulate);
+            umma_tf32_ts(tmem_d, ta_hi + ks * UMMA_K, b_lo, IDESC, 1);
+            umma_tf32_ts(tmem_d, ta_hi + ks * UMMA_K, b_hi, IDESC, 1);
+            accumulate = 1;
           }
-          if (ok) umma_commit(&acc_full[buf]);
+          umma_commit(&empty_b[s]);  // both fire once the MMAs above have read their operands
+          umma_commit(&pfree[sp]);
+          if (closes_chunk(j, count, issuer)) {
+            umma_commit(&acc_full[issuer]);
+            ++cc;
+            opens = true;
+          }
         }
       }
     }
@@ -606,15 +612,14 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
     // ------------------------------------------------ drain + epilogue
     // Two warps per TMEM lane quarter: the first takes columns [0, FIRST), the second [FIRST, BN),
     // both in pieces of 16 columns (FIRST is a multiple of 16, so BN = 112 splits into 64 + 48).
-    // A piece is zeroed right after it has been read: both MMA issuers always accumulate.
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     const uint32_t lane_base = (uint32_t)(q * 32) << 16;
     const int col0 = second_half ? FIRST : 0;
     const int mycols = second_half ? BN - FIRST : FIRST;
     const bool has_bias = a.epi == TCB200_EPI_BIAS || a.epi == TCB200_EPI_BIAS_RELU;
-    uint32_t cc = 0;
+    uint32_t it0 = 0, dc[2] = {0, 0};  // running k-block number of the tile; chunks drained per issuer
     bool ok = true;
-    for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+    for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, it0 += (uint32_t)num_kb) {
       int m0, n0, bz;
       tile_coords(t, &m0, &n0, &bz);
       const int row = m0 + q * 32 + lane;
@@ -660,25 +665,33 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
       for (int g = 0; g < PIECES; ++g)
 #pragma unroll
         for (int j = 0; j < 16; ++j) acc[g][j] = 0.f;
-      for (int c = 0; c < num_chunks; ++c, ++cc) {
-        const uint32_t buf = cc & 1;
-        ok = mbar_wait(&acc_full[buf], (cc >> 1) & 1, 4, a.dev_status, abort_flag);
+      // Chunks of both issuers in the order of the k-block that closes them (the same order on
+      // every run; the two can never tie because their k-blocks differ in parity).
+      const int first0 = own_first(it0, 0), first1 = own_first(it0, 1);
+      const int count0 = own_count(it0, 0), count1 = own_count(it0, 1);
+      int j0 = 0, j1 = 0;  // own k-block index from which the next chunk of each issuer is searched
+      while (j0 < count0 || j1 < count1) {
+        int e0 = j0, e1 = j1;  // own index that closes the next chunk
+        while (e0 < count0 && !closes_chunk(e0, count0, 0)) ++e0;
+        while (e1 < count1 && !closes_chunk(e1, count1, 1)) ++e1;
+        const bool take1 = j0 >= count0 || (j1 < count1 && first1 + 2 * e1 < first0 + 2 * e0);
+        const int i = take1 ? 1 : 0;
+        if (take1) j1 = e1 + 1; else j0 = e0 + 1;
+        ok = mbar_wait(&acc_full[i], dc[i] & 1, 4, a.dev_status, abort_flag);
         if (!ok) break;
+        ++dc[i];
         tc_fence_after();
 #pragma unroll
         for (int g = 0; g < PIECES; ++g) {
           if (g * 16 < mycols) {  // the same for the whole warp
-            const uint32_t taddr = tmem_base + buf * ACC_STRIDE + lane_base + col0 + g * 16;
             float v[16];
-            tmem_ld16(taddr, v);
-            tmem_st16(taddr, zeros);
+            tmem_ld16(tmem_base + i * ACC_STRIDE + lane_base + col0 + g * 16, v);
 #pragma unroll
             for (int j = 0; j < 16; ++j) acc[g][j] += v[j];
           }
         }
-        tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(&acc_empty[buf]);  // zeroed: the MMA warps may accumulate into it again
+        mbar_arrive(&acc_empty[i]);  // issuer i may overwrite its accumulator
       }
       if (!ok) break;
 #pragma unroll
