@@ -209,6 +209,148 @@ __global__ void __launch_bounds__(256) group_conv_rows_kernel(ConvArgs a, int n_
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// item kernel: one CTA of 64 threads per (n, g), W = 16 in registers, OW <= 14, KW <= 3
+// ------------------------------------------------------------------------------------------------
+// Same thread tile as the rows kernel (one output row x four output channels) with three changes
+// that the rows kernel's profile asked for (FMA pipe 44 % busy, a third of the warp time waiting
+// for the staging copies, SMs idle 18 % of the kernel because 512 CTAs do not divide over 148 SMs):
+//  * one item per CTA: 1024 CTAs of 30 KB, seven resident per SM, all in one balanced wave;
+//  * the input planes arrive in four cp.async groups of C/4 channels and the loop over channels
+//    starts as soon as the first group (and the filters) has landed;
+//  * exactly OW accumulators per channel (no padded columns, no zero fill of the row registers)
+//    and the output tile goes through shared memory so that it leaves in 128-bit coalesced stores.
+constexpr int kItemOW = 14;
+constexpr int kItemKW = 3;
+constexpr int kItemThreads = 64;
+
+// KHT > 0: filter height known at compile time (rows and taps fully unrolled); 0: read from the arguments.
+template <int KHT>
+__global__ void __launch_bounds__(kItemThreads) group_conv_item_kernel(ConvArgs a) {
+  extern __shared__ __align__(16) float smem[];
+  const int item = blockIdx.x;  // n * G + g
+  const int g = item % a.G;
+  const int taps = a.C * a.KH * a.KW;
+  const int F = a.F;
+  float* Ws = smem;                      // [taps][F]
+  float* Is = smem + (size_t)taps * F;   // [C][H][kRowsPitch]
+  const int tid = threadIdx.x;
+
+  // group 0: filters (global order (f, tap), scattered to [tap][f]) + first quarter of the channels
+  const float* Wg = a.W + (size_t)g * F * taps;
+  for (int f = 0; f < F; ++f)
+    for (int t = tid; t < taps; t += kItemThreads) cp_async_4(Ws + (size_t)t * F + f, Wg + (size_t)f * taps + t);
+  const float* Ig = a.I + (size_t)item * a.C * a.H * a.Wd;
+  const int rows_q = (a.C / 4) * a.H;  // rows per quarter (C % 4 == 0 checked by the plan)
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    for (int i = tid; i < rows_q * 4; i += kItemThreads) {  // four 16-byte pieces per row of 16 floats
+      const int r = q * rows_q + (i >> 2), piece = i & 3;
+      cp_async_16(Is + (size_t)r * kRowsPitch + 4 * piece, Ig + (size_t)r * 16 + 4 * piece);
+    }
+    cp_async_commit();
+  }
+
+  // Thread -> (channel quad, output row) with the rows of a quad padded to a multiple of 8 lanes: a
+  // 128-bit shared load is served a quarter-warp at a time, and eight consecutive rows (pitch 80 B)
+  // fall into distinct banks, which rows of two different quads in one quarter-warp would not.
+  const int FQ = F / 4;
+  const int hslots = (a.OH + 7) & ~7;
+  const int fq_t = tid / hslots, h_t = tid - fq_t * hslots;
+  const bool active = fq_t < FQ && h_t < a.OH;
+  const int fq = active ? fq_t : 0, h = active ? h_t : 0;
+
+  // accumulators as pairs of output channels: the packed fp32 FMA of sm_100 (two independent,
+  // individually rounded fused multiply-adds per instruction) halves the FMA instruction count
+  float2 acc[2][kItemOW];
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int w = 0; w < kItemOW; ++w) acc[j][w] = make_float2(0.f, 0.f);
+
+  const int KH = KHT > 0 ? KHT : a.KH;
+  const int KW = KHT > 0 ? kItemKW : a.KW;  // the compile-time form is the square 3x3 filter
+  const int plane_step = (a.H - KH) * kRowsPitch;  // from the last filter row of a channel to the next channel
+  auto channels = [&](int c0, int c1) {
+    // running pointers: input row (c, h + kh) and filter vector (c, kh, kw = 0, 4 * fq)
+    const float* rp = Is + (c0 * a.H + h) * kRowsPitch;
+    const float* wrow = Ws + c0 * KH * KW * F + fq * 4;
+    for (int c = c0; c < c1; ++c, rp += plane_step) {
+#pragma unroll
+      for (int kh = 0; kh < KH; ++kh, rp += kRowsPitch, wrow += KW * F) {
+        const float4* row = reinterpret_cast<const float4*>(rp);
+        float x[16];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float4 v = row[q];
+          x[4 * q] = v.x; x[4 * q + 1] = v.y; x[4 * q + 2] = v.z; x[4 * q + 3] = v.w;
+        }
+#pragma unroll
+        for (int kw = 0; kw < kItemKW; ++kw) {
+          if (kw < KW) {
+            const float4 wv = *reinterpret_cast<const float4*>(wrow + kw * F);
+            const float2 w01 = make_float2(wv.x, wv.y), w23 = make_float2(wv.z, wv.w);
+#pragma unroll
+            for (int w = 0; w < kItemOW; ++w) {
+              const float2 xx = make_float2(x[w + kw], x[w + kw]);
+              acc[0][w] = __ffma2_rn(xx, w01, acc[0][w]);
+              acc[1][w] = __ffma2_rn(xx, w23, acc[1][w]);
+            }
+          }
+        }
+      }
+    }
+  };
+  const int cq = a.C / 4;
+  cp_async_wait_group<3>(); __syncthreads(); if (active) channels(0, cq);
+  cp_async_wait_group<2>(); __syncthreads(); if (active) channels(cq, 2 * cq);
+  cp_async_wait_group<1>(); __syncthreads(); if (active) channels(2 * cq, 3 * cq);
+  cp_async_wait_group<0>(); __syncthreads(); if (active) channels(3 * cq, a.C);
+  __syncthreads();  // every thread is done with the input planes: reuse them for the output tile
+
+  // output tile of the item, dense (f, oh, ow): F * OH * OW floats (<= C * H * kRowsPitch)
+  float* Os = Is;
+  const bool has_bias = a.epi == TCB200_EPI_BIAS || a.epi == TCB200_EPI_BIAS_RELU;
+  if (active) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int f = fq * 4 + j;
+      const float bias = has_bias ? __ldg(a.bias + g * F + f) : 0.f;
+      float* o = Os + ((size_t)f * a.OH + h) * a.OW;
+#pragma unroll
+      for (int w = 0; w < kItemOW; ++w) {
+        const float v = (j & 1) ? acc[j >> 1][w].y : acc[j >> 1][w].x;
+        if (w < a.OW) o[w] = a.accumulate ? v : apply_epilogue_rt(a.epi, v, bias);
+      }
+    }
+  }
+  __syncthreads();
+  const int out_elems = F * a.OH * a.OW;
+  float* Og = a.O + (size_t)item * out_elems;
+  if (!a.accumulate && (out_elems & 3) == 0 && (((uintptr_t)a.O) & 15) == 0) {
+    for (int i = tid; i < out_elems / 4; i += kItemThreads)
+      reinterpret_cast<float4*>(Og)[i] = reinterpret_cast<const float4*>(Os)[i];
+  } else if (!a.accumulate) {
+    for (int i = tid; i < out_elems; i += kItemThreads) Og[i] = Os[i];
+  } else {
+    // O = epilogue(O + conv): the bias index needs f again
+    const int per_f = a.OH * a.OW;
+    for (int i = tid; i < out_elems; i += kItemThreads) {
+      const float bias = has_bias ? __ldg(a.bias + g * F + i / per_f) : 0.f;
+      Og[i] = apply_epilogue_rt(a.epi, Os[i] + Og[i], bias);
+    }
+  }
+}
+
+bool item_ok(const tcb200_problem_t& p) {
+  const int64_t C = p.conv[2], F = p.conv[3], H = p.conv[4], W = p.conv[5], KH = p.conv[6], KW = p.conv[7];
+  const int64_t OH = H - KH + 1, OW = W - KW + 1;
+  return W == 16 && OW <= kItemOW && KW <= kItemKW && F % 4 == 0 && C % 4 == 0 &&
+         (F / 4) * ((OH + 7) / 8 * 8) <= kItemThreads &&
+         F * OH * OW <= C * H * kRowsPitch &&
+         sizeof(float) * (size_t)(C * KH * KW * F + C * H * kRowsPitch) <= 48 * 1024;
+}
+
 bool rows_ok(const tcb200_problem_t& p) {
   const int64_t C = p.conv[2], F = p.conv[3], H = p.conv[4], W = p.conv[5], KH = p.conv[6], KW = p.conv[7];
   const int64_t OH = H - KH + 1;
@@ -259,6 +401,10 @@ int pick_band(const tcb200_problem_t& p, int ft, size_t* bytes) {
 int group_conv_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n) {
   if (!valid(p)) return TCB200_ERR_INVALID_ARGUMENT;
   int cnt = 0;
+  if (item_ok(p)) {  // stages = 4: one item per CTA, input staged in four cp.async groups
+    if (cnt < max && out) out[cnt] = tcb200_tile_t{TCB200_VARIANT_SIMT, 0, 4, 1, 4, kItemThreads, 0};
+    ++cnt;
+  }
   if (rows_ok(p)) {
     // bk = n per CTA of the rows kernel
     const int ns[] = {2, 1, 4};
@@ -295,8 +441,22 @@ int group_conv_plan(Plan& plan) {
     t.variant = TCB200_VARIANT_SIMT;
     t.threads = 256;
     t.bk = rows_ok(p) ? 2 : 0;
+    if (item_ok(p)) { t.bk = 1; t.stages = 4; }
   }
   if (t.variant != TCB200_VARIANT_SIMT) return TCB200_ERR_UNSUPPORTED;
+  if (t.bk == 1 && t.stages == 4) {  // item kernel
+    if (!item_ok(p)) return TCB200_ERR_UNSUPPORTED;
+    if (p.conv[0] * p.conv[1] > 0x7fffffffll) return TCB200_ERR_TOO_LARGE;
+    t.bm = 0; t.bn = 4;
+    t.threads = kItemThreads;
+    plan.launch.grid = dim3((unsigned)(p.conv[0] * p.conv[1]), 1, 1);
+    plan.launch.block = dim3(kItemThreads, 1, 1);
+    plan.launch.smem = sizeof(float) * (size_t)(p.conv[2] * p.conv[6] * p.conv[7] * p.conv[3] +
+                                                 p.conv[2] * p.conv[4] * kRowsPitch);
+    plan.kernel_id = 101;
+    return TCB200_OK;
+  }
+  t.stages = 0;
   if (t.bk > 0) {  // rows kernel
     if (!rows_ok(p)) return TCB200_ERR_UNSUPPORTED;
     size_t bytes = 0;
@@ -340,6 +500,14 @@ int group_conv_launch(const Plan& plan, const float* I, const float* W, const fl
   a.OH = a.H - a.KH + 1; a.OW = a.Wd - a.KW + 1;
   a.band = plan.tile.bm;
   a.epi = p.epilogue; a.accumulate = p.accumulate;
+  if (plan.kernel_id == 101) {
+    if (a.KH == 3 && a.KW == 3)
+      group_conv_item_kernel<3><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(a);
+    else
+      group_conv_item_kernel<0><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(a);
+    TCB200_CUDA_TRY(cudaGetLastError());
+    return TCB200_OK;
+  }
   if (plan.kernel_id == 100) {
     static std::atomic<uint64_t> rows_configured{0};
     TCB200_CUDA_TRY(ensure_dynamic_smem(group_conv_rows_kernel, (int)kSmemBudget, plan.device, rows_configured));

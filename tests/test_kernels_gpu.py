@@ -149,6 +149,9 @@ def test_contraction_shared_operand_and_padded_ld(cuda):
 
 @pytest.mark.parametrize("dims", [
     (2, 3, 16, 16, 16, 16, 3, 3),
+    (3, 2, 8, 12, 16, 16, 3, 3),    # item kernel: C=8, F=12
+    (2, 2, 4, 4, 16, 16, 1, 3),     # item kernel: one filter row, 16 output rows
+    (1, 2, 4, 16, 16, 16, 5, 2),    # item kernel: 12 output rows, 15 output columns -> not eligible (rows kernel)
     (1, 2, 4, 4, 56, 56, 3, 3),     # reference benchmark shape family, large image -> row bands
     (2, 2, 3, 5, 9, 7, 3, 3),       # F not a multiple of 4, odd sizes
     (1, 1, 1, 1, 3, 3, 3, 3),       # single output pixel
@@ -169,6 +172,21 @@ def test_group_conv_small(cuda, dims, bias):
     for tile in [None] + cabi.query(p):
         out, plan = run_plan(p, ins, ref.shape, tile)
         assert_close(out, ref, C * KH * KW, [I, W1], STRICT["group_conv"], plan.describe())
+
+
+@pytest.mark.parametrize("bias", [True, False])
+def test_group_conv_accumulate(cuda, bias):
+    """`+=` without `!`: O = epilogue(O_in + conv) for every tile the family lists."""
+    dims = (2, 3, 16, 16, 16, 16, 3, 3)
+    N, G, C, F, H, W, KH, KW = dims
+    I, W1, B = _rand((N, G, C, H, W), 25, "uniform"), _rand((G, F, C, KH, KW), 26, "uniform"), _rand((G, F), 27)
+    init = _rand((N, G, F, H - KH + 1, W - KW + 1), 28)
+    ref = orc.loop_group_conv(I, W1, None) + init.numpy() + (B.numpy()[None, :, :, None, None] if bias else 0)
+    p = cabi.group_conv_problem(*dims, epilogue=cabi.EPI_BIAS if bias else cabi.EPI_NONE, accumulate=True)
+    ins = [I.to(cuda), W1.to(cuda)] + ([B.to(cuda)] if bias else [])
+    for tile in [None] + cabi.query(p):
+        out, plan = run_plan(p, ins, ref.shape, tile, out_init=init.to(cuda))
+        assert_close(out, ref, C * KH * KW, what=plan.describe())
 
 
 def test_group_conv_full_size(cuda):
