@@ -12,6 +12,7 @@
 //     unaligned outputs) and one point of the tile sweep.
 // Both follow the loop nest's semantics (test/test_core.cc:93-127): zero-initialised
 // accumulator, reduction in increasing k.
+#include "async.cuh"
 #include "common.cuh"
 
 namespace tcb200 {
@@ -137,6 +138,9 @@ __global__ void __launch_bounds__(256) simt_tiled_kernel(GemmArgs g, int a_vec, 
 // 16-byte / 8-byte chunk), stages with asynchronous copies, and consumes four k per step with
 // 128-bit loads of A and 64-bit loads of B: 6 shared loads per 16 FMAs.
 //   FAST needs: K % 4 == 0, lda % 4 == 0, 16-byte aligned A slabs; ldb % 2 == 0, 8-byte aligned B slabs.
+//   BULK (MODE 2) is FAST for dense operands (lda == K, ldb == N, even N, slabs that are multiples of
+//   16 bytes): one thread brings each slab in with a single 1-D bulk copy (cp.async.bulk + mbarrier)
+//   instead of ~1400 small asynchronous copies with their index arithmetic per CTA.
 // smem: As[M][lda_s], Bs[K][ldb_s];  FAST: lda_s = K + 4, ldb_s = even(N) + 2;  else K + 1, N | 1.
 // ------------------------------------------------------------------------------------
 __device__ __forceinline__ void cp_async_8(void* smem_dst, const void* gmem_src) {
@@ -146,8 +150,9 @@ __device__ __forceinline__ void cp_async_8(void* smem_dst, const void* gmem_src)
                : "memory");
 }
 
-template <bool FAST>
+template <int MODE>  // 0: any layout, 1: FAST, 2: BULK
 __global__ void __launch_bounds__(256) simt_small_kernel(GemmArgs g, int ldas, int ldbs) {
+  constexpr bool FAST = MODE >= 1;
   extern __shared__ __align__(16) float smem[];
   const int M = g.M, N = g.N, K = g.K;
   float* As = smem;
@@ -159,7 +164,22 @@ __global__ void __launch_bounds__(256) simt_small_kernel(GemmArgs g, int ldas, i
   const int tid = threadIdx.x, nt = blockDim.x;
 
   // Only the A(m,k) / B(k,n) row-major form reaches this kernel (checked by the plan).
-  if (FAST) {
+  if (MODE == 2) {
+    // the barrier sits behind both slabs (their sizes are multiples of 16 bytes)
+    uint64_t* bar = reinterpret_cast<uint64_t*>(Bs + (size_t)K * ldbs);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar + 1);
+    if (tid == 0) {
+      mbar_init(bar, 1);
+      *abort_flag = 0;
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      const uint32_t bytes_a = (uint32_t)M * K * 4, bytes_b = (uint32_t)K * N * 4;
+      mbar_expect_tx(bar, bytes_a + bytes_b);
+      bulk_load(As, A, bytes_a, bar);
+      bulk_load(Bs, B, bytes_b, bar);
+    }
+    __syncthreads();  // the barrier is initialised before anyone polls it
+    if (!mbar_wait(bar, 0, 9, nullptr, abort_flag)) return;
+  } else if (FAST) {
     const int warp = tid >> 5, lane = tid & 31, nw = nt >> 5;
     const int ka = K >> 2, nb = (N + 1) >> 1;
     for (int m = warp; m < M; m += nw)
@@ -180,8 +200,10 @@ __global__ void __launch_bounds__(256) simt_small_kernel(GemmArgs g, int ldas, i
       cp_async_4(Bs + k * ldbs + n, B + (int64_t)k * g.ldb + n);
     }
   }
-  cp_async_wait_all();
-  __syncthreads();
+  if (MODE != 2) {
+    cp_async_wait_all();
+    __syncthreads();
+  }
 
   const int tm = (M + 1) >> 1, tn = (N + 1) >> 1;
   for (int t = tid; t < tm * tn; t += nt) {
@@ -246,7 +268,7 @@ void small_pitches(const tcb200_problem_t& p, bool fast, int* ldas, int* ldbs) {
   *ldbs = fast ? (int)((p.N + 1) / 2 * 2 + 2) : ((int)p.N | 1);  // odd pitch keeps k-strided reads off one bank
 }
 size_t small_smem_bytes(const tcb200_problem_t& p) {
-  return sizeof(float) * ((size_t)p.M * (p.K + 4) + (size_t)p.K * ((p.N + 1) / 2 * 2 + 2));
+  return sizeof(float) * ((size_t)p.M * (p.K + 4) + (size_t)p.K * ((p.N + 1) / 2 * 2 + 2)) + 16;
 }
 
 // simt_small reads A as (m,k) row-major and B as (k,n) row-major: the batchmatmul form.
@@ -309,10 +331,15 @@ int contraction_simt_launch(const Plan& plan, const float* A, const float* B, co
     const bool fast = small_fast_shape(p) && ((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 8 == 0);
     int ldas = 0, ldbs = 0;
     small_pitches(p, fast, &ldas, &ldbs);
-    if (fast)
-      simt_small_kernel<true><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(g, ldas, ldbs);
+    const bool bulk = fast && p.lda == p.K && p.ldb == p.N && p.N % 2 == 0 && (p.M * p.K) % 4 == 0 &&
+                      (p.K * p.N) % 4 == 0 && p.stride_b % 4 == 0 && ((uintptr_t)B % 16 == 0) &&
+                      p.M * p.K * 4 < (1 << 20) && p.K * p.N * 4 < (1 << 20);
+    if (bulk)
+      simt_small_kernel<2><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(g, (int)p.K, (int)p.N);
+    else if (fast)
+      simt_small_kernel<1><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(g, ldas, ldbs);
     else
-      simt_small_kernel<false><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(g, ldas, ldbs);
+      simt_small_kernel<0><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(g, ldas, ldbs);
   } else {
     // 128-bit loads need a 16-byte aligned base, leading dimension and batch stride.
     const int a_vec = ((uintptr_t)A % 16 == 0) && p.lda % 4 == 0 && p.stride_a % 4 == 0;
