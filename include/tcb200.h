@@ -51,7 +51,8 @@ enum {
   TCB200_VARIANT_SIMT = 1,       /* fp32 FMA, shared-memory tiled                                */
   TCB200_VARIANT_SIMT_SMALL = 2, /* fp32 FMA, one whole small matrix pair per CTA (batched)      */
   TCB200_VARIANT_TCGEN05 = 3,    /* tcgen05/TMEM tiles fed by TMA, TF32 with optional 3x split   */
-  TCB200_VARIANT_TCGEN05_TS = 4  /* same, 3xTF32 with the A operand staged in tensor memory     */
+  TCB200_VARIANT_TCGEN05_TS = 4, /* same, 3xTF32 with the A operand staged in tensor memory     */
+  TCB200_VARIANT_TCGEN05_PAIR = 5 /* same on CTA pairs (cta_group::2): 256-row tiles, B split over the pair */
 };
 
 /* Status codes (0 = success, negative = error). */

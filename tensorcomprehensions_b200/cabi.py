@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_PKG, "libtcb200.so")
 
 FAMILY_CONTRACTION, FAMILY_TENSORDOT, FAMILY_GROUP_CONV = 1, 2, 3
 EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_RELU = 0, 1, 2, 3
-VARIANT_AUTO, VARIANT_SIMT, VARIANT_SIMT_SMALL, VARIANT_TCGEN05, VARIANT_TCGEN05_TS = 0, 1, 2, 3, 4
+VARIANT_AUTO, VARIANT_SIMT, VARIANT_SIMT_SMALL, VARIANT_TCGEN05, VARIANT_TCGEN05_TS, VARIANT_TCGEN05_PAIR = 0, 1, 2, 3, 4, 5
 OK = 0
 
 # every symbol include/tcb200.h declares

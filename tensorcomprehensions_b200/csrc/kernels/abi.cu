@@ -32,6 +32,7 @@ const char* variant_name(int v) {
     case TCB200_VARIANT_SIMT_SMALL: return "simt_small";
     case TCB200_VARIANT_TCGEN05: return "tcgen05";
     case TCB200_VARIANT_TCGEN05_TS: return "tcgen05_ts";
+    case TCB200_VARIANT_TCGEN05_PAIR: return "tcgen05_pair";
     default: return "auto";
   }
 }
@@ -145,7 +146,8 @@ int tcb200_plan_create(const tcb200_problem_t* problem, const tcb200_tile_t* til
         if (n == 0) { st = TCB200_ERR_UNSUPPORTED; break; }
         P.tile = first;
       }
-      if (P.tile.variant == TCB200_VARIANT_TCGEN05 || P.tile.variant == TCB200_VARIANT_TCGEN05_TS)
+      if (P.tile.variant == TCB200_VARIANT_TCGEN05 || P.tile.variant == TCB200_VARIANT_TCGEN05_TS ||
+          P.tile.variant == TCB200_VARIANT_TCGEN05_PAIR)
         st = contraction_tc_plan(P);
       else st = contraction_simt_plan(P);
       break;
@@ -237,7 +239,8 @@ int tcb200_launch(const tcb200_plan_t* plan, const void* const* inputs, int n_in
     case TCB200_FAMILY_GROUP_CONV:
       return group_conv_launch(P, in0, in1, bias, out, s, dev_status);
     case TCB200_FAMILY_CONTRACTION:
-      if (P.tile.variant == TCB200_VARIANT_TCGEN05 || P.tile.variant == TCB200_VARIANT_TCGEN05_TS)
+      if (P.tile.variant == TCB200_VARIANT_TCGEN05 || P.tile.variant == TCB200_VARIANT_TCGEN05_TS ||
+          P.tile.variant == TCB200_VARIANT_TCGEN05_PAIR)
         return contraction_tc_launch(P, in0, in1, bias, out, s, dev_status);
       return contraction_simt_launch(P, in0, in1, bias, out, s);
     default:

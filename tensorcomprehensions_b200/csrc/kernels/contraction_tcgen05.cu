@@ -708,6 +708,337 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
   }
 }
 
+// ---------------------------------------------------------------------------------- kernel (TS, CTA pair)
+// The same kernel on a CTA PAIR (cluster of two, tcgen05 cta_group::2): one 256 x 128 output tile per
+// pair.  Each CTA loads and splits its own 128 rows of A into its own tensor memory and HALF of the B
+// tile (64 rows) into its own shared memory; the leader's MMAs (M = 256) read both halves, so per
+// k-block a CTA moves 80 KB through shared memory instead of 128 KB (TMA 16 + 8 in, split 24 out +
+// 8 in, MMA operand reads 24), which is what bounds the single-CTA kernel.  Barriers: everything a CTA's
+// own warps produce and consume stays local; the peer's split and drain warps arrive on the LEADER's
+// `ready` / `acc_empty`, and the leader's commits arrive on `empty_b`, `pfree`, `acc_full` in both CTAs.
+constexpr int kPairBN = 128;
+constexpr int kPairBSlots = 8;
+__host__ __device__ constexpr int ts_pair_smem_bytes() {
+  return kTsASlots * BM * BK * 4 + (kPairBSlots + kTsPSlots) * (kPairBN / 2) * BK * 4 + kTsBarrierBytes + 1024;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTsThreads, 1)
+contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
+                           const __grid_constant__ CUtensorMap tmB, TcArgs a) {
+  constexpr int BN = kPairBN;
+  constexpr int A_SLOTS = kTsASlots, P_SLOTS = kTsPSlots, B_SLOTS = kPairBSlots;
+  constexpr int A_BYTES = BM * BK * 4;
+  constexpr int B_BYTES = (BN / 2) * BK * 4;  // this CTA's half of the B tile
+  constexpr int B_RING = A_SLOTS * A_BYTES;          // byte offset of the raw B ring
+  constexpr int LO_RING = B_RING + B_SLOTS * B_BYTES;  // byte offset of the B lo ring
+  constexpr uint32_t A_RING = 256;         // first TMEM column of the A ring
+  constexpr uint32_t ACC_STRIDE = 128;     // TMEM columns between the two accumulators
+  static_assert(BN <= 128 && BN % 16 == 0, "two accumulators and the A ring share 512 TMEM columns");
+  constexpr uint32_t IDESC = make_idesc_tf32(2 * BM, BN);  // M = 256 over the pair
+  constexpr int SPLIT_WARP0 = 3;  // after the TMA warp and the two MMA issuer warps
+  constexpr int SPLIT_WARPS = 8;
+  constexpr int DRAIN_WARP0 = SPLIT_WARP0 + SPLIT_WARPS;  // 8 warps from here cover every TMEM lane quarter twice
+  constexpr int FIRST = ((BN / 2 + 15) / 16) * 16;         // columns of the first drain warp of a quarter
+  constexpr int PIECES = FIRST / 16;
+  constexpr uint32_t TMEM_COLS = 512;
+  static_assert(B_SLOTS >= 2 && B_SLOTS <= 8 && A_SLOTS <= 4 && P_SLOTS == 4, "barrier arrays / TMEM ring sizes");
+  static_assert(A_SLOTS % 2 == 0 && B_SLOTS % 2 == 0 && P_SLOTS % 2 == 0, "a slot must stay with one set");
+  static_assert(B_BYTES % 1024 == 0, "128-byte swizzle atoms must stay 1024-byte aligned");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_a = reinterpret_cast<uint64_t*>(smem + LO_RING + P_SLOTS * B_BYTES);  // [4]
+  uint64_t* empty_a = full_a + 4;        // [4] raw A slot read by the split warps
+  uint64_t* pfree = empty_a + 4;         // [4] processed slot (A hi/lo, B lo) read by its MMAs
+  uint64_t* ready = pfree + 4;           // [4] processed slot filled
+  uint64_t* full_b = ready + 4;          // [8]
+  uint64_t* empty_b = full_b + 8;        // [8] raw B slot read by its MMAs
+  uint64_t* acc_full = empty_b + 8;      // [2]
+  uint64_t* acc_empty = acc_full + 2;    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0: leader (issues the MMAs), 1: peer
+  const int64_t pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int num_kb = (a.K + BK - 1) / BK;
+  const int tiles_n = (a.N + BN - 1) / BN, tiles_m = (a.M + 2 * BM - 1) / (2 * BM);
+  const int64_t num_tiles = (int64_t)tiles_n * tiles_m * a.batch;  // tiles of 256 x BN, one per pair
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 4; ++s) {
+      mbar_init(&full_a[s], 1);
+      mbar_init(&empty_a[s], 4);  // one elected arrival per warp of the split set
+      mbar_init(&pfree[s], 1);
+      mbar_init(&ready[s], 8);    // used in the leader only: four split warps of each CTA
+    }
+    for (int s = 0; s < 8; ++s) {
+      mbar_init(&full_b[s], 1);
+      mbar_init(&empty_b[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 16);  // used in the leader only: eight drain warps of each CTA
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc_pair(tmem_slot, TMEM_COLS);  // collective over the pair
+  tc_fence_before();
+  cluster_sync_all();  // both CTAs' barriers exist before anything arrives on them from the other CTA
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const bool second_half = warp >= DRAIN_WARP0 + 4;  // drain warps: which column range of the quarter
+
+  // Issuer i takes the k-blocks whose running number (counted over all tiles of this CTA) has
+  // parity i.  Within a tile that starts at running number it0 these are kb = first + 2j,
+  // j = 0 .. count-1; own k-block j closes a chunk when (j + 1 + skew) % kChunkKB == 0 (skew 0 for
+  // issuer 0, kChunkKB / 2 for issuer 1) or when it is the issuer's last k-block of the tile.
+  auto own_first = [](uint32_t it0, int i) { return (int)((it0 ^ (uint32_t)i) & 1u); };
+  auto own_count = [&](uint32_t it0, int i) {
+    const int f = own_first(it0, i);
+    return num_kb > f ? (num_kb - f + 1) / 2 : 0;
+  };
+  auto closes_chunk = [](int j, int count, int i) {
+    return j == count - 1 || (j + 1 + (i ? kChunkKB / 2 : 0)) % kChunkKB == 0;
+  };
+
+  // Static persistent schedule: tile t -> (batch, m-tile, n-tile) with n fastest, so the CTAs that
+  // run at the same time share rows of A (L2 hits) while B tiles differ.
+  auto tile_coords = [&](int64_t t, int* m0, int* n0, int* bz) {
+    *n0 = (int)(t % tiles_n) * BN;
+    *m0 = (int)((t / tiles_n) % tiles_m) * (2 * BM) + (int)rank * BM;  // this CTA's 128 rows
+    *bz = (int)(t / ((int64_t)tiles_n * tiles_m));
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int64_t t = pair; t < num_tiles; t += num_pairs) {
+        int m0, n0, bz;
+        tile_coords(t, &m0, &n0, &bz);
+        const int za = a.a_batched ? bz : 0, zb = a.b_batched ? bz : 0;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int sa = it % A_SLOTS, sb = it % B_SLOTS;
+          ok = mbar_wait(&empty_a[sa], ((it / A_SLOTS) & 1) ^ 1, 1, a.dev_status, abort_flag);
+          if (!ok) break;
+          mbar_expect_tx(&full_a[sa], A_BYTES);
+          tma_load_3d(smem + sa * A_BYTES, &tmA, kb * BK, m0, za, &full_a[sa]);
+          ok = mbar_wait(&empty_b[sb], ((it / B_SLOTS) & 1) ^ 1, 1, a.dev_status, abort_flag);
+          if (!ok) break;
+          mbar_expect_tx(&full_b[sb], B_BYTES);
+          tma_load_3d(smem + B_RING + sb * B_BYTES, &tmB, kb * BK, n0 + (int)rank * (BN / 2), zb, &full_b[sb]);
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp < SPLIT_WARP0) {
+    // ------------------------------------------------ MMA issuers
+    const int issuer = warp - 1;
+    if (lane == 0 && rank == 0) {  // the leader's two issuers drive both CTAs' tensor cores
+      uint32_t it0 = 0, cc = 0;  // running k-block number at the start of the tile; chunks of this issuer
+      bool ok = true;
+      const uint32_t tmem_d = tmem_base + issuer * ACC_STRIDE;
+      for (int64_t t = pair; t < num_tiles && ok; t += num_pairs, it0 += (uint32_t)num_kb) {
+        const int first = own_first(it0, issuer), count = own_count(it0, issuer);
+        bool opens = true;
+        for (int j = 0; j < count; ++j) {
+          const uint32_t it = it0 + (uint32_t)(first + 2 * j);
+          uint32_t accumulate = 1;
+          if (opens) {  // the drain warps have read the previous chunk out of this accumulator
+            ok = mbar_wait_cluster(&acc_empty[issuer], (cc & 1) ^ 1, 5, a.dev_status, abort_flag);
+            if (!ok) break;
+            accumulate = 0;
+            opens = false;
+          }
+          const int s = it % B_SLOTS, sp = it % P_SLOTS;
+          ok = mbar_wait_cluster(&ready[sp], (it / P_SLOTS) & 1, 2, a.dev_status, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sb = smem_u32(smem + B_RING + s * B_BYTES);
+          const uint32_t sl = smem_u32(smem + LO_RING + sp * B_BYTES);
+          const uint32_t ta_hi = tmem_base + A_RING + sp * 64, ta_lo = ta_hi + 32;
+#pragma unroll
+          for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+            const uint32_t koff = ks * UMMA_K * 4;
+            const uint64_t b_hi = make_desc(sb + koff), b_lo = make_desc(sl + koff);
+            umma_tf32_ts_pair(tmem_d, ta_lo + ks * UMMA_K, b_hi, IDESC, accumulate);
+            umma_tf32_ts_pair(tmem_d, ta_hi + ks * UMMA_K, b_lo, IDESC, 1);
+            umma_tf32_ts_pair(tmem_d, ta_hi + ks * UMMA_K, b_hi, IDESC, 1);
+            accumulate = 1;
+          }
+          umma_commit_pair(&empty_b[s]);  // both fire, in both CTAs, once the MMAs above have read their operands
+          umma_commit_pair(&pfree[sp]);
+          if (closes_chunk(j, count, issuer)) {
+            umma_commit_pair(&acc_full[issuer]);
+            ++cc;
+            opens = true;
+          }
+        }
+      }
+    }
+  } else if (warp < DRAIN_WARP0) {
+    // ------------------------------------------------ 3xTF32 split: A -> TMEM, B lo -> smem
+    const int set = (warp - SPLIT_WARP0) >> 2;             // which of the two alternating sets
+    const int tt = (threadIdx.x - SPLIT_WARP0 * 32) & 127;  // 0..127 within the set
+    const int arow = (warp & 3) * 32 + lane;          // TMEM lane quarter of this warp
+    uint32_t it = 0;
+    bool ok = true;
+    for (int64_t t = pair; t < num_tiles && ok; t += num_pairs) {
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        if ((int)(it & 1) != set) continue;
+        const int sa = it % A_SLOTS, sp = it % P_SLOTS, s = it % B_SLOTS;
+        ok = mbar_wait(&pfree[sp], ((it / P_SLOTS) & 1) ^ 1, 6, a.dev_status, abort_flag) &&
+             mbar_wait(&full_a[sa], (it / A_SLOTS) & 1, 3, a.dev_status, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        // A: this thread owns row `arow` of the 128 x 32 tile (TMEM lane = row).  The tile sits in
+        // shared memory with the 128-byte swizzle: 16-byte chunk c of row r is stored at c ^ (r & 7).
+        {
+          const float4* arow_p = reinterpret_cast<const float4*>(smem + sa * A_BYTES + arow * 128);
+          float hi[32], lo[32];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const float4 v = arow_p[c ^ (arow & 7)];
+            hi[4 * c + 0] = v.x; hi[4 * c + 1] = v.y; hi[4 * c + 2] = v.z; hi[4 * c + 3] = v.w;
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) lo[j] = tf32_lo(hi[j]);
+          const uint32_t ta = tmem_base + A_RING + sp * 64 + ((uint32_t)(arow & ~31) << 16);
+          tmem_st32(ta, hi);        // the tensor core truncates the fp32 words itself
+          tmem_st32(ta + 32, lo);
+          // Free the raw A slot only once the stores have consumed the registers the shared-memory
+          // loads filled.  Arriving right after the loads were issued was measured to be too early:
+          // with two slots the refill landed while loads were still queued (wrong results).
+          tmem_wait_st();
+          mbar_arrive_warp(&empty_a[sa]);
+        }
+        ok = mbar_wait(&full_b[s], (it / B_SLOTS) & 1, 7, a.dev_status, abort_flag);
+        if (!ok) break;
+        // B: lo = tf32(v - trunc(v)) into the second buffer, same (swizzled) layout; raw B is hi.
+        {
+          const float4* bh = reinterpret_cast<const float4*>(smem + B_RING + s * B_BYTES);
+          float4* bl = reinterpret_cast<float4*>(smem + LO_RING + sp * B_BYTES);
+#pragma unroll 4
+          for (int i = tt; i < B_BYTES / 16; i += 128) {
+            const float4 v = bh[i];
+            float4 l;
+            l.x = tf32_lo(v.x); l.y = tf32_lo(v.y);
+            l.z = tf32_lo(v.z); l.w = tf32_lo(v.w);
+            bl[i] = l;
+          }
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        // make the generic-proxy writes visible to the tensor core (async proxy)
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive_warp_remote(&ready[sp], 0);  // the leader's barrier counts both CTAs' split warps
+      }
+    }
+  } else {
+    // ------------------------------------------------ drain + epilogue
+    // Two warps per TMEM lane quarter: the first takes columns [0, FIRST), the second [FIRST, BN),
+    // both in pieces of 16 columns (FIRST is a multiple of 16, so BN = 112 splits into 64 + 48).
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+    const int col0 = second_half ? FIRST : 0;
+    const int mycols = second_half ? BN - FIRST : FIRST;
+    const bool has_bias = a.epi == TCB200_EPI_BIAS || a.epi == TCB200_EPI_BIAS_RELU;
+    uint32_t it0 = 0, dc[2] = {0, 0};  // running k-block number of the tile; chunks drained per issuer
+    bool ok = true;
+    for (int64_t t = pair; t < num_tiles && ok; t += num_pairs, it0 += (uint32_t)num_kb) {
+      int m0, n0, bz;
+      tile_coords(t, &m0, &n0, &bz);
+      const int row = m0 + q * 32 + lane;
+      float* crow = a.C + (int64_t)bz * a.stride_c + (int64_t)row * a.ldc;
+      const float bias_m = (has_bias && a.bias_on_m && row < a.M) ? __ldg(a.bias + row) : 0.f;
+
+      auto store16 = [&](const float* v, int c0) {
+        const int nb = n0 + c0;
+        if (row >= a.M || nb >= a.N) return;
+        if (a.c_vec && nb + 16 <= a.N) {
+#pragma unroll
+          for (int j = 0; j < 16; j += 4) {
+            float4 b4 = make_float4(bias_m, bias_m, bias_m, bias_m);
+            if (has_bias && !a.bias_on_m) b4 = __ldg(reinterpret_cast<const float4*>(a.bias + nb + j));
+            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            float4* dst = reinterpret_cast<float4*>(crow + nb + j);
+            if (a.accumulate) {
+              const float4 old = *dst;
+              o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+            }
+            o.x = apply_epilogue_rt(a.epi, o.x, b4.x);
+            o.y = apply_epilogue_rt(a.epi, o.y, b4.y);
+            o.z = apply_epilogue_rt(a.epi, o.z, b4.z);
+            o.w = apply_epilogue_rt(a.epi, o.w, b4.w);
+            *dst = o;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int n = nb + j;
+            if (n < a.N) {
+              float o = v[j];
+              if (a.accumulate) o += crow[n];
+              const float bb = has_bias ? (a.bias_on_m ? bias_m : __ldg(a.bias + n)) : 0.f;
+              crow[n] = apply_epilogue_rt(a.epi, o, bb);
+            }
+          }
+        }
+      };
+
+      float acc[PIECES][16];
+#pragma unroll
+      for (int g = 0; g < PIECES; ++g)
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[g][j] = 0.f;
+      // Chunks of both issuers in the order of the k-block that closes them (the same order on
+      // every run; the two can never tie because their k-blocks differ in parity).
+      const int first0 = own_first(it0, 0), first1 = own_first(it0, 1);
+      const int count0 = own_count(it0, 0), count1 = own_count(it0, 1);
+      int j0 = 0, j1 = 0;  // own k-block index from which the next chunk of each issuer is searched
+      while (j0 < count0 || j1 < count1) {
+        int e0 = j0, e1 = j1;  // own index that closes the next chunk
+        while (e0 < count0 && !closes_chunk(e0, count0, 0)) ++e0;
+        while (e1 < count1 && !closes_chunk(e1, count1, 1)) ++e1;
+        const bool take1 = j0 >= count0 || (j1 < count1 && first1 + 2 * e1 < first0 + 2 * e0);
+        const int i = take1 ? 1 : 0;
+        if (take1) j1 = e1 + 1; else j0 = e0 + 1;
+        ok = mbar_wait(&acc_full[i], dc[i] & 1, 4, a.dev_status, abort_flag);
+        if (!ok) break;
+        ++dc[i];
+        tc_fence_after();
+#pragma unroll
+        for (int g = 0; g < PIECES; ++g) {
+          if (g * 16 < mycols) {  // the same for the whole warp
+            float v[16];
+            tmem_ld16(tmem_base + i * ACC_STRIDE + lane_base + col0 + g * 16, v);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[g][j] += v[j];
+          }
+        }
+        tc_fence_before();
+        mbar_arrive_warp_remote(&acc_empty[i], 0);  // issuer i (in the leader) may overwrite its accumulator
+      }
+      if (!ok) break;
+#pragma unroll
+      for (int g = 0; g < PIECES; ++g)
+        if (g * 16 < mycols) store16(acc[g], col0 + g * 16);
+    }
+  }
+
+  tc_fence_before();
+  __syncwarp();
+  cluster_sync_all();  // no CTA leaves (or frees tensor memory) while its peer may still use it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+
 // ---------------------------------------------------------------------------------- host
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -792,6 +1123,20 @@ int launch_ts(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, co
   return TCB200_OK;
 }
 
+int launch_pair(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const TcArgs& args, cudaStream_t s) {
+  static std::atomic<uint64_t> configured{0};  // bit per device
+  const uint64_t bit = 1ull << (plan.device & 63);
+  if (!(configured.load(std::memory_order_acquire) & bit)) {
+    TCB200_CUDA_TRY(cudaFuncSetAttribute(contraction_ts_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         ts_pair_smem_bytes()));
+    configured.fetch_or(bit, std::memory_order_release);
+  }
+  // the kernel carries its cluster shape (2 CTAs); the grid is a multiple of 2
+  contraction_ts_pair_kernel<<<plan.launch.grid, dim3(kTsThreads, 1, 1), ts_pair_smem_bytes(), s>>>(ta, tb, args);
+  TCB200_CUDA_TRY(cudaGetLastError());
+  return TCB200_OK;
+}
+
 }  // namespace
 
 int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n) {
@@ -823,6 +1168,14 @@ int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max,
   for (int i = 0; i < 3; ++i)
     for (int j = i + 1; j < 3; ++j)
       if (cost[order[j]] < cost[order[i]]) { const int t = order[i]; order[i] = order[j]; order[j] = t; }
+  // CTA pairs (256 x 128 tiles): first wherever there are at least two 128-row tiles to pair up
+  const bool pair_ok = p.M > BM && p.N >= kPairBN;
+  auto push_pair = [&]() {
+    if (cnt < max && out)
+      out[cnt] = tcb200_tile_t{TCB200_VARIANT_TCGEN05_PAIR, 2 * BM, kPairBN, BK, kPairBSlots, kTsThreads, 3};
+    ++cnt;
+  };
+  if (pair_ok) push_pair();
   for (int i = 0; i < 3; ++i)
     if (p.N >= ts_bn[order[i]]) push_ts(ts_bn[order[i]]);
   const int bns[] = {128, 256, 64};
@@ -836,6 +1189,19 @@ int contraction_tc_plan(Plan& plan) {
   const tcb200_problem_t& p = plan.p;
   if (!shape_ok(p)) return TCB200_ERR_UNSUPPORTED;
   tcb200_tile_t& t = plan.tile;
+  if (t.variant == TCB200_VARIANT_TCGEN05_PAIR) {
+    if (t.bn == 0) t.bn = kPairBN;
+    if (t.split_tf32 == 0) t.split_tf32 = 3;
+    if (t.bn != kPairBN || t.split_tf32 != 3) return TCB200_ERR_UNSUPPORTED;
+    if (ceil_div(p.M, 2 * BM) > 65535) return TCB200_ERR_UNSUPPORTED;
+    t.bm = 2 * BM; t.bk = BK; t.stages = kPairBSlots; t.threads = kTsThreads;
+    const int64_t tiles = ceil_div(p.N, kPairBN) * ceil_div(p.M, 2 * BM) * p.batch;
+    plan.launch.grid = dim3(2u * (unsigned)std::min<int64_t>(tiles, kNumSMs / 2), 1, 1);
+    plan.launch.block = dim3(kTsThreads, 1, 1);
+    plan.launch.smem = ts_pair_smem_bytes();
+    plan.kernel_id = 301283;
+    return TCB200_OK;
+  }
   if (t.bn == 0) t.bn = 128;
   if (t.split_tf32 == 0) t.split_tf32 = 3;
   if (t.bn != 64 && t.bn != 128 && t.bn != 256 && !(t.bn == 112 && t.variant == TCB200_VARIANT_TCGEN05_TS))
@@ -863,7 +1229,8 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
   CUtensorMap ta, tb;
   int st = make_operand_map(&ta, A, p.K, p.M, p.lda, p.batch, p.stride_a, BM);
   if (st != TCB200_OK) return st;
-  st = make_operand_map(&tb, B, p.K, p.N, p.ldb, p.batch, p.stride_b, plan.tile.bn);
+  st = make_operand_map(&tb, B, p.K, p.N, p.ldb, p.batch, p.stride_b,
+                        plan.kernel_id == 301283 ? kPairBN / 2 : plan.tile.bn);
   if (st != TCB200_OK) return st;
   TcArgs a;
   a.C = C; a.bias = bias;
@@ -876,6 +1243,7 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
   a.c_vec = ((uintptr_t)C & 15) == 0 && p.ldc % 4 == 0 && p.stride_c % 4 == 0 && bias_vec;
   a.dev_status = dev_status;
   switch (plan.kernel_id) {
+    case 301283: return launch_pair(plan, ta, tb, a, s);
     case 100643: return launch_ts<64>(plan, ta, tb, a, s);
     case 101283: return launch_ts<128>(plan, ta, tb, a, s);
     case 101123: return launch_ts<112>(plan, ta, tb, a, s);

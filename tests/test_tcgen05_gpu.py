@@ -16,9 +16,10 @@ def _rand(shape, seed):
     return torch.randn(shape, generator=g, dtype=torch.float32)
 
 
-def tc_tile(bn, split, ts=False):
+def tc_tile(bn, split, ts=False, pair=False):
     t = cabi.Tile()
-    t.variant, t.bn, t.split_tf32 = (cabi.VARIANT_TCGEN05_TS if ts else cabi.VARIANT_TCGEN05), bn, split
+    variant = cabi.VARIANT_TCGEN05_PAIR if pair else cabi.VARIANT_TCGEN05_TS if ts else cabi.VARIANT_TCGEN05
+    t.variant, t.bn, t.split_tf32 = variant, bn, split
     return t
 
 
@@ -53,9 +54,28 @@ def test_tcgen05_ts_tiles(cuda, bn, shape):
     assert_close(out, ref64(A, B), K, [A, B], 3e-7, plan.describe())
 
 
+@pytest.mark.parametrize("shape", [(1, 256, 128, 128), (1, 512, 384, 512), (1, 70, 200, 132), (3, 130, 96, 256),
+                                   (1, 300, 128, 4096), (2, 700, 300, 1056), (1, 4096, 256, 64)])
+def test_tcgen05_pair_tiles(cuda, shape):
+    """CTA pairs (cta_group::2): 256-row tiles, each CTA stages half of B; ragged rows/columns, batches,
+    odd numbers of k-blocks, tiles where the second CTA of the pair has no rows at all."""
+    b, M, N, K = shape
+    A, B = _rand((b, M, K), 41), _rand((b, N, K), 42)
+    p = cabi.contraction_problem(b, M, N, K, True, True)
+    out, plan = run_plan(p, [A.to(cuda), B.to(cuda)], (b, M, N), tc_tile(128, 3, pair=True))
+    assert "tcgen05_pair" in plan.describe()
+    assert_close(out, ref64(A, B), K, [A, B], 3e-7, plan.describe())
+    out2, _ = run_plan(p, [A.to(cuda), B.to(cuda)], (b, M, N), tc_tile(128, 3, pair=True))
+    assert torch.equal(out, out2)  # one accumulator per issuer: the same bits on every run
+
+
 @pytest.mark.parametrize("epi", [cabi.EPI_NONE, cabi.EPI_BIAS, cabi.EPI_BIAS_RELU, cabi.EPI_RELU])
 @pytest.mark.parametrize("N", [384, 100])  # 100: ragged columns -> scalar stores
-def test_tcgen05_epilogues(cuda, epi, N):
+@pytest.mark.parametrize("kind", ["ss", "ts", "pair"])
+def test_tcgen05_epilogues(cuda, epi, N, kind):
+    tile = lambda: tc_tile(128 if N >= 128 else 64, 3, ts=kind == "ts", pair=kind == "pair")
+    if kind == "pair" and N < 128:
+        tile = lambda: tc_tile(128, 3, pair=True)
     M, K = 200, 320
     I, W, b = _rand((M, K), 23), _rand((N, K), 24), _rand((N,), 25)
     has_bias = epi in (cabi.EPI_BIAS, cabi.EPI_BIAS_RELU)
@@ -63,12 +83,12 @@ def test_tcgen05_epilogues(cuda, epi, N):
                           double=True)
     p = cabi.contraction_problem(1, M, N, K, True, True, epilogue=epi)
     ins = [I.to(cuda), W.to(cuda)] + ([b.to(cuda)] if has_bias else [])
-    out, plan = run_plan(p, ins, (M, N), tc_tile(128, 3))
+    out, plan = run_plan(p, ins, (M, N), tile())
     assert_close(out, ref, K, [I, W], 3e-7, plan.describe())
     if epi == cabi.EPI_NONE:
         p2 = cabi.contraction_problem(1, M, N, K, True, True, accumulate=True)
         init = _rand((M, N), 26).to(cuda)
-        out2, _ = run_plan(p2, ins, (M, N), tc_tile(128, 3), out_init=init)
+        out2, _ = run_plan(p2, ins, (M, N), tile(), out_init=init)
         assert_close(out2, ref + init.cpu().numpy(), K, what="accumulate")
 
 
