@@ -86,41 +86,17 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// One arrival per warp on the barrier at the same shared-memory offset in CTA `rank` of the cluster
-// (release at cluster scope: the waiter may sit on another SM).
+// One arrival per warp on the barrier at the same shared-memory offset in CTA `rank` of the cluster.
+// Default semantics (release at CTA scope), as for a local arrival: the data the arrival publishes is
+// consumed by the tensor core (async proxy) after the writer's own proxy / tcgen05 fences, not by
+// generic loads of the other CTA.  A release at cluster scope was measured to cost ~1500 cycles per
+// arrival in the split warps.
 __device__ __forceinline__ void mbar_arrive_warp_remote(uint64_t* bar, uint32_t rank) {
   __syncwarp();
   if ((threadIdx.x & 31) == 0) {
     uint32_t remote;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(bar)), "r"(rank));
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
-  }
-}
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// mbar_wait for a barrier that threads of the peer CTA arrive on: acquire at cluster scope, same bound.
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, int code, int* dev_status,
-                                                  volatile int* abort_flag) {
-  const long long t0 = clock64();
-  for (int i = 0;; ++i) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    if ((i & 1023) == 1023) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > 4000000000ll) {
-        *abort_flag = code;
-        if (dev_status) atomicCAS(dev_status, 0, code);
-        return false;
-      }
-    }
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
   }
 }
 

@@ -848,13 +848,13 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
           const uint32_t it = it0 + (uint32_t)(first + 2 * j);
           uint32_t accumulate = 1;
           if (opens) {  // the drain warps have read the previous chunk out of this accumulator
-            ok = mbar_wait_cluster(&acc_empty[issuer], (cc & 1) ^ 1, 5, a.dev_status, abort_flag);
+            ok = mbar_wait(&acc_empty[issuer], (cc & 1) ^ 1, 5, a.dev_status, abort_flag);
             if (!ok) break;
             accumulate = 0;
             opens = false;
           }
           const int s = it % B_SLOTS, sp = it % P_SLOTS;
-          ok = mbar_wait_cluster(&ready[sp], (it / P_SLOTS) & 1, 2, a.dev_status, abort_flag);
+          ok = mbar_wait(&ready[sp], (it / P_SLOTS) & 1, 2, a.dev_status, abort_flag);
           if (!ok) break;
           tc_fence_after();
           const uint32_t sb = smem_u32(smem + B_RING + s * B_BYTES);
