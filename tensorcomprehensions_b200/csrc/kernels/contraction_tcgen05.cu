@@ -561,69 +561,50 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         if ((int)(it & 1) != set) continue;
         const int sa = it % A_SLOTS, sp = it % P_SLOTS, s = it % B_SLOTS;
-        // The three barriers this k-block needs are polled together: under load a poll is a ~250-cycle
-        // shared-memory round trip, and three in a row were a fifth of the split's time per k-block.
-        {
-          const uint32_t par_p = ((it / P_SLOTS) & 1) ^ 1, par_a = (it / A_SLOTS) & 1, par_b = (it / B_SLOTS) & 1;
-          const bool got_p = mbar_try_wait(&pfree[sp], par_p);
-          const bool got_a = mbar_try_wait(&full_a[sa], par_a);
-          const bool got_b = mbar_try_wait(&full_b[s], par_b);
-          ok = (got_p || mbar_wait(&pfree[sp], par_p, 6, a.dev_status, abort_flag)) &&
-               (got_a || mbar_wait(&full_a[sa], par_a, 3, a.dev_status, abort_flag)) &&
-               (got_b || mbar_wait(&full_b[s], par_b, 7, a.dev_status, abort_flag));
-        }
+        ok = mbar_wait(&pfree[sp], ((it / P_SLOTS) & 1) ^ 1, 6, a.dev_status, abort_flag) &&
+             mbar_wait(&full_a[sa], (it / A_SLOTS) & 1, 3, a.dev_status, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        // All loads of the k-block go out together (one more round trip): row `arow` of the A tile
-        // (TMEM lane = row; the tile sits in shared memory with the 128-byte swizzle: 16-byte chunk c
-        // of row r is stored at c ^ (r & 7)) and this thread's first pieces of raw B.
-        constexpr int B_PIECES = B_BYTES / 16 / 128;            // 16-byte pieces of B per thread
-        constexpr int B_EARLY = B_PIECES < 4 ? B_PIECES : 4;    // loaded together with A
-        static_assert(B_BYTES % (16 * 128) == 0, "B pieces per thread");
-        const float4* bh = reinterpret_cast<const float4*>(smem + B_RING + s * B_BYTES);
-        float4* bl = reinterpret_cast<float4*>(smem + LO_RING + sp * B_BYTES);
-        const float4* arow_p = reinterpret_cast<const float4*>(smem + sa * A_BYTES + arow * 128);
-        float hi[32];
-        float4 bv[B_EARLY];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const float4 v = arow_p[c ^ (arow & 7)];
-          hi[4 * c + 0] = v.x; hi[4 * c + 1] = v.y; hi[4 * c + 2] = v.z; hi[4 * c + 3] = v.w;
-        }
-#pragma unroll
-        for (int i = 0; i < B_EARLY; ++i) bv[i] = bh[tt + 128 * i];
+        // A: this thread owns row `arow` of the 128 x 32 tile (TMEM lane = row).  The tile sits in
+        // shared memory with the 128-byte swizzle: 16-byte chunk c of row r is stored at c ^ (r & 7).
         {
-          float lo[32];
+          const float4* arow_p = reinterpret_cast<const float4*>(smem + sa * A_BYTES + arow * 128);
+          float hi[32], lo[32];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const float4 v = arow_p[c ^ (arow & 7)];
+            hi[4 * c + 0] = v.x; hi[4 * c + 1] = v.y; hi[4 * c + 2] = v.z; hi[4 * c + 3] = v.w;
+          }
 #pragma unroll
           for (int j = 0; j < 32; ++j) lo[j] = tf32_lo(hi[j]);
           const uint32_t ta = tmem_base + A_RING + sp * 64 + ((uint32_t)(arow & ~31) << 16);
           tmem_st32(ta, hi);        // the tensor core truncates the fp32 words itself
           tmem_st32(ta + 32, lo);
+          // Free the raw A slot only once the stores have consumed the registers the shared-memory
+          // loads filled.  Arriving right after the loads were issued was measured to be too early:
+          // with two slots the refill landed while loads were still queued (wrong results).
+          tmem_wait_st();
+          mbar_arrive_warp(&empty_a[sa]);
         }
-        // B: lo = v - trunc(v), rounded, into the B lo ring with the same (swizzled) layout; raw B is hi.
-#pragma unroll
-        for (int i = 0; i < B_EARLY; ++i) {
-          float4 l;
-          l.x = tf32_lo(bv[i].x); l.y = tf32_lo(bv[i].y);
-          l.z = tf32_lo(bv[i].z); l.w = tf32_lo(bv[i].w);
-          bl[tt + 128 * i] = l;
+        ok = mbar_wait(&full_b[s], (it / B_SLOTS) & 1, 7, a.dev_status, abort_flag);
+        if (!ok) break;
+        // B: lo = tf32(v - trunc(v)) into the second buffer, same (swizzled) layout; raw B is hi.
+        {
+          const float4* bh = reinterpret_cast<const float4*>(smem + B_RING + s * B_BYTES);
+          float4* bl = reinterpret_cast<float4*>(smem + LO_RING + sp * B_BYTES);
+#pragma unroll 4
+          for (int i = tt; i < B_BYTES / 16; i += 128) {
+            const float4 v = bh[i];
+            float4 l;
+            l.x = tf32_lo(v.x); l.y = tf32_lo(v.y);
+            l.z = tf32_lo(v.z); l.w = tf32_lo(v.w);
+            bl[i] = l;
+          }
         }
-#pragma unroll
-        for (int i = B_EARLY; i < B_PIECES; ++i) {
-          const float4 v = bh[tt + 128 * i];
-          float4 l;
-          l.x = tf32_lo(v.x); l.y = tf32_lo(v.y);
-          l.z = tf32_lo(v.z); l.w = tf32_lo(v.w);
-          bl[tt + 128 * i] = l;
-        }
-        // The stores to tensor memory have read their registers (and so the shared-memory loads that
-        // filled them have completed) once tcgen05.wait::st returns: only then is the raw A slot
-        // released.  Releasing right after issuing the loads let the TMA refill overtake them.
         tmem_wait_st();
         tc_fence_before();
         // make the generic-proxy writes visible to the tensor core (async proxy)
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive_warp(&empty_a[sa]);
         mbar_arrive_warp(&ready[sp]);
       }
     }
@@ -909,69 +890,50 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         if ((int)(it & 1) != set) continue;
         const int sa = it % A_SLOTS, sp = it % P_SLOTS, s = it % B_SLOTS;
-        // The three barriers this k-block needs are polled together: under load a poll is a ~250-cycle
-        // shared-memory round trip, and three in a row were a fifth of the split's time per k-block.
-        {
-          const uint32_t par_p = ((it / P_SLOTS) & 1) ^ 1, par_a = (it / A_SLOTS) & 1, par_b = (it / B_SLOTS) & 1;
-          const bool got_p = mbar_try_wait(&pfree[sp], par_p);
-          const bool got_a = mbar_try_wait(&full_a[sa], par_a);
-          const bool got_b = mbar_try_wait(&full_b[s], par_b);
-          ok = (got_p || mbar_wait(&pfree[sp], par_p, 6, a.dev_status, abort_flag)) &&
-               (got_a || mbar_wait(&full_a[sa], par_a, 3, a.dev_status, abort_flag)) &&
-               (got_b || mbar_wait(&full_b[s], par_b, 7, a.dev_status, abort_flag));
-        }
+        ok = mbar_wait(&pfree[sp], ((it / P_SLOTS) & 1) ^ 1, 6, a.dev_status, abort_flag) &&
+             mbar_wait(&full_a[sa], (it / A_SLOTS) & 1, 3, a.dev_status, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        // All loads of the k-block go out together (one more round trip): row `arow` of the A tile
-        // (TMEM lane = row; the tile sits in shared memory with the 128-byte swizzle: 16-byte chunk c
-        // of row r is stored at c ^ (r & 7)) and this thread's first pieces of raw B.
-        constexpr int B_PIECES = B_BYTES / 16 / 128;            // 16-byte pieces of B per thread
-        constexpr int B_EARLY = B_PIECES < 4 ? B_PIECES : 4;    // loaded together with A
-        static_assert(B_BYTES % (16 * 128) == 0, "B pieces per thread");
-        const float4* bh = reinterpret_cast<const float4*>(smem + B_RING + s * B_BYTES);
-        float4* bl = reinterpret_cast<float4*>(smem + LO_RING + sp * B_BYTES);
-        const float4* arow_p = reinterpret_cast<const float4*>(smem + sa * A_BYTES + arow * 128);
-        float hi[32];
-        float4 bv[B_EARLY];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const float4 v = arow_p[c ^ (arow & 7)];
-          hi[4 * c + 0] = v.x; hi[4 * c + 1] = v.y; hi[4 * c + 2] = v.z; hi[4 * c + 3] = v.w;
-        }
-#pragma unroll
-        for (int i = 0; i < B_EARLY; ++i) bv[i] = bh[tt + 128 * i];
+        // A: this thread owns row `arow` of the 128 x 32 tile (TMEM lane = row).  The tile sits in
+        // shared memory with the 128-byte swizzle: 16-byte chunk c of row r is stored at c ^ (r & 7).
         {
-          float lo[32];
+          const float4* arow_p = reinterpret_cast<const float4*>(smem + sa * A_BYTES + arow * 128);
+          float hi[32], lo[32];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const float4 v = arow_p[c ^ (arow & 7)];
+            hi[4 * c + 0] = v.x; hi[4 * c + 1] = v.y; hi[4 * c + 2] = v.z; hi[4 * c + 3] = v.w;
+          }
 #pragma unroll
           for (int j = 0; j < 32; ++j) lo[j] = tf32_lo(hi[j]);
           const uint32_t ta = tmem_base + A_RING + sp * 64 + ((uint32_t)(arow & ~31) << 16);
           tmem_st32(ta, hi);        // the tensor core truncates the fp32 words itself
           tmem_st32(ta + 32, lo);
+          // Free the raw A slot only once the stores have consumed the registers the shared-memory
+          // loads filled.  Arriving right after the loads were issued was measured to be too early:
+          // with two slots the refill landed while loads were still queued (wrong results).
+          tmem_wait_st();
+          mbar_arrive_warp(&empty_a[sa]);
         }
-        // B: lo = v - trunc(v), rounded, into the B lo ring with the same (swizzled) layout; raw B is hi.
-#pragma unroll
-        for (int i = 0; i < B_EARLY; ++i) {
-          float4 l;
-          l.x = tf32_lo(bv[i].x); l.y = tf32_lo(bv[i].y);
-          l.z = tf32_lo(bv[i].z); l.w = tf32_lo(bv[i].w);
-          bl[tt + 128 * i] = l;
+        ok = mbar_wait(&full_b[s], (it / B_SLOTS) & 1, 7, a.dev_status, abort_flag);
+        if (!ok) break;
+        // B: lo = tf32(v - trunc(v)) into the second buffer, same (swizzled) layout; raw B is hi.
+        {
+          const float4* bh = reinterpret_cast<const float4*>(smem + B_RING + s * B_BYTES);
+          float4* bl = reinterpret_cast<float4*>(smem + LO_RING + sp * B_BYTES);
+#pragma unroll 4
+          for (int i = tt; i < B_BYTES / 16; i += 128) {
+            const float4 v = bh[i];
+            float4 l;
+            l.x = tf32_lo(v.x); l.y = tf32_lo(v.y);
+            l.z = tf32_lo(v.z); l.w = tf32_lo(v.w);
+            bl[i] = l;
+          }
         }
-#pragma unroll
-        for (int i = B_EARLY; i < B_PIECES; ++i) {
-          const float4 v = bh[tt + 128 * i];
-          float4 l;
-          l.x = tf32_lo(v.x); l.y = tf32_lo(v.y);
-          l.z = tf32_lo(v.z); l.w = tf32_lo(v.w);
-          bl[tt + 128 * i] = l;
-        }
-        // The stores to tensor memory have read their registers (and so the shared-memory loads that
-        // filled them have completed) once tcgen05.wait::st returns: only then is the raw A slot
-        // released.  Releasing right after issuing the loads let the TMA refill overtake them.
         tmem_wait_st();
         tc_fence_before();
         // make the generic-proxy writes visible to the tensor core (async proxy)
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive_warp(&empty_a[sa]);
         mbar_arrive_warp_remote(&ready[sp], 0);  // the leader's barrier counts both CTAs' split warps
       }
     }
