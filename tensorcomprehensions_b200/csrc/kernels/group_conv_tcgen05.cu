@@ -117,7 +117,6 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tc_kernel(ConvTcArgs a
   // contiguous range of items for this CTA; item = n * G + g is also the slab index of I and O
   const int64_t begin = (int64_t)a.items * blockIdx.x / gridDim.x;
   const int64_t end = (int64_t)a.items * (blockIdx.x + 1) / gridDim.x;
-  const int steps_per_item = a.MT * TAPS;
   const uint32_t shift_bytes = (uint32_t)F * C * 4;   // one shift's B matrix
   const uint32_t lbo = (uint32_t)(F / 8) * 128;       // bytes between 16-byte chunks along k
   const uint32_t idesc = make_idesc_tf32(128, F);
