@@ -39,6 +39,12 @@ std::vector<TunedCandidate> sweepTiles(const std::string& tc, const std::string&
     int n = 0;
     if (tcb200_query(&l.problem, tiles, 32, &n) != TCB200_OK) continue;
     for (int i = 0; i < std::min(n, 32); ++i) {
+      // A plan fills in what a listed tile leaves open (threads, rows per CTA ...): sweep the tile as the
+      // plan will report it, so that the "was it applied" test below compares like with like.
+      tcb200_plan_t* probe = nullptr;
+      if (tcb200_plan_create(&l.problem, &tiles[i], 0, &probe) != TCB200_OK) continue;
+      tcb200_plan_tile(probe, &tiles[i]);
+      tcb200_plan_destroy(probe);
       if (!fixed.admits(tiles[i])) continue;
       bool seen = false;
       for (const auto& c : candidates) seen = seen || key(c) == key(tiles[i]);

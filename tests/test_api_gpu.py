@@ -78,6 +78,19 @@ def test_tune_returns_best_first_and_every_option_compiles(cuda):
         assert_close(exe(X, Y), ref, 72, what=desc)
 
 
+@pytest.mark.parametrize("name", ["tensordot", "group_conv", "tmm"])
+def test_tune_sweeps_every_tile_the_family_lists(cuda, name):
+    """The sweep must not lose a candidate because the plan filled in fields the listed tile left open
+    (the family default, e.g. the bulk-copy tensordot kernel, has to be among the timed ones)."""
+    w = wl.ALL[name](**wl.SMALL[name])
+    ins = [t.to(cuda) for t in wl.make_inputs(w)]
+    ranked = tclib.tune_report(w.tc, w.entry, ins)
+    default = tc.compile(w.tc, w.entry, "naive", *ins).tiles()[0]
+    swept = [options.to_tile() for options, _, _ in ranked]
+    assert default in swept, (default, swept)
+    assert len(swept) >= 2
+
+
 def test_accumulating_reduction_keeps_output(cuda):
     """'+=' without '!' adds to what the output holds (test/cuda/test_compile_and_run.cc:181-200)."""
     tcs = "def mm(float(M,K) A, float(K,N) B) -> (C) { C(m,n) += A(m,k) * B(k,n) }"
