@@ -159,7 +159,8 @@ def window_times_us(prog, n_windows=20, min_window_us=200.0):
         passes = max(1, int(-(-min_window_us // (min(est) * prog.sets))))
         runs = passes * prog.sets
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
+        # thread-local capture mode: other threads of the process (NCCL's watchdog at N > 1) keep their CUDA calls
+        with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
             for _ in range(runs):
                 prog.run()
         for _ in range(2):
