@@ -625,15 +625,32 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
       const int row = m0 + q * 32 + lane;
       float* crow = a.C + (int64_t)bz * a.stride_c + (int64_t)row * a.ldc;
       const float bias_m = (has_bias && a.bias_on_m && row < a.M) ? __ldg(a.bias + row) : 0.f;
+      // Per-column bias of this warp's columns, fetched now: lane l keeps columns col0 + 2l and
+      // col0 + 2l + 1 and the epilogue gets them by shuffle.  Loading them in the epilogue, between
+      // the output stores, serialised sixteen global-load latencies per thread (the compiler may not
+      // move a load across a store that could alias it): ~9000 cycles per tile, measured, during
+      // which the drain warps could not serve the next tile's first chunks.
+      float2 bias_n = make_float2(0.f, 0.f);
+      if (has_bias && !a.bias_on_m && 2 * lane < mycols) {
+        const int c = n0 + col0 + 2 * lane;
+        if (c < a.N) bias_n.x = __ldg(a.bias + c);
+        if (c + 1 < a.N) bias_n.y = __ldg(a.bias + c + 1);
+      }
 
       auto store16 = [&](const float* v, int c0) {
         const int nb = n0 + c0;
+        float bb[16];  // bias of columns c0 .. c0 + 15 (every lane takes part in the shuffles)
+#pragma unroll
+        for (int j = 0; j < 16; j += 2) {
+          const int src = (c0 - col0 + j) >> 1;
+          bb[j] = a.bias_on_m ? bias_m : __shfl_sync(0xffffffffu, bias_n.x, src);
+          bb[j + 1] = a.bias_on_m ? bias_m : __shfl_sync(0xffffffffu, bias_n.y, src);
+        }
         if (row >= a.M || nb >= a.N) return;
         if (a.c_vec && nb + 16 <= a.N) {
 #pragma unroll
           for (int j = 0; j < 16; j += 4) {
-            float4 b4 = make_float4(bias_m, bias_m, bias_m, bias_m);
-            if (has_bias && !a.bias_on_m) b4 = __ldg(reinterpret_cast<const float4*>(a.bias + nb + j));
+            const float4 b4 = make_float4(bb[j], bb[j + 1], bb[j + 2], bb[j + 3]);
             float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
             float4* dst = reinterpret_cast<float4*>(crow + nb + j);
             if (a.accumulate) {
@@ -653,8 +670,7 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
             if (n < a.N) {
               float o = v[j];
               if (a.accumulate) o += crow[n];
-              const float bb = has_bias ? (a.bias_on_m ? bias_m : __ldg(a.bias + n)) : 0.f;
-              crow[n] = apply_epilogue_rt(a.epi, o, bb);
+              crow[n] = apply_epilogue_rt(a.epi, o, bb[j]);
             }
           }
         }
@@ -954,15 +970,32 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       const int row = m0 + q * 32 + lane;
       float* crow = a.C + (int64_t)bz * a.stride_c + (int64_t)row * a.ldc;
       const float bias_m = (has_bias && a.bias_on_m && row < a.M) ? __ldg(a.bias + row) : 0.f;
+      // Per-column bias of this warp's columns, fetched now: lane l keeps columns col0 + 2l and
+      // col0 + 2l + 1 and the epilogue gets them by shuffle.  Loading them in the epilogue, between
+      // the output stores, serialised sixteen global-load latencies per thread (the compiler may not
+      // move a load across a store that could alias it): ~9000 cycles per tile, measured, during
+      // which the drain warps could not serve the next tile's first chunks.
+      float2 bias_n = make_float2(0.f, 0.f);
+      if (has_bias && !a.bias_on_m && 2 * lane < mycols) {
+        const int c = n0 + col0 + 2 * lane;
+        if (c < a.N) bias_n.x = __ldg(a.bias + c);
+        if (c + 1 < a.N) bias_n.y = __ldg(a.bias + c + 1);
+      }
 
       auto store16 = [&](const float* v, int c0) {
         const int nb = n0 + c0;
+        float bb[16];  // bias of columns c0 .. c0 + 15 (every lane takes part in the shuffles)
+#pragma unroll
+        for (int j = 0; j < 16; j += 2) {
+          const int src = (c0 - col0 + j) >> 1;
+          bb[j] = a.bias_on_m ? bias_m : __shfl_sync(0xffffffffu, bias_n.x, src);
+          bb[j + 1] = a.bias_on_m ? bias_m : __shfl_sync(0xffffffffu, bias_n.y, src);
+        }
         if (row >= a.M || nb >= a.N) return;
         if (a.c_vec && nb + 16 <= a.N) {
 #pragma unroll
           for (int j = 0; j < 16; j += 4) {
-            float4 b4 = make_float4(bias_m, bias_m, bias_m, bias_m);
-            if (has_bias && !a.bias_on_m) b4 = __ldg(reinterpret_cast<const float4*>(a.bias + nb + j));
+            const float4 b4 = make_float4(bb[j], bb[j + 1], bb[j + 2], bb[j + 3]);
             float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
             float4* dst = reinterpret_cast<float4*>(crow + nb + j);
             if (a.accumulate) {
@@ -982,8 +1015,7 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
             if (n < a.N) {
               float o = v[j];
               if (a.accumulate) o += crow[n];
-              const float bb = has_bias ? (a.bias_on_m ? bias_m : __ldg(a.bias + n)) : 0.f;
-              crow[n] = apply_epilogue_rt(a.epi, o, bb);
+              crow[n] = apply_epilogue_rt(a.epi, o, bb[j]);
             }
           }
         }
