@@ -57,6 +57,7 @@ struct TcArgs {
   int epi, bias_on_m, accumulate;
   int a_batched, b_batched;  // 0: operand shared by all batch entries
   int c_vec;                 // 128-bit stores allowed
+  int tma_store;             // pair kernel: epilogue through the staging tile and tiled TMA stores
   int* dev_status;
 };
 
@@ -732,15 +733,26 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
 // 8 in, MMA operand reads 24), which is what bounds the single-CTA kernel.  Barriers: everything a CTA's
 // own warps produce and consume stays local; the peer's split and drain warps arrive on the LEADER's
 // `ready` / `acc_empty`, and the leader's commits arrive on `empty_b`, `pfree`, `acc_full` in both CTAs.
+// Epilogue: a thread owns a row of the output tile, so storing straight from registers makes every
+// warp store touch 32 different rows (32 sectors per instruction): ~7500 cycles per tile, measured,
+// during which the drain warps cannot serve the next tile's first chunks.  The CTA's 128 x 128 tile
+// is therefore staged in shared memory (128-byte swizzle, conflict-free 128-bit stores) and written
+// by four tiled TMA stores that clip at the tensor's edge; `accumulate` and unaligned outputs keep
+// the direct path.
 constexpr int kPairBN = 128;
 constexpr int kPairBSlots = 8;
-__host__ __device__ constexpr int ts_pair_smem_bytes() {
-  return kTsASlots * BM * BK * 4 + (kPairBSlots + kTsPSlots) * (kPairBN / 2) * BK * 4 + kTsBarrierBytes + 1024;
+constexpr int kPairOutBytes = BM * kPairBN * 4;  // staging tile of the epilogue
+__host__ __device__ constexpr int ts_pair_rings_bytes() {
+  return kTsASlots * BM * BK * 4 + (kPairBSlots + kTsPSlots) * (kPairBN / 2) * BK * 4 + kTsBarrierBytes;
 }
+__host__ __device__ constexpr int ts_pair_out_offset() { return (ts_pair_rings_bytes() + 1023) / 1024 * 1024; }
+__host__ __device__ constexpr int ts_pair_smem_bytes() { return ts_pair_out_offset() + kPairOutBytes + 1024; }
+static_assert(ts_pair_smem_bytes() <= kTsSmemLimit, "rings + output staging tile exceed shared memory");
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTsThreads, 1)
 contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
-                           const __grid_constant__ CUtensorMap tmB, TcArgs a) {
+                           const __grid_constant__ CUtensorMap tmB,
+                           const __grid_constant__ CUtensorMap tmC, TcArgs a) {
   constexpr int BN = kPairBN;
   constexpr int A_SLOTS = kTsASlots, P_SLOTS = kTsPSlots, B_SLOTS = kPairBSlots;
   constexpr int A_BYTES = BM * BK * 4;
@@ -771,7 +783,9 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   uint64_t* empty_b = full_b + 8;        // [8] raw B slot read by its MMAs
   uint64_t* acc_full = empty_b + 8;      // [2]
   uint64_t* acc_empty = acc_full + 2;    // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* out_ready = acc_empty + 2;   // staging tile written by the eight drain warps
+  uint64_t* out_free = out_ready + 1;    // staging tile read by the TMA stores of the previous tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(out_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -796,6 +810,8 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 16);  // used in the leader only: eight drain warps of each CTA
     }
+    mbar_init(out_ready, 8);
+    mbar_init(out_free, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -963,6 +979,7 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     const int mycols = second_half ? BN - FIRST : FIRST;
     const bool has_bias = a.epi == TCB200_EPI_BIAS || a.epi == TCB200_EPI_BIAS_RELU;
     uint32_t it0 = 0, dc[2] = {0, 0};  // running k-block number of the tile; chunks drained per issuer
+    uint32_t staged = 0;               // tiles that went through the staging tile
     bool ok = true;
     for (int64_t t = pair; t < num_tiles && ok; t += num_pairs, it0 += (uint32_t)num_kb) {
       int m0, n0, bz;
@@ -1055,10 +1072,58 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         mbar_arrive_warp_remote(&acc_empty[i], 0);  // issuer i (in the leader) may overwrite its accumulator
       }
       if (!ok) break;
+      if (!a.tma_store) {
 #pragma unroll
-      for (int g = 0; g < PIECES; ++g)
-        if (g * 16 < mycols) store16(acc[g], col0 + g * 16);
+        for (int g = 0; g < PIECES; ++g)
+          if (g * 16 < mycols) store16(acc[g], col0 + g * 16);
+        continue;
+      }
+      // staged epilogue: the previous tile's TMA stores must have read the staging tile
+      ok = mbar_wait(out_free, (staged & 1) ^ 1, 10, a.dev_status, abort_flag);
+      if (!ok) break;
+      {
+        const int r = q * 32 + lane;  // row of the CTA's tile
+        uint8_t* out_tile = smem + ts_pair_out_offset();
+#pragma unroll
+        for (int g = 0; g < PIECES; ++g) {
+          const int c0 = col0 + g * 16;  // 16 columns = 4 chunks of one 32-column box
+          uint8_t* box_row = out_tile + (c0 >> 5) * (BM * 128) + r * 128;
+#pragma unroll
+          for (int j = 0; j < 16; j += 4) {
+            const int src = (c0 - col0 + j) >> 1;
+            float4 b4;
+            b4.x = a.bias_on_m ? bias_m : __shfl_sync(0xffffffffu, bias_n.x, src);
+            b4.y = a.bias_on_m ? bias_m : __shfl_sync(0xffffffffu, bias_n.y, src);
+            b4.z = a.bias_on_m ? bias_m : __shfl_sync(0xffffffffu, bias_n.x, src + 1);
+            b4.w = a.bias_on_m ? bias_m : __shfl_sync(0xffffffffu, bias_n.y, src + 1);
+            float4 o;
+            o.x = apply_epilogue_rt(a.epi, acc[g][j + 0], b4.x);
+            o.y = apply_epilogue_rt(a.epi, acc[g][j + 1], b4.y);
+            o.z = apply_epilogue_rt(a.epi, acc[g][j + 2], b4.z);
+            o.w = apply_epilogue_rt(a.epi, acc[g][j + 3], b4.w);
+            const int chunk = ((c0 & 31) + j) >> 2;
+            *reinterpret_cast<float4*>(box_row + ((chunk ^ (r & 7)) << 4)) = o;
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      }
+      mbar_arrive_warp(out_ready);
+      if (warp == DRAIN_WARP0 && lane == 0) {
+        ok = mbar_wait(out_ready, staged & 1, 11, a.dev_status, abort_flag);
+        if (ok) {
+          const uint8_t* out_tile = smem + ts_pair_out_offset();
+#pragma unroll
+          for (int bx = 0; bx < BN / 32; ++bx)
+            if (n0 + bx * 32 < a.N && m0 < a.M) tma_store_3d(&tmC, out_tile + bx * (BM * 128), n0 + bx * 32, m0, bz);
+          tma_store_commit();
+          tma_store_wait_read();  // the stores have read the tile: it may be overwritten
+          mbar_arrive(out_free);
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      ++staged;
     }
+    if (warp == DRAIN_WARP0 && lane == 0) tma_store_wait_all();  // global writes done before the kernel ends
   }
 
   tc_fence_before();
@@ -1155,7 +1220,8 @@ int launch_ts(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, co
   return TCB200_OK;
 }
 
-int launch_pair(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const TcArgs& args, cudaStream_t s) {
+int launch_pair(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                const TcArgs& args, cudaStream_t s) {
   static std::atomic<uint64_t> configured{0};  // bit per device
   const uint64_t bit = 1ull << (plan.device & 63);
   if (!(configured.load(std::memory_order_acquire) & bit)) {
@@ -1164,7 +1230,7 @@ int launch_pair(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, 
     configured.fetch_or(bit, std::memory_order_release);
   }
   // the kernel carries its cluster shape (2 CTAs); the grid is a multiple of 2
-  contraction_ts_pair_kernel<<<plan.launch.grid, dim3(kTsThreads, 1, 1), ts_pair_smem_bytes(), s>>>(ta, tb, args);
+  contraction_ts_pair_kernel<<<plan.launch.grid, dim3(kTsThreads, 1, 1), ts_pair_smem_bytes(), s>>>(ta, tb, tc, args);
   TCB200_CUDA_TRY(cudaGetLastError());
   return TCB200_OK;
 }
@@ -1274,8 +1340,17 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
   const bool bias_vec = !bias || p.bias_on_m || ((uintptr_t)bias & 15) == 0;
   a.c_vec = ((uintptr_t)C & 15) == 0 && p.ldc % 4 == 0 && p.stride_c % 4 == 0 && bias_vec;
   a.dev_status = dev_status;
+  a.tma_store = 0;
   switch (plan.kernel_id) {
-    case 301283: return launch_pair(plan, ta, tb, a, s);
+    case 301283: {
+      // output map for the staged epilogue: {N, M, batch}, boxes of 32 columns x 128 rows
+      CUtensorMap tc;
+      a.tma_store = a.c_vec && !p.accumulate;
+      if (a.tma_store && make_operand_map(&tc, C, p.N, p.M, p.ldc, p.batch, p.stride_c, BM) != TCB200_OK)
+        a.tma_store = 0;
+      if (!a.tma_store) tc = tb;  // unused by the kernel then
+      return launch_pair(plan, ta, tb, tc, a, s);
+    }
     case 100643: return launch_ts<64>(plan, ta, tb, a, s);
     case 101283: return launch_ts<128>(plan, ta, tb, a, s);
     case 101123: return launch_ts<112>(plan, ta, tb, a, s);

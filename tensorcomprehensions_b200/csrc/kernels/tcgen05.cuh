@@ -18,6 +18,19 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* tm, in
       : "memory");
 }
 
+// Tiled store shared -> global (the tensor map clips rows / columns outside the tensor), tracked by
+// the issuing thread's bulk async-group.  x must be a multiple of 4 fp32 and no coordinate negative.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* tm, const void* src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(tm), "r"(x),
+               "r"(y), "r"(z), "r"(smem_u32(src))
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the stores of this thread's earlier groups have READ their shared-memory source
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// ... and have been written to global memory
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                    smem_u32(slot)),
