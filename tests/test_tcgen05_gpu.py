@@ -1,4 +1,5 @@
 """The tcgen05/TMEM contraction kernel (explicit tiles) against the CPU checker.  Needs a B200."""
+import numpy as np
 import pytest
 import torch
 
@@ -99,6 +100,41 @@ def test_tcgen05_shared_operand(cuda):
     p = cabi.contraction_problem(b, M, N, K, True, True, stride_b=0)
     out, plan = run_plan(p, [A.to(cuda), B.to(cuda)], (b, M, N), tc_tile(128, 3))
     assert_close(out, ref, K, [A, B], 3e-7, plan.describe())
+
+
+@pytest.mark.parametrize("kind", ["ts", "pair"])
+def test_tcgen05_ts_and_pair_corner_forms(cuda, kind):
+    """Forms the matcher produces besides the plain ones: an operand shared by all batch entries, bias
+    indexed by the row, K that is not a multiple of the k-block, padded leading dimensions, narrow N."""
+    tile = lambda: tc_tile(128, 3, ts=kind == "ts", pair=kind == "pair")
+    # shared B (stride 0) over 3 batches, K = 132 (4 k-blocks + 4 columns)
+    b, M, N, K = 3, 260, 160, 132
+    A, B = _rand((b, M, K), 51), _rand((N, K), 52)
+    p = cabi.contraction_problem(b, M, N, K, True, True, stride_b=0)
+    out, plan = run_plan(p, [A.to(cuda), B.to(cuda)], (b, M, N), tile())
+    assert_close(out, ref64(A, B), K, [A, B], 3e-7, plan.describe())
+    # bias along the rows (O(m,n) + Bias(m)) with ReLU
+    M, N, K = 300, 200, 256
+    A, B, bias = _rand((M, K), 53), _rand((N, K), 54), _rand((M,), 55)
+    ref = np.maximum((A.double() @ B.double().t() + bias.double()[:, None]).numpy(), 0)
+    p = cabi.contraction_problem(1, M, N, K, True, True, epilogue=cabi.EPI_BIAS_RELU, bias_on_m=True)
+    out, plan = run_plan(p, [A.to(cuda), B.to(cuda), bias.to(cuda)], (M, N), tile())
+    assert_close(out, ref, K, [A, B], 3e-7, plan.describe())
+    # padded leading dimensions of all three tensors (views into wider buffers), N narrower than a tile
+    M, N, K = 384, 96, 512
+    Ab, Bb = _rand((M, K + 8), 56), _rand((N, K + 4), 57)
+    A, B = Ab[:, :K], Bb[:, :K]
+    Ad, Bd = Ab.to(cuda), Bb.to(cuda)
+    Cd = torch.full((M, N + 4), float("nan"), device=cuda)
+    p = cabi.contraction_problem(1, M, N, K, True, True, lda=K + 8, ldb=K + 4, ldc=N + 4)
+    plan = cabi.Plan(p, tile())
+    status = torch.zeros(1, dtype=torch.int32, device=cuda)
+    plan.launch_ptrs([Ad.data_ptr(), Bd.data_ptr()], [Cd.data_ptr()],
+                     stream=torch.cuda.current_stream().cuda_stream, dev_status=status.data_ptr())
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert_close(Cd[:, :N].cpu(), ref64(A, B), K, [A, B], 3e-7, plan.describe())
+    assert torch.isnan(Cd[:, N:]).all()  # the padding columns are not written
 
 
 def test_tcgen05_rejects_what_it_cannot_take(cuda):
