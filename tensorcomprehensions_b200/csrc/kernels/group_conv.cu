@@ -222,11 +222,13 @@ __global__ void __launch_bounds__(256) group_conv_rows_kernel(ConvArgs a, int n_
 //    and the output tile goes through shared memory so that it leaves in 128-bit coalesced stores.
 constexpr int kItemOW = 14;
 constexpr int kItemKW = 3;
-constexpr int kItemThreads = 64;
-
+constexpr int kItemThreads = 64;  // default form: four output channels per thread
 // KHT > 0: filter height known at compile time (rows and taps fully unrolled); 0: read from the arguments.
-template <int KHT>
-__global__ void __launch_bounds__(kItemThreads) group_conv_item_kernel(ConvArgs a) {
+// FPT: output channels per thread (4: 64 threads per item; 2: 128 threads, twice the warps in flight
+// at twice the input-row loads).
+template <int KHT, int FPT>
+__global__ void __launch_bounds__(256 / FPT) group_conv_item_kernel(ConvArgs a) {
+  constexpr int kItemThreads = 256 / FPT;
   extern __shared__ __align__(16) float smem[];
   const int item = blockIdx.x;  // n * G + g
   const int g = item % a.G;
@@ -254,7 +256,7 @@ __global__ void __launch_bounds__(kItemThreads) group_conv_item_kernel(ConvArgs 
   // Thread -> (channel quad, output row) with the rows of a quad padded to a multiple of 8 lanes: a
   // 128-bit shared load is served a quarter-warp at a time, and eight consecutive rows (pitch 80 B)
   // fall into distinct banks, which rows of two different quads in one quarter-warp would not.
-  const int FQ = F / 4;
+  const int FQ = F / FPT;
   const int hslots = (a.OH + 7) & ~7;
   const int fq_t = tid / hslots, h_t = tid - fq_t * hslots;
   const bool active = fq_t < FQ && h_t < a.OH;
@@ -262,9 +264,9 @@ __global__ void __launch_bounds__(kItemThreads) group_conv_item_kernel(ConvArgs 
 
   // accumulators as pairs of output channels: the packed fp32 FMA of sm_100 (two independent,
   // individually rounded fused multiply-adds per instruction) halves the FMA instruction count
-  float2 acc[2][kItemOW];
+  float2 acc[FPT / 2][kItemOW];
 #pragma unroll
-  for (int j = 0; j < 2; ++j)
+  for (int j = 0; j < FPT / 2; ++j)
 #pragma unroll
     for (int w = 0; w < kItemOW; ++w) acc[j][w] = make_float2(0.f, 0.f);
 
@@ -274,7 +276,7 @@ __global__ void __launch_bounds__(kItemThreads) group_conv_item_kernel(ConvArgs 
   auto channels = [&](int c0, int c1) {
     // running pointers: input row (c, h + kh) and filter vector (c, kh, kw = 0, 4 * fq)
     const float* rp = Is + (c0 * a.H + h) * kRowsPitch;
-    const float* wrow = Ws + c0 * KH * KW * F + fq * 4;
+    const float* wrow = Ws + c0 * KH * KW * F + fq * FPT;
     for (int c = c0; c < c1; ++c, rp += plane_step) {
 #pragma unroll
       for (int kh = 0; kh < KH; ++kh, rp += kRowsPitch, wrow += KW * F) {
@@ -288,13 +290,19 @@ __global__ void __launch_bounds__(kItemThreads) group_conv_item_kernel(ConvArgs 
 #pragma unroll
         for (int kw = 0; kw < kItemKW; ++kw) {
           if (kw < KW) {
-            const float4 wv = *reinterpret_cast<const float4*>(wrow + kw * F);
-            const float2 w01 = make_float2(wv.x, wv.y), w23 = make_float2(wv.z, wv.w);
+            float2 wp[FPT / 2];
+            if constexpr (FPT == 4) {
+              const float4 wv = *reinterpret_cast<const float4*>(wrow + kw * F);
+              wp[0] = make_float2(wv.x, wv.y);
+              wp[1] = make_float2(wv.z, wv.w);
+            } else {
+              wp[0] = *reinterpret_cast<const float2*>(wrow + kw * F);
+            }
 #pragma unroll
             for (int w = 0; w < kItemOW; ++w) {
               const float2 xx = make_float2(x[w + kw], x[w + kw]);
-              acc[0][w] = __ffma2_rn(xx, w01, acc[0][w]);
-              acc[1][w] = __ffma2_rn(xx, w23, acc[1][w]);
+#pragma unroll
+              for (int j = 0; j < FPT / 2; ++j) acc[j][w] = __ffma2_rn(xx, wp[j], acc[j][w]);
             }
           }
         }
@@ -313,8 +321,8 @@ __global__ void __launch_bounds__(kItemThreads) group_conv_item_kernel(ConvArgs 
   const bool has_bias = a.epi == TCB200_EPI_BIAS || a.epi == TCB200_EPI_BIAS_RELU;
   if (active) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int f = fq * 4 + j;
+    for (int j = 0; j < FPT; ++j) {
+      const int f = fq * FPT + j;
       const float bias = has_bias ? __ldg(a.bias + g * F + f) : 0.f;
       float* o = Os + ((size_t)f * a.OH + h) * a.OW;
 #pragma unroll
@@ -340,6 +348,11 @@ __global__ void __launch_bounds__(kItemThreads) group_conv_item_kernel(ConvArgs 
       Og[i] = apply_epilogue_rt(a.epi, Os[i] + Og[i], bias);
     }
   }
+}
+
+// Threads the two-channels-per-thread form of the item kernel would use (it takes up to 128).
+int item_two_threads(const tcb200_problem_t& p) {
+  return (int)((p.conv[3] / 2) * ((p.conv[4] - p.conv[6] + 1 + 7) / 8 * 8));
 }
 
 bool item_ok(const tcb200_problem_t& p) {
@@ -404,6 +417,10 @@ int group_conv_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int
   if (item_ok(p)) {  // stages = 4: one item per CTA, input staged in four cp.async groups
     if (cnt < max && out) out[cnt] = tcb200_tile_t{TCB200_VARIANT_SIMT, 0, 4, 1, 4, kItemThreads, 0};
     ++cnt;
+    if (item_two_threads(p) <= 128) {
+      if (cnt < max && out) out[cnt] = tcb200_tile_t{TCB200_VARIANT_SIMT, 0, 2, 1, 4, 128, 0};
+      ++cnt;
+    }
   }
   if (rows_ok(p)) {
     // bk = n per CTA of the rows kernel
@@ -441,19 +458,25 @@ int group_conv_plan(Plan& plan) {
     t.variant = TCB200_VARIANT_SIMT;
     t.threads = 256;
     t.bk = rows_ok(p) ? 2 : 0;
-    if (item_ok(p)) { t.bk = 1; t.stages = 4; }
+    if (item_ok(p)) {
+      t.bk = 1; t.stages = 4;
+      // more warps in flight per item when the item has the work for them
+      t.threads = item_two_threads(p) > kItemThreads && item_two_threads(p) <= 128 ? 128 : kItemThreads;
+    }
   }
   if (t.variant != TCB200_VARIANT_SIMT) return TCB200_ERR_UNSUPPORTED;
   if (t.bk == 1 && t.stages == 4) {  // item kernel
     if (!item_ok(p)) return TCB200_ERR_UNSUPPORTED;
     if (p.conv[0] * p.conv[1] > 0x7fffffffll) return TCB200_ERR_TOO_LARGE;
-    t.bm = 0; t.bn = 4;
-    t.threads = kItemThreads;
+    // threads = 128: two output channels per thread (bn = 2), else four
+    const bool two = t.threads == 128 && item_two_threads(p) <= 128;
+    t.bm = 0; t.bn = two ? 2 : 4;
+    t.threads = two ? 128 : kItemThreads;
     plan.launch.grid = dim3((unsigned)(p.conv[0] * p.conv[1]), 1, 1);
-    plan.launch.block = dim3(kItemThreads, 1, 1);
+    plan.launch.block = dim3(t.threads, 1, 1);
     plan.launch.smem = sizeof(float) * (size_t)(p.conv[2] * p.conv[6] * p.conv[7] * p.conv[3] +
                                                  p.conv[2] * p.conv[4] * kRowsPitch);
-    plan.kernel_id = 101;
+    plan.kernel_id = two ? 102 : 101;
     return TCB200_OK;
   }
   t.stages = 0;
@@ -500,11 +523,15 @@ int group_conv_launch(const Plan& plan, const float* I, const float* W, const fl
   a.OH = a.H - a.KH + 1; a.OW = a.Wd - a.KW + 1;
   a.band = plan.tile.bm;
   a.epi = p.epilogue; a.accumulate = p.accumulate;
-  if (plan.kernel_id == 101) {
-    if (a.KH == 3 && a.KW == 3)
-      group_conv_item_kernel<3><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(a);
-    else
-      group_conv_item_kernel<0><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(a);
+  if (plan.kernel_id == 101 || plan.kernel_id == 102) {
+    const bool k33 = a.KH == 3 && a.KW == 3;
+    if (plan.kernel_id == 102) {
+      if (k33) group_conv_item_kernel<3, 2><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(a);
+      else group_conv_item_kernel<0, 2><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(a);
+    } else {
+      if (k33) group_conv_item_kernel<3, 4><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(a);
+      else group_conv_item_kernel<0, 4><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(a);
+    }
     TCB200_CUDA_TRY(cudaGetLastError());
     return TCB200_OK;
   }
