@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define TCB200_ABI_VERSION 1
+#define TCB200_ABI_VERSION 2
 
 /* Opaque CUDA stream handle; identical to cudaStream_t / CUstream. */
 typedef struct CUstream_st* tcb200_stream_t;
@@ -78,8 +78,10 @@ typedef struct tcb200_problem {
   int64_t batch, M, N, K;
   int64_t lda, ldb, ldc;                /* leading dimensions, in elements */
   int64_t stride_a, stride_b, stride_c; /* batch strides, in elements (0 = shared by all batches) */
-  int64_t conv[8];                      /* group conv: N, G, C, F, H, W, KH, KW (valid, unit stride) */
+  int64_t conv[8];                      /* group conv: N, G, C, F, H, W, KH, KW (valid window) */
   int64_t td[5];                        /* tensordot: N, C1, C2, C3, P (P = product of trailing shared dims) */
+  int64_t conv_stride[2];               /* group conv: SH, SW of I(.., SH*h+kh, SW*w+kw) (tc/library/convolution.h:27-31);
+                                           0 reads as 1.  Output extent: (H - KH) / SH + 1 by (W - KW) / SW + 1 */
 } tcb200_problem_t;
 
 /* One point of a family's tile sweep.  Fields a variant does not use are 0. */

@@ -81,15 +81,16 @@ def loop_tmm(A, B, double=False):
     return C
 
 
-def loop_group_conv(I, W1, Bias=None, double=False):
+def loop_group_conv(I, W1, Bias=None, double=False, stride=(1, 1)):
     I, W1 = _np(I), _np(W1)
     Bias = _np(Bias) if Bias is not None else None
     N, G, C, H, W = I.shape
     _, F, _, KH, KW = W1.shape
     assert W1.shape == (G, F, C, KH, KW)
-    O = np.empty((N, G, F, H - KH + 1, W - KW + 1), np.float32)
-    lib().oracle_group_conv_f32(_p(I), _p(W1), _p(Bias), _p(O), _i64(N), _i64(G), _i64(C), _i64(F),
-                                _i64(H), _i64(W), _i64(KH), _i64(KW), int(double))
+    SH, SW = stride
+    O = np.empty((N, G, F, (H - KH) // SH + 1, (W - KW) // SW + 1), np.float32)
+    lib().oracle_group_conv_strided_f32(_p(I), _p(W1), _p(Bias), _p(O), _i64(N), _i64(G), _i64(C), _i64(F),
+                                        _i64(H), _i64(W), _i64(KH), _i64(KW), _i64(SH), _i64(SW), int(double))
     return O
 
 
@@ -127,13 +128,13 @@ def aten_tmm(A, B):
     return A.mm(B.t())
 
 
-def aten_group_conv(I, W1, Bias=None):
+def aten_group_conv(I, W1, Bias=None, stride=(1, 1)):
     import torch
     N, G, C, H, W = I.shape
     _, F, _, KH, KW = W1.shape
     out = torch.nn.functional.conv2d(I.reshape(N, G * C, H, W), W1.reshape(G * F, C, KH, KW),
-                                     Bias.reshape(G * F) if Bias is not None else None, groups=G)
-    return out.reshape(N, G, F, H - KH + 1, W - KW + 1)
+                                     Bias.reshape(G * F) if Bias is not None else None, stride=stride, groups=G)
+    return out.reshape(N, G, F, (H - KH) // stride[0] + 1, (W - KW) // stride[1] + 1)
 
 
 def aten_mlp3(I, W2, B2, W3, B3, W4, B4):

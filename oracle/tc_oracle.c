@@ -105,14 +105,17 @@ void oracle_tmm_f32(const float* A, const float* B, float* C,
     }
 }
 
-/* O(n,g,f,h,w) +=! I(n,g,r_c,h+r_kh,w+r_kw) * W1(g,f,r_c,r_kh,r_kw)
- * O(n,g,f,h,w)  = O(n,g,f,h,w) + B(g,f)        tc/benchmarks/group_convolution.cc:124-132
+/* O(n,g,f,h,w) +=! I(n,g,r_c,SH*h+r_kh,SW*w+r_kw) * W1(g,f,r_c,r_kh,r_kw)
+ * O(n,g,f,h,w)  = O(n,g,f,h,w) + B(g,f)        tc/benchmarks/group_convolution.cc:124-132;
+ * the strides are the literal factors of tc/library/convolution.h:27-31 and
+ * tc/library/group_convolution.h:26-44.  The extent of h is the largest for which every access
+ * stays in bounds: SH*h + (KH-1) <= H-1, i.e. (H-KH)/SH + 1 values (tc/core/tc2halide.cc:270-498).
  * Bias may be NULL (first statement only). */
-void oracle_group_conv_f32(const float* I, const float* W1, const float* Bias, float* O,
-                           int64_t N, int64_t G, int64_t C, int64_t F,
-                           int64_t H, int64_t W, int64_t KH, int64_t KW,
-                           int accumulate_double) {
-  const int64_t OH = H - KH + 1, OW = W - KW + 1;
+void oracle_group_conv_strided_f32(const float* I, const float* W1, const float* Bias, float* O,
+                                   int64_t N, int64_t G, int64_t C, int64_t F,
+                                   int64_t H, int64_t W, int64_t KH, int64_t KW,
+                                   int64_t SH, int64_t SW, int accumulate_double) {
+  const int64_t OH = (H - KH) / SH + 1, OW = (W - KW) / SW + 1;
 #pragma omp parallel for collapse(2) schedule(static)
   for (int64_t n = 0; n < N; ++n)
     for (int64_t g = 0; g < G; ++g)
@@ -124,7 +127,7 @@ void oracle_group_conv_f32(const float* I, const float* W1, const float* Bias, f
             for (int64_t c = 0; c < C; ++c)
               for (int64_t kh = 0; kh < KH; ++kh)
                 for (int64_t kw = 0; kw < KW; ++kw) {
-                  float a = I[(((n * G + g) * C + c) * H + (h + kh)) * W + (w + kw)];
+                  float a = I[(((n * G + g) * C + c) * H + (SH * h + kh)) * W + (SW * w + kw)];
                   float b = W1[(((g * F + f) * C + c) * KH + kh) * KW + kw];
                   if (accumulate_double) accd += (double)a * (double)b;
                   else accf = accf + a * b;
@@ -133,6 +136,14 @@ void oracle_group_conv_f32(const float* I, const float* W1, const float* Bias, f
             if (Bias) r = r + Bias[g * F + f];
             O[(((n * G + g) * F + f) * OH + h) * OW + w] = r;
           }
+}
+
+/* Unit strides: the benchmark's own form. */
+void oracle_group_conv_f32(const float* I, const float* W1, const float* Bias, float* O,
+                           int64_t N, int64_t G, int64_t C, int64_t F,
+                           int64_t H, int64_t W, int64_t KH, int64_t KW,
+                           int accumulate_double) {
+  oracle_group_conv_strided_f32(I, W1, Bias, O, N, G, C, F, H, W, KH, KW, 1, 1, accumulate_double);
 }
 
 /* O1(b,n) +=! I(b,m) * W1(n,m);  O1(b,n) = O1(b,n) + B1(n);  O1(b,n) = fmax(O1(b,n), 0)

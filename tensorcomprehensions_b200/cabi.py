@@ -33,7 +33,7 @@ class Problem(ctypes.Structure):
         ("batch", ctypes.c_int64), ("M", ctypes.c_int64), ("N", ctypes.c_int64), ("K", ctypes.c_int64),
         ("lda", ctypes.c_int64), ("ldb", ctypes.c_int64), ("ldc", ctypes.c_int64),
         ("stride_a", ctypes.c_int64), ("stride_b", ctypes.c_int64), ("stride_c", ctypes.c_int64),
-        ("conv", ctypes.c_int64 * 8), ("td", ctypes.c_int64 * 5),
+        ("conv", ctypes.c_int64 * 8), ("td", ctypes.c_int64 * 5), ("conv_stride", ctypes.c_int64 * 2),
     ]
 
 
@@ -120,11 +120,12 @@ def contraction_problem(batch, M, N, K, a_k_major=True, b_k_major=True, epilogue
     return p
 
 
-def group_conv_problem(N, G, C, F, H, W, KH, KW, epilogue=EPI_BIAS, accumulate=False):
+def group_conv_problem(N, G, C, F, H, W, KH, KW, epilogue=EPI_BIAS, accumulate=False, stride=(1, 1)):
     p = Problem()
     p.family = FAMILY_GROUP_CONV
     p.epilogue, p.accumulate = epilogue, int(accumulate)
     p.conv[:] = [N, G, C, F, H, W, KH, KW]
+    p.conv_stride[:] = list(stride)
     return p
 
 

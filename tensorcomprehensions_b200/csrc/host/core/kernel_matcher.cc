@@ -297,10 +297,12 @@ bool matchConv(const DefAnalysis& def, const StatementAnalysis& st, MatchedLaunc
     auto single = [&](const AffineIndex& a, const std::string& want) {
       return a.isSingleVar(&v) && v == want;
     };
-    auto sumOf = [&](const AffineIndex& a, const std::string& x, std::string* other) {
+    // stride * x + other (tc/library/convolution.h:27-31 writes the strides as literal factors)
+    auto sumOf = [&](const AffineIndex& a, const std::string& x, std::string* other, int64_t* stride) {
       if (!a.affine || a.constant != 0 || a.coeff.size() != 2) return false;
       auto it = a.coeff.find(x);
-      if (it == a.coeff.end() || it->second != 1) return false;
+      if (it == a.coeff.end() || it->second < 1 || it->second > (1 << 16)) return false;
+      *stride = it->second;
       for (const auto& kv : a.coeff)
         if (kv.first != x) {
           if (kv.second != 1) return false;
@@ -311,7 +313,8 @@ bool matchConv(const DefAnalysis& def, const StatementAnalysis& st, MatchedLaunc
     if (!single(I.indices[0], n)) continue;
     if (grouped && (!single(I.indices[1], st.lhsIndices[1]) || !single(W.indices[0], st.lhsIndices[1]))) continue;
     if (!I.indices[1 + g].isSingleVar(&c)) continue;
-    if (!sumOf(I.indices[2 + g], h, &kh) || !sumOf(I.indices[3 + g], w, &kw)) continue;
+    int64_t sh = 1, sw = 1;
+    if (!sumOf(I.indices[2 + g], h, &kh, &sh) || !sumOf(I.indices[3 + g], w, &kw, &sw)) continue;
     if (!single(W.indices[0 + g], f) || !single(W.indices[1 + g], c) || !single(W.indices[2 + g], kh) ||
         !single(W.indices[3 + g], kw))
       continue;
@@ -333,8 +336,11 @@ bool matchConv(const DefAnalysis& def, const StatementAnalysis& st, MatchedLaunc
     p.conv[6] = wsym->shape[2 + g];
     p.conv[7] = wsym->shape[3 + g];
     // output must be the full valid window
-    if (st.ranges.at(h).extent() != p.conv[4] - p.conv[6] + 1 ||
-        st.ranges.at(w).extent() != p.conv[5] - p.conv[7] + 1 || st.ranges.at(c).extent() != p.conv[2])
+    p.conv_stride[0] = sh;
+    p.conv_stride[1] = sw;
+    if (p.conv[4] < p.conv[6] || p.conv[5] < p.conv[7]) continue;
+    if (st.ranges.at(h).extent() != (p.conv[4] - p.conv[6]) / sh + 1 ||
+        st.ranges.at(w).extent() != (p.conv[5] - p.conv[7]) / sw + 1 || st.ranges.at(c).extent() != p.conv[2])
       continue;
     out->inputs = {valueIndex(def, I.tensor), valueIndex(def, W.tensor)};
     out->output = valueIndex(def, st.lhs);

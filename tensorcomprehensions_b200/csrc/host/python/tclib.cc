@@ -59,6 +59,7 @@ py::dict problemDict(const tc::MatchedLaunch& l) {
     d["td"] = std::vector<int64_t>(p.td, p.td + 5);
   } else {
     d["conv"] = std::vector<int64_t>(p.conv, p.conv + 8);
+    d["conv_stride"] = std::vector<int64_t>{p.conv_stride[0] > 0 ? p.conv_stride[0] : 1, p.conv_stride[1] > 0 ? p.conv_stride[1] : 1};
   }
   return d;
 }

@@ -200,6 +200,10 @@ int tcb200_plan_describe(const tcb200_plan_t* plan, char* buf, size_t buflen) {
                (long long)p.conv[0], (long long)p.conv[1], (long long)p.conv[2],
                (long long)p.conv[3], (long long)p.conv[4], (long long)p.conv[5],
                (long long)p.conv[6], (long long)p.conv[7], epilogue_name(p.epilogue));
+      if (conv_sh(p) != 1 || conv_sw(p) != 1) {
+        const size_t used = strlen(head);
+        snprintf(head + used, sizeof(head) - used, " stride=%lldx%lld", (long long)conv_sh(p), (long long)conv_sw(p));
+      }
       break;
     default:
       snprintf(head, sizeof(head),

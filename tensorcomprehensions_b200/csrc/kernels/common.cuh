@@ -30,6 +30,11 @@ struct Plan {
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline int64_t round_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
+// Convolution strides (0 in the problem reads as 1) and the extents of the valid output window.
+inline int64_t conv_sh(const tcb200_problem_t& p) { return p.conv_stride[0] > 0 ? p.conv_stride[0] : 1; }
+inline int64_t conv_sw(const tcb200_problem_t& p) { return p.conv_stride[1] > 0 ? p.conv_stride[1] : 1; }
+inline int64_t conv_oh(const tcb200_problem_t& p) { return (p.conv[4] - p.conv[6]) / conv_sh(p) + 1; }
+inline int64_t conv_ow(const tcb200_problem_t& p) { return (p.conv[5] - p.conv[7]) / conv_sw(p) + 1; }
 
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device): the call costs tens of
 // microseconds, more than the small kernels themselves.  `flags` is a per-kernel static bit set.

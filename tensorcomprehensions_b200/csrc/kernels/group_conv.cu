@@ -1,8 +1,9 @@
-// K3 — grouped 2-D valid convolution, unit stride, fused bias:
-//   O(n,g,f,h,w)  = sum_{c,kh,kw} I(n,g,c,h+kh,w+kw) * W1(g,f,c,kh,kw)
+// K3 — grouped 2-D valid convolution, fused bias:
+//   O(n,g,f,h,w)  = sum_{c,kh,kw} I(n,g,c,SH*h+kh,SW*w+kw) * W1(g,f,c,kh,kw)
 //   O(n,g,f,h,w) += B(g,f)
 // Replaces the kernel the reference generates for tc/benchmarks/group_convolution.cc:124-132
-// (library twin tc/library/group_convolution.h:26-44 with stride 1).
+// (library twins tc/library/group_convolution.h:26-44 and tc/library/convolution.h:26-31, whose
+// strides are template parameters; strides other than 1 run on the band kernel only).
 //
 // SIMT kernels (a tensor-core implicit-GEMM variant lives in group_conv_tcgen05.cu):
 //  * rows kernel (default when W <= 16 and F % 4 == 0): one CTA per (g, pair of n).  A thread owns
@@ -30,6 +31,7 @@ struct ConvArgs {
   float* O;
   int G, C, F, H, Wd, KH, KW, OH, OW;
   int band;     // output rows per CTA
+  int SH, SW;   // strides (band kernel; the other kernels take unit strides only)
   int epi, accumulate;
 };
 
@@ -40,7 +42,8 @@ __global__ void __launch_bounds__(256) group_conv_simt_kernel(ConvArgs a) {
   const int g = ng % a.G;
   const int h0 = blockIdx.y * a.band;
   const int rows = min(a.band, a.OH - h0);
-  const int in_rows = rows + a.KH - 1;
+  const int in_rows = (rows - 1) * a.SH + a.KH;
+  const int h0_in = h0 * a.SH;
   const int taps = a.C * a.KH * a.KW;
   const int Fp = (a.F + FT - 1) / FT * FT;
 
@@ -59,7 +62,7 @@ __global__ void __launch_bounds__(256) group_conv_simt_kernel(ConvArgs a) {
   const int row_elems = in_rows * a.Wd;
   for (int i = tid; i < a.C * row_elems; i += nt) {
     const int c = i / row_elems, r = i - c * row_elems;
-    Is[i] = __ldg(Ig + ((size_t)c * a.H + h0) * a.Wd + r);
+    Is[i] = __ldg(Ig + ((size_t)c * a.H + h0_in) * a.Wd + r);
   }
   __syncthreads();
 
@@ -75,7 +78,7 @@ __global__ void __launch_bounds__(256) group_conv_simt_kernel(ConvArgs a) {
     int t = 0;
     for (int c = 0; c < a.C; ++c)
       for (int kh = 0; kh < a.KH; ++kh) {
-        const float* irow = Is + ((size_t)c * in_rows + h + kh) * a.Wd + w;
+        const float* irow = Is + ((size_t)c * in_rows + h * a.SH + kh) * a.Wd + w * a.SW;
         for (int kw = 0; kw < a.KW; ++kw, ++t) {
           const float x = irow[kw];
           const float* wv = Ws + (size_t)t * Fp + fg * FT;
@@ -355,7 +358,10 @@ int item_two_threads(const tcb200_problem_t& p) {
   return (int)((p.conv[3] / 2) * ((p.conv[4] - p.conv[6] + 1 + 7) / 8 * 8));
 }
 
+bool unit_stride(const tcb200_problem_t& p) { return conv_sh(p) == 1 && conv_sw(p) == 1; }
+
 bool item_ok(const tcb200_problem_t& p) {
+  if (!unit_stride(p)) return false;
   const int64_t C = p.conv[2], F = p.conv[3], H = p.conv[4], W = p.conv[5], KH = p.conv[6], KW = p.conv[7];
   const int64_t OH = H - KH + 1, OW = W - KW + 1;
   return W == 16 && OW <= kItemOW && KW <= kItemKW && F % 4 == 0 && C % 4 == 0 &&
@@ -365,6 +371,7 @@ bool item_ok(const tcb200_problem_t& p) {
 }
 
 bool rows_ok(const tcb200_problem_t& p) {
+  if (!unit_stride(p)) return false;
   const int64_t C = p.conv[2], F = p.conv[3], H = p.conv[4], W = p.conv[5], KH = p.conv[6], KW = p.conv[7];
   const int64_t OH = H - KH + 1;
   return W <= kRowsMaxW && KW <= 4 && F % 4 == 0 && (F / 4) * OH <= 256 &&
@@ -386,6 +393,8 @@ int rows_n_per_cta(const tcb200_problem_t& p, int want, size_t* bytes) {
 bool valid(const tcb200_problem_t& p) {
   for (int i = 0; i < 8; ++i)
     if (p.conv[i] <= 0 || p.conv[i] > (1 << 24)) return false;
+  if (p.conv_stride[0] < 0 || p.conv_stride[1] < 0 || p.conv_stride[0] > (1 << 16) || p.conv_stride[1] > (1 << 16))
+    return false;
   return p.conv[4] >= p.conv[6] && p.conv[5] >= p.conv[7] &&
          p.conv[0] * p.conv[1] < (1ll << 31);
 }
@@ -396,11 +405,11 @@ constexpr size_t kSmemBudget = 96 * 1024;
 int pick_band(const tcb200_problem_t& p, int ft, size_t* bytes) {
   const int64_t C = p.conv[2], F = p.conv[3], H = p.conv[4], W = p.conv[5], KH = p.conv[6],
                 KW = p.conv[7];
-  const int64_t OH = H - KH + 1;
+  const int64_t OH = conv_oh(p), SH = conv_sh(p);
   const int64_t Fp = round_up(F, ft);
   const size_t wbytes = sizeof(float) * (size_t)(C * KH * KW * Fp);
   for (int64_t band = OH; band >= 1; band = (band == 1 ? 0 : (band + 1) / 2)) {
-    const size_t b = wbytes + sizeof(float) * (size_t)(C * (band + KH - 1) * W);
+    const size_t b = wbytes + sizeof(float) * (size_t)(C * ((band - 1) * SH + KH) * W);
     if (b <= kSmemBudget) {
       if (bytes) *bytes = b;
       return (int)band;
@@ -501,7 +510,7 @@ int group_conv_plan(Plan& plan) {
   size_t bytes = 0;
   const int band = pick_band(p, ft, &bytes);
   if (band == 0) return TCB200_ERR_TOO_LARGE;
-  const int64_t OH = p.conv[4] - p.conv[6] + 1;
+  const int64_t OH = conv_oh(p);
   if (ceil_div(OH, band) > 65535) return TCB200_ERR_TOO_LARGE;
   t.bm = band;
   t.bn = ft;
@@ -520,7 +529,8 @@ int group_conv_launch(const Plan& plan, const float* I, const float* W, const fl
   a.I = I; a.W = W; a.bias = bias; a.O = O;
   a.G = (int)p.conv[1]; a.C = (int)p.conv[2]; a.F = (int)p.conv[3];
   a.H = (int)p.conv[4]; a.Wd = (int)p.conv[5]; a.KH = (int)p.conv[6]; a.KW = (int)p.conv[7];
-  a.OH = a.H - a.KH + 1; a.OW = a.Wd - a.KW + 1;
+  a.SH = (int)conv_sh(p); a.SW = (int)conv_sw(p);
+  a.OH = (int)conv_oh(p); a.OW = (int)conv_ow(p);
   a.band = plan.tile.bm;
   a.epi = p.epilogue; a.accumulate = p.accumulate;
   if (plan.kernel_id == 101 || plan.kernel_id == 102) {

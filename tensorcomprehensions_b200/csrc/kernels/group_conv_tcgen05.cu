@@ -302,6 +302,7 @@ struct Geometry {
 };
 
 bool geometry(const tcb200_problem_t& p, Geometry* g) {
+  if (conv_sh(p) != 1 || conv_sw(p) != 1) return false;
   const int64_t C = p.conv[2], F = p.conv[3], H = p.conv[4], W = p.conv[5], KH = p.conv[6], KW = p.conv[7];
   const int64_t OH = H - KH + 1;
   if (!(C == 8 || C == 16)) return false;

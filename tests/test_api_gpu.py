@@ -91,6 +91,20 @@ def test_tune_sweeps_every_tile_the_family_lists(cuda, name):
     assert len(swept) >= 2
 
 
+def test_library_convolution_with_strides(cuda):
+    """makeConvolution2DTc(sh, sw) of tc/library/convolution.h:33-41 through compile / run."""
+    t = ("def convolution(float(N,C,H,W) I, float(M,C,KH,KW) W1, float(M) B) -> (O) {\n"
+         " O(n, m, h, w) +=! I(n, c, %d * h + kh, %d * w + kw) * W1(m, c, kh, kw)\n"
+         " O(n, m, h, w) = O(n, m, h, w) + B(m)\n}")
+    I, W1, B = torch.rand(4, 8, 33, 30, device=cuda), torch.rand(16, 8, 3, 3, device=cuda), torch.rand(16, device=cuda)
+    for sh, sw in ((1, 1), (2, 2), (2, 3)):
+        exe = tc.compile(t % (sh, sw), "convolution", "naive", I, W1, B)
+        out = exe(I, W1, B)
+        ref = torch.nn.functional.conv2d(I.cpu().double(), W1.cpu().double(), B.cpu().double(), stride=(sh, sw)).float()
+        assert list(out.shape) == list(ref.shape)
+        assert_close(out, ref, 72, what=exe.compiled_source)
+
+
 def test_accumulating_reduction_keeps_output(cuda):
     """'+=' without '!' adds to what the output holds (test/cuda/test_compile_and_run.cc:181-200)."""
     tcs = "def mm(float(M,K) A, float(K,N) B) -> (C) { C(m,n) += A(m,k) * B(k,n) }"

@@ -174,6 +174,29 @@ def test_group_conv_small(cuda, dims, bias):
         assert_close(out, ref, C * KH * KW, [I, W1], STRICT["group_conv"], plan.describe())
 
 
+@pytest.mark.parametrize("dims,stride", [
+    ((2, 3, 4, 8, 11, 11, 3, 3), (2, 2)),
+    ((2, 1, 3, 4, 10, 9, 3, 3), (3, 2)),     # ragged: the last rows / columns of the image are never read
+    ((1, 2, 16, 16, 16, 16, 3, 3), (2, 1)),  # item-kernel shape, but strided: band kernel only
+    ((1, 2, 8, 5, 40, 64, 5, 5), (2, 2)),    # several bands per image, F not a multiple of 4
+    ((3, 2, 4, 4, 7, 7, 7, 7), (4, 4)),      # filter as large as the image: one output pixel
+])
+def test_group_conv_strided(cuda, dims, stride):
+    """I(.., SH*h+kh, SW*w+kw): the strides of tc/library/convolution.h:27-31 against the loop nest and
+    against conv2d."""
+    N, G, C, F, H, W, KH, KW = dims
+    I, W1, B = _rand((N, G, C, H, W), 35, "uniform"), _rand((G, F, C, KH, KW), 36, "uniform"), _rand((G, F), 37)
+    ref = orc.loop_group_conv(I, W1, B, stride=stride)
+    p = cabi.group_conv_problem(*dims, stride=stride)
+    tiles = cabi.query(p)
+    assert all(t.variant == cabi.VARIANT_SIMT and t.bk == 0 for t in tiles)  # band kernel only
+    for tile in [None] + tiles:
+        out, plan = run_plan(p, [I.to(cuda), W1.to(cuda), B.to(cuda)], ref.shape, tile)
+        assert "stride=" in plan.describe()
+        assert_close(out, ref, C * KH * KW, [I, W1], STRICT["group_conv"], plan.describe())
+    assert_close(out, orc.aten_group_conv(I, W1, B, stride=stride), C * KH * KW, what="vs conv2d")
+
+
 @pytest.mark.parametrize("bias", [True, False])
 def test_group_conv_accumulate(cuda, bias):
     """`+=` without `!`: O = epilogue(O_in + conv) for every tile the family lists."""

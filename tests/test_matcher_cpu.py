@@ -71,11 +71,30 @@ def test_ungrouped_convolution_is_group_conv_with_one_group():
     assert m["family"] == "group_conv" and m["conv"] == [2, 1, 3, 4, 8, 9, 3, 2]
 
 
+def test_strided_convolution_of_the_library():
+    """tc/library/convolution.h:27-31 and group_convolution.h:26-44 substitute the strides as literal
+    factors; the output extent is the largest that keeps SH*h+kh inside the image."""
+    t = ("def convolution(float(N,C,H,W) I, float(M,C,KH,KW) W1, float(M) B) -> (O) {\n"
+         " O(n, m, h, w) +=! I(n, c, %d * h + kh, %d * w + kw) * W1(m, c, kh, kw)\n"
+         " O(n, m, h, w) = O(n, m, h, w) + B(m)\n}")
+    m = match(t % (1, 1), "convolution", [(2, 3, 10, 9), (4, 3, 3, 3), (4,)])[0]
+    assert m["conv"] == [2, 1, 3, 4, 10, 9, 3, 3] and m["conv_stride"] == [1, 1] and m["epilogue"] == 1
+    m = match(t % (3, 2), "convolution", [(2, 3, 10, 9), (4, 3, 3, 3), (4,)])[0]
+    assert m["conv"] == [2, 1, 3, 4, 10, 9, 3, 3] and m["conv_stride"] == [3, 2]
+    exe = tc.compile(t % (3, 2), "convolution", "naive", torch.empty(2, 3, 10, 9), torch.empty(4, 3, 3, 3), torch.empty(4))
+    assert exe.output_shapes() == [[2, 4, 3, 4]] and "stride=3x2" in exe.compiled_source
+    g = ("def gc(float(N,G,C,H,W) I, float(G,F,C,KH,KW) W1) -> (O) "
+         "{ O(n,g,f,h,w) +=! I(n,g,c,2*h+kh,2*w+kw) * W1(g,f,c,kh,kw) }")
+    m = match(g, "gc", [(2, 3, 4, 11, 11), (3, 8, 4, 3, 3)])[0]
+    assert m["conv"] == [2, 3, 4, 8, 11, 11, 3, 3] and m["conv_stride"] == [2, 2] and m["epilogue"] == 0
+
+
 @pytest.mark.parametrize("tcs,ins,fragment", [
     ("def f(float(N) A, float(N) B) -> (C) { C(i) = A(i) + B(i) }", [(4,), (4,)], "elementwise statement"),
     ("def f(float(N,M) A) -> (O) { O(i) +=! A(i,j) }", [(4, 5)], "not a product of two tensor accesses"),
     ("def f(float(N,M) A, float(M) B) -> (O) { O(i) max=! A(i,j) * B(j) }", [(4, 5), (5,)], "only sum reductions"),
-    ("def f(float(N,C,H,W) I, float(F,C,KH,KW) W1) -> (O) { O(n,f,h,w) +=! I(n,c,2*h+kh,2*w+kw) * W1(f,c,kh,kw) }",
+    # dilated filter taps: strides are covered (next test), dilation is not
+    ("def f(float(N,C,H,W) I, float(F,C,KH,KW) W1) -> (O) { O(n,f,h,w) +=! I(n,c,h+2*kh,w+2*kw) * W1(f,c,kh,kw) }",
      [(1, 1, 9, 9), (1, 1, 3, 3)], "not a plain index variable"),
     ("def f(float(M,K) A, float(N,K) B) -> (C) { C(m,n) +=! A(m,k) * B(n,k)\n C(m,n) = C(m,n) * 2 }", [(4, 6), (5, 6)], "epilogue"),
     ("def f(double(M,K) A, double(N,K) B) -> (C) { C(m,n) +=! A(m,k) * B(n,k) }", [(4, 6), (5, 6)], "float32"),
