@@ -102,14 +102,19 @@ int tcb200_query(const tcb200_problem_t* problem, tcb200_tile_t* out, int max, i
     case TCB200_FAMILY_GROUP_CONV:
       return group_conv_query(*problem, out, max, n);
     case TCB200_FAMILY_CONTRACTION: {
-      // tensor-core tiles first (when the contraction is large enough), then the SIMT ones.
-      int n_tc = 0, n_simt = 0;
-      int st = contraction_tc_query(*problem, out, max, &n_tc);
+      // The first candidate is the family default: the tensor-core tiles when the contraction is
+      // large enough to prefer them, else the SIMT ones.
+      int n_first = 0, n_second = 0;
+      const bool tc_first = contraction_tc_preferred(*problem);
+      auto list = [&](bool tc, tcb200_tile_t* o, int room, int* cnt) {
+        return tc ? contraction_tc_query(*problem, o, room, cnt) : contraction_simt_query(*problem, o, room, cnt);
+      };
+      int st = list(tc_first, out, max, &n_first);
       if (st != TCB200_OK) return st;
-      const int used = n_tc < max ? n_tc : max;
-      st = contraction_simt_query(*problem, out ? out + used : nullptr, max - used, &n_simt);
+      const int used = n_first < max ? n_first : max;
+      st = list(!tc_first, out ? out + used : nullptr, max - used, &n_second);
       if (st != TCB200_OK) return st;
-      *n = n_tc + n_simt;
+      *n = n_first + n_second;
       return TCB200_OK;
     }
     default:

@@ -74,6 +74,7 @@ int contraction_simt_launch(const Plan& plan, const float* A, const float* B, co
                             float* C, cudaStream_t s);
 
 int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n);
+bool contraction_tc_preferred(const tcb200_problem_t& p);  // tensor-core tiles ahead of the SIMT ones
 int contraction_tc_plan(Plan& plan);
 int contraction_tc_launch(const Plan& plan, const float* A, const float* B, const float* bias,
                           float* C, cudaStream_t s, int* dev_status);

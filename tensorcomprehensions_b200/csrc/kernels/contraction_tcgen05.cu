@@ -91,6 +91,12 @@ __host__ __device__ constexpr int num_threads() { return SPLIT == 3 ? 448 : 320;
 // drifts towards zero by up to half an ulp per MMA; draining every 256 K elements and summing the
 // chunks with round-to-nearest FADDs keeps the result at SIMT-fp32 accuracy.
 constexpr int kChunkKB = 8;  // k-blocks of 32
+// Own k-blocks per issuer between drains.  The error the truncation leaves is proportional to the
+// chunk length (all-positive U[0,1) operands, K = 2048: mean error -1.2e-3 of a sum of 511 with chunks
+// of 4, -2.3e-3 with 8); the single-CTA kernel hides drains of 4 behind its shared-memory traffic
+// (2 cost 10 %), the CTA-pair kernel loses 6 % at 4.
+constexpr int kTsChunkKB = 4;
+constexpr int kPairChunkKB = 8;
 
 template <int BN, int SPLIT>
 __global__ void __launch_bounds__(num_threads<SPLIT>(), 1)
@@ -390,7 +396,7 @@ __host__ __device__ constexpr int ts_smem_bytes(int bn) {
 // Two issuers in different warps that alternate k-blocks hide each other's waits (769 cycles per
 // 12 MMAs in the same microbenchmark).  Their MMAs reach the pipe in no fixed order, so each issuer
 // owns one TMEM accumulator: the additions inside an accumulator keep their order and the result is
-// the same bits on every run.  An accumulator is drained into fp32 registers every kChunkKB of its
+// the same bits on every run.  An accumulator is drained into fp32 registers every kTsChunkKB of its
 // issuer's k-blocks (the tensor core's own fp32 accumulation truncates); the second issuer's chunk
 // boundaries are shifted by half a chunk so that while one issuer waits for its drain the other
 // keeps the tensor pipe busy.
@@ -464,15 +470,15 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
 
   // Issuer i takes the k-blocks whose running number (counted over all tiles of this CTA) has
   // parity i.  Within a tile that starts at running number it0 these are kb = first + 2j,
-  // j = 0 .. count-1; own k-block j closes a chunk when (j + 1 + skew) % kChunkKB == 0 (skew 0 for
-  // issuer 0, kChunkKB / 2 for issuer 1) or when it is the issuer's last k-block of the tile.
+  // j = 0 .. count-1; own k-block j closes a chunk when (j + 1 + skew) % kTsChunkKB == 0 (skew 0 for
+  // issuer 0, kTsChunkKB / 2 for issuer 1) or when it is the issuer's last k-block of the tile.
   auto own_first = [](uint32_t it0, int i) { return (int)((it0 ^ (uint32_t)i) & 1u); };
   auto own_count = [&](uint32_t it0, int i) {
     const int f = own_first(it0, i);
     return num_kb > f ? (num_kb - f + 1) / 2 : 0;
   };
   auto closes_chunk = [](int j, int count, int i) {
-    return j == count - 1 || (j + 1 + (i ? kChunkKB / 2 : 0)) % kChunkKB == 0;
+    return j == count - 1 || (j + 1 + (i ? kTsChunkKB / 2 : 0)) % kTsChunkKB == 0;
   };
 
   // Static persistent schedule: tile t -> (batch, m-tile, n-tile) with n fastest, so the CTAs that
@@ -824,15 +830,15 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
 
   // Issuer i takes the k-blocks whose running number (counted over all tiles of this CTA) has
   // parity i.  Within a tile that starts at running number it0 these are kb = first + 2j,
-  // j = 0 .. count-1; own k-block j closes a chunk when (j + 1 + skew) % kChunkKB == 0 (skew 0 for
-  // issuer 0, kChunkKB / 2 for issuer 1) or when it is the issuer's last k-block of the tile.
+  // j = 0 .. count-1; own k-block j closes a chunk when (j + 1 + skew) % kPairChunkKB == 0 (skew 0 for
+  // issuer 0, kPairChunkKB / 2 for issuer 1) or when it is the issuer's last k-block of the tile.
   auto own_first = [](uint32_t it0, int i) { return (int)((it0 ^ (uint32_t)i) & 1u); };
   auto own_count = [&](uint32_t it0, int i) {
     const int f = own_first(it0, i);
     return num_kb > f ? (num_kb - f + 1) / 2 : 0;
   };
   auto closes_chunk = [](int j, int count, int i) {
-    return j == count - 1 || (j + 1 + (i ? kChunkKB / 2 : 0)) % kChunkKB == 0;
+    return j == count - 1 || (j + 1 + (i ? kPairChunkKB / 2 : 0)) % kPairChunkKB == 0;
   };
 
   // Static persistent schedule: tile t -> (batch, m-tile, n-tile) with n fastest, so the CTAs that
@@ -1184,7 +1190,7 @@ bool shape_ok(const tcb200_problem_t& p) {
 }
 
 // "Large enough to be a real dense contraction": at least four 32-wide k-blocks and one full tile
-// of rows; everything smaller is bandwidth/latency bound and stays on the SIMT kernels.
+// of rows; everything smaller is bandwidth/latency bound and is not offered the tensor-core tiles.
 bool worth_it(const tcb200_problem_t& p) { return p.K >= 128 && p.M >= 64 && p.N >= 64; }
 
 template <int BN, int SPLIT>
@@ -1236,6 +1242,14 @@ int launch_pair(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, 
 }
 
 }  // namespace
+
+// Below 2^24 multiply-adds the launch dominates either way and the family default is a SIMT kernel,
+// whose round-to-nearest fp32 FMAs also keep all-positive sums (the reference's U[0,1) test data)
+// within its 3e-7 * L bound, which the truncating tensor-core accumulation does not at small L; the
+// tensor-core tiles stay in the sweep.
+bool contraction_tc_preferred(const tcb200_problem_t& p) {
+  return shape_ok(p) && worth_it(p) && (double)p.batch * p.M * p.N * p.K >= (double)(1 << 24);
+}
 
 int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n) {
   *n = 0;

@@ -137,6 +137,26 @@ def test_tcgen05_ts_and_pair_corner_forms(cuda, kind):
     assert torch.isnan(Cd[:, N:]).all()  # the padding columns are not written
 
 
+@pytest.mark.parametrize("kind,limit", [("ts", 3.2e-6), ("pair", 6.4e-6)])
+def test_tcgen05_all_positive_operands(cuda, kind, limit):
+    """The tensor core truncates when it adds into its fp32 accumulator, so with all-positive operands
+    (the reference's own U[0,1) benchmark data) the error has a sign.  Draining the accumulators into
+    round-to-nearest adds every 4 (single CTA) / 8 (CTA pair) k-blocks bounds it: relative error of a
+    K = 2048 sum below 3.2e-6 / 6.4e-6 (measured 2.7e-6 / 5.2e-6), i.e. inside the 1e-6 * (K + 1) * max|in|
+    bound of the reference's MLP1 / C3 checks (tc/benchmarks/MLP_model.cc:413-417,469-473) for the
+    single-CTA kernel."""
+    M, N, K = 256, 256, 2048
+    g = torch.Generator().manual_seed(61)
+    A, B = torch.rand((M, K), generator=g), torch.rand((N, K), generator=g)
+    ref = A.double() @ B.double().t()
+    p = cabi.contraction_problem(1, M, N, K, True, True)
+    out, plan = run_plan(p, [A.to(cuda), B.to(cuda)], (M, N), tc_tile(128, 3, ts=kind == "ts", pair=kind == "pair"))
+    err = (out.cpu().double() - ref).abs().max().item()
+    assert err / ref.max().item() < limit, (err, plan.describe())
+    if kind == "ts":
+        assert err < 1e-6 * (K + 1) * 1.0
+
+
 def test_tcgen05_rejects_what_it_cannot_take(cuda):
     # K not a multiple of 4 breaks the 16-byte row pitch TMA needs: the plan is refused
     p = cabi.contraction_problem(1, 128, 128, 130, True, True)
