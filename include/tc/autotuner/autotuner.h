@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "tc/autotuner/genetic_search.h"
+#include "tc/autotuner/options_cache.h"
 #include "tc/core/cuda/cuda_backend.h"
 #include "tc/core/tensor.h"
 #include "tc/core/utils/time.h"
@@ -43,37 +44,6 @@ class TuningParameterFixer {
 
   int unroll = -1, split3 = -1;
   std::vector<uint32_t> tiling, blockDims, gridDims;
-};
-
-// Tuned options memoised per (canonical TC, input/output metadata, device name), best first by
-// median runtime (the reference's OptionsCache, tc/autotuner/options_cache.h:86-188, without the
-// protobuf file format: store/load use a line-oriented text file).
-template <typename Backend>
-class OptionsCache {
- public:
-  using MappingOptionsType = typename Backend::MappingOptionsType;
-  void recordRuntime(const lang::CanonicalTcString& tc, const std::vector<TensorInfo>& inputs,
-                     const std::vector<TensorInfo>& outputs, const std::string& deviceStr,
-                     const MappingOptionsType& options, Duration runtime);
-  std::vector<MappingOptionsType> getTopKOptions(const lang::CanonicalTcString& tc,
-                                                 const std::vector<TensorInfo>& inputs,
-                                                 const std::vector<TensorInfo>& outputs,
-                                                 const std::string& deviceStr, size_t k) const;
-  size_t size() const;
-  void clear();
-  // Appends to / reads from a text file; returns the number of entries written / read.
-  size_t storeToFile(const std::string& filename) const;
-  size_t loadFromFile(const std::string& filename);
-
- private:
-  struct Entry {
-    std::string serializedOptions;
-    std::vector<size_t> runtimesUs;
-  };
-  static std::string makeKey(const lang::CanonicalTcString& tc, const std::vector<TensorInfo>& inputs,
-                             const std::vector<TensorInfo>& outputs, const std::string& deviceStr);
-  mutable std::mutex mu_;
-  std::unordered_map<std::string, std::vector<Entry>> entries_;
 };
 
 struct TunedCandidate {

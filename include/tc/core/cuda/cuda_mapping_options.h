@@ -50,13 +50,16 @@ class CudaMappingOptions {
  public:
   CudaMappingOptions(const CudaMappingOptions&) = default;
   CudaMappingOptions& operator=(const CudaMappingOptions&) = default;
-  // Round-trips toSerializedString().
+  // From toProtobufSerializedString() (a serialized CudaMappingOptionsProto, as in the reference:
+  // tc/core/cuda/cuda_mapping_options.cc) or from this library's text form toSerializedString().
   explicit CudaMappingOptions(const std::string& serialized);
   bool operator==(const CudaMappingOptions& o) const;
   bool operator!=(const CudaMappingOptions& o) const { return !(*this == o); }
   std::string toSerializedString() const;
-  // Kept under the reference's name; the bytes are this library's own text form, not protobuf.
-  std::string toProtobufSerializedString() const { return toSerializedString(); }
+  // The wire bytes of CudaMappingOptionsProto (tc/proto/mapping_options.proto:71-91): readable by the
+  // reference's generated classes and the other way round.
+  std::string toProtobufSerializedString() const;
+  static CudaMappingOptions fromProtobufSerializedString(const std::string& bytes);
 
   CudaMappingOptions& mapToThreads(std::initializer_list<uint64_t> t) { block = CudaDim(t); return *this; }
   CudaMappingOptions& mapToThreads(uint64_t x, uint64_t y = CudaDim::defaultDim, uint64_t z = CudaDim::defaultDim) { block = CudaDim(x, y, z); return *this; }

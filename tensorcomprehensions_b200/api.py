@@ -167,31 +167,25 @@ class TunerConfig(object):
 
 
 class MappingOptionsCache(object):
-    """Line-oriented text cache of tuned options keyed by (entry point, input sizes)
-    (the role of the reference's MappingOptionsCache, tensor_comprehensions/__init__.py:186-218)."""
+    """Tuned options on disk, keyed by (canonical TC, input and output sizes, backend): the reference's
+    MappingOptionsCache (tensor_comprehensions/__init__.py:186-218, pybinds/tclib.cc:395-420).  The file is
+    a serialized CudaOptionsCacheProto (tc/proto/compcache.proto), readable by the reference and the other
+    way round."""
 
     def __init__(self, filename: str):
         self.filename = filename
 
-    @staticmethod
-    def _key(entry_point, inputs):
-        return entry_point + "|" + ";".join(",".join(str(s) for s in t.shape) for t in inputs)
-
     def load(self, tc: str, entry_point: str, inputs, count: int = 1) -> List[MappingOptions]:
-        found = []
-        try:
-            with open(self.filename) as f:
-                for line in f:
-                    parts = line.rstrip("\n").split("\t")
-                    if len(parts) == 2 and parts[0] == self._key(entry_point, inputs):
-                        found.append(MappingOptions(parts[1]))
-        except FileNotFoundError:
-            pass
-        return found[-count:][::-1]
+        """Up to `count` options recorded for these sizes, fastest median runtime first."""
+        return tclib.cache_load(self.filename, tc, entry_point, list(inputs), count)
 
-    def store(self, entry_point: str, inputs, options: MappingOptions):
-        with open(self.filename, "a") as f:
-            f.write(self._key(entry_point, inputs) + "\t" + options.serialize() + "\n")
+    def store(self, tc: str, entry_point: str, inputs, options: MappingOptions, runtime_us: int = 0):
+        """Merges one (options, runtime) record into the file (the reference only stores through its
+        Tuner; this is the same merge for options that were obtained elsewhere)."""
+        tclib.cache_store(self.filename, tc, entry_point, list(inputs), options, int(runtime_us))
+
+    def __len__(self):
+        return tclib.cache_size(self.filename)
 
 
 def autotune(tc: str, entry_point: str, *inputs, starting_options=None, tuner_config: TunerConfig = None,
@@ -207,11 +201,11 @@ def autotune(tc: str, entry_point: str, *inputs, starting_options=None, tuner_co
     base = _as_options(starting_options)
     if tuner_config is not None:
         tclib.set_flag("tuner_profile_iterations", str(tuner_config.profile_iterations))
-    best = tclib.tune(tc, entry_point, inputs, base, 1)
-    result = best[0] if best else base
     if cache_filename is not None and store_to_cache:
-        MappingOptionsCache(cache_filename).store(entry_point, inputs, result)
-    return result
+        best = tclib.tune_to_cache(tc, entry_point, inputs, base, 1, cache_filename)
+    else:
+        best = tclib.tune(tc, entry_point, inputs, base, 1)
+    return best[0] if best else base
 
 
 def autotune_and_compile(tc: str, entry_point: str, *inputs, starting_options=None, tuner_config=None,

@@ -11,6 +11,7 @@
 #include "tc/core/flags.h"
 #include "tc/core/mapping_options.h"
 #include "tc/core/tensor.h"
+#include "tc/proto/wire.h"
 
 namespace tc {
 
@@ -396,7 +397,125 @@ std::string CudaMappingOptions::toSerializedString() const {
      << ";pdepth=" << privateDepthValue << ";sdepth=" << sharedDepthValue;
   return ss.str();
 }
+// ---- CudaMappingOptionsProto on the wire (field numbers: tc/proto/mapping_options.proto:19-91) ----
+namespace {
+// FusionStrategy in the proto: Max = 1, Preserve3Coincident = 2, Min = 3
+uint64_t fusionToProto(FusionStrategy f) {
+  return f == FusionStrategy::Max ? 1 : f == FusionStrategy::Preserve3Coincident ? 2 : 3;
+}
+FusionStrategy fusionFromProto(uint64_t v) {
+  TC_CHECK(v >= 1 && v <= 3) << "mapping options: unknown fusion strategy " << v;
+  return v == 1 ? FusionStrategy::Max : v == 2 ? FusionStrategy::Preserve3Coincident : FusionStrategy::Min;
+}
+proto::Writer schedulerToProto(const SchedulerOptions& o) {
+  proto::Writer w;
+  w.varint(1, fusionToProto(o.fusionStrategy));
+  w.boolean(2, o.allowSkewing);
+  w.boolean(3, o.positiveOrthant);
+  return w;
+}
+void schedulerFromProto(proto::Reader r, SchedulerOptions* o) {
+  while (r.next()) {
+    if (r.field() == 1 && r.isVarint()) o->fusionStrategy = fusionFromProto(r.value());
+    else if (r.field() == 2 && r.isVarint()) o->allowSkewing = r.value() != 0;
+    else if (r.field() == 3 && r.isVarint()) o->positiveOrthant = r.value() != 0;
+  }
+  TC_CHECK(r.ok()) << "mapping options: malformed scheduler options";
+}
+// y and z are optional in the proto (absent = not mapped); here an unmapped dimension has extent 1
+proto::Writer dimToProto(const CudaDim& d) {
+  proto::Writer w;
+  w.varint(1, d.x);
+  if (d.y != CudaDim::defaultDim || d.z != CudaDim::defaultDim) w.varint(2, d.y);
+  if (d.z != CudaDim::defaultDim) w.varint(3, d.z);
+  return w;
+}
+void dimFromProto(proto::Reader r, CudaDim* d) {
+  *d = CudaDim(CudaDim::defaultDim);
+  while (r.next()) {
+    if (!r.isVarint()) continue;
+    if (r.field() == 1) d->x = r.value();
+    else if (r.field() == 2) d->y = r.value();
+    else if (r.field() == 3) d->z = r.value();
+  }
+  TC_CHECK(r.ok()) << "mapping options: malformed block / grid";
+}
+}  // namespace
+
+std::string CudaMappingOptions::toProtobufSerializedString() const {
+  proto::Writer g;  // MappingOptionsProto
+  g.message(1, schedulerToProto(generic.outerScheduleOptions));
+  g.message(2, schedulerToProto(generic.intraTileScheduleOptions));
+  g.boolean(3, generic.fixParametersBeforeSchedulingFlag);
+  if (!generic.tiling.empty()) {
+    proto::Writer t;
+    for (uint64_t s : generic.tiling) t.varint(1, s);
+    g.message(4, t);
+  }
+  if (generic.hasUnroll) g.varint(5, generic.unrollFactor);
+  g.boolean(6, generic.tileImperfectlyNestedFlag);
+  g.boolean(7, generic.matchLibraryCallsFlag);
+  proto::Writer w;  // CudaMappingOptionsProto
+  w.message(1, g);
+  w.message(2, dimToProto(block));
+  w.message(3, dimToProto(grid));
+  w.boolean(4, useSharedMemoryFlag);
+  w.boolean(5, usePrivateMemoryFlag);
+  w.boolean(6, unrollCopySharedFlag);
+  if (hasMaxSharedMemory) w.varint(7, maxSharedMemoryBytes);
+  w.boolean(8, useReadOnlyCacheFlag);
+  w.varint(9, privateDepthValue);
+  w.varint(10, sharedDepthValue);
+  return w.str();
+}
+
+CudaMappingOptions CudaMappingOptions::fromProtobufSerializedString(const std::string& bytes) {
+  CudaMappingOptions o = makeUnmappedMappingOptions();
+  o.generic.tiling.clear();
+  o.generic.hasUnroll = false;
+  o.hasMaxSharedMemory = false;
+  bool sawGeneric = false, sawBlock = false, sawGrid = false;
+  proto::Reader r(bytes);
+  while (r.next()) {
+    const uint32_t f = r.field();
+    if (f == 1 && r.isBytes()) {
+      sawGeneric = true;
+      proto::Reader g = r.sub();
+      while (g.next()) {
+        const uint32_t gf = g.field();
+        if (gf == 1 && g.isBytes()) schedulerFromProto(g.sub(), &o.generic.outerScheduleOptions);
+        else if (gf == 2 && g.isBytes()) schedulerFromProto(g.sub(), &o.generic.intraTileScheduleOptions);
+        else if (gf == 3 && g.isVarint()) o.generic.fixParametersBeforeSchedulingFlag = g.value() != 0;
+        else if (gf == 4 && g.isBytes()) {
+          proto::Reader t = g.sub();
+          while (t.next())
+            if (t.field() == 1) t.appendTo(&o.generic.tiling);
+          TC_CHECK(t.ok()) << "mapping options: malformed tiling";
+        } else if (gf == 5 && g.isVarint()) { o.generic.hasUnroll = true; o.generic.unrollFactor = g.value(); }
+        else if (gf == 6 && g.isVarint()) o.generic.tileImperfectlyNestedFlag = g.value() != 0;
+        else if (gf == 7 && g.isVarint()) o.generic.matchLibraryCallsFlag = g.value() != 0;
+      }
+      TC_CHECK(g.ok()) << "mapping options: malformed generic options";
+    } else if (f == 2 && r.isBytes()) { sawBlock = true; dimFromProto(r.sub(), &o.block); }
+    else if (f == 3 && r.isBytes()) { sawGrid = true; dimFromProto(r.sub(), &o.grid); }
+    else if (f == 4 && r.isVarint()) o.useSharedMemoryFlag = r.value() != 0;
+    else if (f == 5 && r.isVarint()) o.usePrivateMemoryFlag = r.value() != 0;
+    else if (f == 6 && r.isVarint()) o.unrollCopySharedFlag = r.value() != 0;
+    else if (f == 7 && r.isVarint()) { o.hasMaxSharedMemory = true; o.maxSharedMemoryBytes = r.value(); }
+    else if (f == 8 && r.isVarint()) o.useReadOnlyCacheFlag = r.value() != 0;
+    else if (f == 9 && r.isVarint()) o.privateDepthValue = (uint32_t)r.value();
+    else if (f == 10 && r.isVarint()) o.sharedDepthValue = (uint32_t)r.value();
+  }
+  TC_CHECK(r.ok() && sawGeneric && sawBlock && sawGrid)
+      << "not a serialized CudaMappingOptionsProto (required fields missing or bytes malformed)";
+  return o;
+}
+
 CudaMappingOptions::CudaMappingOptions(const std::string& serialized) {
+  if (serialized.compare(0, 5, "tile=") != 0) {  // not the text form: protobuf bytes
+    *this = fromProtobufSerializedString(serialized);
+    return;
+  }
   *this = makeUnmappedMappingOptions();
   std::stringstream ss(serialized);
   std::string kv;

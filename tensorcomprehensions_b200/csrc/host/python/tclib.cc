@@ -95,7 +95,10 @@ PYBIND11_MODULE(tclib, m) {
            py::arg("preset") = "naive")
       .def("__str__", [](const CudaMappingOptions& o) { std::stringstream ss; ss << o; return ss.str(); })
       .def("__eq__", [](const CudaMappingOptions& a, const CudaMappingOptions& b) { return a == b; })
-      .def("serialize", &CudaMappingOptions::toSerializedString)
+      // the bytes of a CudaMappingOptionsProto, as the reference's serialize() (tclib.cc:655-659);
+      // the constructor takes them back (and this library's text form)
+      .def("serialize", [](const CudaMappingOptions& o) { return py::bytes(o.toProtobufSerializedString()); })
+      .def("serialize_text", &CudaMappingOptions::toSerializedString)
       .def("tile", [](CudaMappingOptions& o, const std::vector<uint64_t>& s) -> CudaMappingOptions& { return o.tile(s); }, py::return_value_policy::reference_internal)
       .def("unroll", [](CudaMappingOptions& o, uint64_t u) -> CudaMappingOptions& { return o.unroll(u); }, py::return_value_policy::reference_internal)
       .def("mapToThreads", [](CudaMappingOptions& o, const std::vector<uint64_t>& s) -> CudaMappingOptions& { return o.mapToThreads(s); }, py::return_value_policy::reference_internal)
@@ -201,6 +204,48 @@ PYBIND11_MODULE(tclib, m) {
           return tuner.tune(entry, inputs, {base}, topK);
         },
         py::arg("tc"), py::arg("entry_point"), py::arg("inputs"), py::arg("base_options"), py::arg("top_k") = 1);
+
+  // ---- options cache files (serialized CudaOptionsCacheProto, interchangeable with the reference's) ----
+  // tensor_comprehensions/pybinds/tclib.cc:395-420: the k best options recorded for (tc, entry, sizes)
+  m.def("cache_load",
+        [](const std::string& filename, const std::string& tc, const std::string& entry,
+           const std::vector<at::Tensor>& inputs, size_t count) {
+          auto in = tc::aten::makeDLConstTensors(inputs);
+          return tc::autotune::loadTopKFromCacheFile<CudaBackend>(tc, entry, filename, tc::extractRawPtrs(in), count);
+        },
+        py::arg("filename"), py::arg("tc"), py::arg("entry_point"), py::arg("inputs"), py::arg("count") = 1);
+  // merges one (options, runtime) record into the file, keeping what it holds
+  m.def("cache_store",
+        [](const std::string& filename, const std::string& tc, const std::string& entry,
+           const std::vector<at::Tensor>& inputs, const CudaMappingOptions& options, size_t runtimeUs) {
+          auto in = tc::aten::makeDLConstTensors(inputs);
+          auto raw = tc::extractRawPtrs(in);
+          tc::autotune::OptionsCache<CudaBackend> cache;
+          cache.loadCacheFromFile(filename);
+          cache.recordRuntime(lang::canonicalTc(tc::detail::parse(tc).at(entry)), tc::makeTensorInfoVector(raw),
+                              tc::inferOutputTensorInfo(tc, entry, raw), CudaBackend::backendString(), options,
+                              tc::Duration::fromMicroSeconds(runtimeUs));
+          cache.storeCacheToFile(filename);
+        },
+        py::arg("filename"), py::arg("tc"), py::arg("entry_point"), py::arg("inputs"), py::arg("options"),
+        py::arg("runtime_us") = 0);
+  m.def("cache_size", [](const std::string& filename) {
+    tc::autotune::OptionsCache<CudaBackend> cache;
+    cache.loadCacheFromFile(filename);
+    return cache.size();
+  });
+  // tune and merge the best `top_k` of the sweep into `cache_filename` (the reference's Tuner with a
+  // cache file: tclib.cc:570-580, options_cache-inl.h:353-367)
+  m.def("tune_to_cache",
+        [](const std::string& tc, const std::string& entry, const std::vector<at::Tensor>& inputs,
+           const CudaMappingOptions& base, size_t topK, const std::string& cacheFilename) {
+          tc::aten::ATenAutotuner<CudaBackend, tc::autotune::GeneticSearch> tuner(tc);
+          auto best = tuner.tune(entry, inputs, {base}, topK);
+          tc::autotune::appendTopKToCacheFile(*tuner.optionsCache, cacheFilename, (uint32_t)topK);
+          return best;
+        },
+        py::arg("tc"), py::arg("entry_point"), py::arg("inputs"), py::arg("base_options"), py::arg("top_k"),
+        py::arg("cache_filename"));
 
   m.def("tune_report",
         [](const std::string& tc, const std::string& entry, const std::vector<at::Tensor>& inputs) {

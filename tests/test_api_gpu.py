@@ -105,6 +105,23 @@ def test_library_convolution_with_strides(cuda):
         assert_close(out, ref, 72, what=exe.compiled_source)
 
 
+def test_autotune_stores_to_and_loads_from_a_cache_file(cuda, tmp_path):
+    """python/tests/test_tc.py:485-506 of the reference: tune with a cache file, then compile from it."""
+    w = wl.batchmatmul()
+    X, Y = [t.to(cuda) for t in wl.make_inputs(w)]
+    path = str(tmp_path / "bmm.cuda.options")
+    best = tc.autotune(w.tc, w.entry, X, Y, starting_options="naive", cache_filename=path, store_to_cache=True)
+    assert tc.MappingOptionsCache(path).load(w.tc, w.entry, [X, Y]) == [best]
+    assert tc.autotune(w.tc, w.entry, X, Y, cache_filename=path, load_from_cache=True) == best
+    T = tc.define(w.tc, tc.make_load_from_cache_options_factory(path))
+    assert_close(getattr(T, w.entry)(X, Y), orc.loop_batchmatmul(X.cpu(), Y.cpu()), 72)
+    # a second tuning run on other sizes merges into the same file
+    X2, Y2 = X[:100].contiguous(), Y[:100].contiguous()
+    tc.Tuner(w.tc, path).tune(w.entry, [X2, Y2], tc.MappingOptions("naive"))
+    cache = tc.MappingOptionsCache(path)
+    assert len(cache) == 2 and cache.load(w.tc, w.entry, [X, Y]) == [best] and len(cache.load(w.tc, w.entry, [X2, Y2])) == 1
+
+
 def test_accumulating_reduction_keeps_output(cuda):
     """'+=' without '!' adds to what the output holds (test/cuda/test_compile_and_run.cc:181-200)."""
     tcs = "def mm(float(M,K) A, float(K,N) B) -> (C) { C(m,n) += A(m,k) * B(k,n) }"

@@ -150,12 +150,22 @@ def test_mapping_options_roundtrip_and_tile_encoding():
 
 
 def test_options_cache_file(tmp_path):
-    cache = tc.MappingOptionsCache(str(tmp_path / "opts.txt"))
+    cache = tc.MappingOptionsCache(str(tmp_path / "opts.cuda.options"))
     ins = [torch.empty(4, 6), torch.empty(5, 6)]
     o = tc.MappingOptions.from_tile(1, 64, 64, 16, 0, 256, 0)
-    assert cache.load(wl.TMM_TC, "tmm", ins) == []
-    cache.store("tmm", ins, o)
-    assert cache.load(wl.TMM_TC, "tmm", ins) == [o]
+    slow = tc.MappingOptions.from_tile(1, 32, 32, 16, 0, 128, 0)
+    assert cache.load(wl.TMM_TC, "tmm", ins) == [] and len(cache) == 0
+    cache.store(wl.TMM_TC, "tmm", ins, slow, runtime_us=90)
+    cache.store(wl.TMM_TC, "tmm", ins, o, runtime_us=30)
+    cache.store(wl.TMM_TC, "tmm", ins, o, runtime_us=50)     # a second runtime of the same options
+    assert len(cache) == 2
+    assert cache.load(wl.TMM_TC, "tmm", ins) == [o]          # fastest median first
+    assert cache.load(wl.TMM_TC, "tmm", ins, 5) == [o, slow]
     assert cache.load(wl.TMM_TC, "tmm", [torch.empty(4, 7), torch.empty(5, 7)]) == []
-    fac = tc.make_load_from_cache_options_factory(str(tmp_path / "opts.txt"))
+    # the key is the canonical TC: renaming the indices finds the entry, another comprehension does not
+    renamed = wl.TMM_TC.replace("r_k", "q")
+    assert renamed != wl.TMM_TC and cache.load(renamed, "tmm", ins) == [o]
+    other = "def tmm(float(M,K) A, float(N,K) B) -> (C) { C(m,n) +=! A(m,k) * B(n,k) * 2 }"
+    assert cache.load(other, "tmm", ins) == []
+    fac = tc.make_load_from_cache_options_factory(str(tmp_path / "opts.cuda.options"))
     assert fac(wl.TMM_TC, "tmm", *ins) == o
