@@ -32,7 +32,9 @@ typedef struct CUstream_st* tcb200_stream_t;
 enum {
   TCB200_FAMILY_CONTRACTION = 1, /* C(b,m,n) (+)= sum_k A(b,m,k) * B(b,n,k)  [+bias] [relu] */
   TCB200_FAMILY_TENSORDOT = 2,   /* O(n,c1,c3,p) = sum_c2 I0(n,c1,c2,p) * I1(n,c2,c3,p), tiny C2,C3 */
-  TCB200_FAMILY_GROUP_CONV = 3   /* O(n,g,f,h,w) = sum_{c,kh,kw} I(n,g,c,h+kh,w+kw) * W(g,f,c,kh,kw) [+B(g,f)] */
+  TCB200_FAMILY_GROUP_CONV = 3,  /* O(n,g,f,h,w) = sum_{c,kh,kw} I(n,g,c,h+kh,w+kw) * W(g,f,c,kh,kw) [+B(g,f)] */
+  TCB200_FAMILY_REDUCTION = 4    /* O(a,b) (+)= sum_c I(a,c,b): one input, sum over a contiguous group of its indices
+                                    (sum1D / sum2D of test/test_tc_mapper_harness-inl.h:60-146) */
 };
 
 /* Elementwise statements fused after the reduction (how the reference's TCs
@@ -82,6 +84,7 @@ typedef struct tcb200_problem {
   int64_t td[5];                        /* tensordot: N, C1, C2, C3, P (P = product of trailing shared dims) */
   int64_t conv_stride[2];               /* group conv: SH, SW of I(.., SH*h+kh, SW*w+kw) (tc/library/convolution.h:27-31);
                                            0 reads as 1.  Output extent: (H - KH) / SH + 1 by (W - KW) / SW + 1 */
+  int64_t red[3];                       /* reduction: A, C, B of the [A][C][B] view of the input (C is summed) */
 } tcb200_problem_t;
 
 /* One point of a family's tile sweep.  Fields a variant does not use are 0. */

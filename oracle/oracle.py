@@ -94,6 +94,15 @@ def loop_group_conv(I, W1, Bias=None, double=False, stride=(1, 1)):
     return O
 
 
+def loop_reduce(I, double=False):
+    """Sum over the middle axis of a 3-D [A, C, B] array (the family's canonical view)."""
+    I = _np(I)
+    A, C, B = I.shape
+    O = np.empty((A, B), np.float32)
+    lib().oracle_reduce_f32(_p(I), _p(O), _i64(A), _i64(C), _i64(B), int(double))
+    return O
+
+
 def loop_fcrelu(I, W1, Bias=None, relu=True, double=False):
     I, W1 = _np(I), _np(W1)
     Bias = _np(Bias) if Bias is not None else None

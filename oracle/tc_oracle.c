@@ -138,6 +138,25 @@ void oracle_group_conv_strided_f32(const float* I, const float* W1, const float*
           }
 }
 
+/* O(a,b) +=! I(a,r_c,b): a sum over a contiguous group of the input's indices, the [A][C][B] view of
+ * C +=! A(r_m) and C(m) +=! A(m,r_n) (test/test_tc_mapper_harness-inl.h:60-146).  The reduction loop is
+ * innermost and runs in index order (tc/core/tc2halide.cc:729-754), starting from the identity 0
+ * (tc/core/tc2halide.cc:573-601). */
+void oracle_reduce_f32(const float* I, float* O, int64_t A, int64_t C, int64_t B, int accumulate_double) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t a = 0; a < A; ++a)
+    for (int64_t b = 0; b < B; ++b) {
+      double accd = 0.0;
+      float accf = 0.0f;
+      for (int64_t c = 0; c < C; ++c) {
+        float v = I[(a * C + c) * B + b];
+        if (accumulate_double) accd += (double)v;
+        else accf = accf + v;
+      }
+      O[a * B + b] = accumulate_double ? (float)accd : accf;
+    }
+}
+
 /* Unit strides: the benchmark's own form. */
 void oracle_group_conv_f32(const float* I, const float* W1, const float* Bias, float* O,
                            int64_t N, int64_t G, int64_t C, int64_t F,

@@ -11,7 +11,7 @@ import os
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libtcb200.so")
 
-FAMILY_CONTRACTION, FAMILY_TENSORDOT, FAMILY_GROUP_CONV = 1, 2, 3
+FAMILY_CONTRACTION, FAMILY_TENSORDOT, FAMILY_GROUP_CONV, FAMILY_REDUCTION = 1, 2, 3, 4
 EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_RELU = 0, 1, 2, 3
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_SIMT_SMALL, VARIANT_TCGEN05, VARIANT_TCGEN05_TS, VARIANT_TCGEN05_PAIR = 0, 1, 2, 3, 4, 5
 OK = 0
@@ -33,7 +33,7 @@ class Problem(ctypes.Structure):
         ("batch", ctypes.c_int64), ("M", ctypes.c_int64), ("N", ctypes.c_int64), ("K", ctypes.c_int64),
         ("lda", ctypes.c_int64), ("ldb", ctypes.c_int64), ("ldc", ctypes.c_int64),
         ("stride_a", ctypes.c_int64), ("stride_b", ctypes.c_int64), ("stride_c", ctypes.c_int64),
-        ("conv", ctypes.c_int64 * 8), ("td", ctypes.c_int64 * 5), ("conv_stride", ctypes.c_int64 * 2),
+        ("conv", ctypes.c_int64 * 8), ("td", ctypes.c_int64 * 5), ("conv_stride", ctypes.c_int64 * 2), ("red", ctypes.c_int64 * 3),
     ]
 
 
@@ -126,6 +126,15 @@ def group_conv_problem(N, G, C, F, H, W, KH, KW, epilogue=EPI_BIAS, accumulate=F
     p.epilogue, p.accumulate = epilogue, int(accumulate)
     p.conv[:] = [N, G, C, F, H, W, KH, KW]
     p.conv_stride[:] = list(stride)
+    return p
+
+
+def reduction_problem(A, C, B, accumulate=False):
+    """O(a, b) (+)= sum_c I(a, c, b) over the [A][C][B] view of one input."""
+    p = Problem()
+    p.family = FAMILY_REDUCTION
+    p.epilogue, p.accumulate = EPI_NONE, int(accumulate)
+    p.red[:] = [A, C, B]
     return p
 
 

@@ -18,6 +18,7 @@ std::string MatchedLaunch::family() const {
     case TCB200_FAMILY_CONTRACTION: return "contraction";
     case TCB200_FAMILY_TENSORDOT: return "tensordot";
     case TCB200_FAMILY_GROUP_CONV: return "group_conv";
+    case TCB200_FAMILY_REDUCTION: return "reduction";
     default: return "?";
   }
 }
@@ -28,7 +29,8 @@ namespace {
   throw ErrorReport(st.tree)
       << "no kernel family of the B200 backend matches this comprehension (" << why
       << "); supported: batched/transposed contractions O +=! A * B, tensordot with shared "
-         "trailing indices, grouped convolution, each optionally followed by + bias and fmax(., 0)";
+         "trailing indices, grouped convolution (each optionally followed by + bias and fmax(., 0)), sums of one tensor over "
+         "adjacent indices";
 }
 
 struct Operand {
@@ -350,6 +352,65 @@ bool matchConv(const DefAnalysis& def, const StatementAnalysis& st, MatchedLaunc
 }
 
 // ----------------------------------------------------------------------------------------------
+// reduction statement: sum of one tensor over a contiguous group of its indices
+//   O(kept leading..., kept trailing...) +=! I(kept leading..., reduced..., kept trailing...)
+// (C +=! A(r_m), C(m) +=! A(m, r_n): test/test_tc_mapper_harness-inl.h:60-146)
+// ----------------------------------------------------------------------------------------------
+bool matchReduction(const DefAnalysis& def, const StatementAnalysis& st, MatchedLaunch* out, std::string* why) {
+  const TreeRef rhs = stripParens(lang::Comprehension(st.tree).rhs());
+  if (rhs->kind() != lang::TK_ACCESS || st.reads.size() != 1) return false;
+  const TensorAccess& I = st.reads[0];
+  const TensorSymbol* isym = def.find(I.tensor), *osym = def.find(st.lhs);
+  if (!isym || !osym) return false;
+  if (!isFloat32(isym) || !isFloat32(osym)) { *why = "only float32 tensors are supported"; return false; }
+  // every input index a distinct variable spanning its whole dimension from 0
+  std::vector<std::string> vars;
+  for (size_t d = 0; d < I.indices.size(); ++d) {
+    std::string v;
+    if (!I.indices[d].isSingleVar(&v)) { *why = "an operand index is not a plain index variable"; return false; }
+    if (std::find(vars.begin(), vars.end(), v) != vars.end()) { *why = "an operand index is repeated"; return false; }
+    const IndexRange& r = st.ranges.at(v);
+    if (r.min != 0 || r.extent() != isym->shape[d]) { *why = "index " + v + " does not span its dimension"; return false; }
+    vars.push_back(v);
+  }
+  // the kept indices, in the input's order, must be exactly the output's indices; an output index that
+  // is not an input index (C(i) +=! A(r_m) where i in 0:1) must have extent 1
+  std::set<std::string> red(st.reductionVars.begin(), st.reductionVars.end());
+  std::vector<std::string> kept, lhsKept;
+  for (const auto& v : vars)
+    if (!red.count(v)) kept.push_back(v);
+  for (const auto& v : st.lhsIndices) {
+    if (std::find(vars.begin(), vars.end(), v) != vars.end()) lhsKept.push_back(v);
+    else if (st.ranges.at(v).min != 0 || st.ranges.at(v).extent() != 1) {
+      *why = "output index " + v + " does not index the operand";
+      return false;
+    }
+  }
+  if (kept != lhsKept) { *why = "the output's indices are not the operand's kept indices in the same order"; return false; }
+  for (const auto& v : red)
+    if (std::find(vars.begin(), vars.end(), v) == vars.end()) { *why = "a reduction index does not index the operand"; return false; }
+  if (red.empty()) return false;
+  // reduced indices must be one contiguous run of the operand's dimensions
+  int64_t A = 1, C = 1, B = 1;
+  int phase = 0;  // 0: leading kept, 1: reduced, 2: trailing kept
+  for (size_t d = 0; d < vars.size(); ++d) {
+    const bool r = red.count(vars[d]) != 0;
+    if (phase == 0 && r) phase = 1;
+    else if (phase == 1 && !r) phase = 2;
+    else if (phase == 2 && r) { *why = "the reduced indices are not adjacent dimensions of the operand"; return false; }
+    (phase == 0 ? A : phase == 1 ? C : B) *= isym->shape[d];
+  }
+  tcb200_problem_t& p = out->problem;
+  memset(&p, 0, sizeof(p));
+  p.family = TCB200_FAMILY_REDUCTION;
+  p.accumulate = st.assignment == lang::TK_PLUS_EQ ? 1 : 0;
+  p.red[0] = A; p.red[1] = C; p.red[2] = B;
+  out->inputs = {valueIndex(def, I.tensor)};
+  out->output = valueIndex(def, st.lhs);
+  return true;
+}
+
+// ----------------------------------------------------------------------------------------------
 // elementwise follow-ups on the tensor just produced
 // ----------------------------------------------------------------------------------------------
 // O(idx) = O(idx) [+ Bias(sub)]: returns the access that is NOT the self access, or null.
@@ -450,7 +511,10 @@ std::vector<MatchedLaunch> matchKernels(const DefAnalysis& def) {
         unmatched(st, "only sum reductions (+=, +=!) map to a kernel family");
       MatchedLaunch l;
       std::string why;
-      if (!matchConv(def, st, &l) && !matchProduct(def, st, &l, &why)) unmatched(st, why);
+      if (!matchConv(def, st, &l) && !matchReduction(def, st, &l, &why)) {
+        if (!why.empty()) unmatched(st, why);  // one operand, but not a sum this backend takes
+        if (!matchProduct(def, st, &l, &why)) unmatched(st, why);
+      }
       l.statements.push_back((int)s);
       launches.push_back(std::move(l));
       continue;

@@ -4,6 +4,8 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
+#include <mutex>
 #include <new>
 
 #include "common.cuh"
@@ -22,6 +24,7 @@ __global__ void l2_flush_kernel(float4* buf, size_t n4, float v) {
 }
 
 int n_inputs_expected(const tcb200_problem_t& p) {
+  if (p.family == TCB200_FAMILY_REDUCTION) return 1;
   const bool has_bias = p.epilogue == TCB200_EPI_BIAS || p.epilogue == TCB200_EPI_BIAS_RELU;
   return 2 + (has_bias ? 1 : 0);
 }
@@ -53,6 +56,10 @@ using namespace tcb200;
 
 struct tcb200_plan {
   Plan impl;
+  // Scratch of a plan that needs some (impl.scratch_*): allocated and zeroed at the first launch,
+  // freed with the plan.  Launches of one such plan share it, so they must not overlap in time.
+  std::mutex scratch_mu;
+  std::atomic<void*> scratch{nullptr};
 };
 
 struct tcb200_timer {
@@ -101,6 +108,8 @@ int tcb200_query(const tcb200_problem_t* problem, tcb200_tile_t* out, int max, i
       return tensordot_query(*problem, out, max, n);
     case TCB200_FAMILY_GROUP_CONV:
       return group_conv_query(*problem, out, max, n);
+    case TCB200_FAMILY_REDUCTION:
+      return reduce_query(*problem, out, max, n);
     case TCB200_FAMILY_CONTRACTION: {
       // The first candidate is the family default: the tensor-core tiles when the contraction is
       // large enough to prefer them, else the SIMT ones.
@@ -141,6 +150,9 @@ int tcb200_plan_create(const tcb200_problem_t* problem, const tcb200_tile_t* til
     case TCB200_FAMILY_GROUP_CONV:
       st = group_conv_plan(P);
       break;
+    case TCB200_FAMILY_REDUCTION:
+      st = reduce_plan(P);
+      break;
     case TCB200_FAMILY_CONTRACTION:
       if (P.tile.variant == TCB200_VARIANT_AUTO) {
         // Family default = first candidate of the sweep.
@@ -168,9 +180,43 @@ int tcb200_plan_create(const tcb200_problem_t* problem, const tcb200_tile_t* til
 }
 
 int tcb200_plan_destroy(tcb200_plan_t* plan) {
-  delete plan;
+  if (plan) {
+    if (void* s = plan->scratch.load()) cudaFree(s);
+    delete plan;
+  }
   return TCB200_OK;
 }
+
+namespace {
+// Device scratch of the plan: tickets first (zeroed), then the partial sums.  The allocation and the
+// memset are synchronous host calls: the first launch of such a plan must not be inside a stream capture.
+int plan_scratch(const tcb200_plan_t* cplan, float** partial, unsigned** tickets) {
+  *partial = nullptr;
+  *tickets = nullptr;
+  const Plan& P = cplan->impl;
+  if (P.scratch_floats == 0 && P.scratch_tickets == 0) return TCB200_OK;
+  tcb200_plan_t* plan = const_cast<tcb200_plan_t*>(cplan);
+  const size_t ticket_bytes = (P.scratch_tickets * sizeof(unsigned) + 255) / 256 * 256;
+  void* base = plan->scratch.load(std::memory_order_acquire);
+  if (!base) {
+    std::lock_guard<std::mutex> lock(plan->scratch_mu);
+    base = plan->scratch.load(std::memory_order_relaxed);
+    if (!base) {
+      TCB200_CUDA_TRY(cudaMalloc(&base, ticket_bytes + P.scratch_floats * sizeof(float)));
+      cudaError_t e = cudaMemset(base, 0, ticket_bytes);
+      if (e != cudaSuccess) {
+        cudaFree(base);
+        set_last_cuda_error(e);
+        return TCB200_ERR_CUDA;
+      }
+      plan->scratch.store(base, std::memory_order_release);
+    }
+  }
+  *tickets = static_cast<unsigned*>(base);
+  *partial = reinterpret_cast<float*>(static_cast<char*>(base) + ticket_bytes);
+  return TCB200_OK;
+}
+}  // namespace
 
 int tcb200_plan_geometry(const tcb200_plan_t* plan, int64_t grid[3], int64_t block[3]) {
   if (!plan || !grid || !block) return TCB200_ERR_INVALID_ARGUMENT;
@@ -198,6 +244,10 @@ int tcb200_plan_describe(const tcb200_plan_t* plan, char* buf, size_t buflen) {
       snprintf(head, sizeof(head), "tcb200::tensordot N=%lld C1=%lld C2=%lld C3=%lld P=%lld",
                (long long)p.td[0], (long long)p.td[1], (long long)p.td[2], (long long)p.td[3],
                (long long)p.td[4]);
+      break;
+    case TCB200_FAMILY_REDUCTION:
+      snprintf(head, sizeof(head), "tcb200::reduction A=%lld C=%lld B=%lld%s", (long long)p.red[0],
+               (long long)p.red[1], (long long)p.red[2], p.accumulate ? " accumulate" : "");
       break;
     case TCB200_FAMILY_GROUP_CONV:
       snprintf(head, sizeof(head),
@@ -239,7 +289,7 @@ int tcb200_launch(const tcb200_plan_t* plan, const void* const* inputs, int n_in
   if (cur != P.device) return TCB200_ERR_INVALID_ARGUMENT;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const float* in0 = static_cast<const float*>(inputs[0]);
-  const float* in1 = static_cast<const float*>(inputs[1]);
+  const float* in1 = n_inputs > 1 ? static_cast<const float*>(inputs[1]) : nullptr;
   const float* bias = n_inputs > 2 ? static_cast<const float*>(inputs[2]) : nullptr;
   float* out = static_cast<float*>(outputs[0]);
   switch (P.p.family) {
@@ -247,6 +297,13 @@ int tcb200_launch(const tcb200_plan_t* plan, const void* const* inputs, int n_in
       return tensordot_launch(P, in0, in1, out, s, dev_status);
     case TCB200_FAMILY_GROUP_CONV:
       return group_conv_launch(P, in0, in1, bias, out, s, dev_status);
+    case TCB200_FAMILY_REDUCTION: {
+      float* partial;
+      unsigned* tickets;
+      const int st = plan_scratch(plan, &partial, &tickets);
+      if (st != TCB200_OK) return st;
+      return reduce_launch(P, in0, out, partial, tickets, s);
+    }
     case TCB200_FAMILY_CONTRACTION:
       if (P.tile.variant == TCB200_VARIANT_TCGEN05 || P.tile.variant == TCB200_VARIANT_TCGEN05_TS ||
           P.tile.variant == TCB200_VARIANT_TCGEN05_PAIR)

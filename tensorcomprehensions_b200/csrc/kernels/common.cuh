@@ -26,6 +26,9 @@ struct Plan {
   int device;
   Launch launch;
   int kernel_id;  // family-private selector of the instantiated kernel
+  // Scratch global memory the launches of this plan need (reduction family, when the reduced range is
+  // split over several CTAs): partial sums and one ticket counter per output tile.  0 = none.
+  size_t scratch_floats = 0, scratch_tickets = 0;
 };
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
@@ -83,6 +86,13 @@ int group_conv_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int
 int group_conv_plan(Plan& plan);
 int group_conv_launch(const Plan& plan, const float* I, const float* W, const float* bias,
                       float* O, cudaStream_t s, int* dev_status);
+// reduction family (reduce.cu); partial / tickets: scratch of plan.scratch_floats floats and
+// plan.scratch_tickets zeroed counters (may be null when the plan needs none)
+constexpr int kReduceMaxSegments = 1024;
+int reduce_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n);
+int reduce_plan(Plan& plan);
+int reduce_launch(const Plan& plan, const float* I, float* O, float* partial, unsigned* tickets, cudaStream_t s);
+
 // tensor-core variant (group_conv_tcgen05.cu)
 bool group_conv_tc_ok(const tcb200_problem_t& p);
 int group_conv_tc_plan(Plan& plan);

@@ -1,0 +1,252 @@
+// K4 — sum reductions of one tensor over a contiguous group of its indices:
+//   O(a, b) (+)= sum_c I(a, c, b)            I viewed as [A][C][B], O as [A][B]
+// with A / B the products of the kept leading / trailing dimensions (either may be 1).  These are the
+// comprehensions the reference's mapper tests exercise as sum1D / sum2D
+// (test/test_tc_mapper_harness-inl.h:60-146: C +=! A(r_m), C(m) +=! A(m, r_n)) and the building
+// blocks of its moment / normalisation examples; they replace the kernels it generates for them,
+// including the CUB block reductions those call (tc/core/cuda/cuda_libraries.h:128-282).
+//
+// All of it is HBM streaming (4 * (A*C*B + A*B) bytes, one add per element).  Two kernels:
+//  * tile kernel (any shape): a CTA of 256 threads owns CP output columns (a power of two <= 256)
+//    of one row a and one segment of the reduced range; thread (tx, ty) of the CP x (256 / CP) layout
+//    adds the elements c = ty, ty + TY, ... of column tx, so a warp reads consecutive addresses
+//    whatever B is (B = 1: consecutive c; B >= 32: consecutive columns).  The TY partial sums of a
+//    column are combined through shared memory in a fixed order.
+//    When the output alone gives too few CTAs to fill 148 SMs, the reduced range is cut into S
+//    segments (grid.y); each CTA leaves its partial sums in scratch memory, takes a ticket, and the
+//    CTA that draws the last ticket of a tile adds the S partials in segment order and writes the
+//    output.  Same bits on every run, one launch, no atomics on data.
+//  * warp-rows kernel (B = 1, short rows): one warp per row, 128-bit loads when the rows allow.
+#include "common.cuh"
+
+namespace tcb200 {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;
+
+struct ReduceArgs {
+  const float* I;
+  float* O;
+  long long A, C, B;
+  long long tiles_b;  // column tiles per row a
+  long long seg;      // reduced elements per segment
+  int S;              // segments
+  int cp_log2;        // log2 of the columns per CTA
+  int accumulate;
+  float* partial;     // [tile][S][CP]
+  unsigned* tickets;  // [tile], zero between launches
+};
+
+__global__ void __launch_bounds__(kThreads) reduce_tile_kernel(ReduceArgs a) {
+  __shared__ float red[kThreads];
+  __shared__ int is_last;
+  const int CP = 1 << a.cp_log2, TY = kThreads >> a.cp_log2;
+  const int tid = threadIdx.x, tx = tid & (CP - 1), ty = tid >> a.cp_log2;
+  const long long tile = blockIdx.x;
+  const int s = blockIdx.y;
+  const long long arow = tile / a.tiles_b, ct = tile - arow * a.tiles_b;
+  const long long col = ct * CP + tx;
+  const long long c0 = (long long)s * a.seg, c1 = min(a.C, c0 + a.seg);
+  float acc[kUnroll];
+#pragma unroll
+  for (int k = 0; k < kUnroll; ++k) acc[k] = 0.f;
+  if (col < a.B) {
+    const float* base = a.I + (size_t)arow * a.C * a.B + col;
+    long long c = c0 + ty;
+    for (; c + (long long)(kUnroll - 1) * TY < c1; c += (long long)kUnroll * TY) {
+      float v[kUnroll];
+#pragma unroll
+      for (int k = 0; k < kUnroll; ++k) v[k] = __ldg(base + (size_t)(c + (long long)k * TY) * a.B);
+#pragma unroll
+      for (int k = 0; k < kUnroll; ++k) acc[k] += v[k];
+    }
+    for (int k = 0; c < c1; c += TY, ++k) acc[k] += __ldg(base + (size_t)c * a.B);
+  }
+  red[tid] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+  __syncthreads();
+  // rows of the CP x TY layout are ty-major: element (ty, tx) sits at ty * CP + tx = tid
+  for (int h = TY >> 1; h > 0; h >>= 1) {
+    if (ty < h) red[tid] += red[tid + h * CP];
+    __syncthreads();
+  }
+  const bool writer = ty == 0 && col < a.B;
+  float* out = a.O + (size_t)arow * a.B + col;
+  if (a.S == 1) {
+    if (writer) *out = a.accumulate ? *out + red[tid] : red[tid];
+    return;
+  }
+  float* mine = a.partial + ((size_t)tile * a.S + s) * CP;
+  if (ty == 0) mine[tx] = red[tid];
+  __threadfence();  // the partial sums are visible device-wide before the ticket is drawn
+  __syncthreads();
+  if (tid == 0) is_last = atomicAdd(a.tickets + tile, 1u) == (unsigned)(a.S - 1);
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  if (writer) {
+    const volatile float* p = a.partial + (size_t)tile * a.S * CP + tx;
+    float sum = 0.f;
+    for (int k = 0; k < a.S; ++k) sum += p[(size_t)k * CP];
+    *out = a.accumulate ? *out + sum : sum;
+  }
+  if (tid == 0) a.tickets[tile] = 0;  // the next launch on this scratch starts from zero again
+}
+
+// B = 1: O(a) = sum_c I(a, c), one warp per row.
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads) reduce_rows_warp_kernel(ReduceArgs a) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int WARPS = kThreads / 32;
+  for (long long r = (long long)blockIdx.x * WARPS + warp; r < a.A; r += (long long)gridDim.x * WARPS) {
+    const float* row = a.I + (size_t)r * a.C;
+    float s0 = 0.f, s1 = 0.f;
+    if (VEC) {
+      const float4* row4 = reinterpret_cast<const float4*>(row);
+      const long long n4 = a.C >> 2;
+      long long i = lane;
+      for (; i + 32 < n4; i += 64) {
+        const float4 u = __ldg(row4 + i), v = __ldg(row4 + i + 32);
+        s0 += (u.x + u.y) + (u.z + u.w);
+        s1 += (v.x + v.y) + (v.z + v.w);
+      }
+      if (i < n4) {
+        const float4 u = __ldg(row4 + i);
+        s0 += (u.x + u.y) + (u.z + u.w);
+      }
+    } else {
+      long long i = lane;
+      for (; i + 32 < a.C; i += 64) {
+        s0 += __ldg(row + i);
+        s1 += __ldg(row + i + 32);
+      }
+      if (i < a.C) s0 += __ldg(row + i);
+    }
+    float s = s0 + s1;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    if (lane == 0) a.O[r] = a.accumulate ? a.O[r] + s : s;
+  }
+}
+
+bool valid(const tcb200_problem_t& p) {
+  for (int i = 0; i < 3; ++i)
+    if (p.red[i] <= 0 || p.red[i] > (1ll << 40)) return false;
+  return (double)p.red[0] * (double)p.red[1] * (double)p.red[2] < 9.0e18;
+}
+
+int pow2_ceil_log2(long long v, int cap_log2) {
+  int l = 0;
+  while (l < cap_log2 && (1ll << l) < v) ++l;
+  return l;
+}
+
+// Segments of the tile kernel: enough CTAs for two per SM, at least 64 reduced elements per thread row.
+int auto_segments(const tcb200_problem_t& p, int cp_log2) {
+  const long long CP = 1ll << cp_log2, TY = kThreads / CP;
+  const long long tiles = p.red[0] * ceil_div(p.red[2], CP);
+  const long long want = ceil_div(2 * kNumSMs, tiles);
+  const long long most = std::max<long long>(1, p.red[1] / (64 * TY));
+  return (int)std::max<long long>(1, std::min<long long>({want, most, (long long)kReduceMaxSegments}));
+}
+
+bool warp_rows_ok(const tcb200_problem_t& p) { return p.red[2] == 1 && p.red[1] <= (1 << 20); }
+
+}  // namespace
+
+int reduce_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n) {
+  if (!valid(p)) return TCB200_ERR_INVALID_ARGUMENT;
+  int cnt = 0;
+  auto add = [&](int cp, int s, int mode) {
+    if (cnt < max && out) out[cnt] = tcb200_tile_t{TCB200_VARIANT_SIMT, cp, s, mode, 0, kThreads, 0};
+    ++cnt;
+  };
+  const int cp = 1 << pow2_ceil_log2(p.red[2], 8);
+  // short rows, many of them: a warp per row first; else the tile kernel
+  const bool warp_first = warp_rows_ok(p) && p.red[1] <= 4096 && p.red[0] >= 2 * kNumSMs;
+  if (warp_first) add(1, 1, 1);
+  add(cp, 0, 0);
+  if (warp_rows_ok(p) && !warp_first) add(1, 1, 1);
+  if (cp > 32) add(cp / 2, 0, 0);  // narrower column tiles: more rows of threads per column
+  *n = cnt;
+  return TCB200_OK;
+}
+
+// tile: bm = columns per CTA (power of two), bn = segments (0 = chosen here), bk = 1 for the warp-rows kernel
+int reduce_plan(Plan& plan) {
+  const tcb200_problem_t& p = plan.p;
+  if (!valid(p)) return TCB200_ERR_INVALID_ARGUMENT;
+  if (p.epilogue != TCB200_EPI_NONE) return TCB200_ERR_UNSUPPORTED;
+  tcb200_tile_t& t = plan.tile;
+  if (t.variant == TCB200_VARIANT_AUTO) {
+    tcb200_tile_t first;
+    int n = 0;
+    reduce_query(p, &first, 1, &n);
+    t = first;
+  }
+  if (t.variant != TCB200_VARIANT_SIMT) return TCB200_ERR_UNSUPPORTED;
+  t.threads = kThreads;
+  t.stages = 0; t.split_tf32 = 0;
+  plan.scratch_floats = 0;
+  plan.scratch_tickets = 0;
+  if (t.bk == 1) {
+    if (!warp_rows_ok(p)) return TCB200_ERR_UNSUPPORTED;
+    t.bm = 1; t.bn = 1;
+    plan.launch.grid = dim3((unsigned)std::min<long long>(ceil_div(p.red[0], kThreads / 32), 8 * kNumSMs), 1, 1);
+    plan.launch.block = dim3(kThreads, 1, 1);
+    plan.kernel_id = 2;
+    return TCB200_OK;
+  }
+  if (t.bk != 0) return TCB200_ERR_INVALID_ARGUMENT;
+  int cp_log2 = 0;
+  if (t.bm <= 0) cp_log2 = pow2_ceil_log2(p.red[2], 8);
+  else {
+    while ((1 << cp_log2) < t.bm) ++cp_log2;
+    if ((1 << cp_log2) != t.bm || cp_log2 > 8) return TCB200_ERR_INVALID_ARGUMENT;
+  }
+  t.bm = 1 << cp_log2;
+  const long long tiles = p.red[0] * ceil_div(p.red[2], t.bm);
+  if (tiles > 0x7fffffffll) return TCB200_ERR_TOO_LARGE;
+  int S = t.bn > 0 ? t.bn : auto_segments(p, cp_log2);
+  if (S > kReduceMaxSegments) return TCB200_ERR_INVALID_ARGUMENT;
+  S = (int)std::min<long long>(S, p.red[1]);
+  const long long seg = ceil_div(p.red[1], S);
+  S = (int)ceil_div(p.red[1], seg);  // no empty segment
+  t.bn = S;
+  plan.launch.grid = dim3((unsigned)tiles, (unsigned)S, 1);
+  plan.launch.block = dim3(kThreads, 1, 1);
+  plan.kernel_id = 1;
+  if (S > 1) {
+    plan.scratch_floats = (size_t)tiles * S * t.bm;
+    plan.scratch_tickets = (size_t)tiles;
+  }
+  return TCB200_OK;
+}
+
+int reduce_launch(const Plan& plan, const float* I, float* O, float* partial, unsigned* tickets, cudaStream_t s) {
+  const tcb200_problem_t& p = plan.p;
+  ReduceArgs a;
+  a.I = I; a.O = O;
+  a.A = p.red[0]; a.C = p.red[1]; a.B = p.red[2];
+  a.accumulate = p.accumulate;
+  a.partial = partial; a.tickets = tickets;
+  if (plan.kernel_id == 2) {
+    a.S = 1; a.seg = a.C; a.cp_log2 = 0; a.tiles_b = 1;
+    const bool vec = (a.C & 3) == 0 && (((uintptr_t)I) & 15) == 0;
+    if (vec) reduce_rows_warp_kernel<true><<<plan.launch.grid, plan.launch.block, 0, s>>>(a);
+    else reduce_rows_warp_kernel<false><<<plan.launch.grid, plan.launch.block, 0, s>>>(a);
+    TCB200_CUDA_TRY(cudaGetLastError());
+    return TCB200_OK;
+  }
+  a.cp_log2 = 0;
+  while ((1 << a.cp_log2) < plan.tile.bm) ++a.cp_log2;
+  a.tiles_b = ceil_div(a.B, plan.tile.bm);
+  a.S = plan.tile.bn;
+  a.seg = ceil_div(a.C, a.S);
+  if (a.S > 1 && (!partial || !tickets)) return TCB200_ERR_INVALID_ARGUMENT;
+  reduce_tile_kernel<<<plan.launch.grid, plan.launch.block, 0, s>>>(a);
+  TCB200_CUDA_TRY(cudaGetLastError());
+  return TCB200_OK;
+}
+
+}  // namespace tcb200

@@ -65,6 +65,22 @@ def test_bias_on_rows_and_relu_only():
     assert match(t, "f", [(4, 6), (5, 6)])[0]["epilogue"] == 3
 
 
+def test_sum_reductions():
+    """sum1D / sum2D of the reference's mapper tests (test/test_tc_mapper_harness-inl.h:60-146) and the
+    general form: one operand, the reduced indices adjacent, the kept ones in the operand's order."""
+    for body in ("C() +=! A(r_m)", "C +=! A(r_m)", "C(i) +=! A(r_m) where i in 0:1"):
+        m = match("def sum1D(float(M) A) -> (C) { %s }" % body, "sum1D", [(100,)])
+        assert len(m) == 1 and m[0]["family"] == "reduction" and m[0]["red"] == [1, 100, 1] and m[0]["inputs"] == [0]
+    m = match("def sum2D(float(M, N) A) -> (C) { C(m) +=! A(m, r_n) }", "sum2D", [(7, 9)])[0]
+    assert m["red"] == [7, 9, 1] and m["accumulate"] == 0
+    m = match("def cols(float(M, N) A) -> (C) { C(n) += A(r_m, n) }", "cols", [(7, 9)])[0]
+    assert m["red"] == [1, 7, 9] and m["accumulate"] == 1
+    m = match("def f(float(N, C, D, H, W) I) -> (O) { O(n, h, w) +=! I(n, c, d, h, w) }", "f", [(2, 3, 4, 5, 6)])[0]
+    assert m["red"] == [2, 12, 30]
+    exe = tc.compile("def sum2D(float(M, N) A) -> (C) { C(m) +=! A(m, r_n) }", "sum2D", "naive", torch.empty(7, 9))
+    assert exe.output_shapes() == [[7]] and "tcb200::reduction A=7 C=9 B=1" in exe.compiled_source
+
+
 def test_ungrouped_convolution_is_group_conv_with_one_group():
     t = "def c(float(N,C,H,W) I, float(F,C,KH,KW) W1) -> (O) { O(n,f,h,w) +=! I(n,c,h+kh,w+kw) * W1(f,c,kh,kw) }"
     m = match(t, "c", [(2, 3, 8, 9), (4, 3, 3, 2)])[0]
@@ -91,7 +107,8 @@ def test_strided_convolution_of_the_library():
 
 @pytest.mark.parametrize("tcs,ins,fragment", [
     ("def f(float(N) A, float(N) B) -> (C) { C(i) = A(i) + B(i) }", [(4,), (4,)], "elementwise statement"),
-    ("def f(float(N,M) A) -> (O) { O(i) +=! A(i,j) }", [(4, 5)], "not a product of two tensor accesses"),
+    ("def f(float(N,M) A) -> (O) { O(i) +=! exp(A(i,j)) }", [(4, 5)], "not a product of two tensor accesses"),
+    ("def f(float(N,M,K) A) -> (O) { O(m) +=! A(n,m,k) }", [(4, 5, 6)], "not adjacent dimensions"),
     ("def f(float(N,M) A, float(M) B) -> (O) { O(i) max=! A(i,j) * B(j) }", [(4, 5), (5,)], "only sum reductions"),
     # dilated filter taps: strides are covered (next test), dilation is not
     ("def f(float(N,C,H,W) I, float(F,C,KH,KW) W1) -> (O) { O(n,f,h,w) +=! I(n,c,h+2*kh,w+2*kw) * W1(f,c,kh,kw) }",
