@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the hot path: compile the five benchmark comprehensions and run them on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload suite|tensordot|batchmatmul|tmm|group_conv|mlp3]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload suite|tensordot|batchmatmul|tmm|group_conv|mlp3|sum1d|sum2d|colsum]
     python bench.py --impl reference ...        # the CPU reference arm (ATen on the host cores)
 
 A "step" is one pass over the selected comprehensions (default: all five, "tc5_suite") on one
@@ -204,7 +204,7 @@ def run_product(args):
     peaks = load_peaks()
 
     names = list(wl.ALL) if args.workload == "suite" else [args.workload]
-    progs = [Program(wl.ALL[n](), dev, seed=20240 + wl.ALL[n]().index + 1000 * rank,
+    progs = [Program(wl.BY_NAME[n](), dev, seed=20240 + wl.BY_NAME[n]().index + 1000 * rank,
                      rotate_bytes=192 << 20, tune=args.tune) for n in names]
     launches_per_step = sum(p.launches_per_run for p in progs)
 
@@ -342,7 +342,7 @@ def cpu_suite(names):
     import torch
     from oracle import oracle as orc
     from tensorcomprehensions_b200 import workloads as wl
-    ws = [wl.ALL[n]() for n in names]
+    ws = [wl.BY_NAME[n]() for n in names]
     inputs = [wl.make_inputs(w) for w in ws]
 
     def step():
@@ -404,7 +404,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="suite",
-                    choices=["suite", "tensordot", "batchmatmul", "tmm", "group_conv", "mlp3"])
+                    choices=["suite", "tensordot", "batchmatmul", "tmm", "group_conv", "mlp3", "sum1d", "sum2d", "colsum"])
     ap.add_argument("--cpu-seconds", type=float, default=20.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--tune", action="store_true",

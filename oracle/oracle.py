@@ -156,7 +156,8 @@ def aten_mlp3(I, W2, B2, W3, B3, W4, B4):
 LOOP = {"tensordot": loop_tensordot, "batchmatmul": loop_batchmatmul, "tmm": loop_tmm,
         "group_conv": loop_group_conv, "mlp3": loop_mlp3}
 ATEN = {"tensordot": aten_tensordot, "batchmatmul": aten_batchmatmul, "tmm": aten_tmm,
-        "group_conv": aten_group_conv, "mlp3": aten_mlp3}
+        "group_conv": aten_group_conv, "mlp3": aten_mlp3,
+        "sum1d": lambda A: A.sum(), "sum2d": lambda A: A.sum(1), "colsum": lambda A: A.sum(0)}
 
 
 def as_list(x):

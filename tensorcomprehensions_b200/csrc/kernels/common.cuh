@@ -88,7 +88,7 @@ int group_conv_launch(const Plan& plan, const float* I, const float* W, const fl
                       float* O, cudaStream_t s, int* dev_status);
 // reduction family (reduce.cu); partial / tickets: scratch of plan.scratch_floats floats and
 // plan.scratch_tickets zeroed counters (may be null when the plan needs none)
-constexpr int kReduceMaxSegments = 1024;
+constexpr int kReduceMaxSegments = 4096;
 int reduce_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n);
 int reduce_plan(Plan& plan);
 int reduce_launch(const Plan& plan, const float* I, float* O, float* partial, unsigned* tickets, cudaStream_t s);

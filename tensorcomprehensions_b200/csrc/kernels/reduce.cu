@@ -7,7 +7,8 @@
 // including the CUB block reductions those call (tc/core/cuda/cuda_libraries.h:128-282).
 //
 // All of it is HBM streaming (4 * (A*C*B + A*B) bytes, one add per element).  Two kernels:
-//  * tile kernel (any shape): a CTA of 256 threads owns CP output columns (a power of two <= 256)
+//  * tile kernel (any shape): a CTA of 256 threads owns CP output columns (a power of two, one warp
+//    wide by default: narrow tiles give many CTAs and few segments)
 //    of one row a and one segment of the reduced range; thread (tx, ty) of the CP x (256 / CP) layout
 //    adds the elements c = ty, ty + TY, ... of column tx, so a warp reads consecutive addresses
 //    whatever B is (B = 1: consecutive c; B >= 32: consecutive columns).  The TY partial sums of a
@@ -17,29 +18,43 @@
 //    CTA that draws the last ticket of a tile adds the S partials in segment order and writes the
 //    output.  Same bits on every run, one launch, no atomics on data.
 //  * warp-rows kernel (B = 1, short rows): one warp per row, 128-bit loads when the rows allow.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace tcb200 {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kUnroll = 4;
 
 struct ReduceArgs {
   const float* I;
   float* O;
-  long long A, C, B;
+  long long A, C, B;  // in elements of the kernel's value type (see reduce_tile_kernel)
   long long tiles_b;  // column tiles per row a
   long long seg;      // reduced elements per segment
   int S;              // segments
   int cp_log2;        // log2 of the columns per CTA
   int accumulate;
-  float* partial;     // [tile][S][CP]
+  float* partial;     // [tile][S][CP] output values
   unsigned* tickets;  // [tile], zero between launches
 };
 
+__device__ __forceinline__ float vadd(float a, float b) { return a + b; }
+__device__ __forceinline__ float4 vadd(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+__device__ __forceinline__ void vzero(float& a) { a = 0.f; }
+__device__ __forceinline__ void vzero(float4& a) { a = make_float4(0.f, 0.f, 0.f, 0.f); }
+__device__ __forceinline__ float hsum(float4 a) { return (a.x + a.y) + (a.z + a.w); }
+
+// T = float: the plain form.  T = float4, HSUM = false: four adjacent output columns per thread
+// (B a multiple of 4; A.B counts float4 columns).  T = float4, HSUM = true: B = 1 and the reduced range
+// itself is read four elements at a time (C a multiple of 4; A.C counts float4 elements), the four
+// lanes of a thread's sum are added at the end.  16 to 64 bytes of loads per thread are in flight.
+template <typename T, bool HSUM>
 __global__ void __launch_bounds__(kThreads) reduce_tile_kernel(ReduceArgs a) {
-  __shared__ float red[kThreads];
+  using OutT = typename std::conditional<HSUM, float, T>::type;
+  constexpr int UNROLL = sizeof(T) == 4 ? 8 : 4;
+  __shared__ T red[kThreads];
   __shared__ int is_last;
   const int CP = 1 << a.cp_log2, TY = kThreads >> a.cp_log2;
   const int tid = threadIdx.x, tx = tid & (CP - 1), ty = tid >> a.cp_log2;
@@ -48,48 +63,61 @@ __global__ void __launch_bounds__(kThreads) reduce_tile_kernel(ReduceArgs a) {
   const long long arow = tile / a.tiles_b, ct = tile - arow * a.tiles_b;
   const long long col = ct * CP + tx;
   const long long c0 = (long long)s * a.seg, c1 = min(a.C, c0 + a.seg);
-  float acc[kUnroll];
+  T acc[UNROLL];
 #pragma unroll
-  for (int k = 0; k < kUnroll; ++k) acc[k] = 0.f;
+  for (int k = 0; k < UNROLL; ++k) vzero(acc[k]);
   if (col < a.B) {
-    const float* base = a.I + (size_t)arow * a.C * a.B + col;
+    const T* base = reinterpret_cast<const T*>(a.I) + (size_t)arow * a.C * a.B + col;
     long long c = c0 + ty;
-    for (; c + (long long)(kUnroll - 1) * TY < c1; c += (long long)kUnroll * TY) {
-      float v[kUnroll];
+    for (; c + (long long)(UNROLL - 1) * TY < c1; c += (long long)UNROLL * TY) {
+      T v[UNROLL];
 #pragma unroll
-      for (int k = 0; k < kUnroll; ++k) v[k] = __ldg(base + (size_t)(c + (long long)k * TY) * a.B);
+      for (int k = 0; k < UNROLL; ++k) v[k] = __ldg(base + (size_t)(c + (long long)k * TY) * a.B);
 #pragma unroll
-      for (int k = 0; k < kUnroll; ++k) acc[k] += v[k];
+      for (int k = 0; k < UNROLL; ++k) acc[k] = vadd(acc[k], v[k]);
     }
-    for (int k = 0; c < c1; c += TY, ++k) acc[k] += __ldg(base + (size_t)c * a.B);
+    for (; c < c1; c += TY) acc[0] = vadd(acc[0], __ldg(base + (size_t)c * a.B));  // fewer than UNROLL left
   }
-  red[tid] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+#pragma unroll
+  for (int h = UNROLL / 2; h > 0; h >>= 1)
+#pragma unroll
+    for (int k = 0; k < h; ++k) acc[k] = vadd(acc[k], acc[k + h]);
+  red[tid] = acc[0];
   __syncthreads();
   // rows of the CP x TY layout are ty-major: element (ty, tx) sits at ty * CP + tx = tid
   for (int h = TY >> 1; h > 0; h >>= 1) {
-    if (ty < h) red[tid] += red[tid + h * CP];
+    if (ty < h) red[tid] = vadd(red[tid], red[tid + h * CP]);
     __syncthreads();
   }
   const bool writer = ty == 0 && col < a.B;
-  float* out = a.O + (size_t)arow * a.B + col;
+  OutT mine_v;
+  if constexpr (HSUM) mine_v = hsum(red[tid]); else mine_v = red[tid];
+  OutT* out = reinterpret_cast<OutT*>(a.O) + (size_t)arow * a.B + col;
   if (a.S == 1) {
-    if (writer) *out = a.accumulate ? *out + red[tid] : red[tid];
+    if (writer) *out = a.accumulate ? vadd(*out, mine_v) : mine_v;
     return;
   }
-  float* mine = a.partial + ((size_t)tile * a.S + s) * CP;
-  if (ty == 0) mine[tx] = red[tid];
+  OutT* part = reinterpret_cast<OutT*>(a.partial) + (size_t)tile * a.S * CP;
+  if (ty == 0) part[(size_t)s * CP + tx] = mine_v;
   __threadfence();  // the partial sums are visible device-wide before the ticket is drawn
   __syncthreads();
   if (tid == 0) is_last = atomicAdd(a.tickets + tile, 1u) == (unsigned)(a.S - 1);
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  if (writer) {
-    const volatile float* p = a.partial + (size_t)tile * a.S * CP + tx;
-    float sum = 0.f;
-    for (int k = 0; k < a.S; ++k) sum += p[(size_t)k * CP];
-    *out = a.accumulate ? *out + sum : sum;
+  // The S partial sums of every column, added by the same thread layout in the same fixed order:
+  // thread (tx, ty) takes segments ty, ty + TY, ..., then the TY rows are combined as above.
+  OutT* redo = reinterpret_cast<OutT*>(red);
+  OutT sum;
+  vzero(sum);
+  for (int k = ty; k < a.S; k += TY) sum = vadd(sum, __ldcg(part + (size_t)k * CP + tx));  // L2: written by other SMs
+  redo[tid] = sum;
+  __syncthreads();
+  for (int h = TY >> 1; h > 0; h >>= 1) {
+    if (ty < h) redo[tid] = vadd(redo[tid], redo[tid + h * CP]);
+    __syncthreads();
   }
+  if (writer) *out = a.accumulate ? vadd(*out, redo[tid]) : redo[tid];
   if (tid == 0) a.tickets[tile] = 0;  // the next launch on this scratch starts from zero again
 }
 
@@ -141,12 +169,23 @@ int pow2_ceil_log2(long long v, int cap_log2) {
   return l;
 }
 
-// Segments of the tile kernel: enough CTAs for two per SM, at least 64 reduced elements per thread row.
-int auto_segments(const tcb200_problem_t& p, int cp_log2) {
+// The problem in units of the tile kernel's value type.  vec = 4: float4 loads, along the reduced range
+// when B = 1 (C a multiple of 4), else along the columns (B a multiple of 4); vec = 1: plain floats.
+struct Units { long long A, C, B; bool hsum; };
+bool vec_ok(const tcb200_problem_t& p) { return p.red[2] == 1 ? p.red[1] % 4 == 0 : p.red[2] % 4 == 0; }
+Units units(const tcb200_problem_t& p, int vec) {
+  if (vec != 4) return Units{p.red[0], p.red[1], p.red[2], false};
+  if (p.red[2] == 1) return Units{p.red[0], p.red[1] / 4, 1, true};
+  return Units{p.red[0], p.red[1], p.red[2] / 4, false};
+}
+
+// Segments of the tile kernel: enough CTAs for eight per SM (all that fit), at least 16 reduced
+// elements per thread row.
+int auto_segments(const Units& u, int cp_log2) {
   const long long CP = 1ll << cp_log2, TY = kThreads / CP;
-  const long long tiles = p.red[0] * ceil_div(p.red[2], CP);
-  const long long want = ceil_div(2 * kNumSMs, tiles);
-  const long long most = std::max<long long>(1, p.red[1] / (64 * TY));
+  const long long tiles = u.A * ceil_div(u.B, CP);
+  const long long want = ceil_div(8 * kNumSMs, tiles);
+  const long long most = std::max<long long>(1, u.C / (16 * TY));
   return (int)std::max<long long>(1, std::min<long long>({want, most, (long long)kReduceMaxSegments}));
 }
 
@@ -157,22 +196,25 @@ bool warp_rows_ok(const tcb200_problem_t& p) { return p.red[2] == 1 && p.red[1] 
 int reduce_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n) {
   if (!valid(p)) return TCB200_ERR_INVALID_ARGUMENT;
   int cnt = 0;
-  auto add = [&](int cp, int s, int mode) {
-    if (cnt < max && out) out[cnt] = tcb200_tile_t{TCB200_VARIANT_SIMT, cp, s, mode, 0, kThreads, 0};
+  auto add = [&](int cp, int s, int mode, int vec) {
+    if (cnt < max && out) out[cnt] = tcb200_tile_t{TCB200_VARIANT_SIMT, cp, s, mode, vec, kThreads, 0};
     ++cnt;
   };
-  const int cp = 1 << pow2_ceil_log2(p.red[2], 8);
+  const int vec = vec_ok(p) ? 4 : 1;
+  const int cp = 1 << pow2_ceil_log2(units(p, vec).B, 5);
   // short rows, many of them: a warp per row first; else the tile kernel
   const bool warp_first = warp_rows_ok(p) && p.red[1] <= 4096 && p.red[0] >= 2 * kNumSMs;
-  if (warp_first) add(1, 1, 1);
-  add(cp, 0, 0);
-  if (warp_rows_ok(p) && !warp_first) add(1, 1, 1);
-  if (cp > 32) add(cp / 2, 0, 0);  // narrower column tiles: more rows of threads per column
+  if (warp_first) add(1, 1, 1, 0);
+  add(cp, 0, 0, vec);
+  if (warp_rows_ok(p) && !warp_first) add(1, 1, 1, 0);
+  if (units(p, vec).B > 64) add(64, 0, 0, vec);  // two warps wide: half the tiles, longer row pieces
+  if (vec == 4) add(1 << pow2_ceil_log2(p.red[2], 5), 0, 0, 1);  // plain floats: no alignment rule
   *n = cnt;
   return TCB200_OK;
 }
 
-// tile: bm = columns per CTA (power of two), bn = segments (0 = chosen here), bk = 1 for the warp-rows kernel
+// tile: bm = columns per CTA in units of the value type (power of two), bn = segments (0 = chosen here),
+// bk = 1 for the warp-rows kernel, stages = 4 for 128-bit loads (pointers must then be 16-byte aligned)
 int reduce_plan(Plan& plan) {
   const tcb200_problem_t& p = plan.p;
   if (!valid(p)) return TCB200_ERR_INVALID_ARGUMENT;
@@ -186,38 +228,41 @@ int reduce_plan(Plan& plan) {
   }
   if (t.variant != TCB200_VARIANT_SIMT) return TCB200_ERR_UNSUPPORTED;
   t.threads = kThreads;
-  t.stages = 0; t.split_tf32 = 0;
+  t.split_tf32 = 0;
   plan.scratch_floats = 0;
   plan.scratch_tickets = 0;
   if (t.bk == 1) {
     if (!warp_rows_ok(p)) return TCB200_ERR_UNSUPPORTED;
-    t.bm = 1; t.bn = 1;
+    t.bm = 1; t.bn = 1; t.stages = 0;
     plan.launch.grid = dim3((unsigned)std::min<long long>(ceil_div(p.red[0], kThreads / 32), 8 * kNumSMs), 1, 1);
     plan.launch.block = dim3(kThreads, 1, 1);
     plan.kernel_id = 2;
     return TCB200_OK;
   }
   if (t.bk != 0) return TCB200_ERR_INVALID_ARGUMENT;
+  if (t.stages == 0) t.stages = vec_ok(p) ? 4 : 1;
+  if (t.stages != 1 && !(t.stages == 4 && vec_ok(p))) return TCB200_ERR_UNSUPPORTED;
+  const Units u = units(p, t.stages);
   int cp_log2 = 0;
-  if (t.bm <= 0) cp_log2 = pow2_ceil_log2(p.red[2], 8);
+  if (t.bm <= 0) cp_log2 = pow2_ceil_log2(u.B, 5);
   else {
     while ((1 << cp_log2) < t.bm) ++cp_log2;
     if ((1 << cp_log2) != t.bm || cp_log2 > 8) return TCB200_ERR_INVALID_ARGUMENT;
   }
   t.bm = 1 << cp_log2;
-  const long long tiles = p.red[0] * ceil_div(p.red[2], t.bm);
+  const long long tiles = u.A * ceil_div(u.B, t.bm);
   if (tiles > 0x7fffffffll) return TCB200_ERR_TOO_LARGE;
-  int S = t.bn > 0 ? t.bn : auto_segments(p, cp_log2);
+  int S = t.bn > 0 ? t.bn : auto_segments(u, cp_log2);
   if (S > kReduceMaxSegments) return TCB200_ERR_INVALID_ARGUMENT;
-  S = (int)std::min<long long>(S, p.red[1]);
-  const long long seg = ceil_div(p.red[1], S);
-  S = (int)ceil_div(p.red[1], seg);  // no empty segment
+  S = (int)std::min<long long>(S, u.C);
+  const long long seg = ceil_div(u.C, S);
+  S = (int)ceil_div(u.C, seg);  // no empty segment
   t.bn = S;
   plan.launch.grid = dim3((unsigned)tiles, (unsigned)S, 1);
   plan.launch.block = dim3(kThreads, 1, 1);
   plan.kernel_id = 1;
   if (S > 1) {
-    plan.scratch_floats = (size_t)tiles * S * t.bm;
+    plan.scratch_floats = (size_t)tiles * S * t.bm * (u.hsum ? 1 : t.stages);
     plan.scratch_tickets = (size_t)tiles;
   }
   return TCB200_OK;
@@ -238,13 +283,19 @@ int reduce_launch(const Plan& plan, const float* I, float* O, float* partial, un
     TCB200_CUDA_TRY(cudaGetLastError());
     return TCB200_OK;
   }
+  const int vec = plan.tile.stages;
+  const Units u = units(p, vec);
+  if (vec == 4 && ((((uintptr_t)I) & 15) || (!u.hsum && (((uintptr_t)O) & 15)))) return TCB200_ERR_ALIGNMENT;
+  a.A = u.A; a.C = u.C; a.B = u.B;
   a.cp_log2 = 0;
   while ((1 << a.cp_log2) < plan.tile.bm) ++a.cp_log2;
   a.tiles_b = ceil_div(a.B, plan.tile.bm);
   a.S = plan.tile.bn;
   a.seg = ceil_div(a.C, a.S);
   if (a.S > 1 && (!partial || !tickets)) return TCB200_ERR_INVALID_ARGUMENT;
-  reduce_tile_kernel<<<plan.launch.grid, plan.launch.block, 0, s>>>(a);
+  if (vec == 4 && u.hsum) reduce_tile_kernel<float4, true><<<plan.launch.grid, plan.launch.block, 0, s>>>(a);
+  else if (vec == 4) reduce_tile_kernel<float4, false><<<plan.launch.grid, plan.launch.block, 0, s>>>(a);
+  else reduce_tile_kernel<float, false><<<plan.launch.grid, plan.launch.block, 0, s>>>(a);
   TCB200_CUDA_TRY(cudaGetLastError());
   return TCB200_OK;
 }

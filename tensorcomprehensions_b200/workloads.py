@@ -106,6 +106,42 @@ def mlp3(B=16384, N=2048, O=1024, P=512, Q=256):
 ALL = {"tensordot": tensordot, "batchmatmul": batchmatmul, "tmm": tmm, "group_conv": group_conv,
        "mlp3": mlp3}
 
+# Reductions (not part of the five-comprehension suite; `bench.py --workload <name>` measures one alone):
+# the reference's sum1D / sum2D (test/test_tc_mapper_harness-inl.h:60-146) at sizes that stream 256 MB,
+# and the column-sum form.
+SUM1D_TC = """
+def sum1D(float(M) A) -> (C) {
+    C +=! A(r_m)
+}
+"""
+SUM2D_TC = """
+def sum2D(float(M, N) A) -> (C) {
+    C(m) +=! A(m, r_n)
+}
+"""
+COLSUM_TC = """
+def colsum(float(M, N) A) -> (C) {
+    C(n) +=! A(r_m, n)
+}
+"""
+
+
+def sum1d(M=1 << 26):
+    return Workload("sum1d", 6, SUM1D_TC, "sum1D", [(M,)], ["uniform"], [None], [None], [M], 4 * (M + 1), M, "hbm")
+
+
+def sum2d(M=16384, N=4096):
+    return Workload("sum2d", 7, SUM2D_TC, "sum2D", [(M, N)], ["uniform"], [0], [0], [N], 4 * (M * N + M), M * N, "hbm")
+
+
+def colsum(M=16384, N=4096):
+    return Workload("colsum", 8, COLSUM_TC, "colsum", [(M, N)], ["uniform"], [None], [None], [M], 4 * (M * N + N), M * N,
+                    "hbm")
+
+
+EXTRA = {"sum1d": sum1d, "sum2d": sum2d, "colsum": colsum}
+BY_NAME = dict(ALL, **EXTRA)
+
 # Small instances of the same comprehensions for quick parity checks (odd sizes on purpose).
 SMALL = {
     "tensordot": dict(N=3, C1=20, C2=8, C3=2, H=6, W=10),
