@@ -127,12 +127,15 @@ int tcb200_plan_tile(const tcb200_plan_t* plan, tcb200_tile_t* tile);
 /* Enqueues the plan on `stream` of the CURRENT device (which must be the plan's
  * device) and returns without synchronising.  Replaces CudaRTCFunction::Launch
  * (tc/core/cuda/cuda_rtc.cc:299-387).
- *   inputs : contraction {A, B[, bias]}; tensordot {I0, I1}; group conv {I, W[, bias]}
+ *   inputs : contraction {A, B[, bias]}; tensordot {I0, I1}; group conv {I, W[, bias]}; reduction {I}
  *   outputs: {O}
  *   dev_status: optional device int; a kernel whose bounded wait gives up stores a
  *               nonzero code there instead of spinning (NULL: not reported).
  * The plan is immutable: it may be launched concurrently from several host threads
- * and streams. */
+ * and streams.  One exception: a reduction plan that splits the reduced range over several CTAs
+ * (tile.bn > 1) keeps partial sums in scratch memory owned by the plan, allocated and zeroed by its
+ * first launch (synchronous calls: not inside a stream capture) and freed by tcb200_plan_destroy;
+ * launches of one such plan must not overlap in time. */
 int tcb200_launch(const tcb200_plan_t* plan, const void* const* inputs, int n_inputs,
                   void* const* outputs, int n_outputs, tcb200_stream_t stream,
                   int* dev_status);
