@@ -136,6 +136,23 @@ int tcb200_plan_tile(const tcb200_plan_t* plan, tcb200_tile_t* tile);
  * (tile.bn > 1) keeps partial sums in scratch memory owned by the plan, allocated and zeroed by its
  * first launch (synchronous calls: not inside a stream capture) and freed by tcb200_plan_destroy;
  * launches of one such plan must not overlap in time. */
+/* The same launch for a reduction plan, with its scratch (tickets + partial sums) taken from a fixed
+ * array in device memory that is part of the library image instead of memory the plan allocates: no
+ * allocation happens in this call, at the first launch or ever.  No counterpart in the reference (it
+ * generates single-pass reductions and has no scratch memory to place).
+ *   - Limit: TCB200_STATIC_SCRATCH_TICKETS counters and TCB200_STATIC_SCRATCH_FLOATS partial sums
+ *     (the array is 1 MiB + 16 KiB per device); a plan that needs more is refused with
+ *     TCB200_ERR_TOO_LARGE and nothing is launched.  Plans of other families: TCB200_ERR_INVALID_ARGUMENT.
+ *   - The first call on a device looks the array's address up (cudaGetSymbolAddress, which may load the
+ *     module and synchronise): make that call before any stream capture begins.
+ *   - Every call, and every plan, uses the same array of its device: two calls whose kernels can overlap
+ *     in time (different streams, or host threads) race on it and give wrong sums.  Calls on one stream
+ *     are ordered and safe.  The counters the launch uses are cleared on `stream` ahead of the kernel. */
+#define TCB200_STATIC_SCRATCH_TICKETS 4096
+#define TCB200_STATIC_SCRATCH_FLOATS (256 * 1024)
+int tcb200_reduce_launch_static(const tcb200_plan_t* plan, const void* input, void* output,
+                                tcb200_stream_t stream);
+
 int tcb200_launch(const tcb200_plan_t* plan, const void* const* inputs, int n_inputs,
                   void* const* outputs, int n_outputs, tcb200_stream_t stream,
                   int* dev_status);

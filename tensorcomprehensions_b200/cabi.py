@@ -22,7 +22,7 @@ SYMBOLS = [
     "tcb200_query", "tcb200_plan_create", "tcb200_plan_destroy", "tcb200_plan_geometry",
     "tcb200_plan_describe", "tcb200_plan_tile", "tcb200_launch", "tcb200_l2_flush",
     "tcb200_get_device", "tcb200_set_device", "tcb200_device_name", "tcb200_stream_synchronize",
-    "tcb200_timer_start", "tcb200_timer_stop",
+    "tcb200_timer_start", "tcb200_timer_stop", "tcb200_reduce_launch_static",
 ]
 
 
@@ -192,6 +192,16 @@ class Plan:
         outs = (ctypes.c_void_p * len(out_ptrs))(*out_ptrs)
         check(lib().tcb200_launch(self._h, ins, len(in_ptrs), outs, len(out_ptrs),
                                   ctypes.c_void_p(stream), ctypes.c_void_p(dev_status)), "tcb200_launch")
+
+    def launch_static(self, input, output, stream=None):
+        """Reduction plans only: the launch with the library's fixed scratch array (no allocation; calls
+        share the array, so calls that can overlap in time race)."""
+        import torch
+        if stream is None:
+            stream = torch.cuda.current_stream().cuda_stream
+        check(lib().tcb200_reduce_launch_static(self._h, ctypes.c_void_p(input.data_ptr()),
+                                                ctypes.c_void_p(output.data_ptr()), ctypes.c_void_p(stream)),
+              "tcb200_reduce_launch_static")
 
     def launch(self, inputs, outputs, stream=None, dev_status=None):
         """inputs/outputs: CUDA torch tensors (float32, contiguous).  Enqueues on torch's current stream."""

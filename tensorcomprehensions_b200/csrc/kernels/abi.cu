@@ -62,6 +62,10 @@ struct tcb200_plan {
   std::atomic<void*> scratch{nullptr};
 };
 
+namespace tcb200 {
+const Plan* plan_of(const tcb200_plan_t* handle) { return handle ? &handle->impl : nullptr; }
+}  // namespace tcb200
+
 struct tcb200_timer {
   cudaEvent_t start = nullptr, stop = nullptr;
 };

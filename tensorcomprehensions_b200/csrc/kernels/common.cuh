@@ -92,6 +92,8 @@ constexpr int kReduceMaxSegments = 4096;
 int reduce_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n);
 int reduce_plan(Plan& plan);
 int reduce_launch(const Plan& plan, const float* I, float* O, float* partial, unsigned* tickets, cudaStream_t s);
+// The plan behind the opaque handle (abi.cu owns the handle type).
+const Plan* plan_of(const tcb200_plan_t* handle);
 
 // tensor-core variant (group_conv_tcgen05.cu)
 bool group_conv_tc_ok(const tcb200_problem_t& p);

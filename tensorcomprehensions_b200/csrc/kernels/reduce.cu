@@ -18,6 +18,8 @@
 //    CTA that draws the last ticket of a tile adds the S partials in segment order and writes the
 //    output.  Same bits on every run, one launch, no atomics on data.
 //  * warp-rows kernel (B = 1, short rows): one warp per row, 128-bit loads when the rows allow.
+#include <atomic>
+#include <mutex>
 #include <type_traits>
 
 #include "common.cuh"
@@ -300,4 +302,62 @@ int reduce_launch(const Plan& plan, const float* I, float* O, float* partial, un
   return TCB200_OK;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Launch with the scratch in a fixed array of the library image (no allocation, see tcb200.h)
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+// Tickets first (as 32-bit counters), then the partial sums.  Part of the module image: zero when the
+// module is loaded; the kernel leaves every ticket it used at zero again.
+constexpr size_t kStaticWords = TCB200_STATIC_SCRATCH_TICKETS + TCB200_STATIC_SCRATCH_FLOATS;
+static __device__ __align__(256) float g_static_scratch[kStaticWords];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+std::atomic<float*> g_static_ptr[kMaxDevices];  // address of the array on each device, looked up once
+
+// Once per device: the device address of g_static_scratch.
+int static_scratch(int device, float** ptr) {
+  if (device < 0 || device >= kMaxDevices) return TCB200_ERR_INVALID_ARGUMENT;
+  float* p = g_static_ptr[device].load(std::memory_order_acquire);
+  if (!p) {
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    p = g_static_ptr[device].load(std::memory_order_relaxed);
+    if (!p) {
+      TCB200_CUDA_TRY(cudaGetSymbolAddress((void**)&p, g_static_scratch));
+      if (!p) return TCB200_ERR_CUDA;
+      g_static_ptr[device].store(p, std::memory_order_release);
+    }
+  }
+  *ptr = p;
+  return TCB200_OK;
+}
+
+}  // namespace
 }  // namespace tcb200
+
+extern "C" int tcb200_reduce_launch_static(const tcb200_plan_t* handle, const void* input, void* output,
+                                           tcb200_stream_t stream) {
+  using namespace tcb200;
+  const Plan* plan = plan_of(handle);
+  if (!plan || !input || !output || plan->p.family != TCB200_FAMILY_REDUCTION) return TCB200_ERR_INVALID_ARGUMENT;
+  if (plan->scratch_tickets > (size_t)TCB200_STATIC_SCRATCH_TICKETS ||
+      plan->scratch_floats > (size_t)TCB200_STATIC_SCRATCH_FLOATS)
+    return TCB200_ERR_TOO_LARGE;  // the fixed array cannot hold this plan's partial sums: nothing is launched
+  int cur = -1;
+  TCB200_CUDA_TRY(cudaGetDevice(&cur));
+  if (cur != plan->device) return TCB200_ERR_INVALID_ARGUMENT;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  float* base = nullptr;
+  unsigned* tickets = nullptr;
+  float* partial = nullptr;
+  if (plan->scratch_tickets > 0) {
+    const int st = static_scratch(cur, &base);
+    if (st != TCB200_OK) return st;
+    tickets = reinterpret_cast<unsigned*>(base);
+    partial = base + TCB200_STATIC_SCRATCH_TICKETS;
+    // the counters must start at zero even if an earlier kernel on this array did not run to its end
+    TCB200_CUDA_TRY(cudaMemsetAsync(tickets, 0, plan->scratch_tickets * sizeof(unsigned), s));
+  }
+  return reduce_launch(*plan, static_cast<const float*>(input), static_cast<float*>(output), partial, tickets, s);
+}
