@@ -8,15 +8,15 @@
 //
 // All of it is HBM streaming (4 * (A*C*B + A*B) bytes, one add per element).  Two kernels:
 //  * tile kernel (any shape): a CTA of 256 threads owns CP output columns (a power of two, one warp
-//    wide by default: narrow tiles give many CTAs and few segments)
-//    of one row a and one segment of the reduced range; thread (tx, ty) of the CP x (256 / CP) layout
-//    adds the elements c = ty, ty + TY, ... of column tx, so a warp reads consecutive addresses
+//    wide by default: narrow tiles give many CTAs and few segments) of one row a and one of S
+//    interleaved shares ("segments") of the reduced range; thread (tx, ty) of the CP x (256 / CP)
+//    layout adds elements ty, ty + TY, ... of column tx, so a warp reads consecutive addresses
 //    whatever B is (B = 1: consecutive c; B >= 32: consecutive columns).  The TY partial sums of a
 //    column are combined through shared memory in a fixed order.
-//    When the output alone gives too few CTAs to fill 148 SMs, the reduced range is cut into S
-//    segments (grid.y); each CTA leaves its partial sums in scratch memory, takes a ticket, and the
-//    CTA that draws the last ticket of a tile adds the S partials in segment order and writes the
-//    output.  Same bits on every run, one launch, no atomics on data.
+//    When the output alone gives too few CTAs to fill 148 SMs, S > 1 (grid.y): each CTA leaves its
+//    partial sums in scratch memory, takes a ticket, and the CTA that draws the last ticket of a tile
+//    adds the S partials in a fixed order and writes the output.  Same bits on every run, one launch,
+//    no atomics on data.
 //  * warp-rows kernel (B = 1, short rows): one warp per row, 128-bit loads when the rows allow.
 #include <atomic>
 #include <mutex>
@@ -34,7 +34,6 @@ struct ReduceArgs {
   float* O;
   long long A, C, B;  // in elements of the kernel's value type (see reduce_tile_kernel)
   long long tiles_b;  // column tiles per row a
-  long long seg;      // reduced elements per segment
   int S;              // segments
   int cp_log2;        // log2 of the columns per CTA
   int accumulate;
@@ -64,21 +63,28 @@ __global__ void __launch_bounds__(kThreads) reduce_tile_kernel(ReduceArgs a) {
   const int s = blockIdx.y;
   const long long arow = tile / a.tiles_b, ct = tile - arow * a.tiles_b;
   const long long col = ct * CP + tx;
-  const long long c0 = (long long)s * a.seg, c1 = min(a.C, c0 + a.seg);
+  // Segment s takes the blocks s, s + S, s + 2S, ... of UNROLL * TY reduced elements: interleaved, so
+  // that all segments of a tile end within one block of each other whatever the number of CTAs per SM.
+  const long long BLK = (long long)UNROLL * TY;
   T acc[UNROLL];
 #pragma unroll
   for (int k = 0; k < UNROLL; ++k) vzero(acc[k]);
   if (col < a.B) {
     const T* base = reinterpret_cast<const T*>(a.I) + (size_t)arow * a.C * a.B + col;
-    long long c = c0 + ty;
-    for (; c + (long long)(UNROLL - 1) * TY < c1; c += (long long)UNROLL * TY) {
-      T v[UNROLL];
+    for (long long b0 = (long long)s * BLK; b0 < a.C; b0 += (long long)a.S * BLK) {
+      const long long c = b0 + ty;
+      if (b0 + BLK <= a.C) {
+        T v[UNROLL];
 #pragma unroll
-      for (int k = 0; k < UNROLL; ++k) v[k] = __ldg(base + (size_t)(c + (long long)k * TY) * a.B);
+        for (int k = 0; k < UNROLL; ++k) v[k] = __ldg(base + (size_t)(c + (long long)k * TY) * a.B);
 #pragma unroll
-      for (int k = 0; k < UNROLL; ++k) acc[k] = vadd(acc[k], v[k]);
+        for (int k = 0; k < UNROLL; ++k) acc[k] = vadd(acc[k], v[k]);
+      } else {  // the last, ragged block of the range
+#pragma unroll
+        for (int k = 0; k < UNROLL; ++k)
+          if (c + (long long)k * TY < a.C) acc[k] = vadd(acc[k], __ldg(base + (size_t)(c + (long long)k * TY) * a.B));
+      }
     }
-    for (; c < c1; c += TY) acc[0] = vadd(acc[0], __ldg(base + (size_t)c * a.B));  // fewer than UNROLL left
   }
 #pragma unroll
   for (int h = UNROLL / 2; h > 0; h >>= 1)
@@ -181,13 +187,12 @@ Units units(const tcb200_problem_t& p, int vec) {
   return Units{p.red[0], p.red[1], p.red[2] / 4, false};
 }
 
-// Segments of the tile kernel: enough CTAs for eight per SM (all that fit), at least 16 reduced
-// elements per thread row.
+// Segments of the tile kernel: enough CTAs for eight per SM, at least 32 reduced elements per thread row.
 int auto_segments(const Units& u, int cp_log2) {
   const long long CP = 1ll << cp_log2, TY = kThreads / CP;
   const long long tiles = u.A * ceil_div(u.B, CP);
   const long long want = ceil_div(8 * kNumSMs, tiles);
-  const long long most = std::max<long long>(1, u.C / (16 * TY));
+  const long long most = std::max<long long>(1, u.C / (32 * TY));
   return (int)std::max<long long>(1, std::min<long long>({want, most, (long long)kReduceMaxSegments}));
 }
 
@@ -256,9 +261,8 @@ int reduce_plan(Plan& plan) {
   if (tiles > 0x7fffffffll) return TCB200_ERR_TOO_LARGE;
   int S = t.bn > 0 ? t.bn : auto_segments(u, cp_log2);
   if (S > kReduceMaxSegments) return TCB200_ERR_INVALID_ARGUMENT;
-  S = (int)std::min<long long>(S, u.C);
-  const long long seg = ceil_div(u.C, S);
-  S = (int)ceil_div(u.C, seg);  // no empty segment
+  const long long unroll = t.stages == 4 ? 4 : 8, TY = kThreads >> cp_log2;
+  S = (int)std::min<long long>(S, ceil_div(u.C, unroll * TY));  // no segment without a block
   t.bn = S;
   plan.launch.grid = dim3((unsigned)tiles, (unsigned)S, 1);
   plan.launch.block = dim3(kThreads, 1, 1);
@@ -278,7 +282,7 @@ int reduce_launch(const Plan& plan, const float* I, float* O, float* partial, un
   a.accumulate = p.accumulate;
   a.partial = partial; a.tickets = tickets;
   if (plan.kernel_id == 2) {
-    a.S = 1; a.seg = a.C; a.cp_log2 = 0; a.tiles_b = 1;
+    a.S = 1; a.cp_log2 = 0; a.tiles_b = 1;
     const bool vec = (a.C & 3) == 0 && (((uintptr_t)I) & 15) == 0;
     if (vec) reduce_rows_warp_kernel<true><<<plan.launch.grid, plan.launch.block, 0, s>>>(a);
     else reduce_rows_warp_kernel<false><<<plan.launch.grid, plan.launch.block, 0, s>>>(a);
@@ -293,7 +297,6 @@ int reduce_launch(const Plan& plan, const float* I, float* O, float* partial, un
   while ((1 << a.cp_log2) < plan.tile.bm) ++a.cp_log2;
   a.tiles_b = ceil_div(a.B, plan.tile.bm);
   a.S = plan.tile.bn;
-  a.seg = ceil_div(a.C, a.S);
   if (a.S > 1 && (!partial || !tickets)) return TCB200_ERR_INVALID_ARGUMENT;
   if (vec == 4 && u.hsum) reduce_tile_kernel<float4, true><<<plan.launch.grid, plan.launch.block, 0, s>>>(a);
   else if (vec == 4) reduce_tile_kernel<float4, false><<<plan.launch.grid, plan.launch.block, 0, s>>>(a);
