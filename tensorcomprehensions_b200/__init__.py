@@ -13,7 +13,9 @@ def __getattr__(name):
     if name in ("define", "compile", "autotune", "autotune_and_compile", "MappingOptions", "TC", "HostStagedExecutor",
                 "Tuner", "TunerConfig", "Executor", "assert_almost_equal", "make_naive_options_factory",
                 "make_load_from_cache_options_factory", "make_autotuned_options_factory",
-                "MappingOptionsCache", "tclib", "sharding"):
+                "MappingOptionsCache", "tclib", "sharding", "make_autograd", "logtostderr", "debug_lang",
+                "debug_halide", "debug_tc_mapper", "debug_tuner", "dump_cuda", "dump_ptx", "cuda_compiler",
+                "llvm_flags", "nvcc_flags"):
         import importlib
         api = importlib.import_module(".api", __name__)
         return getattr(api, name)

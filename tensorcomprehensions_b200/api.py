@@ -290,3 +290,62 @@ class TC(object):
 
 def define(tc: str, mapping_options_factory: Callable) -> TC:
     return TC(tc, mapping_options_factory)
+
+
+class _AutogradFunction(torch.autograd.Function):
+    """Saves the inputs of the forward call; backward hands (inputs..., output gradients...) to the
+    user's backward function and returns what it computes, one gradient per input."""
+
+    @staticmethod
+    def forward(ctx, forward_fun, backward_fun, *inputs):
+        ctx.backward_fun = backward_fun
+        ctx.save_for_backward(*inputs)
+        return forward_fun(*inputs)
+
+    @staticmethod
+    def backward(ctx, *gradients):
+        if ctx.backward_fun is None:
+            return (None, None) + (None,) * len(ctx.saved_tensors)
+        grads = ctx.backward_fun(*ctx.saved_tensors, *(g.contiguous() for g in gradients))
+        if isinstance(grads, torch.Tensor):
+            grads = (grads,)
+        # no gradient for the two callables that travel as the first arguments
+        return (None, None) + tuple(grads)
+
+
+class Autograd(object):
+    def __init__(self, forward_fun, backward_fun):
+        self.forward_fun, self.backward_fun = forward_fun, backward_fun
+
+    def __call__(self, *inputs):
+        return _AutogradFunction.apply(self.forward_fun, self.backward_fun, *inputs)
+
+
+def make_autograd(forward_fun: Callable, backward_fun: Callable) -> Autograd:
+    """A callable with torch.autograd support from a forward and a backward function, both usually entry
+    points of a tc.define()d object (tensor_comprehensions/__init__.py:513-601): the backward function
+    receives the forward inputs followed by the gradients of the outputs and returns one gradient per
+    input.  The backward comprehensions must themselves match a kernel family (the matmul gradients are
+    contractions; gradients written with `where` windows are not matched and raise at first use)."""
+    return Autograd(forward_fun, backward_fun)
+
+
+# Debug toggles of the reference's tclib (tensor_comprehensions/__init__.py:25-34).  The stages they
+# print from (Halide, the polyhedral mapper, NVRTC, LLVM) do not exist in this backend: the calls are
+# accepted and recorded so that scripts written for the reference run unchanged.
+_debug_state = {}
+
+
+def _toggle(name):
+    def setter(value=True):
+        _debug_state[name] = value
+        return value
+    setter.__name__ = name
+    setter.__doc__ = "Accepted for source compatibility with the reference; nothing is printed by this backend."
+    return setter
+
+
+logtostderr, debug_lang, debug_halide, debug_tc_mapper, debug_tuner, dump_cuda, dump_ptx = (
+    _toggle(n) for n in ("logtostderr", "debug_lang", "debug_halide", "debug_tc_mapper", "debug_tuner",
+                         "dump_cuda", "dump_ptx"))
+cuda_compiler, llvm_flags, nvcc_flags = (_toggle(n) for n in ("cuda_compiler", "llvm_flags", "nvcc_flags"))

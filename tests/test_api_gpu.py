@@ -122,6 +122,30 @@ def test_autotune_stores_to_and_loads_from_a_cache_file(cuda, tmp_path):
     assert len(cache) == 2 and cache.load(w.tc, w.entry, [X, Y]) == [best] and len(cache.load(w.tc, w.entry, [X2, Y2])) == 1
 
 
+def test_make_autograd_with_matmul_gradients(cuda):
+    """tc.make_autograd (tensor_comprehensions/__init__.py:513-601) with the matmul gradients of
+    python/benchmarks/python_overhead.py:40-50: all three comprehensions are contractions."""
+    T = tc.define("""
+def matmul(float(M, K) A, float(K, N) B) -> (C) { C(m, n) +=! A(m, r_k) * B(r_k, n) }
+def matmul_agrad(float(K, N) B, float(M, N) d_C) -> (d_A) { d_A(m, k) +=! d_C(m, r_n) * B(k, r_n) }
+def matmul_bgrad(float(M, K) A, float(M, N) d_C) -> (d_B) { d_B(k, n) +=! d_C(r_m, n) * A(r_m, k) }
+""", tc.make_naive_options_factory())
+
+    def backward(A, B, d_C):
+        return T.matmul_agrad(B, d_C), T.matmul_bgrad(A, d_C)
+
+    fn = tc.make_autograd(T.matmul, backward)
+    A = torch.randn(70, 40, device=cuda, requires_grad=True)
+    B = torch.randn(40, 50, device=cuda, requires_grad=True)
+    w = torch.randn(70, 50, device=cuda)
+    (fn(A, B) * w).sum().backward()
+    A2, B2 = A.detach().clone().requires_grad_(), B.detach().clone().requires_grad_()
+    ((A2.double() @ B2.double()).float() * w).sum().backward()
+    assert_close(A.grad, A2.grad.cpu(), 50, what="d_A")
+    assert_close(B.grad, B2.grad.cpu(), 70, what="d_B")
+    assert tc.debug_tc_mapper(True) is True and tc.dump_cuda(False) is False  # accepted, no effect
+
+
 def test_accumulating_reduction_keeps_output(cuda):
     """'+=' without '!' adds to what the output holds (test/cuda/test_compile_and_run.cc:181-200)."""
     tcs = "def mm(float(M,K) A, float(K,N) B) -> (C) { C(m,n) += A(m,k) * B(k,n) }"
