@@ -3,15 +3,16 @@
 
 #include <string>
 
+#include "tc/library/tc_text.h"
+
 namespace tc {
 
 static constexpr auto TC_MATMUL_NAME = "matmul";
 
 // transposeFirst: A is stored (K, N) and read A(k, i); transposeSecond: B is stored (M, K) and read B(j, k).
 inline std::string makeMatmulTc(bool transposeFirst = false, bool transposeSecond = false) {
-  const std::string a = transposeFirst ? "float(K, N) A" : "float(N, K) A", ai = transposeFirst ? "A(k, i)" : "A(i, k)";
-  const std::string b = transposeSecond ? "float(M, K) B" : "float(K, M) B", bi = transposeSecond ? "B(j, k)" : "B(k, j)";
-  return "def matmul(" + a + ", " + b + ") -> (O) {\n  O(i, j) +=! " + ai + " * " + bi + "\n}\n";
+  return library_detail::matmulText(TC_MATMUL_NAME, false, transposeFirst, transposeSecond, "A", "B", "O", "N", "K", "M",
+                                    "i", "k", "j");
 }
 
 }  // namespace tc

@@ -30,6 +30,26 @@ inline std::string fcreluChain(int layers, const std::string& name) {
   return "def " + name + "(" + params + ") -> (" + outs + ") {\n" + body + "}\n";
 }
 
+// matmul in its four storage forms and its batched form (tc/library/matmul.h:24-45,
+// batch_matmul.h:22-26): out(rows, cols) +=! lhs * rhs with an optional leading batch index.
+inline std::string matmulText(const std::string& name, bool batched, bool transposeFirst, bool transposeSecond,
+                              const char* lhs, const char* rhs, const char* out, const char* rowSize, const char* redSize,
+                              const char* colSize, const char* row, const char* red, const char* col) {
+  const std::string B = batched ? "B, " : "", b = batched ? "b, " : "";
+  auto decl = [&](const char* t, const char* s0, const char* s1) {
+    return "float(" + B + s0 + ", " + s1 + ") " + t;
+  };
+  auto use = [&](const char* t, const char* i0, const char* i1) {
+    return std::string(t) + "(" + b + i0 + ", " + i1 + ")";
+  };
+  const std::string a = transposeFirst ? decl(lhs, redSize, rowSize) : decl(lhs, rowSize, redSize);
+  const std::string c = transposeSecond ? decl(rhs, colSize, redSize) : decl(rhs, redSize, colSize);
+  const std::string ai = transposeFirst ? use(lhs, red, row) : use(lhs, row, red);
+  const std::string ci = transposeSecond ? use(rhs, col, red) : use(rhs, red, col);
+  return "def " + name + "(" + a + ", " + c + ") -> (" + out + ") {\n  " + use(out, row, col) + " +=! " + ai + " * " + ci +
+         "\n}\n";
+}
+
 // convolution / group_convolution with literal strides (tc/library/convolution.h:27-31,
 // group_convolution.h:26-34): the image index is  stride * out + tap.
 inline std::string conv2d(bool grouped, int strideH, int strideW) {
