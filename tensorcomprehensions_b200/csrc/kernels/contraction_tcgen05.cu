@@ -58,6 +58,7 @@ struct TcArgs {
   int a_batched, b_batched;  // 0: operand shared by all batch entries
   int c_vec;                 // 128-bit stores allowed
   int tma_store;             // pair kernel: epilogue through the staging tile and tiled TMA stores
+  int transpose_out;         // pair kernel: the tile's element (row, col) goes to C[col * ldc + row] (operands swapped)
   int* dev_status;
 };
 
@@ -1015,6 +1016,22 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
           bb[j + 1] = a.bias_on_m ? bias_m : __shfl_sync(0xffffffffu, bias_n.y, src);
         }
         if (row >= a.M || nb >= a.N) return;
+        if (a.transpose_out) {
+          // operands swapped by the host: this tile's rows are columns of C.  For a fixed column j the
+          // 32 lanes of the warp hold 32 consecutive rows, i.e. 32 consecutive floats of C's row nb + j.
+          float* ccol = a.C + (int64_t)bz * a.stride_c + row;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int n = nb + j;
+            if (n < a.N) {
+              float* dst = ccol + (int64_t)n * a.ldc;
+              float o = v[j];
+              if (a.accumulate) o += *dst;
+              *dst = apply_epilogue_rt(a.epi, o, bb[j]);
+            }
+          }
+          return;
+        }
         if (a.c_vec && nb + 16 <= a.N) {
 #pragma unroll
           for (int j = 0; j < 16; j += 4) {
@@ -1288,8 +1305,22 @@ int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max,
     ++cnt;
   };
   if (pair_ok) push_pair();
+  // Operands swapped (tile 128 x 256): pairs along N when there are no two row tiles to pair.  Measured on
+  // the transposed matmul (M = 128, N = 16384, K = 4096): 87 us against 86 us for 112-wide single-CTA tiles
+  // - the large operand then streams from HBM through the four-slot A ring (64 KB in flight per SM), which
+  // eats what the pair saves in shared-memory traffic; a wave of its tiles is costed at 1.02 single-CTA waves.
+  const bool swap_ok = !pair_ok && p.N >= 2 * BM;
+  const double swap_cost = (double)ceil_div(ceil_div(p.N, 2 * BM) * ceil_div(p.M, kPairBN) * p.batch, kNumSMs / 2) * 1.02;
+  auto push_swapped = [&]() {
+    if (cnt < max && out)
+      out[cnt] = tcb200_tile_t{TCB200_VARIANT_TCGEN05_PAIR, BM, 2 * BM, BK, kPairBSlots, kTsThreads, 3};
+    ++cnt;
+  };
+  const bool swap_first = swap_ok && swap_cost < cost[order[0]];
+  if (swap_first) push_swapped();
   for (int i = 0; i < 3; ++i)
     if (p.N >= ts_bn[order[i]]) push_ts(ts_bn[order[i]]);
+  if (swap_ok && !swap_first) push_swapped();
   const int bns[] = {128, 256, 64};
   for (int bn : bns)
     if (p.N >= bn) push(bn, 3);
@@ -1302,16 +1333,22 @@ int contraction_tc_plan(Plan& plan) {
   if (!shape_ok(p)) return TCB200_ERR_UNSUPPORTED;
   tcb200_tile_t& t = plan.tile;
   if (t.variant == TCB200_VARIANT_TCGEN05_PAIR) {
+    // tile 128 x 256: the operands trade places (C^T = B * A^T), so the 256-row pair tile runs along N
+    // and a problem with few rows but many columns (the transposed matmul: M = 128) still pairs up
+    const bool swapped = t.bm == BM && t.bn == 2 * BM;
     if (t.bn == 0) t.bn = kPairBN;
     if (t.split_tf32 == 0) t.split_tf32 = 3;
-    if (t.bn != kPairBN || t.split_tf32 != 3) return TCB200_ERR_UNSUPPORTED;
-    if (ceil_div(p.M, 2 * BM) > 65535) return TCB200_ERR_UNSUPPORTED;
-    t.bm = 2 * BM; t.bk = BK; t.stages = kPairBSlots; t.threads = kTsThreads;
-    const int64_t tiles = ceil_div(p.N, kPairBN) * ceil_div(p.M, 2 * BM) * p.batch;
+    if (!swapped && t.bn != kPairBN) return TCB200_ERR_UNSUPPORTED;
+    if (t.split_tf32 != 3) return TCB200_ERR_UNSUPPORTED;
+    const int64_t rows = swapped ? p.N : p.M, cols = swapped ? p.M : p.N;
+    if (ceil_div(rows, 2 * BM) > 65535) return TCB200_ERR_UNSUPPORTED;
+    t.bm = swapped ? BM : 2 * BM; t.bn = swapped ? 2 * BM : kPairBN;
+    t.bk = BK; t.stages = kPairBSlots; t.threads = kTsThreads;
+    const int64_t tiles = ceil_div(cols, kPairBN) * ceil_div(rows, 2 * BM) * p.batch;
     plan.launch.grid = dim3(2u * (unsigned)std::min<int64_t>(tiles, kNumSMs / 2), 1, 1);
     plan.launch.block = dim3(kTsThreads, 1, 1);
     plan.launch.smem = ts_pair_smem_bytes();
-    plan.kernel_id = 301283;
+    plan.kernel_id = swapped ? 301284 : 301283;
     return TCB200_OK;
   }
   if (t.bn == 0) t.bn = 128;
@@ -1339,10 +1376,17 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
   const tcb200_problem_t& p = plan.p;
   if (((uintptr_t)A | (uintptr_t)B) & 15) return TCB200_ERR_ALIGNMENT;
   CUtensorMap ta, tb;
-  int st = make_operand_map(&ta, A, p.K, p.M, p.lda, p.batch, p.stride_a, BM);
-  if (st != TCB200_OK) return st;
-  st = make_operand_map(&tb, B, p.K, p.N, p.ldb, p.batch, p.stride_b,
-                        plan.kernel_id == 301283 ? kPairBN / 2 : plan.tile.bn);
+  int st;
+  if (plan.kernel_id == 301284) {  // operands swapped: B feeds the 128-row A slots, A the 64-row B halves
+    st = make_operand_map(&ta, B, p.K, p.N, p.ldb, p.batch, p.stride_b, BM);
+    if (st != TCB200_OK) return st;
+    st = make_operand_map(&tb, A, p.K, p.M, p.lda, p.batch, p.stride_a, kPairBN / 2);
+  } else {
+    st = make_operand_map(&ta, A, p.K, p.M, p.lda, p.batch, p.stride_a, BM);
+    if (st != TCB200_OK) return st;
+    st = make_operand_map(&tb, B, p.K, p.N, p.ldb, p.batch, p.stride_b,
+                          plan.kernel_id == 301283 ? kPairBN / 2 : plan.tile.bn);
+  }
   if (st != TCB200_OK) return st;
   TcArgs a;
   a.C = C; a.bias = bias;
@@ -1355,7 +1399,14 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
   a.c_vec = ((uintptr_t)C & 15) == 0 && p.ldc % 4 == 0 && p.stride_c % 4 == 0 && bias_vec;
   a.dev_status = dev_status;
   a.tma_store = 0;
+  a.transpose_out = 0;
   switch (plan.kernel_id) {
+    case 301284:
+      a.M = (int)p.N; a.N = (int)p.M;
+      std::swap(a.a_batched, a.b_batched);
+      a.bias_on_m = !p.bias_on_m;
+      a.transpose_out = 1;
+      return launch_pair(plan, ta, tb, tb, a, s);  // no staging tile: the third map is unused
     case 301283: {
       // output map for the staged epilogue: {N, M, batch}, boxes of 32 columns x 128 rows
       CUtensorMap tc;
