@@ -29,15 +29,21 @@ def _decl(name, idx, size_of):
     return "float(%s) %s" % (", ".join(size_of[i] for i in idx), name)
 
 
-def _contraction_case(rng):
-    """O(batch..., m..., n...) +=! A(batch..., m.. | k..) * B(batch..., n.. | k..) with either group first."""
+def _contraction_case(rng, large=False):
+    """O(batch..., m..., n...) +=! A(batch..., m.. | k..) * B(batch..., n.. | k..) with either group first.
+    large: extents that reach the tensor-core tiles (two indices per group at most, 8..48 each)."""
     taken = set()
     nb, nm, nn, nk = rng.randint(0, 2), rng.randint(1, 2), rng.randint(0, 2), rng.randint(1, 2)
+    if large:
+        nb, nn = rng.randint(0, 1), rng.randint(1, 2)
     b, m, n, k = (_names(rng, c, taken) for c in (nb, nm, nn, nk))
     ext = {v: rng.randint(1, 24) for v in b + m + n + k}
+    if large:
+        ext = {v: (rng.randint(1, 3) if v in b else 4 * rng.randint(2, 12)) for v in ext}
     size_of = {v: "S" + v.upper() for v in ext}
-    a_idx = b + (m + k if rng.random() < 0.5 else k + m)
-    b_idx = b + (n + k if rng.random() < 0.5 else k + n)
+    k_last = 0.85 if large else 0.5  # the tensor-core tiles take operands whose reduction index is innermost
+    a_idx = b + (m + k if rng.random() < k_last else k + m)
+    b_idx = b + (n + k if rng.random() < k_last else k + n)
     o_idx = b + m + n
     ops = [("A", a_idx), ("B", b_idx)]
     if rng.random() < 0.5:
@@ -101,7 +107,7 @@ def _reduction_case(rng):
     return text, [ext], lambda I: I.sum(dims), red
 
 
-CASES = {"contraction": (_contraction_case, 40), "tensordot": (_tensordot_case, 12), "conv": (_conv_case, 20),
+CASES = {"contraction": (_contraction_case, 40), "contraction_large": (lambda rng: _contraction_case(rng, True), 16), "tensordot": (_tensordot_case, 12), "conv": (_conv_case, 20),
          "reduction": (_reduction_case, 20)}
 
 
