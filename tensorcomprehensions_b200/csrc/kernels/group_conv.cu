@@ -237,14 +237,22 @@ __global__ void __launch_bounds__(256 / FPT) group_conv_item_kernel(ConvArgs a) 
   const int g = item % a.G;
   const int taps = a.C * a.KH * a.KW;
   const int F = a.F;
-  float* Ws = smem;                      // [taps][F]
-  float* Is = smem + (size_t)taps * F;   // [C][H][kRowsPitch]
+  // Filters stay in their global order (f, tap), rows padded to `wp` floats: 16-byte copies in, and the
+  // FPT rows a thread reads at one tap fall into distinct banks (wp = taps + 4: 2 * wp = 8 mod 32 for the
+  // benchmark's 144 taps).  Transposing them to [tap][f] on the way in took 2304 four-byte cp.async per
+  // item whose shared-memory writes conflict 16 ways: 4.7 us of the kernel, measured by leaving it out.
+  const int wp = taps + 4;
+  float* Ws = smem;                       // [F][wp]
+  float* Is = smem + (size_t)F * wp;      // [C][H][kRowsPitch]
   const int tid = threadIdx.x;
 
-  // group 0: filters (global order (f, tap), scattered to [tap][f]) + first quarter of the channels
+  // group 0: filters + first quarter of the channels
   const float* Wg = a.W + (size_t)g * F * taps;
-  for (int f = 0; f < F; ++f)
-    for (int t = tid; t < taps; t += kItemThreads) cp_async_4(Ws + (size_t)t * F + f, Wg + (size_t)f * taps + t);
+  const int tq = taps >> 2;  // 16-byte pieces per filter (taps % 4 == 0 because C % 4 == 0)
+  for (int i = tid; i < F * tq; i += kItemThreads) {
+    const int f = i / tq, piece = i - f * tq;
+    cp_async_16(Ws + (size_t)f * wp + 4 * piece, Wg + (size_t)f * taps + 4 * piece);
+  }
   const float* Ig = a.I + (size_t)item * a.C * a.H * a.Wd;
   const int rows_q = (a.C / 4) * a.H;  // rows per quarter (C % 4 == 0 checked by the plan)
 #pragma unroll
@@ -277,12 +285,12 @@ __global__ void __launch_bounds__(256 / FPT) group_conv_item_kernel(ConvArgs a) 
   const int KW = KHT > 0 ? kItemKW : a.KW;  // the compile-time form is the square 3x3 filter
   const int plane_step = (a.H - KH) * kRowsPitch;  // from the last filter row of a channel to the next channel
   auto channels = [&](int c0, int c1) {
-    // running pointers: input row (c, h + kh) and filter vector (c, kh, kw = 0, 4 * fq)
+    // running pointers: input row (c, h + kh) and the taps (c, kh, kw = 0) of filter FPT * fq
     const float* rp = Is + (c0 * a.H + h) * kRowsPitch;
-    const float* wrow = Ws + c0 * KH * KW * F + fq * FPT;
+    const float* wrow = Ws + (size_t)(fq * FPT) * wp + c0 * KH * KW;
     for (int c = c0; c < c1; ++c, rp += plane_step) {
 #pragma unroll
-      for (int kh = 0; kh < KH; ++kh, rp += kRowsPitch, wrow += KW * F) {
+      for (int kh = 0; kh < KH; ++kh, rp += kRowsPitch, wrow += KW) {
         const float4* row = reinterpret_cast<const float4*>(rp);
         float x[16];
 #pragma unroll
@@ -293,19 +301,14 @@ __global__ void __launch_bounds__(256 / FPT) group_conv_item_kernel(ConvArgs a) 
 #pragma unroll
         for (int kw = 0; kw < kItemKW; ++kw) {
           if (kw < KW) {
-            float2 wp[FPT / 2];
-            if constexpr (FPT == 4) {
-              const float4 wv = *reinterpret_cast<const float4*>(wrow + kw * F);
-              wp[0] = make_float2(wv.x, wv.y);
-              wp[1] = make_float2(wv.z, wv.w);
-            } else {
-              wp[0] = *reinterpret_cast<const float2*>(wrow + kw * F);
-            }
+            float2 wv[FPT / 2];
+#pragma unroll
+            for (int j = 0; j < FPT / 2; ++j) wv[j] = make_float2(wrow[(2 * j) * wp + kw], wrow[(2 * j + 1) * wp + kw]);
 #pragma unroll
             for (int w = 0; w < kItemOW; ++w) {
               const float2 xx = make_float2(x[w + kw], x[w + kw]);
 #pragma unroll
-              for (int j = 0; j < FPT / 2; ++j) acc[j][w] = __ffma2_rn(xx, wp[j], acc[j][w]);
+              for (int j = 0; j < FPT / 2; ++j) acc[j][w] = __ffma2_rn(xx, wv[j], acc[j][w]);
             }
           }
         }
@@ -367,7 +370,7 @@ bool item_ok(const tcb200_problem_t& p) {
   return W == 16 && OW <= kItemOW && KW <= kItemKW && F % 4 == 0 && C % 4 == 0 &&
          (F / 4) * ((OH + 7) / 8 * 8) <= kItemThreads &&
          F * OH * OW <= C * H * kRowsPitch &&
-         sizeof(float) * (size_t)(C * KH * KW * F + C * H * kRowsPitch) <= 48 * 1024;
+         sizeof(float) * (size_t)((C * KH * KW + 4) * F + C * H * kRowsPitch) <= 48 * 1024;
 }
 
 bool rows_ok(const tcb200_problem_t& p) {
@@ -483,7 +486,7 @@ int group_conv_plan(Plan& plan) {
     t.threads = two ? 128 : kItemThreads;
     plan.launch.grid = dim3((unsigned)(p.conv[0] * p.conv[1]), 1, 1);
     plan.launch.block = dim3(t.threads, 1, 1);
-    plan.launch.smem = sizeof(float) * (size_t)(p.conv[2] * p.conv[6] * p.conv[7] * p.conv[3] +
+    plan.launch.smem = sizeof(float) * (size_t)((p.conv[2] * p.conv[6] * p.conv[7] + 4) * p.conv[3] +
                                                  p.conv[2] * p.conv[4] * kRowsPitch);
     plan.kernel_id = two ? 102 : 101;
     return TCB200_OK;
