@@ -24,7 +24,7 @@ def test_small_instances_through_define(cuda, name):
     refs = orc.as_list(orc.LOOP[name](*ins))
     assert len(outs) == len(refs)
     for o, r, L in zip(outs, refs, w.reduction):
-        assert_close(o, r, L, ins, STRICT[name], name, strict_is_gate=False)
+        assert_close(o, r, L, ins, STRICT[name], name, strict_is_gate=True)
     # second call hits the per-shape executor cache and gives the same bits
     outs2 = getattr(T, w.entry)(*[t.to(cuda) for t in ins])
     outs2 = list(outs2) if isinstance(outs2, tuple) else [outs2]
@@ -42,8 +42,10 @@ def test_full_size_through_compile(cuda, name):
     res = exe(*dev_ins, outputs=tuple(outs))
     torch.cuda.synchronize()
     refs = orc.as_list(orc.ATEN[name](*ins))
+    # the family defaults meet the reference's own checkRtol (test/test_harness_aten.h:36-54) at its
+    # benchmark precisions on these inputs, not only the benchmark criterion
     for o, r, L in zip(outs, refs, w.reduction):
-        assert_close(o, r, L, ins, STRICT[name], exe.compiled_source, strict_is_gate=False)
+        assert_close(o, r, L, ins, STRICT[name], exe.compiled_source, strict_is_gate=True)
     prof = exe.profile(*dev_ins, outputs=outs)
     assert prof["kernel_runtime_us"] > 0
 

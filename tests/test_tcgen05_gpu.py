@@ -211,8 +211,10 @@ def test_tmm_full_size_tcgen05(cuda, bn, split, ts):
     A, B = wl.make_inputs(w)
     p = cabi.contraction_problem(1, 128, 16384, 4096, True, True)
     out, plan = run_plan(p, [A.to(cuda), B.to(cuda)], (128, 16384), tc_tile(bn, split, ts))
+    # gate on the reference's own checkRtol for the A-in-tensor-memory tiles (the family default among them);
+    # the plain SS tiles with one long accumulation per tile only log it
     assert_close(out, orc.aten_tmm(A, B), 4096, [A, B], STRICT["tmm"] if split == 3 else None, plan.describe(),
-                 strict_is_gate=False)
+                 strict_is_gate=ts)
 
 
 def test_mlp3_full_size_tcgen05(cuda):
