@@ -71,3 +71,27 @@ def test_query_and_plan_without_gpu():
     assert pt.geometry() == ((148, 1, 1), (448, 1, 1)) and "tcgen05_ts" in pt.describe()  # implicit GEMM
     band = [t for t in cabi.query(c) if t.variant == cabi.VARIANT_SIMT and t.bk == 0][0]
     assert cabi.Plan(c, band).geometry()[0][0] == 32 * 32
+
+
+def test_reduction_plans_and_the_static_scratch_limit_without_a_device():
+    """Planning needs no GPU; the no-allocation launch refuses an oversize plan (and a plan of another family)
+    on the sizes alone, before any CUDA call."""
+    p = cabi.reduction_problem(1, 1 << 26, 1)
+    plan = cabi.Plan(p)
+    grid, block = plan.geometry()
+    assert block == (256, 1, 1) and grid[0] == 1 and grid[1] > 1          # one output tile, many segments
+    assert "tcb200::reduction A=1 C=67108864 B=1" in plan.describe() and "stages=4" in plan.describe()
+    assert cabi.Plan(cabi.reduction_problem(16384, 4096, 1)).geometry()[0][1] == 1  # warp per row: no segments
+    odd = cabi.Plan(cabi.reduction_problem(3, 1001, 7))                    # no 128-bit loads possible
+    assert "stages=1" in odd.describe()
+    t = cabi.Tile()
+    t.variant, t.bm, t.bn, t.stages = cabi.VARIANT_SIMT, 32, 512, 1
+    big = cabi.Plan(cabi.reduction_problem(64, 1 << 16, 1024), t)          # 2048 tiles x 512 segments x 32 columns
+    L = cabi.lib()
+    null = ctypes.c_void_p(8)  # never dereferenced: the call must fail first
+    assert L.tcb200_reduce_launch_static(big._h, null, null, None) == -7    # TCB200_ERR_TOO_LARGE
+    other = cabi.Plan(cabi.contraction_problem(1, 64, 64, 64))
+    assert L.tcb200_reduce_launch_static(other._h, null, null, None) == -1  # not a reduction plan
+    bad = cabi.reduction_problem(0, 5, 1)
+    with pytest.raises(cabi.Tcb200Error):
+        cabi.Plan(bad)
