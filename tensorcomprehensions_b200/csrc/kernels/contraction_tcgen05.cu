@@ -58,7 +58,6 @@ struct TcArgs {
   int a_batched, b_batched;  // 0: operand shared by all batch entries
   int c_vec;                 // 128-bit stores allowed
   int tma_store;             // pair kernel: epilogue through the staging tile and tiled TMA stores
-  int transpose_out;         // pair kernel: the tile's element (row, col) goes to C[col * ldc + row] (operands swapped)
   int* dev_status;
 };
 
@@ -749,31 +748,19 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
 constexpr int kPairBN = 128;
 constexpr int kPairBSlots = 8;
 constexpr int kPairOutBytes = BM * kPairBN * 4;  // staging tile of the epilogue
-// Two ring configurations.  Staged (default): 4 raw-A slots, 8 raw-B slots and the 64 KB staging tile of
-// the epilogue.  Deep (operands swapped, direct transposed stores, no staging tile): the large operand
-// comes through the A ring straight from HBM, so that ring gets 8 slots (128 KB in flight per SM) and
-// the small, L2-resident operand 6.
-constexpr int kPairDeepASlots = 8;
-constexpr int kPairDeepBSlots = 6;
-__host__ __device__ constexpr int ts_pair_rings_bytes(int a_slots = kTsASlots, int b_slots = kPairBSlots) {
-  return a_slots * BM * BK * 4 + (b_slots + kTsPSlots) * (kPairBN / 2) * BK * 4 + kTsBarrierBytes;
+__host__ __device__ constexpr int ts_pair_rings_bytes() {
+  return kTsASlots * BM * BK * 4 + (kPairBSlots + kTsPSlots) * (kPairBN / 2) * BK * 4 + kTsBarrierBytes;
 }
 __host__ __device__ constexpr int ts_pair_out_offset() { return (ts_pair_rings_bytes() + 1023) / 1024 * 1024; }
 __host__ __device__ constexpr int ts_pair_smem_bytes() { return ts_pair_out_offset() + kPairOutBytes + 1024; }
-__host__ __device__ constexpr int ts_pair_deep_smem_bytes() {
-  return ts_pair_rings_bytes(kPairDeepASlots, kPairDeepBSlots) + 1024;
-}
 static_assert(ts_pair_smem_bytes() <= kTsSmemLimit, "rings + output staging tile exceed shared memory");
-static_assert(ts_pair_deep_smem_bytes() <= kTsSmemLimit, "deep rings exceed shared memory");
 
-template <bool DEEP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTsThreads, 1)
 contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
                            const __grid_constant__ CUtensorMap tmB,
                            const __grid_constant__ CUtensorMap tmC, TcArgs a) {
   constexpr int BN = kPairBN;
-  constexpr int A_SLOTS = DEEP ? kPairDeepASlots : kTsASlots, P_SLOTS = kTsPSlots;
-  constexpr int B_SLOTS = DEEP ? kPairDeepBSlots : kPairBSlots;
+  constexpr int A_SLOTS = kTsASlots, P_SLOTS = kTsPSlots, B_SLOTS = kPairBSlots;
   constexpr int A_BYTES = BM * BK * 4;
   constexpr int B_BYTES = (BN / 2) * BK * 4;  // this CTA's half of the B tile
   constexpr int B_RING = A_SLOTS * A_BYTES;          // byte offset of the raw B ring
@@ -788,15 +775,15 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   constexpr int FIRST = ((BN / 2 + 15) / 16) * 16;         // columns of the first drain warp of a quarter
   constexpr int PIECES = FIRST / 16;
   constexpr uint32_t TMEM_COLS = 512;
-  static_assert(B_SLOTS >= 2 && B_SLOTS <= 8 && A_SLOTS <= 8 && P_SLOTS == 4, "barrier arrays / TMEM ring sizes");
+  static_assert(B_SLOTS >= 2 && B_SLOTS <= 8 && A_SLOTS <= 4 && P_SLOTS == 4, "barrier arrays / TMEM ring sizes");
   static_assert(A_SLOTS % 2 == 0 && B_SLOTS % 2 == 0 && P_SLOTS % 2 == 0, "a slot must stay with one set");
   static_assert(B_BYTES % 1024 == 0, "128-byte swizzle atoms must stay 1024-byte aligned");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* full_a = reinterpret_cast<uint64_t*>(smem + LO_RING + P_SLOTS * B_BYTES);  // [8]
-  uint64_t* empty_a = full_a + 8;        // [8] raw A slot read by the split warps
-  uint64_t* pfree = empty_a + 8;         // [4] processed slot (A hi/lo, B lo) read by its MMAs
+  uint64_t* full_a = reinterpret_cast<uint64_t*>(smem + LO_RING + P_SLOTS * B_BYTES);  // [4]
+  uint64_t* empty_a = full_a + 4;        // [4] raw A slot read by the split warps
+  uint64_t* pfree = empty_a + 4;         // [4] processed slot (A hi/lo, B lo) read by its MMAs
   uint64_t* ready = pfree + 4;           // [4] processed slot filled
   uint64_t* full_b = ready + 4;          // [8]
   uint64_t* empty_b = full_b + 8;        // [8] raw B slot read by its MMAs
@@ -815,11 +802,9 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   const int64_t num_tiles = (int64_t)tiles_n * tiles_m * a.batch;  // tiles of 256 x BN, one per pair
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < A_SLOTS; ++s) {
+    for (int s = 0; s < 4; ++s) {
       mbar_init(&full_a[s], 1);
       mbar_init(&empty_a[s], 4);  // one elected arrival per warp of the split set
-    }
-    for (int s = 0; s < 4; ++s) {
       mbar_init(&pfree[s], 1);
       mbar_init(&ready[s], 8);    // used in the leader only: four split warps of each CTA
     }
@@ -852,11 +837,8 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     const int f = own_first(it0, i);
     return num_kb > f ? (num_kb - f + 1) / 2 : 0;
   };
-  // the deep-ring form serves the transposed matmul, whose long reductions (K = 4096) want the shorter
-  // chunks of the single-CTA kernel it replaces there
-  constexpr int CHUNK_KB = DEEP ? kTsChunkKB : kPairChunkKB;
   auto closes_chunk = [](int j, int count, int i) {
-    return j == count - 1 || (j + 1 + (i ? CHUNK_KB / 2 : 0)) % CHUNK_KB == 0;
+    return j == count - 1 || (j + 1 + (i ? kPairChunkKB / 2 : 0)) % kPairChunkKB == 0;
   };
 
   // Static persistent schedule: tile t -> (batch, m-tile, n-tile) with n fastest, so the CTAs that
@@ -1033,22 +1015,6 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
           bb[j + 1] = a.bias_on_m ? bias_m : __shfl_sync(0xffffffffu, bias_n.y, src);
         }
         if (row >= a.M || nb >= a.N) return;
-        if (a.transpose_out) {
-          // operands swapped by the host: this tile's rows are columns of C.  For a fixed column j the
-          // 32 lanes of the warp hold 32 consecutive rows, i.e. 32 consecutive floats of C's row nb + j.
-          float* ccol = a.C + (int64_t)bz * a.stride_c + row;
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int n = nb + j;
-            if (n < a.N) {
-              float* dst = ccol + (int64_t)n * a.ldc;
-              float o = v[j];
-              if (a.accumulate) o += *dst;
-              *dst = apply_epilogue_rt(a.epi, o, bb[j]);
-            }
-          }
-          return;
-        }
         if (a.c_vec && nb + 16 <= a.N) {
 #pragma unroll
           for (int j = 0; j < 16; j += 4) {
@@ -1112,7 +1078,7 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         mbar_arrive_warp_remote(&acc_empty[i], 0);  // issuer i (in the leader) may overwrite its accumulator
       }
       if (!ok) break;
-      if (DEEP || !a.tma_store) {  // the deep-ring form has no staging tile
+      if (!a.tma_store) {
 #pragma unroll
         for (int g = 0; g < PIECES; ++g)
           if (g * 16 < mycols) store16(acc[g], col0 + g * 16);
@@ -1260,19 +1226,17 @@ int launch_ts(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, co
   return TCB200_OK;
 }
 
-template <bool DEEP>
 int launch_pair(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
                 const TcArgs& args, cudaStream_t s) {
   static std::atomic<uint64_t> configured{0};  // bit per device
-  constexpr int kBytes = DEEP ? ts_pair_deep_smem_bytes() : ts_pair_smem_bytes();
   const uint64_t bit = 1ull << (plan.device & 63);
   if (!(configured.load(std::memory_order_acquire) & bit)) {
-    TCB200_CUDA_TRY(cudaFuncSetAttribute(contraction_ts_pair_kernel<DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kBytes));
+    TCB200_CUDA_TRY(cudaFuncSetAttribute(contraction_ts_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         ts_pair_smem_bytes()));
     configured.fetch_or(bit, std::memory_order_release);
   }
   // the kernel carries its cluster shape (2 CTAs); the grid is a multiple of 2
-  contraction_ts_pair_kernel<DEEP><<<plan.launch.grid, dim3(kTsThreads, 1, 1), kBytes, s>>>(ta, tb, tc, args);
+  contraction_ts_pair_kernel<<<plan.launch.grid, dim3(kTsThreads, 1, 1), ts_pair_smem_bytes(), s>>>(ta, tb, tc, args);
   TCB200_CUDA_TRY(cudaGetLastError());
   return TCB200_OK;
 }
@@ -1324,23 +1288,8 @@ int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max,
     ++cnt;
   };
   if (pair_ok) push_pair();
-  // Operands swapped (tile 128 x 256): pairs along N when there are no two row tiles to pair.  Measured on
-  // the transposed matmul (M = 128, N = 16384, K = 4096), same run: 89.2 us against 89.7 us for 112-wide
-  // single-CTA tiles at the same chunk length (86.7 us with chunks of 8) - 64 pair tiles leave 10 of the 74
-  // pairs idle and the large operand streams from HBM.  A wave of its tiles is costed like a single-CTA
-  // wave, so the 112-wide tiles (0.97) stay ahead there.
-  const bool swap_ok = !pair_ok && p.N >= 2 * BM;
-  const double swap_cost = (double)ceil_div(ceil_div(p.N, 2 * BM) * ceil_div(p.M, kPairBN) * p.batch, kNumSMs / 2) * 1.0;
-  auto push_swapped = [&]() {
-    if (cnt < max && out)
-      out[cnt] = tcb200_tile_t{TCB200_VARIANT_TCGEN05_PAIR, BM, 2 * BM, BK, kPairDeepBSlots, kTsThreads, 3};
-    ++cnt;
-  };
-  const bool swap_first = swap_ok && swap_cost < cost[order[0]];
-  if (swap_first) push_swapped();
   for (int i = 0; i < 3; ++i)
     if (p.N >= ts_bn[order[i]]) push_ts(ts_bn[order[i]]);
-  if (swap_ok && !swap_first) push_swapped();
   const int bns[] = {128, 256, 64};
   for (int bn : bns)
     if (p.N >= bn) push(bn, 3);
@@ -1353,22 +1302,16 @@ int contraction_tc_plan(Plan& plan) {
   if (!shape_ok(p)) return TCB200_ERR_UNSUPPORTED;
   tcb200_tile_t& t = plan.tile;
   if (t.variant == TCB200_VARIANT_TCGEN05_PAIR) {
-    // tile 128 x 256: the operands trade places (C^T = B * A^T), so the 256-row pair tile runs along N
-    // and a problem with few rows but many columns (the transposed matmul: M = 128) still pairs up
-    const bool swapped = t.bm == BM && t.bn == 2 * BM;
     if (t.bn == 0) t.bn = kPairBN;
     if (t.split_tf32 == 0) t.split_tf32 = 3;
-    if (!swapped && t.bn != kPairBN) return TCB200_ERR_UNSUPPORTED;
-    if (t.split_tf32 != 3) return TCB200_ERR_UNSUPPORTED;
-    const int64_t rows = swapped ? p.N : p.M, cols = swapped ? p.M : p.N;
-    if (ceil_div(rows, 2 * BM) > 65535) return TCB200_ERR_UNSUPPORTED;
-    t.bm = swapped ? BM : 2 * BM; t.bn = swapped ? 2 * BM : kPairBN;
-    t.bk = BK; t.stages = swapped ? kPairDeepBSlots : kPairBSlots; t.threads = kTsThreads;
-    const int64_t tiles = ceil_div(cols, kPairBN) * ceil_div(rows, 2 * BM) * p.batch;
+    if (t.bn != kPairBN || t.split_tf32 != 3) return TCB200_ERR_UNSUPPORTED;
+    if (ceil_div(p.M, 2 * BM) > 65535) return TCB200_ERR_UNSUPPORTED;
+    t.bm = 2 * BM; t.bk = BK; t.stages = kPairBSlots; t.threads = kTsThreads;
+    const int64_t tiles = ceil_div(p.N, kPairBN) * ceil_div(p.M, 2 * BM) * p.batch;
     plan.launch.grid = dim3(2u * (unsigned)std::min<int64_t>(tiles, kNumSMs / 2), 1, 1);
     plan.launch.block = dim3(kTsThreads, 1, 1);
-    plan.launch.smem = swapped ? ts_pair_deep_smem_bytes() : ts_pair_smem_bytes();
-    plan.kernel_id = swapped ? 301284 : 301283;
+    plan.launch.smem = ts_pair_smem_bytes();
+    plan.kernel_id = 301283;
     return TCB200_OK;
   }
   if (t.bn == 0) t.bn = 128;
@@ -1396,17 +1339,10 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
   const tcb200_problem_t& p = plan.p;
   if (((uintptr_t)A | (uintptr_t)B) & 15) return TCB200_ERR_ALIGNMENT;
   CUtensorMap ta, tb;
-  int st;
-  if (plan.kernel_id == 301284) {  // operands swapped: B feeds the 128-row A slots, A the 64-row B halves
-    st = make_operand_map(&ta, B, p.K, p.N, p.ldb, p.batch, p.stride_b, BM);
-    if (st != TCB200_OK) return st;
-    st = make_operand_map(&tb, A, p.K, p.M, p.lda, p.batch, p.stride_a, kPairBN / 2);
-  } else {
-    st = make_operand_map(&ta, A, p.K, p.M, p.lda, p.batch, p.stride_a, BM);
-    if (st != TCB200_OK) return st;
-    st = make_operand_map(&tb, B, p.K, p.N, p.ldb, p.batch, p.stride_b,
-                          plan.kernel_id == 301283 ? kPairBN / 2 : plan.tile.bn);
-  }
+  int st = make_operand_map(&ta, A, p.K, p.M, p.lda, p.batch, p.stride_a, BM);
+  if (st != TCB200_OK) return st;
+  st = make_operand_map(&tb, B, p.K, p.N, p.ldb, p.batch, p.stride_b,
+                        plan.kernel_id == 301283 ? kPairBN / 2 : plan.tile.bn);
   if (st != TCB200_OK) return st;
   TcArgs a;
   a.C = C; a.bias = bias;
@@ -1419,14 +1355,7 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
   a.c_vec = ((uintptr_t)C & 15) == 0 && p.ldc % 4 == 0 && p.stride_c % 4 == 0 && bias_vec;
   a.dev_status = dev_status;
   a.tma_store = 0;
-  a.transpose_out = 0;
   switch (plan.kernel_id) {
-    case 301284:
-      a.M = (int)p.N; a.N = (int)p.M;
-      std::swap(a.a_batched, a.b_batched);
-      a.bias_on_m = !p.bias_on_m;
-      a.transpose_out = 1;
-      return launch_pair<true>(plan, ta, tb, tb, a, s);  // no staging tile: the third map is unused
     case 301283: {
       // output map for the staged epilogue: {N, M, batch}, boxes of 32 columns x 128 rows
       CUtensorMap tc;
@@ -1434,7 +1363,7 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
       if (a.tma_store && make_operand_map(&tc, C, p.N, p.M, p.ldc, p.batch, p.stride_c, BM) != TCB200_OK)
         a.tma_store = 0;
       if (!a.tma_store) tc = tb;  // unused by the kernel then
-      return launch_pair<false>(plan, ta, tb, tc, a, s);
+      return launch_pair(plan, ta, tb, tc, a, s);
     }
     case 100643: return launch_ts<64>(plan, ta, tb, a, s);
     case 101283: return launch_ts<128>(plan, ta, tb, a, s);

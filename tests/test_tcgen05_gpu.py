@@ -70,43 +70,6 @@ def test_tcgen05_pair_tiles(cuda, shape):
     assert torch.equal(out, out2)  # one accumulator per issuer: the same bits on every run
 
 
-def swapped_tile():
-    t = tc_tile(256, 3, pair=True)
-    t.bm = 128  # 128 x 256: the operands trade places, the pair tile runs along N
-    return t
-
-
-@pytest.mark.parametrize("shape", [(1, 128, 512, 256), (1, 70, 1000, 132), (3, 100, 300, 64), (1, 128, 16384, 4096),
-                                   (2, 260, 700, 320)])
-@pytest.mark.parametrize("epi", [cabi.EPI_NONE, cabi.EPI_BIAS_RELU])
-def test_tcgen05_pair_swapped_operands(cuda, shape, epi):
-    """C^T = B * A^T on the CTA-pair kernel: few rows, many columns (the transposed matmul).  Bias along
-    the columns of C becomes a bias along the tile's rows; `+=` adds into C through the transposed stores."""
-    b, M, N, K = shape
-    A, B, bias = _rand((b, M, K), 43), _rand((b, N, K), 44), _rand((N,), 45)
-    ref = ref64(A, B)
-    ins = [A.to(cuda), B.to(cuda)]
-    if epi == cabi.EPI_BIAS_RELU:
-        ref = torch.relu(torch.matmul(A.double(), B.double().transpose(-1, -2)) + bias.double()).float()
-        ins.append(bias.to(cuda))
-    p = cabi.contraction_problem(b, M, N, K, True, True, epilogue=epi)
-    out, plan = run_plan(p, ins, (b, M, N), swapped_tile())
-    assert "tile=128x256" in plan.describe()
-    assert_close(out, ref, K, [A, B], 3e-7, plan.describe())
-    out2, _ = run_plan(p, ins, (b, M, N), swapped_tile())
-    assert torch.equal(out, out2)
-    if epi == cabi.EPI_NONE and M * N < 1 << 20:
-        p2 = cabi.contraction_problem(b, M, N, K, True, True, accumulate=True)
-        init = _rand((b, M, N), 46).to(cuda)
-        out3, _ = run_plan(p2, ins, (b, M, N), swapped_tile(), out_init=init)
-        assert_close(out3, ref + init.cpu(), K, what="accumulate")
-        # bias along the rows of C (columns of the swapped tile)
-        bm = _rand((M,), 47)
-        p3 = cabi.contraction_problem(b, M, N, K, True, True, epilogue=cabi.EPI_BIAS, bias_on_m=True)
-        out4, _ = run_plan(p3, ins + [bm.to(cuda)], (b, M, N), swapped_tile())
-        assert_close(out4, ref + bm[None, :, None], K, what="row bias")
-
-
 @pytest.mark.parametrize("epi", [cabi.EPI_NONE, cabi.EPI_BIAS, cabi.EPI_BIAS_RELU, cabi.EPI_RELU])
 @pytest.mark.parametrize("N", [384, 100])  # 100: ragged columns -> scalar stores
 @pytest.mark.parametrize("kind", ["ss", "ts", "pair"])
