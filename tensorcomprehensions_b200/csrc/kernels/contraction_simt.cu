@@ -154,6 +154,7 @@ template <int MODE>  // 0: any layout, 1: FAST, 2: BULK
 __global__ void __launch_bounds__(256) simt_small_kernel(GemmArgs g, int ldas, int ldbs) {
   constexpr bool FAST = MODE >= 1;
   extern __shared__ __align__(16) float smem[];
+  pdl_sync();  // launched as a programmatic dependent: wait for the preceding kernel before any global access
   const int M = g.M, N = g.N, K = g.K;
   float* As = smem;
   float* Bs = smem + (size_t)M * ldas;
@@ -335,11 +336,12 @@ int contraction_simt_launch(const Plan& plan, const float* A, const float* B, co
                       (p.K * p.N) % 4 == 0 && p.stride_b % 4 == 0 && ((uintptr_t)B % 16 == 0) &&
                       p.M * p.K * 4 < (1 << 20) && p.K * p.N * 4 < (1 << 20);
     if (bulk)
-      simt_small_kernel<2><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(g, (int)p.K, (int)p.N);
+      TCB200_CUDA_TRY(launch_pdl(simt_small_kernel<2>, plan.launch.grid, plan.launch.block, plan.launch.smem, s, g,
+                                 (int)p.K, (int)p.N));
     else if (fast)
-      simt_small_kernel<1><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(g, ldas, ldbs);
+      TCB200_CUDA_TRY(launch_pdl(simt_small_kernel<1>, plan.launch.grid, plan.launch.block, plan.launch.smem, s, g, ldas, ldbs));
     else
-      simt_small_kernel<0><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(g, ldas, ldbs);
+      TCB200_CUDA_TRY(launch_pdl(simt_small_kernel<0>, plan.launch.grid, plan.launch.block, plan.launch.smem, s, g, ldas, ldbs));
   } else {
     // 128-bit loads need a 16-byte aligned base, leading dimension and batch stride.
     const int a_vec = ((uintptr_t)A % 16 == 0) && p.lda % 4 == 0 && p.stride_a % 4 == 0;

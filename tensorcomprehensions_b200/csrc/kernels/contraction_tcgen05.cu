@@ -465,6 +465,7 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_sync();  // nothing above touches global memory
   const uint32_t tmem_base = *tmem_slot;
   const bool second_half = warp >= DRAIN_WARP0 + 4;  // drain warps: which column range of the quarter
 
@@ -825,6 +826,7 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   tc_fence_before();
   cluster_sync_all();  // both CTAs' barriers exist before anything arrives on them from the other CTA
   tc_fence_after();
+  pdl_sync();  // nothing above touches global memory
   const uint32_t tmem_base = *tmem_slot;
   const bool second_half = warp >= DRAIN_WARP0 + 4;  // drain warps: which column range of the quarter
 
@@ -1221,8 +1223,8 @@ int launch_ts(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, co
                                          ts_smem_bytes(BN)));
     configured.fetch_or(bit, std::memory_order_release);
   }
-  contraction_ts_kernel<BN><<<plan.launch.grid, dim3(kTsThreads, 1, 1), ts_smem_bytes(BN), s>>>(ta, tb, args);
-  TCB200_CUDA_TRY(cudaGetLastError());
+  TCB200_CUDA_TRY(launch_pdl(contraction_ts_kernel<BN>, plan.launch.grid, dim3(kTsThreads, 1, 1),
+                             (size_t)ts_smem_bytes(BN), s, ta, tb, args));
   return TCB200_OK;
 }
 
@@ -1236,8 +1238,8 @@ int launch_pair(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, 
     configured.fetch_or(bit, std::memory_order_release);
   }
   // the kernel carries its cluster shape (2 CTAs); the grid is a multiple of 2
-  contraction_ts_pair_kernel<<<plan.launch.grid, dim3(kTsThreads, 1, 1), ts_pair_smem_bytes(), s>>>(ta, tb, tc, args);
-  TCB200_CUDA_TRY(cudaGetLastError());
+  TCB200_CUDA_TRY(launch_pdl(contraction_ts_pair_kernel, plan.launch.grid, dim3(kTsThreads, 1, 1),
+                             (size_t)ts_pair_smem_bytes(), s, ta, tb, tc, args));
   return TCB200_OK;
 }
 

@@ -233,6 +233,7 @@ template <int KHT, int FPT>
 __global__ void __launch_bounds__(256 / FPT) group_conv_item_kernel(ConvArgs a) {
   constexpr int kItemThreads = 256 / FPT;
   extern __shared__ __align__(16) float smem[];
+  pdl_sync();  // launched as a programmatic dependent: wait for the preceding kernel before any global access
   const int item = blockIdx.x;  // n * G + g
   const int g = item % a.G;
   const int taps = a.C * a.KH * a.KW;
@@ -539,11 +540,11 @@ int group_conv_launch(const Plan& plan, const float* I, const float* W, const fl
   if (plan.kernel_id == 101 || plan.kernel_id == 102) {
     const bool k33 = a.KH == 3 && a.KW == 3;
     if (plan.kernel_id == 102) {
-      if (k33) group_conv_item_kernel<3, 2><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(a);
-      else group_conv_item_kernel<0, 2><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(a);
+      if (k33) TCB200_CUDA_TRY(launch_pdl(group_conv_item_kernel<3, 2>, plan.launch.grid, plan.launch.block, plan.launch.smem, s, a));
+      else TCB200_CUDA_TRY(launch_pdl(group_conv_item_kernel<0, 2>, plan.launch.grid, plan.launch.block, plan.launch.smem, s, a));
     } else {
-      if (k33) group_conv_item_kernel<3, 4><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(a);
-      else group_conv_item_kernel<0, 4><<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(a);
+      if (k33) TCB200_CUDA_TRY(launch_pdl(group_conv_item_kernel<3, 4>, plan.launch.grid, plan.launch.block, plan.launch.smem, s, a));
+      else TCB200_CUDA_TRY(launch_pdl(group_conv_item_kernel<0, 4>, plan.launch.grid, plan.launch.block, plan.launch.smem, s, a));
     }
     TCB200_CUDA_TRY(cudaGetLastError());
     return TCB200_OK;

@@ -102,6 +102,7 @@ __global__ void __launch_bounds__(kBulkThreads, 1) tensordot_bulk_kernel(BulkArg
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  pdl_sync();  // nothing above touches global memory
 
   const int groups = (a.C1 + a.R - 1) / a.R;          // work items per n
   const int64_t items = (int64_t)a.N * groups;
@@ -349,7 +350,7 @@ int tensordot_launch(const Plan& plan, const float* I0, const float* I1, float* 
     static std::atomic<uint64_t> configured[17][5];  // one flag word per (C2 <= 16, C3 <= 4) instantiation
     TCB200_CUDA_TRY(ensure_dynamic_smem(fn, (int)kBulkSmemBudget + 1024, plan.device,
                                         configured[p.td[2]][p.td[3]]));
-    fn<<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(a);
+    TCB200_CUDA_TRY(launch_pdl(fn, plan.launch.grid, plan.launch.block, plan.launch.smem, s, a));
   } else if (plan.kernel_id >= 1 && aligned) {
     vec4_fn fn = pick_vec4((int)p.td[2], (int)p.td[3]);
     dim3 grid = plan.launch.grid, block = plan.launch.block;
