@@ -1067,17 +1067,28 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         if (!ok) break;
         ++dc[i];
         tc_fence_after();
+        // Two pieces per round trip to tensor memory; the accumulator is handed back as soon as the last
+        // pieces sit in registers, before they are added.
 #pragma unroll
-        for (int g = 0; g < PIECES; ++g) {
-          if (g * 16 < mycols) {  // the same for the whole warp
-            float v[16];
-            tmem_ld16(tmem_base + i * ACC_STRIDE + lane_base + col0 + g * 16, v);
+        for (int g = 0; g < PIECES; g += 2) {
+          float v0[16], v1[16];
+          const bool has0 = g * 16 < mycols, has1 = g + 1 < PIECES && (g + 1) * 16 < mycols;  // warp-uniform
+          if (has0) tmem_ld16_nowait(tmem_base + i * ACC_STRIDE + lane_base + col0 + g * 16, v0);
+          if (has1) tmem_ld16_nowait(tmem_base + i * ACC_STRIDE + lane_base + col0 + (g + 1) * 16, v1);
+          tmem_wait_ld();
+          if (g + 2 >= PIECES) {
+            tc_fence_before();
+            mbar_arrive_warp_remote(&acc_empty[i], 0);  // issuer i (in the leader) may overwrite its accumulator
+          }
+          if (has0) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) acc[g][j] += v[j];
+            for (int j = 0; j < 16; ++j) acc[g][j] += v0[j];
+          }
+          if (has1) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[g + 1][j] += v1[j];
           }
         }
-        tc_fence_before();
-        mbar_arrive_warp_remote(&acc_empty[i], 0);  // issuer i (in the leader) may overwrite its accumulator
       }
       if (!ok) break;
       if (!a.tma_store) {
