@@ -93,8 +93,9 @@ __host__ __device__ constexpr int num_threads() { return SPLIT == 3 ? 448 : 320;
 constexpr int kChunkKB = 8;  // k-blocks of 32
 // Own k-blocks per issuer between drains.  The error the truncation leaves is proportional to the
 // chunk length (all-positive U[0,1) operands, K = 2048: mean error -1.2e-3 of a sum of 511 with chunks
-// of 4, -2.3e-3 with 8); the single-CTA kernel hides drains of 4 behind its shared-memory traffic
-// (2 cost 10 %), the CTA-pair kernel loses 6 % at 4.
+// of 4, -2.3e-3 with 8).  Measured with the library swapped between runs on one GPU: the single-CTA kernel
+// on the transposed matmul 84.5 / 85.8 / 90.6 us at 8 / 4 / 2, the CTA-pair kernel on MLP3 360 / 376 / 386 us at
+// 8 / 6 / 4 (and 358 us at 12).
 constexpr int kTsChunkKB = 4;
 constexpr int kPairChunkKB = 8;
 
