@@ -69,6 +69,8 @@ enum {
   TCB200_ERR_TOO_LARGE = -7
 };
 
+enum { TCB200_REDUCE_SUM = 0, TCB200_REDUCE_MAX = 1, TCB200_REDUCE_MIN = 2, TCB200_REDUCE_PROD = 3 };
+
 typedef struct tcb200_problem {
   int32_t family;
   int32_t epilogue;
@@ -84,7 +86,9 @@ typedef struct tcb200_problem {
   int64_t td[5];                        /* tensordot: N, C1, C2, C3, P (P = product of trailing shared dims) */
   int64_t conv_stride[2];               /* group conv: SH, SW of I(.., SH*h+kh, SW*w+kw) (tc/library/convolution.h:27-31);
                                            0 reads as 1.  Output extent: (H - KH) / SH + 1 by (W - KW) / SW + 1 */
-  int64_t red[3];                       /* reduction: A, C, B of the [A][C][B] view of the input (C is summed) */
+  int64_t red[3];                       /* reduction: A, C, B of the [A][C][B] view of the input (C is reduced) */
+  int32_t reduce_op;                    /* reduction: TCB200_REDUCE_SUM (+=), _MAX (max=), _MIN (min=), _PROD (*=) */
+  int32_t reserved;
 } tcb200_problem_t;
 
 /* One point of a family's tile sweep.  Fields a variant does not use are 0. */

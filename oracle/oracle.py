@@ -103,6 +103,15 @@ def loop_reduce(I, double=False):
     return O
 
 
+def loop_reduce_op(I, op):
+    """max (1), min (2) or product (3) over the middle axis of a 3-D [A, C, B] array, accumulated in double."""
+    I = _np(I)
+    A, C, B = I.shape
+    O = np.empty((A, B), np.float32)
+    lib().oracle_reduce_op_f32(_p(I), _p(O), _i64(A), _i64(C), _i64(B), int(op))
+    return O
+
+
 def loop_fcrelu(I, W1, Bias=None, relu=True, double=False):
     I, W1 = _np(I), _np(W1)
     Bias = _np(Bias) if Bias is not None else None

@@ -142,6 +142,25 @@ void oracle_group_conv_strided_f32(const float* I, const float* W1, const float*
  * C +=! A(r_m) and C(m) +=! A(m,r_n) (test/test_tc_mapper_harness-inl.h:60-146).  The reduction loop is
  * innermost and runs in index order (tc/core/tc2halide.cc:729-754), starting from the identity 0
  * (tc/core/tc2halide.cc:573-601). */
+/* The same nest for the other reduction assignments (tc/lang/tree.h TK_MAX_EQ_B, TK_MIN_EQ_B,
+ * TK_TIMES_EQ_B): op 1 = max, 2 = min, 3 = product, starting from the operator's identity
+ * (tc/core/tc2halide.cc:573-601). */
+void oracle_reduce_op_f32(const float* I, float* O, int64_t A, int64_t C, int64_t B, int op) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t a = 0; a < A; ++a)
+    for (int64_t b = 0; b < B; ++b) {
+      double acc = op == 1 ? -3.402823466e38 : op == 2 ? 3.402823466e38 : op == 3 ? 1.0 : 0.0;
+      for (int64_t c = 0; c < C; ++c) {
+        double v = (double)I[(a * C + c) * B + b];
+        if (op == 1) acc = v > acc ? v : acc;
+        else if (op == 2) acc = v < acc ? v : acc;
+        else if (op == 3) acc *= v;
+        else acc += v;
+      }
+      O[a * B + b] = (float)acc;
+    }
+}
+
 void oracle_reduce_f32(const float* I, float* O, int64_t A, int64_t C, int64_t B, int accumulate_double) {
 #pragma omp parallel for collapse(2) schedule(static)
   for (int64_t a = 0; a < A; ++a)

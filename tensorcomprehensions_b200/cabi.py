@@ -34,6 +34,7 @@ class Problem(ctypes.Structure):
         ("lda", ctypes.c_int64), ("ldb", ctypes.c_int64), ("ldc", ctypes.c_int64),
         ("stride_a", ctypes.c_int64), ("stride_b", ctypes.c_int64), ("stride_c", ctypes.c_int64),
         ("conv", ctypes.c_int64 * 8), ("td", ctypes.c_int64 * 5), ("conv_stride", ctypes.c_int64 * 2), ("red", ctypes.c_int64 * 3),
+        ("reduce_op", ctypes.c_int32), ("reserved", ctypes.c_int32),
     ]
 
 
@@ -129,12 +130,17 @@ def group_conv_problem(N, G, C, F, H, W, KH, KW, epilogue=EPI_BIAS, accumulate=F
     return p
 
 
-def reduction_problem(A, C, B, accumulate=False):
-    """O(a, b) (+)= sum_c I(a, c, b) over the [A][C][B] view of one input."""
+REDUCE_SUM, REDUCE_MAX, REDUCE_MIN, REDUCE_PROD = 0, 1, 2, 3
+
+
+def reduction_problem(A, C, B, accumulate=False, op=REDUCE_SUM):
+    """O(a, b) = reduce_c I(a, c, b) over the [A][C][B] view of one input (sum, max, min or product);
+    accumulate: the output's old value takes part in the reduction (+=, max=, ... without '!')."""
     p = Problem()
     p.family = FAMILY_REDUCTION
     p.epilogue, p.accumulate = EPI_NONE, int(accumulate)
     p.red[:] = [A, C, B]
+    p.reduce_op = op
     return p
 
 

@@ -403,7 +403,15 @@ bool matchReduction(const DefAnalysis& def, const StatementAnalysis& st, Matched
   tcb200_problem_t& p = out->problem;
   memset(&p, 0, sizeof(p));
   p.family = TCB200_FAMILY_REDUCTION;
-  p.accumulate = st.assignment == lang::TK_PLUS_EQ ? 1 : 0;
+  switch (st.assignment) {
+    case lang::TK_MAX_EQ: case lang::TK_MAX_EQ_B: p.reduce_op = TCB200_REDUCE_MAX; break;
+    case lang::TK_MIN_EQ: case lang::TK_MIN_EQ_B: p.reduce_op = TCB200_REDUCE_MIN; break;
+    case lang::TK_TIMES_EQ: case lang::TK_TIMES_EQ_B: p.reduce_op = TCB200_REDUCE_PROD; break;
+    default: p.reduce_op = TCB200_REDUCE_SUM; break;
+  }
+  // without '!' the output's old value takes part in the reduction
+  p.accumulate = st.assignment == lang::TK_PLUS_EQ || st.assignment == lang::TK_MAX_EQ ||
+                 st.assignment == lang::TK_MIN_EQ || st.assignment == lang::TK_TIMES_EQ;
   p.red[0] = A; p.red[1] = C; p.red[2] = B;
   out->inputs = {valueIndex(def, I.tensor)};
   out->output = valueIndex(def, st.lhs);
@@ -507,12 +515,14 @@ std::vector<MatchedLaunch> matchKernels(const DefAnalysis& def) {
     const StatementAnalysis& st = def.statements[s];
     const bool reduction = !st.reductionVars.empty();
     if (reduction) {
-      if (st.assignment != lang::TK_PLUS_EQ_B && st.assignment != lang::TK_PLUS_EQ)
-        unmatched(st, "only sum reductions (+=, +=!) map to a kernel family");
+      const bool sum = st.assignment == lang::TK_PLUS_EQ_B || st.assignment == lang::TK_PLUS_EQ;
       MatchedLaunch l;
       std::string why;
-      if (!matchConv(def, st, &l) && !matchReduction(def, st, &l, &why)) {
-        if (!why.empty()) unmatched(st, why);  // one operand, but not a sum this backend takes
+      if (!sum) {  // max=, min=, *=: the reduction family takes them for one operand
+        if (!matchReduction(def, st, &l, &why))
+          unmatched(st, why.empty() ? "only sum reductions (+=, +=!) of a product map to a kernel family" : why);
+      } else if (!matchConv(def, st, &l) && !matchReduction(def, st, &l, &why)) {
+        if (!why.empty()) unmatched(st, why);  // one operand, but not a reduction this backend takes
         if (!matchProduct(def, st, &l, &why)) unmatched(st, why);
       }
       l.statements.push_back((int)s);

@@ -57,6 +57,7 @@ py::dict problemDict(const tc::MatchedLaunch& l) {
     d["stride_a"] = p.stride_a; d["stride_b"] = p.stride_b; d["stride_c"] = p.stride_c;
   } else if (p.family == TCB200_FAMILY_REDUCTION) {
     d["red"] = std::vector<int64_t>(p.red, p.red + 3);
+    d["reduce_op"] = p.reduce_op;
   } else if (p.family == TCB200_FAMILY_TENSORDOT) {
     d["td"] = std::vector<int64_t>(p.td, p.td + 5);
   } else {

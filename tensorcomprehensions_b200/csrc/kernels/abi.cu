@@ -250,8 +250,10 @@ int tcb200_plan_describe(const tcb200_plan_t* plan, char* buf, size_t buflen) {
                (long long)p.td[4]);
       break;
     case TCB200_FAMILY_REDUCTION:
-      snprintf(head, sizeof(head), "tcb200::reduction A=%lld C=%lld B=%lld%s", (long long)p.red[0],
-               (long long)p.red[1], (long long)p.red[2], p.accumulate ? " accumulate" : "");
+      snprintf(head, sizeof(head), "tcb200::reduction %s A=%lld C=%lld B=%lld%s",
+               p.reduce_op == TCB200_REDUCE_MAX ? "max" : p.reduce_op == TCB200_REDUCE_MIN ? "min"
+               : p.reduce_op == TCB200_REDUCE_PROD ? "prod" : "sum",
+               (long long)p.red[0], (long long)p.red[1], (long long)p.red[2], p.accumulate ? " accumulate" : "");
       break;
     case TCB200_FAMILY_GROUP_CONV:
       snprintf(head, sizeof(head),

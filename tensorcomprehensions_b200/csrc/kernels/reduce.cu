@@ -1,5 +1,5 @@
-// K4 — sum reductions of one tensor over a contiguous group of its indices:
-//   O(a, b) (+)= sum_c I(a, c, b)            I viewed as [A][C][B], O as [A][B]
+// K4 — reductions (sum, max, min, product) of one tensor over a contiguous group of its indices:
+//   O(a, b) (op)= reduce_c I(a, c, b)        I viewed as [A][C][B], O as [A][B]
 // with A / B the products of the kept leading / trailing dimensions (either may be 1).  These are the
 // comprehensions the reference's mapper tests exercise as sum1D / sum2D
 // (test/test_tc_mapper_harness-inl.h:60-146: C +=! A(r_m), C(m) +=! A(m, r_n)) and the building
@@ -41,17 +41,36 @@ struct ReduceArgs {
   unsigned* tickets;  // [tile], zero between launches
 };
 
-__device__ __forceinline__ float vadd(float a, float b) { return a + b; }
-__device__ __forceinline__ float4 vadd(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
-__device__ __forceinline__ void vzero(float& a) { a = 0.f; }
-__device__ __forceinline__ void vzero(float4& a) { a = make_float4(0.f, 0.f, 0.f, 0.f); }
-__device__ __forceinline__ float hsum(float4 a) { return (a.x + a.y) + (a.z + a.w); }
+// The reduction operator (TCB200_REDUCE_*) and its identity (tc/core/tc2halide.cc:573-601: 0 for +=,
+// 1 for *=, the type's lowest / largest value for max= / min=).
+template <int OP>
+__device__ __forceinline__ float rop(float a, float b) {
+  if (OP == TCB200_REDUCE_MAX) return fmaxf(a, b);
+  if (OP == TCB200_REDUCE_MIN) return fminf(a, b);
+  if (OP == TCB200_REDUCE_PROD) return a * b;
+  return a + b;
+}
+template <int OP>
+__device__ __forceinline__ float4 rop(float4 a, float4 b) {
+  return make_float4(rop<OP>(a.x, b.x), rop<OP>(a.y, b.y), rop<OP>(a.z, b.z), rop<OP>(a.w, b.w));
+}
+template <int OP>
+__device__ __forceinline__ float identity() {
+  return OP == TCB200_REDUCE_MAX ? -3.402823466e38f : OP == TCB200_REDUCE_MIN ? 3.402823466e38f
+       : OP == TCB200_REDUCE_PROD ? 1.f : 0.f;
+}
+template <int OP> __device__ __forceinline__ void vinit(float& a) { a = identity<OP>(); }
+template <int OP> __device__ __forceinline__ void vinit(float4& a) {
+  const float i = identity<OP>();
+  a = make_float4(i, i, i, i);
+}
+template <int OP> __device__ __forceinline__ float hred(float4 a) { return rop<OP>(rop<OP>(a.x, a.y), rop<OP>(a.z, a.w)); }
 
 // T = float: the plain form.  T = float4, HSUM = false: four adjacent output columns per thread
 // (B a multiple of 4; A.B counts float4 columns).  T = float4, HSUM = true: B = 1 and the reduced range
 // itself is read four elements at a time (C a multiple of 4; A.C counts float4 elements), the four
 // lanes of a thread's sum are added at the end.  16 to 64 bytes of loads per thread are in flight.
-template <typename T, bool HSUM>
+template <typename T, bool HSUM, int OP>
 __global__ void __launch_bounds__(kThreads) reduce_tile_kernel(ReduceArgs a) {
   using OutT = typename std::conditional<HSUM, float, T>::type;
   constexpr int UNROLL = sizeof(T) == 4 ? 8 : 4;
@@ -68,7 +87,7 @@ __global__ void __launch_bounds__(kThreads) reduce_tile_kernel(ReduceArgs a) {
   const long long BLK = (long long)UNROLL * TY;
   T acc[UNROLL];
 #pragma unroll
-  for (int k = 0; k < UNROLL; ++k) vzero(acc[k]);
+  for (int k = 0; k < UNROLL; ++k) vinit<OP>(acc[k]);
   if (col < a.B) {
     const T* base = reinterpret_cast<const T*>(a.I) + (size_t)arow * a.C * a.B + col;
     for (long long b0 = (long long)s * BLK; b0 < a.C; b0 += (long long)a.S * BLK) {
@@ -78,31 +97,31 @@ __global__ void __launch_bounds__(kThreads) reduce_tile_kernel(ReduceArgs a) {
 #pragma unroll
         for (int k = 0; k < UNROLL; ++k) v[k] = __ldg(base + (size_t)(c + (long long)k * TY) * a.B);
 #pragma unroll
-        for (int k = 0; k < UNROLL; ++k) acc[k] = vadd(acc[k], v[k]);
+        for (int k = 0; k < UNROLL; ++k) acc[k] = rop<OP>(acc[k], v[k]);
       } else {  // the last, ragged block of the range
 #pragma unroll
         for (int k = 0; k < UNROLL; ++k)
-          if (c + (long long)k * TY < a.C) acc[k] = vadd(acc[k], __ldg(base + (size_t)(c + (long long)k * TY) * a.B));
+          if (c + (long long)k * TY < a.C) acc[k] = rop<OP>(acc[k], __ldg(base + (size_t)(c + (long long)k * TY) * a.B));
       }
     }
   }
 #pragma unroll
   for (int h = UNROLL / 2; h > 0; h >>= 1)
 #pragma unroll
-    for (int k = 0; k < h; ++k) acc[k] = vadd(acc[k], acc[k + h]);
+    for (int k = 0; k < h; ++k) acc[k] = rop<OP>(acc[k], acc[k + h]);
   red[tid] = acc[0];
   __syncthreads();
   // rows of the CP x TY layout are ty-major: element (ty, tx) sits at ty * CP + tx = tid
   for (int h = TY >> 1; h > 0; h >>= 1) {
-    if (ty < h) red[tid] = vadd(red[tid], red[tid + h * CP]);
+    if (ty < h) red[tid] = rop<OP>(red[tid], red[tid + h * CP]);
     __syncthreads();
   }
   const bool writer = ty == 0 && col < a.B;
   OutT mine_v;
-  if constexpr (HSUM) mine_v = hsum(red[tid]); else mine_v = red[tid];
+  if constexpr (HSUM) mine_v = hred<OP>(red[tid]); else mine_v = red[tid];
   OutT* out = reinterpret_cast<OutT*>(a.O) + (size_t)arow * a.B + col;
   if (a.S == 1) {
-    if (writer) *out = a.accumulate ? vadd(*out, mine_v) : mine_v;
+    if (writer) *out = a.accumulate ? rop<OP>(*out, mine_v) : mine_v;
     return;
   }
   OutT* part = reinterpret_cast<OutT*>(a.partial) + (size_t)tile * a.S * CP;
@@ -117,57 +136,58 @@ __global__ void __launch_bounds__(kThreads) reduce_tile_kernel(ReduceArgs a) {
   // thread (tx, ty) takes segments ty, ty + TY, ..., then the TY rows are combined as above.
   OutT* redo = reinterpret_cast<OutT*>(red);
   OutT sum;
-  vzero(sum);
-  for (int k = ty; k < a.S; k += TY) sum = vadd(sum, __ldcg(part + (size_t)k * CP + tx));  // L2: written by other SMs
+  vinit<OP>(sum);
+  for (int k = ty; k < a.S; k += TY) sum = rop<OP>(sum, __ldcg(part + (size_t)k * CP + tx));  // L2: written by other SMs
   redo[tid] = sum;
   __syncthreads();
   for (int h = TY >> 1; h > 0; h >>= 1) {
-    if (ty < h) redo[tid] = vadd(redo[tid], redo[tid + h * CP]);
+    if (ty < h) redo[tid] = rop<OP>(redo[tid], redo[tid + h * CP]);
     __syncthreads();
   }
-  if (writer) *out = a.accumulate ? vadd(*out, redo[tid]) : redo[tid];
+  if (writer) *out = a.accumulate ? rop<OP>(*out, redo[tid]) : redo[tid];
   if (tid == 0) a.tickets[tile] = 0;  // the next launch on this scratch starts from zero again
 }
 
 // B = 1: O(a) = sum_c I(a, c), one warp per row.
-template <bool VEC>
+template <bool VEC, int OP>
 __global__ void __launch_bounds__(kThreads) reduce_rows_warp_kernel(ReduceArgs a) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr int WARPS = kThreads / 32;
   for (long long r = (long long)blockIdx.x * WARPS + warp; r < a.A; r += (long long)gridDim.x * WARPS) {
     const float* row = a.I + (size_t)r * a.C;
-    float s0 = 0.f, s1 = 0.f;
+    float s0 = identity<OP>(), s1 = identity<OP>();
     if (VEC) {
       const float4* row4 = reinterpret_cast<const float4*>(row);
       const long long n4 = a.C >> 2;
       long long i = lane;
       for (; i + 32 < n4; i += 64) {
         const float4 u = __ldg(row4 + i), v = __ldg(row4 + i + 32);
-        s0 += (u.x + u.y) + (u.z + u.w);
-        s1 += (v.x + v.y) + (v.z + v.w);
+        s0 = rop<OP>(s0, hred<OP>(u));
+        s1 = rop<OP>(s1, hred<OP>(v));
       }
       if (i < n4) {
         const float4 u = __ldg(row4 + i);
-        s0 += (u.x + u.y) + (u.z + u.w);
+        s0 = rop<OP>(s0, hred<OP>(u));
       }
     } else {
       long long i = lane;
       for (; i + 32 < a.C; i += 64) {
-        s0 += __ldg(row + i);
-        s1 += __ldg(row + i + 32);
+        s0 = rop<OP>(s0, __ldg(row + i));
+        s1 = rop<OP>(s1, __ldg(row + i + 32));
       }
-      if (i < a.C) s0 += __ldg(row + i);
+      if (i < a.C) s0 = rop<OP>(s0, __ldg(row + i));
     }
-    float s = s0 + s1;
+    float s = rop<OP>(s0, s1);
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-    if (lane == 0) a.O[r] = a.accumulate ? a.O[r] + s : s;
+    for (int off = 16; off > 0; off >>= 1) s = rop<OP>(s, __shfl_xor_sync(0xffffffffu, s, off));
+    if (lane == 0) a.O[r] = a.accumulate ? rop<OP>(a.O[r], s) : s;
   }
 }
 
 bool valid(const tcb200_problem_t& p) {
   for (int i = 0; i < 3; ++i)
     if (p.red[i] <= 0 || p.red[i] > (1ll << 40)) return false;
+  if (p.reduce_op < TCB200_REDUCE_SUM || p.reduce_op > TCB200_REDUCE_PROD) return false;
   return (double)p.red[0] * (double)p.red[1] * (double)p.red[2] < 9.0e18;
 }
 
@@ -197,6 +217,38 @@ int auto_segments(const Units& u, int cp_log2) {
 }
 
 bool warp_rows_ok(const tcb200_problem_t& p) { return p.red[2] == 1 && p.red[1] <= (1 << 20); }
+
+template <int OP>
+int launch_tile_op(bool vec, bool hsum, const Plan& plan, const ReduceArgs& a, cudaStream_t s) {
+  if (vec && hsum) reduce_tile_kernel<float4, true, OP><<<plan.launch.grid, plan.launch.block, 0, s>>>(a);
+  else if (vec) reduce_tile_kernel<float4, false, OP><<<plan.launch.grid, plan.launch.block, 0, s>>>(a);
+  else reduce_tile_kernel<float, false, OP><<<plan.launch.grid, plan.launch.block, 0, s>>>(a);
+  TCB200_CUDA_TRY(cudaGetLastError());
+  return TCB200_OK;
+}
+int launch_tile(int op, bool vec, bool hsum, const Plan& plan, const ReduceArgs& a, cudaStream_t s) {
+  switch (op) {
+    case TCB200_REDUCE_MAX: return launch_tile_op<TCB200_REDUCE_MAX>(vec, hsum, plan, a, s);
+    case TCB200_REDUCE_MIN: return launch_tile_op<TCB200_REDUCE_MIN>(vec, hsum, plan, a, s);
+    case TCB200_REDUCE_PROD: return launch_tile_op<TCB200_REDUCE_PROD>(vec, hsum, plan, a, s);
+    default: return launch_tile_op<TCB200_REDUCE_SUM>(vec, hsum, plan, a, s);
+  }
+}
+template <int OP>
+int launch_rows_op(bool vec, const Plan& plan, const ReduceArgs& a, cudaStream_t s) {
+  if (vec) reduce_rows_warp_kernel<true, OP><<<plan.launch.grid, plan.launch.block, 0, s>>>(a);
+  else reduce_rows_warp_kernel<false, OP><<<plan.launch.grid, plan.launch.block, 0, s>>>(a);
+  TCB200_CUDA_TRY(cudaGetLastError());
+  return TCB200_OK;
+}
+int launch_rows(int op, bool vec, const Plan& plan, const ReduceArgs& a, cudaStream_t s) {
+  switch (op) {
+    case TCB200_REDUCE_MAX: return launch_rows_op<TCB200_REDUCE_MAX>(vec, plan, a, s);
+    case TCB200_REDUCE_MIN: return launch_rows_op<TCB200_REDUCE_MIN>(vec, plan, a, s);
+    case TCB200_REDUCE_PROD: return launch_rows_op<TCB200_REDUCE_PROD>(vec, plan, a, s);
+    default: return launch_rows_op<TCB200_REDUCE_SUM>(vec, plan, a, s);
+  }
+}
 
 }  // namespace
 
@@ -284,10 +336,7 @@ int reduce_launch(const Plan& plan, const float* I, float* O, float* partial, un
   if (plan.kernel_id == 2) {
     a.S = 1; a.cp_log2 = 0; a.tiles_b = 1;
     const bool vec = (a.C & 3) == 0 && (((uintptr_t)I) & 15) == 0;
-    if (vec) reduce_rows_warp_kernel<true><<<plan.launch.grid, plan.launch.block, 0, s>>>(a);
-    else reduce_rows_warp_kernel<false><<<plan.launch.grid, plan.launch.block, 0, s>>>(a);
-    TCB200_CUDA_TRY(cudaGetLastError());
-    return TCB200_OK;
+    return launch_rows(p.reduce_op, vec, plan, a, s);
   }
   const int vec = plan.tile.stages;
   const Units u = units(p, vec);
@@ -298,11 +347,7 @@ int reduce_launch(const Plan& plan, const float* I, float* O, float* partial, un
   a.tiles_b = ceil_div(a.B, plan.tile.bm);
   a.S = plan.tile.bn;
   if (a.S > 1 && (!partial || !tickets)) return TCB200_ERR_INVALID_ARGUMENT;
-  if (vec == 4 && u.hsum) reduce_tile_kernel<float4, true><<<plan.launch.grid, plan.launch.block, 0, s>>>(a);
-  else if (vec == 4) reduce_tile_kernel<float4, false><<<plan.launch.grid, plan.launch.block, 0, s>>>(a);
-  else reduce_tile_kernel<float, false><<<plan.launch.grid, plan.launch.block, 0, s>>>(a);
-  TCB200_CUDA_TRY(cudaGetLastError());
-  return TCB200_OK;
+  return launch_tile(p.reduce_op, vec == 4, u.hsum, plan, a, s);
 }
 
 // ------------------------------------------------------------------------------------------------

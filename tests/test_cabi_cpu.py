@@ -80,7 +80,7 @@ def test_reduction_plans_and_the_static_scratch_limit_without_a_device():
     plan = cabi.Plan(p)
     grid, block = plan.geometry()
     assert block == (256, 1, 1) and grid[0] == 1 and grid[1] > 1          # one output tile, many segments
-    assert "tcb200::reduction A=1 C=67108864 B=1" in plan.describe() and "stages=4" in plan.describe()
+    assert "tcb200::reduction sum A=1 C=67108864 B=1" in plan.describe() and "stages=4" in plan.describe()
     assert cabi.Plan(cabi.reduction_problem(16384, 4096, 1)).geometry()[0][1] == 1  # warp per row: no segments
     odd = cabi.Plan(cabi.reduction_problem(3, 1001, 7))                    # no 128-bit loads possible
     assert "stages=1" in odd.describe()

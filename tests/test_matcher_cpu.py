@@ -78,7 +78,11 @@ def test_sum_reductions():
     m = match("def f(float(N, C, D, H, W) I) -> (O) { O(n, h, w) +=! I(n, c, d, h, w) }", "f", [(2, 3, 4, 5, 6)])[0]
     assert m["red"] == [2, 12, 30]
     exe = tc.compile("def sum2D(float(M, N) A) -> (C) { C(m) +=! A(m, r_n) }", "sum2D", "naive", torch.empty(7, 9))
-    assert exe.output_shapes() == [[7]] and "tcb200::reduction A=7 C=9 B=1" in exe.compiled_source
+    assert exe.output_shapes() == [[7]] and "tcb200::reduction sum A=7 C=9 B=1" in exe.compiled_source
+    # the other reduction assignments of the language, for one operand
+    for assign, op, acc in (("max=!", 1, 0), ("min=!", 2, 0), ("*=!", 3, 0), ("max=", 1, 1), ("*=", 3, 1)):
+        m = match("def r(float(M, N) A) -> (C) { C(m) %s A(m, r_n) }" % assign, "r", [(7, 9)])[0]
+        assert (m["family"], m["red"], m["reduce_op"], m["accumulate"]) == ("reduction", [7, 9, 1], op, acc)
 
 
 def test_ungrouped_convolution_is_group_conv_with_one_group():
@@ -110,6 +114,7 @@ def test_strided_convolution_of_the_library():
     ("def f(float(N,M) A) -> (O) { O(i) +=! exp(A(i,j)) }", [(4, 5)], "not a product of two tensor accesses"),
     ("def f(float(N,M,K) A) -> (O) { O(m) +=! A(n,m,k) }", [(4, 5, 6)], "not adjacent dimensions"),
     ("def f(float(N,M) A, float(M) B) -> (O) { O(i) max=! A(i,j) * B(j) }", [(4, 5), (5,)], "only sum reductions"),
+    ("def f(float(N,M,K) A) -> (O) { O(m) min=! A(n,m,k) }", [(4, 5, 6)], "not adjacent dimensions"),
     # dilated filter taps: strides are covered (next test), dilation is not
     ("def f(float(N,C,H,W) I, float(F,C,KH,KW) W1) -> (O) { O(n,f,h,w) +=! I(n,c,h+2*kh,w+2*kw) * W1(f,c,kh,kw) }",
      [(1, 1, 9, 9), (1, 1, 3, 3)], "not a plain index variable"),

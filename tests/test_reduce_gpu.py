@@ -67,6 +67,45 @@ def test_reduce_accumulates_into_the_output(cuda):
             assert_close(out, orc.loop_reduce(I, double=True) + init.numpy(), dims[1], what=plan.describe())
 
 
+@pytest.mark.parametrize("op", [cabi.REDUCE_MAX, cabi.REDUCE_MIN, cabi.REDUCE_PROD])
+@pytest.mark.parametrize("dims", [(1, 100, 1), (7, 9, 1), (111, 7, 1), (3, 5, 2), (5, 33, 257), (600, 1024, 1),
+                                  (64, 100000, 1), (1, 300001, 1), (1, 5000, 4096), (2, 70000, 3)])
+def test_max_min_product_every_tile(cuda, dims, op):
+    """max=!, min=! and *=! of one operand (tc/lang/tree.h TK_MAX_EQ_B ...): exact for max / min; the product
+    of values near 1 against a float64 product."""
+    A, C, B = dims
+    g = torch.Generator().manual_seed(73)
+    if op == cabi.REDUCE_PROD:
+        I = 1.0 + (torch.rand((A, C, B), generator=g) - 0.5) * (2.0 / C ** 0.5)  # keeps the product O(1)
+    else:
+        I = torch.randn((A, C, B), generator=g)
+    ref = orc.loop_reduce_op(I, op)
+    p = cabi.reduction_problem(A, C, B, op=op)
+    for tile in [None] + cabi.query(p):
+        out, plan = run_plan(p, [I.to(cuda)], (A, B), tile)
+        if op == cabi.REDUCE_PROD:
+            assert_close(out, ref, C, what=plan.describe())
+        else:
+            assert torch.equal(out.cpu(), torch.from_numpy(ref)), plan.describe()
+    # without '!' the old output takes part
+    init = torch.randn((A, B), generator=g) if op != cabi.REDUCE_PROD else 1.0 + torch.rand((A, B), generator=g)
+    pa = cabi.reduction_problem(A, C, B, accumulate=True, op=op)
+    out, plan = run_plan(pa, [I.to(cuda)], (A, B), None, out_init=init.to(cuda))
+    r = torch.from_numpy(ref)
+    expect = torch.maximum(r, init) if op == cabi.REDUCE_MAX else torch.minimum(r, init) if op == cabi.REDUCE_MIN else r * init
+    assert_close(out, expect, C, what=plan.describe() + " accumulate")
+
+
+def test_max_min_product_through_the_api(cuda):
+    T = tc.define("def rowmax(float(M, N) A) -> (C) { C(m) max=! A(m, r_n) }\n"
+                  "def colmin(float(M, N) A) -> (C) { C(n) min=! A(r_m, n) }\n"
+                  "def prod(float(M) A) -> (C) { C *=! A(r_m) }", tc.make_naive_options_factory())
+    A = torch.randn(513, 77, device=cuda)
+    assert torch.equal(T.rowmax(A), A.max(1).values) and torch.equal(T.colmin(A), A.min(0).values)
+    v = 1.0 + (torch.rand(4000, device=cuda) - 0.5) * 0.02
+    assert_close(T.prod(v).reshape(1), v.double().prod().float().reshape(1).cpu(), 4000)
+
+
 @pytest.mark.parametrize("body", ["C() +=! A(r_m)", "C +=! A(r_m)", "C(i) +=! A(r_m) where i in 0:1"])
 def test_sum1d_forms_through_the_api(cuda, body):
     A = torch.rand(1000003, device=cuda)
