@@ -11,9 +11,12 @@ per-comprehension kernel time, GB/s, TFLOP/s and roofline fraction; `e2e` is the
 from pinned host buffers (host->device copies of every input and device->host copies of every
 output inside the timed region).
 
-Multi-GPU (torchrun, one rank per GPU): every comprehension shards along an output index that also
-indexes its large operand, no reduction crosses GPUs, so there is no data-path collective; each
-rank runs a full-size shard (weak scaling) and timing is the max over ranks of device time.
+Multi-GPU (torchrun, one rank per GPU): every comprehension is split along an output index that also
+indexes its large operand (tensordot, group convolution: n; batchmatmul: b; transposed matmul: the rows of
+B = the columns of C; MLP3: the batch), each rank compiles and runs its shard, no reduction crosses
+GPUs, so computing needs no collective.  The total work is the same at every N (strong scaling); time
+is the max over ranks of device time.  At N > 1 the opt-in exchange that assembles the full outputs (an
+all-gather over NCCL) is timed separately per comprehension and reported beside the kernel-only time.
 """
 import argparse
 import json
@@ -104,30 +107,85 @@ class ClockSampler:
 # The product arm
 # ------------------------------------------------------------------------------------------------
 
-class Program:
-    """One comprehension compiled for its shapes: device buffers, plans, launch."""
+SHARD_NOTE = ("strong scaling: every comprehension split across the GPUs along one output index "
+              "(tensordot n, batchmatmul b, tmm the rows of B = columns of C, group_conv n, mlp3 the batch), "
+              "remainders on the first ranks; replicated operands (A of tmm, filters, MLP weights) on every GPU; "
+              "no data-path collective")
 
-    def __init__(self, w, dev, seed, rotate_bytes, tune=False):
+
+def make_config(args):
+    """The `config` object of the JSON line: the same for both arms at the same arguments."""
+    names = suite_names(args)
+    return {"workload": "tc5_suite" if args.workload == "suite" else args.workload, "configs": names,
+            "tiles": "autotuned" if args.tune else "family default", "shard": SHARD_NOTE,
+            "l2": "inputs larger than L2: every comprehension rotates over buffer sets that total >= 192 MB"}
+
+
+def suite_names(args):
+    from tensorcomprehensions_b200 import workloads as wl
+    return list(wl.ALL) if args.workload == "suite" else [args.workload]
+
+
+class Program:
+    """One rank's shard of one comprehension, compiled for its shapes: device buffers, plans, launch."""
+
+    def __init__(self, name, world, rank, dev, rotate_bytes, tune=False):
         import torch
         from tensorcomprehensions_b200 import workloads as wl
         from tensorcomprehensions_b200 import runtime
-        self.w, self.dev = w, dev
-        self.host_inputs = [t.pin_memory() for t in wl.make_inputs(w, seed=seed)]
-        self.exe = runtime.compile_workload(w, dev, tune=tune)
-        # rotating sets: a small problem is timed over enough copies of its buffers to exceed L2
-        per_set = w.bytes
+        self.name, self.dev, self.world = name, dev, world
+        self.full = wl.BY_NAME[name]()
+        if name in wl.ALL:
+            self.w, draws = wl.make_shard_inputs(name, world, rank)
+        else:  # the extra single-GPU workloads are not sharded
+            self.w, draws = self.full, wl.make_inputs(self.full)
+        self.host_inputs = [t.pin_memory() for t in draws]
+        self.exe = runtime.compile_workload(self.w, dev, tune=tune)
+        # rotating sets: the comprehension is timed over enough copies of its buffers to exceed L2
+        per_set = self.w.bytes
         self.sets = max(1, -(-rotate_bytes // per_set)) if per_set < rotate_bytes else 1
         self.inputs = [[t.to(dev) for t in self.host_inputs] for _ in range(self.sets)]
         self.outputs = [self.exe.prepare_outputs() for _ in range(self.sets)]
         self.host_outputs = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in self.outputs[0]]
         self.cursor = 0
         self.staged = None
+        self.gatherers = None
         self.launches_per_run = self.exe.launches
 
     def run(self):
         i = self.cursor
         self.cursor = (i + 1) % self.sets
         self.exe.run(self.inputs[i], self.outputs[i])
+        return self.outputs[i]
+
+    def run_gathered(self):
+        """The shard's launch followed by the all-gather of every output (NCCL) and its assembly."""
+        from tensorcomprehensions_b200 import sharding
+        outs = self.run()
+        if self.gatherers is None:
+            self.gatherers = [sharding.Gatherer(tuple(o.shape), d, full_shape[d], self.dev)
+                              for o, d, full_shape in zip(outs, self.w.shard_outputs, self.full_output_shapes())]
+        return [g.gather(o) for g, o in zip(self.gatherers, outs)]
+
+    def full_output_shapes(self):
+        """Unsharded output shapes: the shard's with the sharded dimension at its full extent."""
+        dim = next(d for d in self.full.shard_inputs if d is not None)
+        total = next(s for s, d in zip(self.full.shapes, self.full.shard_inputs) if d is not None)[dim]
+        shapes = []
+        for o, d in zip(self.outputs[0], self.w.shard_outputs):
+            s = list(o.shape)
+            s[d] = total
+            shapes.append(tuple(s))
+        return shapes
+
+    def gathered_bytes(self):
+        n = 0
+        for s in self.full_output_shapes():
+            k = 4
+            for x in s:
+                k *= x
+            n += k
+        return n
 
     def run_e2e(self):
         """Host buffers in, host buffers out through the public HostStagedExecutor: H2D of every input,
@@ -143,7 +201,7 @@ class Program:
         return sum(t.numel() * 4 for t in self.host_outputs)
 
 
-def window_times_us(prog, n_windows=20, min_window_us=200.0):
+def window_times_us(run, sets, n_windows=20, min_window_us=200.0):
     """Per-launch device time of one comprehension: windows of R graph-replayed runs over the rotating sets."""
     import torch
     stream = torch.cuda.Stream()
@@ -152,17 +210,17 @@ def window_times_us(prog, n_windows=20, min_window_us=200.0):
         for _ in range(3):   # warm-up on this stream and a first estimate
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            prog.run()
+            run()
             e1.record()
             e1.synchronize()
             est.append(e0.elapsed_time(e1) * 1e3)
-        passes = max(1, int(-(-min_window_us // (min(est) * prog.sets))))
-        runs = passes * prog.sets
+        passes = max(1, int(-(-min_window_us // (min(est) * sets))))
+        runs = passes * sets
         graph = torch.cuda.CUDAGraph()
         # thread-local capture mode: other threads of the process (NCCL's watchdog at N > 1) keep their CUDA calls
         with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
             for _ in range(runs):
-                prog.run()
+                run()
         for _ in range(2):
             graph.replay()
         ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_windows)]
@@ -176,12 +234,20 @@ def window_times_us(prog, n_windows=20, min_window_us=200.0):
             "runs_per_window": runs}
 
 
-def roofline_time_us(w, peaks, split):
-    """max(bytes / BW_hbm, k * flops / P_tf32); k = 3 under the 3xTF32 split; no tensor term for SIMT kernels."""
-    t_mem = w.bytes / (peaks["hbm_gbs"] * 1e3)
+def roofline_time_us(w, peaks, split, gpus=1, burst=False):
+    """max(bytes / BW_hbm, k * flops / P_tf32) over `gpus` GPUs; k = 3 under the 3xTF32 split; no tensor term for
+    SIMT kernels."""
+    t_mem = w.bytes / (peaks["hbm_gbs"] * 1e3 * gpus)
     if split == 0:
         return t_mem
-    return max(t_mem, split * w.flops / (peaks["tf32_tflops"] * 1e6))
+    p = peaks["tf32_tflops_burst"] if burst else peaks["tf32_tflops"]
+    return max(t_mem, split * w.flops / (p * 1e6 * gpus))
+
+
+# fp32 FMA rate of the part, measured with a register-resident FMA loop (both the scalar and the packed
+# fp32x2 form): 36.9 T fused multiply-adds per second.  The group convolution at C = F = 16 is bound by it
+# (464 M multiply-adds), not by HBM.
+FMA_PEAK_TFMA = 36.9
 
 
 def run_product(args):
@@ -203,9 +269,10 @@ def run_product(args):
         dist.init_process_group("nccl", device_id=dev)
     peaks = load_peaks()
 
-    names = list(wl.ALL) if args.workload == "suite" else [args.workload]
-    progs = [Program(wl.BY_NAME[n](), dev, seed=20240 + wl.BY_NAME[n]().index + 1000 * rank,
-                     rotate_bytes=192 << 20, tune=args.tune) for n in names]
+    names = suite_names(args)
+    if world > 1 and any(n not in wl.ALL for n in names):
+        raise SystemExit("bench.py: %s is a single-GPU workload" % args.workload)
+    progs = [Program(n, world, rank, dev, rotate_bytes=192 << 20, tune=args.tune) for n in names]
     launches_per_step = sum(p.launches_per_run for p in progs)
 
     def barrier():
@@ -213,12 +280,18 @@ def run_product(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def max_over_ranks(x):
+    def over_ranks(values, op):
         if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+            return list(values)
+        t = torch.tensor(list(values), dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=op)
+        return [float(x) for x in t.tolist()]
+
+    def max_over_ranks(values):
+        return over_ranks(values, dist.ReduceOp.MAX if world > 1 else None)
+
+    def sum_over_ranks(values):
+        return over_ranks(values, dist.ReduceOp.SUM if world > 1 else None)
 
     # ---- timed region 1: device-resident inputs ----------------------------------------------
     sampler = ClockSampler(local)
@@ -238,14 +311,45 @@ def run_product(args):
     total_ms = ev[0][0].elapsed_time(ev[-1][-1])
     per_prog_us = [statistics.mean(ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(args.steps)) * 1e3
                    for i in range(len(progs))]
-    total_ms = max_over_ranks(total_ms)
+    total_ms = max_over_ranks([total_ms])[0]
+    per_prog_us = max_over_ranks(per_prog_us)
     ms_per_step = total_ms / args.steps
 
     # ---- per-config windows: R back-to-back launches over the rotating sets in ONE event pair --------
     # (the reference's benchmark fixture times a kernel this way; a CUDA graph replays the launches so
-    # that the window holds device time, not the host's launch rate: the two smallest kernels run
-    # 7-30 us, the order of a launch through Python).  min / p50 / p90 over the windows.
-    windows = [window_times_us(p) for p in progs]
+    # that the window holds device time, not the host's launch rate: the smallest kernels run a few
+    # microseconds, the order of a launch through Python).  min / p50 / p90 over the windows, each the max
+    # over ranks.
+    windows = []
+    for p in progs:
+        win = window_times_us(p.run, p.sets)
+        m = max_over_ranks([win["min"], win["p50"], win["p90"]])
+        win.update({"min": round(m[0], 2), "p50": round(m[1], 2), "p90": round(m[2], 2)})
+        windows.append(win)
+
+    # ---- the opt-in exchange: shard launch + all-gather of every output over NCCL, per comprehension ----
+    gather = [None] * len(progs)
+    if world > 1:
+        reps = 10
+        for i, p in enumerate(progs):
+            for _ in range(3):
+                p.run_gathered()
+            barrier()
+            e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            e0.record()
+            for _ in range(reps):
+                p.run()
+            e1.record()
+            for _ in range(reps):
+                p.run_gathered()
+            e2.record()
+            barrier()
+            k_us, kg_us = max_over_ranks([e0.elapsed_time(e1) * 1e3 / reps, e1.elapsed_time(e2) * 1e3 / reps])
+            gather[i] = {"kernel_us": round(k_us, 2), "kernel_plus_gather_us": round(kg_us, 2),
+                         "gathered_bytes": p.gathered_bytes(),
+                         "how": "%d back-to-back calls each, host-launched; all_gather_into_tensor (NCCL) of "
+                                "equal padded shards + assembly kernel where the split is uneven or not on "
+                                "dimension 0" % reps}
 
     # ---- timed region 2: host buffers (e2e) -----------------------------------------------------
     for _ in range(min(args.warmup, 3)):
@@ -267,44 +371,74 @@ def run_product(args):
         p.staged.join()
     e1.record()
     barrier()
-    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
+    e2e_ms = max_over_ranks([e0.elapsed_time(e1)])[0] / e2e_steps
+    h2d, d2h, launches = sum_over_ranks([sum(p.h2d_bytes() for p in progs), sum(p.d2h_bytes() for p in progs),
+                                         launches_per_step])
     clocks = sampler.stop() if rank == 0 else None
 
-    flops_step = sum(p.w.flops for p in progs) * world
+    # the three reductions of the fourth kernel family, alone, on one GPU (not part of the suite's value)
+    reductions = None
+    if world == 1 and args.workload == "suite" and not args.no_reductions:
+        reductions = []
+        for n in wl.EXTRA:
+            rp = Program(n, 1, 0, dev, rotate_bytes=0)
+            win = window_times_us(rp.run, rp.sets)
+            reductions.append({"workload": n, "window_us": win, "gbs": round(rp.w.bytes / win["p50"] / 1e3, 1),
+                               "roofline_frac_window": round(rp.w.bytes / win["p50"] / 1e3 / peaks["hbm_gbs"], 3),
+                               "kernel": rp.exe.describe()})
+            del rp
+            torch.cuda.empty_cache()
+
+    flops_step = sum(p.full.flops for p in progs)   # the whole job: the shards of all ranks add up to this
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
+    # the timed region is a burst (milliseconds to a second) unless many steps are asked for: the tensor peak
+    # it is compared with is the burst figure then, the sustained one for regions of a second and more
+    burst = total_ms < 1000.0
     per_config = []
-    for p, us, win in zip(progs, per_prog_us, windows):
+    for p, us, win, ga in zip(progs, per_prog_us, windows, gather):
         split = p.exe.split_tf32
-        troof = roofline_time_us(p.w, peaks, split)
-        per_config.append({
-            "workload": p.w.name, "kernel_us": round(us, 2), "launches": p.launches_per_run,
-            "gbs": round(p.w.bytes / us / 1e3, 1), "tflops": round(p.w.flops / us / 1e6, 2),
+        troof = roofline_time_us(p.full, peaks, split, world, burst)
+        t_tensor = split * p.full.flops / ((peaks["tf32_tflops_burst"] if burst else peaks["tf32_tflops"]) * 1e6 * world)
+        t_hbm = p.full.bytes / (peaks["hbm_gbs"] * 1e3 * world)
+        entry = {
+            "workload": p.name, "kernel_us": round(us, 2), "launches": p.launches_per_run,
+            "gbs": round(p.full.bytes / us / 1e3, 1), "tflops": round(p.full.flops / us / 1e6, 2),
             "roofline_us": round(troof, 2), "roofline_frac": round(troof / us, 3),
             "window_us": win, "roofline_frac_window": round(troof / win["p50"], 3),
-            "bound": "tensor" if split and split * p.w.flops / (peaks["tf32_tflops"] * 1e6) >
-            p.w.bytes / (peaks["hbm_gbs"] * 1e3) else "hbm",
-            "kernel": p.exe.describe(), "rotating_sets": p.sets})
+            "bound": "tensor" if split and t_tensor > t_hbm else "hbm",
+            "kernel": p.exe.describe(), "rotating_sets": p.sets, "shard_shapes": [list(s) for s in p.w.shapes]}
+        if p.name == "group_conv":
+            # C = F = 16: an MMA would be 128 x 16 x 8 and the fp32 path is bound by the FMA pipe, not by HBM
+            fma_us = (p.full.flops / 2.0) / (FMA_PEAK_TFMA * 1e6 * world)
+            entry.update({"bound": "fma", "fma_floor_us": round(fma_us, 2),
+                          "fma_frac": round(fma_us / us, 3), "fma_frac_window": round(fma_us / win["p50"], 3)})
+        if ga:
+            entry["gather"] = ga
+        per_config.append(entry)
     # dominant kernel = largest share of the step
     dom = max(range(len(progs)), key=lambda i: per_prog_us[i])
     dp, dus, dc = progs[dom], per_prog_us[dom], per_config[dom]
     if dc["bound"] == "tensor":
         split = dp.exe.split_tf32
-        roof = {"bound": "tensor", "achieved": round(split * dp.w.flops / dus / 1e6, 1),
-                "peak": round(peaks["tf32_tflops"], 1), "unit": "TFLOP/s",
-                "frac": round(split * dp.w.flops / dus / 1e6 / peaks["tf32_tflops"], 3),
-                "note": "tensor-pipe flops issued = %d x algorithmic (3xTF32 split); peak = bf16_tflops_sustained/2 "
-                        "(%s); algorithmic %.1f TFLOP/s" % (split, peaks["source"], dp.w.flops / dus / 1e6)}
+        peak = (peaks["tf32_tflops_burst"] if burst else peaks["tf32_tflops"]) * world
+        roof = {"bound": "tensor", "achieved": round(split * dp.full.flops / dus / 1e6, 1),
+                "peak": round(peak, 1), "unit": "TFLOP/s",
+                "frac": round(split * dp.full.flops / dus / 1e6 / peak, 3),
+                "note": "tensor-pipe flops issued = %d x algorithmic (3xTF32 split); peak = %d x %s / 2 (%s; the "
+                        "timed region lasted %.1f ms); algorithmic %.1f TFLOP/s" %
+                        (split, world, "bf16_tflops (burst)" if burst else "bf16_tflops_sustained",
+                         peaks["source"], total_ms, dp.full.flops / dus / 1e6)}
     else:
-        roof = {"bound": "hbm", "achieved": round(dp.w.bytes / dus / 1e3, 1), "peak": peaks["hbm_gbs"],
-                "unit": "GB/s", "frac": round(dp.w.bytes / dus / 1e3 / peaks["hbm_gbs"], 3),
+        roof = {"bound": "hbm", "achieved": round(dp.full.bytes / dus / 1e3, 1), "peak": peaks["hbm_gbs"] * world,
+                "unit": "GB/s", "frac": round(dp.full.bytes / dus / 1e3 / (peaks["hbm_gbs"] * world), 3),
                 "note": "of %s" % peaks["source"]}
-    roof["kernel"] = dp.w.name
-    roof["traffic"] = NCU_TRAFFIC_BYTES.get(dp.w.name)
-    if dp.w.name == "mlp3":
+    roof["kernel"] = dp.name
+    roof["traffic"] = NCU_TRAFFIC_BYTES.get(dp.name) if world == 1 else None
+    if dp.name == "mlp3" and world == 1:
         roof["traffic_note"] = ("ncu capture of the first of the three launches (layer 1: 209.7 MB algorithmic, "
                                 "76 % of the flops); achieved/frac cover all three")
 
@@ -313,20 +447,16 @@ def run_product(args):
     line = {
         "metric": METRIC, "value": round(flops_step / (ms_per_step * 1e-3) / 1e12, 3), "unit": UNIT,
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic",
-        "config": {"workload": "tc5_suite" if args.workload == "suite" else args.workload,
-                   "configs": names, "tiles": "autotuned" if args.tune else "family default",
-                   "shard": "one full-size instance of every comprehension per GPU",
-                   "l2": "inputs larger than L2 (suite streams 1.2 GB per step; small problems rotate over "
-                         ">=192 MB of buffer sets)"},
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": make_config(args),
         "e2e": {"value": round(flops_step / (e2e_ms * 1e-3) / 1e12, 3), "unit": UNIT,
                 "ms_per_step": round(e2e_ms, 3),
-                "h2d_bytes_per_step": sum(p.h2d_bytes() for p in progs),
-                "d2h_bytes_per_step": sum(p.d2h_bytes() for p in progs)},
-        "gpu_launches": launches_per_step * args.steps,
+                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+        "gpu_launches": int(launches) * args.steps,
         "clocks": clocks, "roofline": roof, "per_config": per_config,
     }
+    if reductions:
+        line["reductions"] = reductions
     if cpu:
         line["cpu_baseline"] = cpu
     print(json.dumps(line), flush=True)
@@ -338,10 +468,20 @@ def run_product(args):
 # The CPU arm: the reference's own CPU-side comparator (ATen on the host cores)
 # ------------------------------------------------------------------------------------------------
 
+def host_threads():
+    """Host cores this process may use.  torchrun exports OMP_NUM_THREADS=1 to its workers, which would leave
+    ATen on one thread: the CPU arm sets its thread count from the affinity mask instead."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_suite(names):
     import torch
     from oracle import oracle as orc
     from tensorcomprehensions_b200 import workloads as wl
+    torch.set_num_threads(host_threads())
     ws = [wl.BY_NAME[n]() for n in names]
     inputs = [wl.make_inputs(w) for w in ws]
 
@@ -368,27 +508,27 @@ def cpu_baseline(names, budget_s=20.0):
 
 
 def run_reference(args):
+    """The CPU arm: the whole (unsharded) suite through ATen on all the host cores this process may use, with
+    exactly the steps and warm-up asked for.  Under torchrun rank 0 alone runs it; the total work per step is
+    the same as the product arm's at every N (the product arm splits it, this arm has one host)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from tensorcomprehensions_b200 import workloads as wl
-    names = list(wl.ALL) if args.workload == "suite" else [args.workload]
+    names = suite_names(args)
     ws, step, threads = cpu_suite(names)
-    for _ in range(min(args.warmup, 2)):
+    for _ in range(args.warmup):
         step()
-    steps = max(1, min(args.steps, 10))
     t0 = time.perf_counter()
-    for _ in range(steps):
+    for _ in range(args.steps):
         step()
-    ms = (time.perf_counter() - t0) / steps * 1e3
+    ms = (time.perf_counter() - t0) / args.steps * 1e3
     flops = sum(w.flops for w in ws)
     v = round(flops / (ms * 1e-3) / 1e12, 4)
     line = {
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT,
-        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": steps, "warmup": min(args.warmup, 2),
-        "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "tc5_suite" if args.workload == "suite" else args.workload, "configs": names},
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": make_config(args),
         "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": "whole steps of the suite through ATen-CPU, the comparator the reference's own "
                                    "harness uses (its CPU executor is a stub and its JIT needs Halide/isl/LLVM)"},
@@ -407,6 +547,8 @@ def main():
                     choices=["suite", "tensordot", "batchmatmul", "tmm", "group_conv", "mlp3", "sum1d", "sum2d", "colsum"])
     ap.add_argument("--cpu-seconds", type=float, default=20.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-reductions", action="store_true",
+                    help="skip the stand-alone timing of the three reduction workloads (one GPU, suite only)")
     ap.add_argument("--tune", action="store_true",
                     help="pick each comprehension's tile with the autotuner's sweep instead of the family default")
     args = ap.parse_args()

@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define TCB200_ABI_VERSION 2
+#define TCB200_ABI_VERSION 3
 
 /* Opaque CUDA stream handle; identical to cudaStream_t / CUstream. */
 typedef struct CUstream_st* tcb200_stream_t;
@@ -98,6 +98,9 @@ typedef struct tcb200_tile {
   int32_t stages;      /* TMA pipeline depth (tcgen05) */
   int32_t threads;     /* CTA size */
   int32_t split_tf32;  /* tcgen05: 1 = one TF32 pass, 3 = 3xTF32 split keeping fp32 accuracy */
+  int32_t split_k;     /* tensor-memory contraction tiles: CTAs that share the reduction of one output tile
+                          (0 or 1 = none).  A split contraction keeps S x M x N partial sums in scratch memory
+                          owned by the plan and adds them in a fixed order in a second small kernel. */
 } tcb200_tile_t;
 
 typedef struct tcb200_plan tcb200_plan_t;
@@ -137,9 +140,15 @@ int tcb200_plan_tile(const tcb200_plan_t* plan, tcb200_tile_t* tile);
  *               nonzero code there instead of spinning (NULL: not reported).
  * The plan is immutable: it may be launched concurrently from several host threads
  * and streams.  One exception: a reduction plan that splits the reduced range over several CTAs
- * (tile.bn > 1) keeps partial sums in scratch memory owned by the plan, allocated and zeroed by its
- * first launch (synchronous calls: not inside a stream capture) and freed by tcb200_plan_destroy;
- * launches of one such plan must not overlap in time. */
+ * (tile.bn > 1) and a contraction plan that splits its reduction (tile.split_k > 1) keep partial sums in
+ * scratch memory owned by the plan, allocated and zeroed by its
+ * first launch (cudaMalloc is a synchronous call: not inside a stream capture; the counters are zeroed on
+ * `stream`, ahead of the kernel) and freed by tcb200_plan_destroy; launches of one such plan must not
+ * overlap in time. */
+int tcb200_launch(const tcb200_plan_t* plan, const void* const* inputs, int n_inputs,
+                  void* const* outputs, int n_outputs, tcb200_stream_t stream,
+                  int* dev_status);
+
 /* The same launch for a reduction plan, with its scratch (tickets + partial sums) taken from a fixed
  * array in device memory that is part of the library image instead of memory the plan allocates: no
  * allocation happens in this call, at the first launch or ever.  No counterpart in the reference (it
@@ -157,9 +166,6 @@ int tcb200_plan_tile(const tcb200_plan_t* plan, tcb200_tile_t* tile);
 int tcb200_reduce_launch_static(const tcb200_plan_t* plan, const void* input, void* output,
                                 tcb200_stream_t stream);
 
-int tcb200_launch(const tcb200_plan_t* plan, const void* const* inputs, int n_inputs,
-                  void* const* outputs, int n_outputs, tcb200_stream_t stream,
-                  int* dev_status);
 
 /* Device plumbing for hosts that do not link the CUDA runtime themselves (the C++ host library
  * reaches CUDA only through this ABI).  tcb200_set_device / tcb200_get_device wrap the calling
@@ -178,6 +184,46 @@ int tcb200_stream_synchronize(tcb200_stream_t stream);
 typedef struct tcb200_timer tcb200_timer_t;
 int tcb200_timer_start(tcb200_stream_t stream, tcb200_timer_t** timer);
 int tcb200_timer_stop(tcb200_timer_t* timer, tcb200_stream_t stream, float* elapsed_us);
+
+/* Device status word: a device int that the kernels' bounded waits report into (the dev_status argument of
+ * tcb200_launch).  create allocates and zeroes one on the current device; check waits for `stream`, copies the
+ * word to *code, clears it, and returns TCB200_OK when it was zero, TCB200_ERR_DEVICE_TIMEOUT otherwise (the
+ * context stays usable: a wait that gives up makes its kernel stop issuing work and leave through its normal
+ * exit).  This is how a failed launch reaches the host, where the reference's enforce macros throw
+ * (tc/core/cuda/cuda.h:38-73) and its tuner discards the candidate (tc/autotuner/autotuner-inl.h:204-214). */
+int tcb200_status_create(int** dev_status);
+int tcb200_status_destroy(int* dev_status);
+int tcb200_status_check(int* dev_status, tcb200_stream_t stream, int* code);
+
+/* Self-test of the bounded waits: launches one warp that waits on an mbarrier nothing ever arrives on, through
+ * the same wait routine the kernels use, with the limit set to `limit_cycles` SM cycles (the kernels use ~4e9).
+ * The wait runs out, the warp records TCB200_SELFTEST_WAIT_CODE in *dev_status and the kernel returns.  No
+ * counterpart in the reference (its generated kernels never wait on one another). */
+#define TCB200_SELFTEST_WAIT_CODE 99
+int tcb200_selftest_wait(long long limit_cycles, int* dev_status, tcb200_stream_t stream);
+
+/* Device time of very short launches.  begin creates a private stream and starts capturing it (thread-local
+ * capture mode); the caller enqueues any number of launches on *capture_stream; end closes the capture,
+ * instantiates the graph, replays it once untimed and `timed_replays` times between two events, and returns
+ * the device time of ONE replay in microseconds.  A kernel of a few microseconds is then timed at the
+ * device's pace, not at the host's launch rate (the reference times one launch between two events,
+ * tc/core/cuda/cuda_rtc.cc:373-386, which its whole-microsecond Duration then truncates).  Everything the
+ * launches need to allocate or configure must have happened before (one plain launch does that).  end
+ * destroys the object whether it succeeds or not. */
+typedef struct tcb200_replay tcb200_replay_t;
+int tcb200_replay_begin(tcb200_replay_t** replay, tcb200_stream_t* capture_stream);
+int tcb200_replay_end(tcb200_replay_t* replay, int timed_replays, float* elapsed_us_per_replay);
+
+/* Assembles an all-gathered output on `stream`.  `gathered` holds the shards of `world` ranks one after the
+ * other, each padded to the largest shard: [world][rows][max_count * inner] floats, where the sharded
+ * dimension has `total` entries split as total / world per rank with the remainder on the first ranks,
+ * `rows` is the product of the dimensions in front of it and `inner` of those behind it.  `out` receives the
+ * unsharded row-major tensor [rows][total * inner].  rows = 1 trims the padding of a dimension-0 shard;
+ * rows = M turns the transposed matmul's [world][M][N / world] into C[M][N].  No counterpart in the
+ * reference, which runs a comprehension on one device (its only multi-GPU code is the tuner's,
+ * tc/autotuner/autotuner-inl.h:279-295). */
+int tcb200_assemble_shards(const void* gathered, void* out, int world, int64_t rows, int64_t total,
+                           int64_t inner, tcb200_stream_t stream);
 
 /* Writes `bytes` of a rotating pattern to `buf` on `stream`: the bench uses it to
  * evict L2 between timed launches of the small problems. */

@@ -22,7 +22,9 @@ SYMBOLS = [
     "tcb200_query", "tcb200_plan_create", "tcb200_plan_destroy", "tcb200_plan_geometry",
     "tcb200_plan_describe", "tcb200_plan_tile", "tcb200_launch", "tcb200_l2_flush",
     "tcb200_get_device", "tcb200_set_device", "tcb200_device_name", "tcb200_stream_synchronize",
-    "tcb200_timer_start", "tcb200_timer_stop", "tcb200_reduce_launch_static",
+    "tcb200_timer_start", "tcb200_timer_stop", "tcb200_reduce_launch_static", "tcb200_assemble_shards",
+    "tcb200_status_create", "tcb200_status_destroy", "tcb200_status_check", "tcb200_selftest_wait",
+    "tcb200_replay_begin", "tcb200_replay_end",
 ]
 
 
@@ -41,13 +43,14 @@ class Problem(ctypes.Structure):
 class Tile(ctypes.Structure):
     _fields_ = [("variant", ctypes.c_int32), ("bm", ctypes.c_int32), ("bn", ctypes.c_int32),
                 ("bk", ctypes.c_int32), ("stages", ctypes.c_int32), ("threads", ctypes.c_int32),
-                ("split_tf32", ctypes.c_int32)]
+                ("split_tf32", ctypes.c_int32), ("split_k", ctypes.c_int32)]
 
     def as_tuple(self):
-        return (self.variant, self.bm, self.bn, self.bk, self.stages, self.threads, self.split_tf32)
+        return (self.variant, self.bm, self.bn, self.bk, self.stages, self.threads, self.split_tf32, self.split_k)
 
     def __repr__(self):
-        return "Tile(variant=%d, bm=%d, bn=%d, bk=%d, stages=%d, threads=%d, split_tf32=%d)" % self.as_tuple()
+        return ("Tile(variant=%d, bm=%d, bn=%d, bk=%d, stages=%d, threads=%d, split_tf32=%d, split_k=%d)"
+                % self.as_tuple())
 
 
 class Tcb200Error(RuntimeError):
@@ -84,6 +87,15 @@ def lib():
                                     ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_void_p,
                                     ctypes.c_void_p]
         L.tcb200_l2_flush.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
+        L.tcb200_status_create.argtypes = [ctypes.POINTER(ctypes.c_void_p)]
+        L.tcb200_status_destroy.argtypes = [ctypes.c_void_p]
+        L.tcb200_status_check.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]
+        L.tcb200_selftest_wait.argtypes = [ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p]
+        L.tcb200_replay_begin.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p)]
+        L.tcb200_replay_end.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_float)]
+        L.tcb200_reduce_launch_static.argtypes = [ctypes.c_void_p] * 4
+        L.tcb200_assemble_shards.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int64,
+                                             ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]
         _lib = L
     return _lib
 

@@ -32,7 +32,7 @@ std::vector<TunedCandidate> sweepTiles(const std::string& tc, const std::string&
   auto base = tc::compile<CudaBackend>(tc, entryPoint, inputs, CudaMappingOptions::makeNaiveMappingOptions());
   std::vector<tcb200_tile_t> candidates;
   auto key = [](const tcb200_tile_t& t) {
-    return std::make_tuple(t.variant, t.bm, t.bn, t.bk, t.stages, t.threads, t.split_tf32);
+    return std::make_tuple(t.variant, t.bm, t.bn, t.bk, t.stages, t.threads, t.split_tf32, t.split_k > 1 ? t.split_k : 1);
   };
   for (const auto& l : base->launches()) {
     tcb200_tile_t tiles[32];

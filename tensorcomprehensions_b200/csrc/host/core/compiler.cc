@@ -3,6 +3,7 @@
 #include "tc/core/compiler.h"
 
 #include <iostream>
+#include <memory>
 #include <sstream>
 
 #include "tc/core/check.h"
@@ -134,30 +135,74 @@ CudaTcExecutor::CudaTcExecutor(const std::vector<TensorInfo>& inputsInfo,
                                const CudaCompilationResult& result)
     : TcExecutor<CudaBackend>(inputsInfo, outputsInfo, def, result), launches_(result.launches),
       tiles_(result.tiles), grid_(result.grid), block_(result.block), device_(result.device) {
-  for (size_t i = 0; i < launches_.size(); ++i) {
-    tcb200_plan_t* plan = nullptr;
-    TC_TCB200_ENFORCE(tcb200_plan_create(&launches_[i].problem, &tiles_[i], device_, &plan));
-    plans_.push_back(plan);
-  }
+  for (auto& s : states_) s.store(nullptr, std::memory_order_relaxed);
+  for (const auto& l : launches_) accumulates_ = accumulates_ || l.problem.accumulate != 0;
 }
 
 CudaTcExecutor::~CudaTcExecutor() {
-  for (auto* p : plans_) tcb200_plan_destroy(p);
+  for (auto& slot : states_) {
+    DeviceState* st = slot.load(std::memory_order_acquire);
+    if (!st) continue;
+    for (auto* p : st->plans) tcb200_plan_destroy(p);
+    if (st->status) tcb200_status_destroy(st->status);
+    delete st;
+  }
+}
+
+// Plans and status word of the calling thread's current device; created at the first use there.
+const CudaTcExecutor::DeviceState& CudaTcExecutor::stateForCurrentDevice() const {
+  int dev = 0;
+  TC_TCB200_ENFORCE(tcb200_get_device(&dev));
+  if (dev < 0 || dev >= kMaxDevices) throw std::runtime_error("CudaTcExecutor: device index out of range");
+  DeviceState* st = states_[dev].load(std::memory_order_acquire);
+  if (st) return *st;
+  std::lock_guard<std::mutex> lock(mu_);
+  st = states_[dev].load(std::memory_order_relaxed);
+  if (st) return *st;
+  std::unique_ptr<DeviceState> fresh(new DeviceState());
+  try {
+    for (size_t i = 0; i < launches_.size(); ++i) {
+      tcb200_plan_t* plan = nullptr;
+      TC_TCB200_ENFORCE(tcb200_plan_create(&launches_[i].problem, &tiles_[i], dev, &plan));
+      fresh->plans.push_back(plan);
+    }
+    TC_TCB200_ENFORCE(tcb200_status_create(&fresh->status));
+  } catch (...) {
+    for (auto* p : fresh->plans) tcb200_plan_destroy(p);
+    throw;
+  }
+  st = fresh.release();
+  states_[dev].store(st, std::memory_order_release);
+  return *st;
 }
 
 void CudaTcExecutor::uncheckedRun(const std::vector<const void*>& inputs, const std::vector<void*>& outputs,
                                   CudaBackend::RuntimeInformation info) const {
+  const DeviceState& st = stateForCurrentDevice();
+  int* status = info.deviceStatus ? info.deviceStatus : st.status;
   const size_t nIn = inputs.size();
   auto value = [&](int idx) -> const void* {
     return (size_t)idx < nIn ? inputs[idx] : outputs[idx - nIn];
   };
-  for (size_t i = 0; i < plans_.size(); ++i) {
+  for (size_t i = 0; i < st.plans.size(); ++i) {
     const MatchedLaunch& l = launches_[i];
     const void* ins[3];
     for (size_t j = 0; j < l.inputs.size(); ++j) ins[j] = value(l.inputs[j]);
     void* outs[1] = {outputs[l.output - nIn]};
-    TC_TCB200_ENFORCE(tcb200_launch(plans_[i], ins, (int)l.inputs.size(), outs, 1, info.stream, info.deviceStatus));
+    TC_TCB200_ENFORCE(tcb200_launch(st.plans[i], ins, (int)l.inputs.size(), outs, 1, info.stream, status));
   }
+}
+
+void CudaTcExecutor::checkDeviceStatus(tcb200_stream_t stream) const {
+  const DeviceState& st = stateForCurrentDevice();
+  int code = 0;
+  const int rc = tcb200_status_check(st.status, stream, &code);
+  if (rc == TCB200_ERR_DEVICE_TIMEOUT) {
+    std::ostringstream err;
+    err << "a device-side wait gave up (code " << code << ") while running\n" << compiledSource;
+    throw std::runtime_error(err.str());
+  }
+  TC_TCB200_ENFORCE(rc);
 }
 
 ProfilingInfo CudaTcExecutor::profileUnchecked(const std::vector<const void*>& inputs,
@@ -174,6 +219,24 @@ ProfilingInfo CudaTcExecutor::profileUnchecked(const std::vector<const void*>& i
   }
   float us = 0.f;
   TC_TCB200_ENFORCE(tcb200_timer_stop(timer, nullptr, &us));
+  // Short defs: R runs replayed from a graph so that the window holds ~200 us of device time.  The plain
+  // run above has done whatever the launches set up at their first use.
+  if (!accumulates_ && us < 100.f) {
+    const int runs = std::max(2, std::min(256, (int)(200.f / std::max(us, 0.5f)) + 1));
+    tcb200_replay_t* replay = nullptr;
+    tcb200_stream_t cs = nullptr;
+    if (tcb200_replay_begin(&replay, &cs) == TCB200_OK) {
+      bool ok = true;
+      try {
+        for (int i = 0; i < runs; ++i) uncheckedRun(inputs, outputs, CudaBackend::RuntimeInformation(cs));
+      } catch (...) {
+        ok = false;  // a launch that cannot be captured: keep the single-launch time
+      }
+      float perReplay = 0.f;
+      if (tcb200_replay_end(replay, 3, &perReplay) == TCB200_OK && ok && perReplay > 0.f) us = perReplay / (float)runs;
+    }
+  }
+  checkDeviceStatus(nullptr);
   Duration kernel = Duration::fromMicroSeconds((size_t)us);
   Duration cpu = Duration::since(start);
   cpu = cpu - kernel;

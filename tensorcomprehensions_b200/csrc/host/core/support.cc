@@ -357,8 +357,10 @@ CudaMappingOptions CudaMappingOptions::makeGroupConvolutionMappingOptions() {
 
 CudaMappingOptions CudaMappingOptions::fromTile(const tcb200_tile_t& t) {
   CudaMappingOptions mo = makeUnmappedMappingOptions();
-  mo.tile((uint64_t)t.bm, (uint64_t)t.bn, (uint64_t)t.bk)
-      .mapToThreads((uint64_t)std::max(t.threads, 1))
+  // a fourth tile size carries the split of the reduction (split-K) when there is one
+  if (t.split_k > 1) mo.tile((uint64_t)t.bm, (uint64_t)t.bn, (uint64_t)t.bk, (uint64_t)t.split_k);
+  else mo.tile((uint64_t)t.bm, (uint64_t)t.bn, (uint64_t)t.bk);
+  mo.mapToThreads((uint64_t)std::max(t.threads, 1))
       .mapToBlocks(1)
       .unroll((uint64_t)t.stages)
       .useSharedMemory(true)
@@ -369,7 +371,9 @@ CudaMappingOptions CudaMappingOptions::fromTile(const tcb200_tile_t& t) {
   return mo;
 }
 bool CudaMappingOptions::toTile(tcb200_tile_t* t) const {
-  if (!generic.matchLibraryCallsFlag || generic.tiling.size() != 3 || privateDepthValue == 0) return false;
+  if (!generic.matchLibraryCallsFlag || (generic.tiling.size() != 3 && generic.tiling.size() != 4) ||
+      privateDepthValue == 0)
+    return false;
   memset(t, 0, sizeof(*t));
   t->variant = (int)privateDepthValue;
   t->bm = (int)generic.tiling[0];
@@ -378,6 +382,7 @@ bool CudaMappingOptions::toTile(tcb200_tile_t* t) const {
   t->stages = generic.hasUnroll ? (int)generic.unrollFactor : 0;
   t->threads = (int)block.x;
   t->split_tf32 = (int)sharedDepthValue;
+  t->split_k = generic.tiling.size() == 4 ? (int)generic.tiling[3] : 0;
   return true;
 }
 
@@ -561,7 +566,7 @@ std::ostream& operator<<(std::ostream& os, const CudaMappingOptions& o) {
   tcb200_tile_t t;
   if (o.toTile(&t))
     os << "# tile sweep point: variant=" << t.variant << " tile=" << t.bm << "x" << t.bn << "x" << t.bk
-       << " stages=" << t.stages << " threads=" << t.threads << " split_tf32=" << t.split_tf32 << "\n";
+       << " stages=" << t.stages << " threads=" << t.threads << " split_tf32=" << t.split_tf32 << " split_k=" << t.split_k << "\n";
   return os;
 }
 

@@ -77,6 +77,15 @@ struct PyExecutor {
   std::string tc, entry;
 };
 
+// The executor runs on the calling thread's current device (like the reference's); Python callers hand over
+// tensors, so the device of the first input is made current for the duration of the call.
+struct OnDeviceOf {
+  explicit OnDeviceOf(const std::vector<at::Tensor>& inputs) {
+    if (!inputs.empty() && inputs[0].is_cuda()) guard.reset(new tc::WithCudaDevice((size_t)inputs[0].get_device()));
+  }
+  std::unique_ptr<tc::WithCudaDevice> guard;
+};
+
 }  // namespace
 
 PYBIND11_MODULE(tclib, m) {
@@ -116,13 +125,14 @@ PYBIND11_MODULE(tclib, m) {
       .def("scheduleFusionStrategy", [](CudaMappingOptions& o, const std::string& s) -> CudaMappingOptions& { return o.scheduleFusionStrategy(s); }, py::return_value_policy::reference_internal)
       .def("outerScheduleFusionStrategy", [](CudaMappingOptions& o, const std::string& s) -> CudaMappingOptions& { return o.outerScheduleFusionStrategy(s); }, py::return_value_policy::reference_internal)
       .def("intraTileScheduleFusionStrategy", [](CudaMappingOptions& o, const std::string& s) -> CudaMappingOptions& { return o.intraTileScheduleFusionStrategy(s); }, py::return_value_policy::reference_internal)
-      .def_static("from_tile", [](int variant, int bm, int bn, int bk, int stages, int threads, int split) {
-        return CudaMappingOptions::fromTile(tcb200_tile_t{variant, bm, bn, bk, stages, threads, split});
-      })
+      .def_static("from_tile", [](int variant, int bm, int bn, int bk, int stages, int threads, int split, int split_k) {
+        return CudaMappingOptions::fromTile(tcb200_tile_t{variant, bm, bn, bk, stages, threads, split, split_k});
+      }, py::arg("variant"), py::arg("bm"), py::arg("bn"), py::arg("bk"), py::arg("stages"), py::arg("threads"),
+         py::arg("split_tf32"), py::arg("split_k") = 0)
       .def("to_tile", [](const CudaMappingOptions& o) -> py::object {
         tcb200_tile_t t;
         if (!o.toTile(&t)) return py::none();
-        return py::make_tuple(t.variant, t.bm, t.bn, t.bk, t.stages, t.threads, t.split_tf32);
+        return py::make_tuple(t.variant, t.bm, t.bn, t.bk, t.stages, t.threads, t.split_tf32, t.split_k);
       });
 
   py::class_<PyExecutor>(m, "TcExecutor")
@@ -131,6 +141,7 @@ PYBIND11_MODULE(tclib, m) {
              if (outputs.empty()) outputs = tc::aten::prepareOutputs(e.tc, e.entry, inputs);
              auto in = tc::aten::makeDLConstTensors(inputs);
              auto out = tc::aten::makeDLTensors(outputs);
+             OnDeviceOf dev(inputs);
              e.exe->run(tc::extractRawPtrs(in), tc::extractRawPtrs(out),
                         tc::CudaRuntimeInformation(currentStream(inputs, stream)));
              return outputs;
@@ -142,6 +153,7 @@ PYBIND11_MODULE(tclib, m) {
              std::vector<void*> rawOut;
              for (const auto& t : inputs) rawIn.push_back(t.data_ptr());
              for (auto& t : outputs) rawOut.push_back(t.data_ptr());
+             OnDeviceOf dev(inputs);
              e.exe->uncheckedRun(rawIn, rawOut, tc::CudaRuntimeInformation(currentStream(inputs, stream)));
              return outputs;
            },
@@ -149,6 +161,7 @@ PYBIND11_MODULE(tclib, m) {
       .def("profile",
            [](PyExecutor& e, const std::vector<at::Tensor>& inputs, std::vector<at::Tensor> outputs) {
              if (outputs.empty()) outputs = tc::aten::prepareOutputs(e.tc, e.entry, inputs);
+             OnDeviceOf dev(inputs);
              tc::ProfilingInfo pi = tc::aten::profile(*e.exe, inputs, outputs);
              py::dict d;
              d["cpu_overhead_us"] = pi.cpuOverhead.toMicroSeconds();
@@ -156,6 +169,13 @@ PYBIND11_MODULE(tclib, m) {
              return d;
            },
            py::arg("inputs"), py::arg("outputs") = std::vector<at::Tensor>())
+      .def("check_device_status",
+           [](PyExecutor& e, int device, py::object stream) {
+             tc::WithCudaDevice dev((size_t)device);
+             e.exe->checkDeviceStatus(stream.is_none() ? nullptr : reinterpret_cast<tcb200_stream_t>(stream.cast<uintptr_t>()));
+           },
+           py::arg("device") = 0, py::arg("stream") = py::none(),
+           "Waits for the stream and raises if a kernel's bounded device-side wait gave up since the last check.")
       .def_property_readonly("compiled_source", [](const PyExecutor& e) { return e.exe->compiledSource; })
       .def_property_readonly("num_launches", [](const PyExecutor& e) { return e.exe->numLaunches(); })
       .def_property_readonly("device", [](const PyExecutor& e) { return e.exe->device(); })
@@ -174,7 +194,7 @@ PYBIND11_MODULE(tclib, m) {
       .def("tiles", [](const PyExecutor& e) {
         py::list r;
         for (const auto& t : e.exe->tiles())
-          r.append(py::make_tuple(t.variant, t.bm, t.bn, t.bk, t.stages, t.threads, t.split_tf32));
+          r.append(py::make_tuple(t.variant, t.bm, t.bn, t.bk, t.stages, t.threads, t.split_tf32, t.split_k));
         return r;
       });
 

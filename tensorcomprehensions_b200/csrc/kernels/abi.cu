@@ -8,6 +8,7 @@
 #include <mutex>
 #include <new>
 
+#include "async.cuh"
 #include "common.cuh"
 
 namespace tcb200 {
@@ -15,12 +16,42 @@ namespace tcb200 {
 static thread_local cudaError_t g_last_cuda_error = cudaSuccess;
 void set_last_cuda_error(cudaError_t e) { g_last_cuda_error = e; }
 
+int sm_count(int device) {
+  static std::atomic<int> cached[64];
+  if (device < 0 && cudaGetDevice(&device) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return kNumSMs;
+  }
+  if (device < 0 || device >= 64) return kNumSMs;
+  int n = cached[device].load(std::memory_order_relaxed);
+  if (n > 0) return n;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) {
+    (void)cudaGetLastError();
+    return kNumSMs;
+  }
+  cached[device].store(n, std::memory_order_relaxed);
+  return n;
+}
+
 namespace {
 
 __global__ void l2_flush_kernel(float4* buf, size_t n4, float v) {
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4;
        i += (size_t)gridDim.x * blockDim.x)
     buf[i] = make_float4(v, v, v, v);
+}
+
+// One warp waits on a barrier that nothing arrives on; the bounded wait gives up after `limit` cycles.
+__global__ void selftest_wait_kernel(long long limit, int* dev_status) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  mbar_wait_slow(&bar, 0, TCB200_SELFTEST_WAIT_CODE, dev_status, &abort_flag, limit);
 }
 
 int n_inputs_expected(const tcb200_problem_t& p) {
@@ -60,6 +91,8 @@ struct tcb200_plan {
   // freed with the plan.  Launches of one such plan share it, so they must not overlap in time.
   std::mutex scratch_mu;
   std::atomic<void*> scratch{nullptr};
+  // tensor-core contraction plans: tensor maps of the last few sets of base pointers
+  void* map_cache = nullptr;
 };
 
 namespace tcb200 {
@@ -68,6 +101,11 @@ const Plan* plan_of(const tcb200_plan_t* handle) { return handle ? &handle->impl
 
 struct tcb200_timer {
   cudaEvent_t start = nullptr, stop = nullptr;
+};
+
+struct tcb200_replay {
+  cudaStream_t stream = nullptr;
+  bool capturing = false;
 };
 
 extern "C" {
@@ -145,6 +183,7 @@ int tcb200_plan_create(const tcb200_problem_t* problem, const tcb200_tile_t* til
   P.p = *problem;
   if (tile) P.tile = *tile; else memset(&P.tile, 0, sizeof(P.tile));
   P.device = device;
+  P.sms = sm_count(device);
   P.kernel_id = 0;
   int st = TCB200_ERR_INVALID_ARGUMENT;
   switch (problem->family) {
@@ -168,9 +207,12 @@ int tcb200_plan_create(const tcb200_problem_t* problem, const tcb200_tile_t* til
         P.tile = first;
       }
       if (P.tile.variant == TCB200_VARIANT_TCGEN05 || P.tile.variant == TCB200_VARIANT_TCGEN05_TS ||
-          P.tile.variant == TCB200_VARIANT_TCGEN05_PAIR)
+          P.tile.variant == TCB200_VARIANT_TCGEN05_PAIR) {
         st = contraction_tc_plan(P);
-      else st = contraction_simt_plan(P);
+        if (st == TCB200_OK) pl->map_cache = tc_map_cache_new();
+      } else {
+        st = contraction_simt_plan(P);
+      }
       break;
     default:
       break;
@@ -186,15 +228,19 @@ int tcb200_plan_create(const tcb200_problem_t* problem, const tcb200_tile_t* til
 int tcb200_plan_destroy(tcb200_plan_t* plan) {
   if (plan) {
     if (void* s = plan->scratch.load()) cudaFree(s);
+    if (plan->map_cache) tc_map_cache_delete(plan->map_cache);
     delete plan;
   }
   return TCB200_OK;
 }
 
 namespace {
-// Device scratch of the plan: tickets first (zeroed), then the partial sums.  The allocation and the
-// memset are synchronous host calls: the first launch of such a plan must not be inside a stream capture.
-int plan_scratch(const tcb200_plan_t* cplan, float** partial, unsigned** tickets) {
+// Device scratch of the plan: tickets first (zeroed), then the partial sums.  The allocation is a
+// synchronous host call: the first launch of such a plan must not be inside a stream capture.  The tickets
+// are zeroed on the launch stream `s`, so the kernel that follows on `s` is ordered behind the zeroing
+// whatever kind of stream `s` is (a memset on the legacy default stream would not be ordered against a
+// non-blocking stream).
+int plan_scratch(const tcb200_plan_t* cplan, float** partial, unsigned** tickets, cudaStream_t s) {
   *partial = nullptr;
   *tickets = nullptr;
   const Plan& P = cplan->impl;
@@ -207,7 +253,7 @@ int plan_scratch(const tcb200_plan_t* cplan, float** partial, unsigned** tickets
     base = plan->scratch.load(std::memory_order_relaxed);
     if (!base) {
       TCB200_CUDA_TRY(cudaMalloc(&base, ticket_bytes + P.scratch_floats * sizeof(float)));
-      cudaError_t e = cudaMemset(base, 0, ticket_bytes);
+      cudaError_t e = ticket_bytes ? cudaMemsetAsync(base, 0, ticket_bytes, s) : cudaSuccess;
       if (e != cudaSuccess) {
         cudaFree(base);
         set_last_cuda_error(e);
@@ -274,10 +320,12 @@ int tcb200_plan_describe(const tcb200_plan_t* plan, char* buf, size_t buflen) {
                epilogue_name(p.epilogue), p.accumulate ? " accumulate" : "");
       break;
   }
+  char split[32] = "";
+  if (t.split_k > 1) snprintf(split, sizeof(split), " split_k=%d", t.split_k);
   snprintf(buf, buflen,
-           "%s | variant=%s tile=%dx%dx%d stages=%d threads=%d split_tf32=%d | grid=(%u,%u,%u) "
+           "%s | variant=%s tile=%dx%dx%d stages=%d threads=%d split_tf32=%d%s | grid=(%u,%u,%u) "
            "block=(%u,%u,%u) smem=%zu",
-           head, variant_name(t.variant), t.bm, t.bn, t.bk, t.stages, t.threads, t.split_tf32,
+           head, variant_name(t.variant), t.bm, t.bn, t.bk, t.stages, t.threads, t.split_tf32, split,
            l.grid.x, l.grid.y, l.grid.z, l.block.x, l.block.y, l.block.z, l.smem);
   return TCB200_OK;
 }
@@ -306,14 +354,19 @@ int tcb200_launch(const tcb200_plan_t* plan, const void* const* inputs, int n_in
     case TCB200_FAMILY_REDUCTION: {
       float* partial;
       unsigned* tickets;
-      const int st = plan_scratch(plan, &partial, &tickets);
+      const int st = plan_scratch(plan, &partial, &tickets, s);
       if (st != TCB200_OK) return st;
       return reduce_launch(P, in0, out, partial, tickets, s);
     }
     case TCB200_FAMILY_CONTRACTION:
       if (P.tile.variant == TCB200_VARIANT_TCGEN05 || P.tile.variant == TCB200_VARIANT_TCGEN05_TS ||
-          P.tile.variant == TCB200_VARIANT_TCGEN05_PAIR)
-        return contraction_tc_launch(P, in0, in1, bias, out, s, dev_status);
+          P.tile.variant == TCB200_VARIANT_TCGEN05_PAIR) {
+        float* partial;
+        unsigned* tickets;
+        const int st = plan_scratch(plan, &partial, &tickets, s);
+        if (st != TCB200_OK) return st;
+        return contraction_tc_launch(P, in0, in1, bias, out, s, dev_status, partial, plan->map_cache);
+      }
       return contraction_simt_launch(P, in0, in1, bias, out, s);
     default:
       return TCB200_ERR_INVALID_ARGUMENT;
@@ -380,11 +433,107 @@ int tcb200_timer_stop(tcb200_timer_t* timer, tcb200_stream_t stream, float* elap
   return TCB200_OK;
 }
 
+int tcb200_status_create(int** dev_status) {
+  if (!dev_status) return TCB200_ERR_INVALID_ARGUMENT;
+  *dev_status = nullptr;
+  int* p = nullptr;
+  TCB200_CUDA_TRY(cudaMalloc(&p, sizeof(int)));
+  cudaError_t e = cudaMemset(p, 0, sizeof(int));
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    set_last_cuda_error(e);
+    return TCB200_ERR_CUDA;
+  }
+  *dev_status = p;
+  return TCB200_OK;
+}
+
+int tcb200_status_destroy(int* dev_status) {
+  if (dev_status) cudaFree(dev_status);
+  return TCB200_OK;
+}
+
+int tcb200_status_check(int* dev_status, tcb200_stream_t stream, int* code) {
+  if (!dev_status) return TCB200_ERR_INVALID_ARGUMENT;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  int v = 0;
+  TCB200_CUDA_TRY(cudaMemcpyAsync(&v, dev_status, sizeof(int), cudaMemcpyDeviceToHost, s));
+  TCB200_CUDA_TRY(cudaStreamSynchronize(s));
+  if (code) *code = v;
+  if (v == 0) return TCB200_OK;
+  TCB200_CUDA_TRY(cudaMemsetAsync(dev_status, 0, sizeof(int), s));
+  TCB200_CUDA_TRY(cudaStreamSynchronize(s));
+  return TCB200_ERR_DEVICE_TIMEOUT;
+}
+
+int tcb200_selftest_wait(long long limit_cycles, int* dev_status, tcb200_stream_t stream) {
+  // the limit is capped at the kernels' own, so the call cannot be used to keep an SM busy for long
+  if (limit_cycles <= 0 || limit_cycles > kWaitLimitCycles) return TCB200_ERR_INVALID_ARGUMENT;
+  selftest_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(limit_cycles, dev_status);
+  TCB200_CUDA_TRY(cudaGetLastError());
+  return TCB200_OK;
+}
+
+int tcb200_replay_begin(tcb200_replay_t** replay, tcb200_stream_t* capture_stream) {
+  if (!replay || !capture_stream) return TCB200_ERR_INVALID_ARGUMENT;
+  *replay = nullptr;
+  *capture_stream = nullptr;
+  tcb200_replay_t* r = new (std::nothrow) tcb200_replay_t();
+  if (!r) return TCB200_ERR_INVALID_ARGUMENT;
+  cudaError_t e = cudaStreamCreateWithFlags(&r->stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaStreamBeginCapture(r->stream, cudaStreamCaptureModeThreadLocal);
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e);
+    (void)cudaGetLastError();
+    if (r->stream) cudaStreamDestroy(r->stream);
+    delete r;
+    return TCB200_ERR_CUDA;
+  }
+  r->capturing = true;
+  *replay = r;
+  *capture_stream = reinterpret_cast<tcb200_stream_t>(r->stream);
+  return TCB200_OK;
+}
+
+int tcb200_replay_end(tcb200_replay_t* r, int timed_replays, float* elapsed_us_per_replay) {
+  if (!r) return TCB200_ERR_INVALID_ARGUMENT;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  cudaError_t e = cudaStreamEndCapture(r->stream, &graph);  // always: leaves the stream out of capture mode
+  r->capturing = false;
+  if (e == cudaSuccess && (!elapsed_us_per_replay || timed_replays <= 0)) e = cudaErrorInvalidValue;
+  if (e == cudaSuccess) e = cudaGraphInstantiate(&exec, graph, 0);
+  if (e == cudaSuccess) e = cudaEventCreate(&e0);
+  if (e == cudaSuccess) e = cudaEventCreate(&e1);
+  if (e == cudaSuccess) e = cudaGraphLaunch(exec, r->stream);  // untimed: uploads the graph, warms the caches
+  if (e == cudaSuccess) e = cudaEventRecord(e0, r->stream);
+  for (int i = 0; e == cudaSuccess && i < timed_replays; ++i) e = cudaGraphLaunch(exec, r->stream);
+  if (e == cudaSuccess) e = cudaEventRecord(e1, r->stream);
+  if (e == cudaSuccess) e = cudaEventSynchronize(e1);
+  float ms = 0.f;
+  if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+  if (e0) cudaEventDestroy(e0);
+  if (e1) cudaEventDestroy(e1);
+  if (exec) cudaGraphExecDestroy(exec);
+  if (graph) cudaGraphDestroy(graph);
+  cudaStreamDestroy(r->stream);
+  delete r;
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e);
+    (void)cudaGetLastError();
+    return TCB200_ERR_CUDA;
+  }
+  *elapsed_us_per_replay = ms * 1000.f / (float)timed_replays;
+  return TCB200_OK;
+}
+
 int tcb200_l2_flush(void* buf, size_t bytes, tcb200_stream_t stream) {
   if (!buf || bytes < 16 || ((uintptr_t)buf & 15)) return TCB200_ERR_INVALID_ARGUMENT;
   static unsigned counter = 0;
   const float v = (float)(++counter & 1023);
-  l2_flush_kernel<<<kNumSMs * 4, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  l2_flush_kernel<<<sm_count(-1) * 4, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       static_cast<float4*>(buf), bytes / 16, v);
   TCB200_CUDA_TRY(cudaGetLastError());
   return TCB200_OK;

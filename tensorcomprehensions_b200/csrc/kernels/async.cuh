@@ -40,17 +40,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after ~4e9 SM cycles (about two seconds), records `code` and returns false.
-// The SM cycle counter is used because it is cheap to read; a wait that succeeds within the first
-// few thousand polls (every wait of a healthy pipeline) never reads a timer at all.
+// Bounded wait: gives up after `limit` SM cycles (default ~4e9, about two seconds), records `code` and
+// returns false.  The SM cycle counter is used because it is cheap to read; a wait that succeeds within the
+// first few thousand polls (every wait of a healthy pipeline) never reads a timer at all.
+constexpr long long kWaitLimitCycles = 4000000000ll;
 static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int code,
-                                                   int* dev_status, volatile int* abort_flag) {
+                                                   int* dev_status, volatile int* abort_flag,
+                                                   long long limit = kWaitLimitCycles) {
   const long long t0 = clock64();
   for (;;) {
     for (int i = 0; i < 1024; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > 4000000000ll) {
+    if (clock64() - t0 > limit) {
       *abort_flag = code;
       if (dev_status) atomicCAS(dev_status, 0, code);
       return false;

@@ -12,7 +12,12 @@
 
 namespace tcb200 {
 
-constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs; grids are sized in multiples of this
+constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs; used only when no device can be asked
+// Multiprocessors of `device` (< 0: the calling thread's current device), asked once per device and cached;
+// kNumSMs when there is no usable device (plans can be created and inspected on a host without a GPU).
+// Persistent grids are sized from this, so a MIG slice or another Blackwell part is neither over- nor
+// under-subscribed.
+int sm_count(int device);
 
 // Launch geometry + resolved tile of one plan.
 struct Launch {
@@ -25,6 +30,7 @@ struct Plan {
   tcb200_problem_t p;
   tcb200_tile_t tile;
   int device;
+  int sms = kNumSMs;  // multiprocessors of `device`, filled in by tcb200_plan_create
   Launch launch;
   int kernel_id;  // family-private selector of the instantiated kernel
   // Scratch global memory the launches of this plan need (reduction family, when the reduced range is
@@ -110,8 +116,13 @@ int contraction_simt_launch(const Plan& plan, const float* A, const float* B, co
 int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n);
 bool contraction_tc_preferred(const tcb200_problem_t& p);  // tensor-core tiles ahead of the SIMT ones
 int contraction_tc_plan(Plan& plan);
+// scratch: plan.scratch_floats floats when the plan splits the reduction (tile.split_k > 1), else unused;
+// map_cache: a cache made by tc_map_cache_new() (may be null: the tensor maps are then encoded per launch)
 int contraction_tc_launch(const Plan& plan, const float* A, const float* B, const float* bias,
-                          float* C, cudaStream_t s, int* dev_status);
+                          float* C, cudaStream_t s, int* dev_status, float* scratch, void* map_cache);
+constexpr int kTcMapSlots = 8;
+void* tc_map_cache_new();
+void tc_map_cache_delete(void* cache);
 
 int group_conv_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n);
 int group_conv_plan(Plan& plan);

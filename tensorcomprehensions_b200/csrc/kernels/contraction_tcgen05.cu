@@ -58,6 +58,8 @@ struct TcArgs {
   int a_batched, b_batched;  // 0: operand shared by all batch entries
   int c_vec;                 // 128-bit stores allowed
   int tma_store;             // pair kernel: epilogue through the staging tile and tiled TMA stores
+  int ksplit_kb;             // split-K launch (TS and pair kernels): k-blocks per split, the "batch" index is the
+                             // split and selects the k range, not an operand slab; 0 = the whole reduction
   int* dev_status;
 };
 
@@ -440,7 +442,8 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_kb = (a.K + BK - 1) / BK;
+  // split-K: every split runs the same number of k-blocks; those past the end of K read zeros (TMA fill)
+  const int num_kb = a.ksplit_kb > 0 ? a.ksplit_kb : (a.K + BK - 1) / BK;
   const int tiles_n = (a.N + BN - 1) / BN, tiles_m = (a.M + BM - 1) / BM;
   const int64_t num_tiles = (int64_t)tiles_n * tiles_m * a.batch;
 
@@ -499,17 +502,18 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
         int m0, n0, bz;
         tile_coords(t, &m0, &n0, &bz);
         const int za = a.a_batched ? bz : 0, zb = a.b_batched ? bz : 0;
+        const int k0 = a.ksplit_kb > 0 ? bz * a.ksplit_kb * BK : 0;  // first k of this split
         bool ok = true;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int sa = it % A_SLOTS, sb = it % B_SLOTS;
           ok = mbar_wait(&empty_a[sa], ((it / A_SLOTS) & 1) ^ 1, 1, a.dev_status, abort_flag);
           if (!ok) break;
           mbar_expect_tx(&full_a[sa], A_BYTES);
-          tma_load_3d(smem + sa * A_BYTES, &tmA, kb * BK, m0, za, &full_a[sa]);
+          tma_load_3d(smem + sa * A_BYTES, &tmA, k0 + kb * BK, m0, za, &full_a[sa]);
           ok = mbar_wait(&empty_b[sb], ((it / B_SLOTS) & 1) ^ 1, 1, a.dev_status, abort_flag);
           if (!ok) break;
           mbar_expect_tx(&full_b[sb], B_BYTES);
-          tma_load_3d(smem + B_RING + sb * B_BYTES, &tmB, kb * BK, n0, zb, &full_b[sb]);
+          tma_load_3d(smem + B_RING + sb * B_BYTES, &tmB, k0 + kb * BK, n0, zb, &full_b[sb]);
         }
         if (!ok) break;
       }
@@ -799,7 +803,8 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();          // 0: leader (issues the MMAs), 1: peer
   const int64_t pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-  const int num_kb = (a.K + BK - 1) / BK;
+  // split-K: every split runs the same number of k-blocks; those past the end of K read zeros (TMA fill)
+  const int num_kb = a.ksplit_kb > 0 ? a.ksplit_kb : (a.K + BK - 1) / BK;
   const int tiles_n = (a.N + BN - 1) / BN, tiles_m = (a.M + 2 * BM - 1) / (2 * BM);
   const int64_t num_tiles = (int64_t)tiles_n * tiles_m * a.batch;  // tiles of 256 x BN, one per pair
 
@@ -860,17 +865,18 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         int m0, n0, bz;
         tile_coords(t, &m0, &n0, &bz);
         const int za = a.a_batched ? bz : 0, zb = a.b_batched ? bz : 0;
+        const int k0 = a.ksplit_kb > 0 ? bz * a.ksplit_kb * BK : 0;  // first k of this split
         bool ok = true;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int sa = it % A_SLOTS, sb = it % B_SLOTS;
           ok = mbar_wait(&empty_a[sa], ((it / A_SLOTS) & 1) ^ 1, 1, a.dev_status, abort_flag);
           if (!ok) break;
           mbar_expect_tx(&full_a[sa], A_BYTES);
-          tma_load_3d(smem + sa * A_BYTES, &tmA, kb * BK, m0, za, &full_a[sa]);
+          tma_load_3d(smem + sa * A_BYTES, &tmA, k0 + kb * BK, m0, za, &full_a[sa]);
           ok = mbar_wait(&empty_b[sb], ((it / B_SLOTS) & 1) ^ 1, 1, a.dev_status, abort_flag);
           if (!ok) break;
           mbar_expect_tx(&full_b[sb], B_BYTES);
-          tma_load_3d(smem + B_RING + sb * B_BYTES, &tmB, kb * BK, n0 + (int)rank * (BN / 2), zb, &full_b[sb]);
+          tma_load_3d(smem + B_RING + sb * B_BYTES, &tmB, k0 + kb * BK, n0 + (int)rank * (BN / 2), zb, &full_b[sb]);
         }
         if (!ok) break;
       }
@@ -1156,6 +1162,66 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
 }
 
 
+// ---------------------------------------------------------------------------------- split-K, second pass
+// A contraction whose output has too few tiles for the SMs (a 128 x 2048 x 4096 shard of the transposed matmul:
+// 16 tiles for 148 SMs) splits its reduction over S CTAs per tile.  The tensor-core kernel runs as a "batch" of
+// S splits that write raw partial sums P[s][m][n] to scratch memory owned by the plan; this kernel adds the S
+// partials of every element in the fixed order s = 0 .. S-1 (the same bits on every run), then applies what the
+// single-pass kernel's epilogue would: the old output for "+=", bias, ReLU.
+struct SplitKArgs {
+  const float* P;
+  float* C;
+  const float* bias;
+  int M, N, S;
+  int64_t ldc;
+  int epi, bias_on_m, accumulate;
+};
+
+template <bool VEC>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(SplitKArgs a) {
+  pdl_sync();  // the partial sums come from the kernel launched just before this one
+  const bool has_bias = a.epi == TCB200_EPI_BIAS || a.epi == TCB200_EPI_BIAS_RELU;
+  const int64_t plane = (int64_t)a.M * a.N;
+  if (VEC) {
+    const int n4 = a.N >> 2;
+    const int64_t total = (int64_t)a.M * n4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+      const int m = (int)(i / n4), n = (int)(i - (int64_t)m * n4) * 4;
+      const float4* src = reinterpret_cast<const float4*>(a.P + (int64_t)m * a.N + n);
+      float4 acc = src[0];
+      for (int s = 1; s < a.S; ++s) {
+        const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src) + s * plane);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      float4* dst = reinterpret_cast<float4*>(a.C + (int64_t)m * a.ldc + n);
+      if (a.accumulate) {
+        const float4 old = *dst;
+        acc.x += old.x; acc.y += old.y; acc.z += old.z; acc.w += old.w;
+      }
+      float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (has_bias) {
+        if (a.bias_on_m) b.x = b.y = b.z = b.w = __ldg(a.bias + m);
+        else b = make_float4(__ldg(a.bias + n), __ldg(a.bias + n + 1), __ldg(a.bias + n + 2), __ldg(a.bias + n + 3));
+      }
+      acc.x = apply_epilogue_rt(a.epi, acc.x, b.x);
+      acc.y = apply_epilogue_rt(a.epi, acc.y, b.y);
+      acc.z = apply_epilogue_rt(a.epi, acc.z, b.z);
+      acc.w = apply_epilogue_rt(a.epi, acc.w, b.w);
+      *dst = acc;
+    }
+  } else {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < plane; i += (int64_t)gridDim.x * blockDim.x) {
+      const int m = (int)(i / a.N), n = (int)(i - (int64_t)m * a.N);
+      float acc = a.P[i];
+      for (int s = 1; s < a.S; ++s) acc += a.P[i + s * plane];
+      float* dst = a.C + (int64_t)m * a.ldc + n;
+      if (a.accumulate) acc += *dst;
+      const float b = has_bias ? __ldg(a.bias + (a.bias_on_m ? m : n)) : 0.f;
+      *dst = apply_epilogue_rt(a.epi, acc, b);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------- host
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -1265,46 +1331,85 @@ bool contraction_tc_preferred(const tcb200_problem_t& p) {
   return shape_ok(p) && worth_it(p) && (double)p.batch * p.M * p.N * p.K >= (double)(1 << 24);
 }
 
+// Split-K choice.  Estimated time of a tile shape with the reduction split S ways, in microseconds, from the
+// measured cost of one 32-wide k-block of a tile (single CTA 128 x 128: 0.62 us, CTA pair 256 x 128: 0.56 us; a
+// narrower tile is not proportionally cheaper), ~3 us per tile for pipeline fill, drain and epilogue, and for
+// S > 1 the second pass (launch + S partial planes through L2 at ~5 TB/s).  waves = units / slots rounded up.
+constexpr int kMaxSplitK = 32;
+double tc_time_estimate(const tcb200_problem_t& p, int64_t tiles, int slots, double kb_us, int S) {
+  const int64_t kbs = ceil_div(p.K, BK);
+  const int64_t waves = ceil_div(tiles * S, slots);
+  double t = (double)waves * ((double)ceil_div(kbs, S) * kb_us + 3.0);
+  if (S > 1) t += 2.0 + (double)(S + 1) * p.M * p.N * 4.0 / 5.0e6;
+  return t;
+}
+// Best S for a tile shape: 1 unless the problem is a single (unbatched) contraction whose tiles leave SMs idle.
+int pick_split_k(const tcb200_problem_t& p, int64_t tiles, int slots, double kb_us, double* est) {
+  int best = 1;
+  double best_t = tc_time_estimate(p, tiles, slots, kb_us, 1);
+  const int64_t kbs = ceil_div(p.K, BK);
+  if (p.batch == 1 && tiles < slots) {
+    for (int S = 2; S <= kMaxSplitK && kbs / S >= 4; ++S) {
+      const double t = tc_time_estimate(p, tiles, slots, kb_us, S);
+      if (t < best_t * 0.97) { best_t = t; best = S; }  // a split has to pay for itself
+    }
+  }
+  if (est) *est = best_t;
+  return best;
+}
+
 int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n) {
   *n = 0;
   if (!shape_ok(p) || !worth_it(p)) return TCB200_OK;
+  const int sms = sm_count(-1);
   int cnt = 0;
   auto push = [&](int bn, int split) {
     if (cnt < max && out)
-      out[cnt] = tcb200_tile_t{TCB200_VARIANT_TCGEN05, BM, bn, BK, num_stages(bn, split), split == 3 ? 448 : 320, split};
+      out[cnt] = tcb200_tile_t{TCB200_VARIANT_TCGEN05, BM, bn, BK, num_stages(bn, split), split == 3 ? 448 : 320, split, 1};
     ++cnt;
   };
-  auto push_ts = [&](int bn) {
-    if (cnt < max && out)
-      out[cnt] = tcb200_tile_t{TCB200_VARIANT_TCGEN05_TS, BM, bn, BK, ts_b_slots(bn), kTsThreads, 3};
-    ++cnt;
-  };
-  // Preferred tile first: fewest waves of the persistent grid, weighted by the measured time of a
-  // tile of each width relative to a 128-wide one (the tensor pipe does not run a narrower MMA
-  // proportionally faster).  N = 16384 with M = 128 gives 128 tiles at BN = 128 but 147 at BN = 112,
-  // which fills 147 of the 148 SMs in the same single wave.
+  // Candidates in the order of their estimated time: the tensor-memory tiles of three widths and, where there are
+  // two 128-row tiles to pair up, the CTA-pair tile, each with the split of the reduction that suits it.
+  // N = 16384 with M = 128 gives 128 tiles at BN = 128 but 147 at BN = 112, which fills 147 of the 148 SMs in the
+  // same single wave; a 2048-column shard of it has 16 tiles and splits its K = 4096 nine ways.
+  struct Cand { int variant, bm, bn, stages, split_k; double t; };
+  Cand cands[4];
+  int nc = 0;
   const int ts_bn[3] = {128, 112, 64};
-  const double ts_cost[3] = {1.0, 0.97, 0.65};
-  int order[3] = {0, 1, 2};
-  double cost[3];
+  const double ts_kb_us[3] = {0.62, 0.60, 0.40};
   for (int i = 0; i < 3; ++i) {
+    if (p.N < ts_bn[i]) continue;
     const int64_t tiles = ceil_div(p.N, ts_bn[i]) * ceil_div(p.M, BM) * p.batch;
-    cost[i] = (double)ceil_div(tiles, kNumSMs) * ts_cost[i];
+    Cand c{TCB200_VARIANT_TCGEN05_TS, BM, ts_bn[i], ts_b_slots(ts_bn[i]), 1, 0.0};
+    c.split_k = pick_split_k(p, tiles, sms, ts_kb_us[i], &c.t);
+    cands[nc++] = c;
   }
-  for (int i = 0; i < 3; ++i)
-    for (int j = i + 1; j < 3; ++j)
-      if (cost[order[j]] < cost[order[i]]) { const int t = order[i]; order[i] = order[j]; order[j] = t; }
-  // CTA pairs (256 x 128 tiles): first wherever there are at least two 128-row tiles to pair up
-  const bool pair_ok = p.M > BM && p.N >= kPairBN;
-  auto push_pair = [&]() {
+  if (p.M > BM && p.N >= kPairBN) {
+    const int64_t tiles = ceil_div(p.N, kPairBN) * ceil_div(p.M, 2 * BM) * p.batch;
+    Cand c{TCB200_VARIANT_TCGEN05_PAIR, 2 * BM, kPairBN, kPairBSlots, 1, 0.0};
+    c.split_k = pick_split_k(p, tiles, std::max(1, sms / 2), 0.56, &c.t);
+    c.t *= 0.999;  // ties go to the pair tile
+    cands[nc++] = c;
+  }
+  for (int i = 0; i < nc; ++i)
+    for (int j = i + 1; j < nc; ++j)
+      if (cands[j].t < cands[i].t) std::swap(cands[i], cands[j]);
+  for (int i = 0; i < nc; ++i) {
     if (cnt < max && out)
-      out[cnt] = tcb200_tile_t{TCB200_VARIANT_TCGEN05_PAIR, 2 * BM, kPairBN, BK, kPairBSlots, kTsThreads, 3};
+      out[cnt] = tcb200_tile_t{cands[i].variant, cands[i].bm, cands[i].bn, BK, cands[i].stages, kTsThreads, 3,
+                               cands[i].split_k};
     ++cnt;
-  };
-  if (pair_ok) push_pair();
-  for (int i = 0; i < 3; ++i)
-    if (p.N >= ts_bn[order[i]]) push_ts(ts_bn[order[i]]);
-  const int bns[] = {128, 256, 64};
+  }
+  for (int i = 0; i < nc; ++i) {  // the unsplit forms of the split candidates stay in the sweep
+    if (cands[i].split_k == 1) continue;
+    if (cnt < max && out)
+      out[cnt] = tcb200_tile_t{cands[i].variant, cands[i].bm, cands[i].bn, BK, cands[i].stages, kTsThreads, 3, 1};
+    ++cnt;
+  }
+  // both operands in shared memory.  The 256-wide form of this kernel keeps one accumulation over the whole K
+  // per tile and does not meet the reference's own precision bound at K = 4096: it is not listed (a plan
+  // still takes it, as a one-pass TF32 tile only, when asked for by name).
+  const int bns[] = {128, 64};
   for (int bn : bns)
     if (p.N >= bn) push(bn, 3);
   *n = cnt;
@@ -1315,24 +1420,35 @@ int contraction_tc_plan(Plan& plan) {
   const tcb200_problem_t& p = plan.p;
   if (!shape_ok(p)) return TCB200_ERR_UNSUPPORTED;
   tcb200_tile_t& t = plan.tile;
+  if (t.split_k <= 0) t.split_k = 1;
+  if (t.split_k > 1) {
+    // split-K: tensor-memory tiles only, one unbatched contraction, every split at least one k-block
+    if (t.variant == TCB200_VARIANT_TCGEN05 || p.batch != 1 || t.split_k > kMaxSplitK ||
+        ceil_div(p.K, BK) < t.split_k || p.M * p.N > (1ll << 40))
+      return TCB200_ERR_UNSUPPORTED;
+    plan.scratch_floats = (size_t)t.split_k * (size_t)p.M * (size_t)p.N;
+  }
   if (t.variant == TCB200_VARIANT_TCGEN05_PAIR) {
     if (t.bn == 0) t.bn = kPairBN;
     if (t.split_tf32 == 0) t.split_tf32 = 3;
     if (t.bn != kPairBN || t.split_tf32 != 3) return TCB200_ERR_UNSUPPORTED;
     if (ceil_div(p.M, 2 * BM) > 65535) return TCB200_ERR_UNSUPPORTED;
     t.bm = 2 * BM; t.bk = BK; t.stages = kPairBSlots; t.threads = kTsThreads;
-    const int64_t tiles = ceil_div(p.N, kPairBN) * ceil_div(p.M, 2 * BM) * p.batch;
-    plan.launch.grid = dim3(2u * (unsigned)std::min<int64_t>(tiles, kNumSMs / 2), 1, 1);
+    const int64_t tiles = ceil_div(p.N, kPairBN) * ceil_div(p.M, 2 * BM) * p.batch * t.split_k;
+    plan.launch.grid = dim3(2u * (unsigned)std::min<int64_t>(tiles, std::max(1, plan.sms / 2)), 1, 1);
     plan.launch.block = dim3(kTsThreads, 1, 1);
     plan.launch.smem = ts_pair_smem_bytes();
     plan.kernel_id = 301283;
     return TCB200_OK;
   }
   if (t.bn == 0) t.bn = 128;
-  if (t.split_tf32 == 0) t.split_tf32 = 3;
+  if (t.split_tf32 == 0) t.split_tf32 = t.bn == 256 ? 1 : 3;
   if (t.bn != 64 && t.bn != 128 && t.bn != 256 && !(t.bn == 112 && t.variant == TCB200_VARIANT_TCGEN05_TS))
     return TCB200_ERR_UNSUPPORTED;
   if (t.split_tf32 != 1 && t.split_tf32 != 3) return TCB200_ERR_UNSUPPORTED;
+  // the 256-wide tile accumulates the whole K in tensor memory: with the 3xTF32 split it would claim fp32
+  // accuracy that its truncating accumulation does not deliver at large K
+  if (t.bn == 256 && t.split_tf32 == 3) return TCB200_ERR_UNSUPPORTED;
   t.bm = BM;
   t.bk = BK;
   const bool ts_mode = t.variant == TCB200_VARIANT_TCGEN05_TS;
@@ -1340,56 +1456,115 @@ int contraction_tc_plan(Plan& plan) {
   t.stages = ts_mode ? ts_b_slots(t.bn) : num_stages(t.bn, t.split_tf32);
   t.threads = ts_mode ? kTsThreads : (t.split_tf32 == 3 ? 448 : 320);
   // persistent CTAs, one per SM, walking the tiles with a static stride
-  const int64_t tiles = ceil_div(p.N, t.bn) * ceil_div(p.M, BM) * p.batch;
-  plan.launch.grid = dim3((unsigned)std::min<int64_t>(tiles, kNumSMs), 1, 1);
+  const int64_t tiles = ceil_div(p.N, t.bn) * ceil_div(p.M, BM) * p.batch * t.split_k;
+  plan.launch.grid = dim3((unsigned)std::min<int64_t>(tiles, plan.sms), 1, 1);
   plan.launch.block = dim3(t.threads, 1, 1);
   plan.launch.smem = ts_mode ? ts_smem_bytes(t.bn) : smem_bytes(t.bn, t.split_tf32);
   plan.kernel_id = t.bn * 10 + t.split_tf32 + (ts_mode ? 100000 : 0);
   return TCB200_OK;
 }
 
+// Tensor maps of one set of base pointers.  Encoding a map is host work of the order of a microsecond; a plan
+// that is launched again and again on the same few buffers (an executor in a loop, a benchmark rotating
+// over buffer sets) takes them from this small per-plan cache instead.
+struct TcMaps {
+  const void* key[3] = {nullptr, nullptr, nullptr};
+  CUtensorMap ta, tb, tc;
+  bool valid = false, has_tc = false;
+};
+struct TcMapCache {
+  std::mutex mu;
+  TcMaps slot[kTcMapSlots];
+  int next = 0;
+};
+
+void* tc_map_cache_new() { return new (std::nothrow) TcMapCache(); }
+void tc_map_cache_delete(void* c) { delete static_cast<TcMapCache*>(c); }
+
 int contraction_tc_launch(const Plan& plan, const float* A, const float* B, const float* bias,
-                          float* C, cudaStream_t s, int* dev_status) {
+                          float* C, cudaStream_t s, int* dev_status, float* scratch, void* map_cache) {
   const tcb200_problem_t& p = plan.p;
   if (((uintptr_t)A | (uintptr_t)B) & 15) return TCB200_ERR_ALIGNMENT;
-  CUtensorMap ta, tb;
-  int st = make_operand_map(&ta, A, p.K, p.M, p.lda, p.batch, p.stride_a, BM);
-  if (st != TCB200_OK) return st;
-  st = make_operand_map(&tb, B, p.K, p.N, p.ldb, p.batch, p.stride_b,
-                        plan.kernel_id == 301283 ? kPairBN / 2 : plan.tile.bn);
-  if (st != TCB200_OK) return st;
+  const int S = plan.tile.split_k > 1 ? plan.tile.split_k : 1;
+  if (S > 1 && !scratch) return TCB200_ERR_INVALID_ARGUMENT;
+  const bool pair = plan.kernel_id == 301283;
+  // where the tensor-core kernel writes: the output, or the partial planes [S][M][N] of a split-K launch
+  float* Ck = S > 1 ? scratch : C;
+  const int64_t ldck = S > 1 ? p.N : p.ldc, stride_ck = S > 1 ? p.M * p.N : p.stride_c;
+  const int64_t batch_k = S > 1 ? S : p.batch;
+
   TcArgs a;
-  a.C = C; a.bias = bias;
-  a.M = (int)p.M; a.N = (int)p.N; a.K = (int)p.K; a.batch = (int)p.batch;
-  a.ldc = p.ldc; a.stride_c = p.stride_c;
-  a.epi = p.epilogue; a.bias_on_m = p.bias_on_m; a.accumulate = p.accumulate;
-  a.a_batched = p.batch > 1 && p.stride_a > 0;
-  a.b_batched = p.batch > 1 && p.stride_b > 0;
-  const bool bias_vec = !bias || p.bias_on_m || ((uintptr_t)bias & 15) == 0;
-  a.c_vec = ((uintptr_t)C & 15) == 0 && p.ldc % 4 == 0 && p.stride_c % 4 == 0 && bias_vec;
+  a.C = Ck; a.bias = S > 1 ? nullptr : bias;
+  a.M = (int)p.M; a.N = (int)p.N; a.K = (int)p.K; a.batch = (int)batch_k;
+  a.ldc = ldck; a.stride_c = stride_ck;
+  a.epi = S > 1 ? TCB200_EPI_NONE : p.epilogue; a.bias_on_m = p.bias_on_m; a.accumulate = S > 1 ? 0 : p.accumulate;
+  a.a_batched = S == 1 && p.batch > 1 && p.stride_a > 0;
+  a.b_batched = S == 1 && p.batch > 1 && p.stride_b > 0;
+  a.ksplit_kb = S > 1 ? (int)ceil_div(ceil_div(p.K, BK), S) : 0;
+  const bool bias_vec = !a.bias || p.bias_on_m || ((uintptr_t)a.bias & 15) == 0;
+  a.c_vec = ((uintptr_t)Ck & 15) == 0 && ldck % 4 == 0 && stride_ck % 4 == 0 && bias_vec;
   a.dev_status = dev_status;
-  a.tma_store = 0;
-  switch (plan.kernel_id) {
-    case 301283: {
-      // output map for the staged epilogue: {N, M, batch}, boxes of 32 columns x 128 rows
-      CUtensorMap tc;
-      a.tma_store = a.c_vec && !p.accumulate;
-      if (a.tma_store && make_operand_map(&tc, C, p.N, p.M, p.ldc, p.batch, p.stride_c, BM) != TCB200_OK)
-        a.tma_store = 0;
-      if (!a.tma_store) tc = tb;  // unused by the kernel then
-      return launch_pair(plan, ta, tb, tc, a, s);
+  a.tma_store = pair && a.c_vec && !a.accumulate;
+
+  TcMaps local;
+  TcMaps* m = &local;
+  TcMapCache* cache = static_cast<TcMapCache*>(map_cache);
+  std::unique_lock<std::mutex> lock;
+  if (cache) {
+    lock = std::unique_lock<std::mutex>(cache->mu);
+    m = nullptr;
+    for (int i = 0; i < kTcMapSlots; ++i)
+      if (cache->slot[i].valid && cache->slot[i].key[0] == A && cache->slot[i].key[1] == B && cache->slot[i].key[2] == Ck)
+        m = &cache->slot[i];
+    if (!m) {
+      m = &cache->slot[cache->next];
+      cache->next = (cache->next + 1) % kTcMapSlots;
+      m->valid = false;
     }
-    case 100643: return launch_ts<64>(plan, ta, tb, a, s);
-    case 101283: return launch_ts<128>(plan, ta, tb, a, s);
-    case 101123: return launch_ts<112>(plan, ta, tb, a, s);
-    case 643: return launch_inst<64, 3>(plan, ta, tb, a, s);
-    case 641: return launch_inst<64, 1>(plan, ta, tb, a, s);
-    case 1283: return launch_inst<128, 3>(plan, ta, tb, a, s);
-    case 1281: return launch_inst<128, 1>(plan, ta, tb, a, s);
-    case 2563: return launch_inst<256, 3>(plan, ta, tb, a, s);
-    case 2561: return launch_inst<256, 1>(plan, ta, tb, a, s);
-    default: return TCB200_ERR_UNSUPPORTED;
   }
+  if (!m->valid) {
+    // split-K: the operands are not batched (the split index selects a k range inside the kernel)
+    int st = make_operand_map(&m->ta, A, p.K, p.M, p.lda, S > 1 ? 1 : p.batch, p.stride_a, BM);
+    if (st != TCB200_OK) return st;
+    st = make_operand_map(&m->tb, B, p.K, p.N, p.ldb, S > 1 ? 1 : p.batch, p.stride_b, pair ? kPairBN / 2 : plan.tile.bn);
+    if (st != TCB200_OK) return st;
+    m->tc = m->tb;  // unused by the kernel unless the staged epilogue is on
+    // output map for the staged epilogue: {N, M, batch}, boxes of 32 columns x 128 rows
+    m->has_tc = a.tma_store && make_operand_map(&m->tc, Ck, p.N, p.M, ldck, batch_k, stride_ck, BM) == TCB200_OK;
+    m->key[0] = A; m->key[1] = B; m->key[2] = Ck;
+    m->valid = true;
+  }
+  a.tma_store = a.tma_store && m->has_tc;
+  const CUtensorMap ta = m->ta, tb = m->tb, tc = m->tc;
+  if (cache) lock.unlock();
+
+  int st;
+  switch (plan.kernel_id) {
+    case 301283: st = launch_pair(plan, ta, tb, tc, a, s); break;
+    case 100643: st = launch_ts<64>(plan, ta, tb, a, s); break;
+    case 101283: st = launch_ts<128>(plan, ta, tb, a, s); break;
+    case 101123: st = launch_ts<112>(plan, ta, tb, a, s); break;
+    case 643: st = launch_inst<64, 3>(plan, ta, tb, a, s); break;
+    case 641: st = launch_inst<64, 1>(plan, ta, tb, a, s); break;
+    case 1283: st = launch_inst<128, 3>(plan, ta, tb, a, s); break;
+    case 1281: st = launch_inst<128, 1>(plan, ta, tb, a, s); break;
+    case 2561: st = launch_inst<256, 1>(plan, ta, tb, a, s); break;
+    default: st = TCB200_ERR_UNSUPPORTED; break;
+  }
+  if (st != TCB200_OK || S == 1) return st;
+
+  // second pass: C = epilogue([C +] sum_s P[s])
+  SplitKArgs r;
+  r.P = scratch; r.C = C; r.bias = bias;
+  r.M = (int)p.M; r.N = (int)p.N; r.S = S;
+  r.ldc = p.ldc;
+  r.epi = p.epilogue; r.bias_on_m = p.bias_on_m; r.accumulate = p.accumulate;
+  const bool vec = p.N % 4 == 0 && p.ldc % 4 == 0 && (((uintptr_t)C | (uintptr_t)scratch) & 15) == 0;
+  const int64_t work = vec ? p.M * p.N / 4 : p.M * p.N;
+  const dim3 grid((unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div(work, 256), (int64_t)plan.sms * 8)), 1, 1);
+  if (vec) TCB200_CUDA_TRY(launch_pdl(splitk_reduce_kernel<true>, grid, dim3(256, 1, 1), (size_t)0, s, r));
+  else TCB200_CUDA_TRY(launch_pdl(splitk_reduce_kernel<false>, grid, dim3(256, 1, 1), (size_t)0, s, r));
+  return TCB200_OK;
 }
 
 }  // namespace tcb200

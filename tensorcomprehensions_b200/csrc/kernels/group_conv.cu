@@ -537,7 +537,11 @@ int group_conv_launch(const Plan& plan, const float* I, const float* W, const fl
   a.OH = (int)conv_oh(p); a.OW = (int)conv_ow(p);
   a.band = plan.tile.bm;
   a.epi = p.epilogue; a.accumulate = p.accumulate;
-  if (plan.kernel_id == 101 || plan.kernel_id == 102) {
+  // The item kernel stages I and W with 16-byte asynchronous copies.  A dense tensor may still start at any
+  // 4-byte offset of a larger buffer (a view): such a launch runs on the band kernel, which uses 4-byte loads.
+  const bool item_misaligned =
+      (plan.kernel_id == 101 || plan.kernel_id == 102) && ((((uintptr_t)I) | ((uintptr_t)W)) & 15) != 0;
+  if ((plan.kernel_id == 101 || plan.kernel_id == 102) && !item_misaligned) {
     const bool k33 = a.KH == 3 && a.KW == 3;
     if (plan.kernel_id == 102) {
       if (k33) TCB200_CUDA_TRY(launch_pdl(group_conv_item_kernel<3, 2>, plan.launch.grid, plan.launch.block, plan.launch.smem, s, a));
@@ -557,10 +561,21 @@ int group_conv_launch(const Plan& plan, const float* I, const float* W, const fl
     TCB200_CUDA_TRY(cudaGetLastError());
     return TCB200_OK;
   }
-  auto fn = plan.kernel_id == 4 ? group_conv_simt_kernel<4> : group_conv_simt_kernel<1>;
+  int ft = plan.kernel_id;
+  dim3 grid = plan.launch.grid, block = plan.launch.block;
+  size_t smem = plan.launch.smem;
+  if (item_misaligned) {  // geometry of the band kernel for this problem, worked out here
+    ft = p.conv[3] % 4 == 0 ? 4 : 1;
+    const int band = pick_band(p, ft, &smem);
+    if (band == 0 || ceil_div((int64_t)a.OH, band) > 65535) return TCB200_ERR_ALIGNMENT;
+    a.band = band;
+    grid = dim3((unsigned)(p.conv[0] * p.conv[1]), (unsigned)ceil_div((int64_t)a.OH, band), 1);
+    block = dim3(256, 1, 1);
+  }
+  auto fn = ft == 4 ? group_conv_simt_kernel<4> : group_conv_simt_kernel<1>;
   static std::atomic<uint64_t> band_configured[2];
-  TCB200_CUDA_TRY(ensure_dynamic_smem(fn, (int)kSmemBudget, plan.device, band_configured[plan.kernel_id == 4]));
-  fn<<<plan.launch.grid, plan.launch.block, plan.launch.smem, s>>>(a);
+  TCB200_CUDA_TRY(ensure_dynamic_smem(fn, (int)kSmemBudget, plan.device, band_configured[ft == 4]));
+  fn<<<grid, block, smem, s>>>(a);
   TCB200_CUDA_TRY(cudaGetLastError());
   return TCB200_OK;
 }

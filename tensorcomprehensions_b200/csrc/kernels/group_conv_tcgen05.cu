@@ -339,7 +339,7 @@ int group_conv_tc_plan(Plan& plan) {
   t.variant = TCB200_VARIANT_TCGEN05_TS;
   t.bm = 128; t.bn = (int)plan.p.conv[3]; t.bk = 8; t.stages = kSlots; t.threads = kThreads; t.split_tf32 = 3;
   const int64_t items = plan.p.conv[0] * plan.p.conv[1];
-  plan.launch.grid = dim3((unsigned)std::min<int64_t>(items, kNumSMs), 1, 1);
+  plan.launch.grid = dim3((unsigned)std::min<int64_t>(items, plan.sms), 1, 1);
   plan.launch.block = dim3(kThreads, 1, 1);
   plan.launch.smem = g.smem;
   plan.kernel_id = 200;

@@ -208,10 +208,10 @@ Units units(const tcb200_problem_t& p, int vec) {
 }
 
 // Segments of the tile kernel: enough CTAs for eight per SM, at least 32 reduced elements per thread row.
-int auto_segments(const Units& u, int cp_log2) {
+int auto_segments(const Units& u, int cp_log2, int sms) {
   const long long CP = 1ll << cp_log2, TY = kThreads / CP;
   const long long tiles = u.A * ceil_div(u.B, CP);
-  const long long want = ceil_div(8 * kNumSMs, tiles);
+  const long long want = ceil_div(8 * sms, tiles);
   const long long most = std::max<long long>(1, u.C / (32 * TY));
   return (int)std::max<long long>(1, std::min<long long>({want, most, (long long)kReduceMaxSegments}));
 }
@@ -262,7 +262,7 @@ int reduce_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n)
   const int vec = vec_ok(p) ? 4 : 1;
   const int cp = 1 << pow2_ceil_log2(units(p, vec).B, 5);
   // short rows, many of them: a warp per row first; else the tile kernel
-  const bool warp_first = warp_rows_ok(p) && p.red[1] <= 4096 && p.red[0] >= 2 * kNumSMs;
+  const bool warp_first = warp_rows_ok(p) && p.red[1] <= 4096 && p.red[0] >= 2 * sm_count(-1);
   if (warp_first) add(1, 1, 1, 0);
   add(cp, 0, 0, vec);
   if (warp_rows_ok(p) && !warp_first) add(1, 1, 1, 0);
@@ -293,7 +293,7 @@ int reduce_plan(Plan& plan) {
   if (t.bk == 1) {
     if (!warp_rows_ok(p)) return TCB200_ERR_UNSUPPORTED;
     t.bm = 1; t.bn = 1; t.stages = 0;
-    plan.launch.grid = dim3((unsigned)std::min<long long>(ceil_div(p.red[0], kThreads / 32), 8 * kNumSMs), 1, 1);
+    plan.launch.grid = dim3((unsigned)std::min<long long>(ceil_div(p.red[0], kThreads / 32), 8 * plan.sms), 1, 1);
     plan.launch.block = dim3(kThreads, 1, 1);
     plan.kernel_id = 2;
     return TCB200_OK;
@@ -311,7 +311,7 @@ int reduce_plan(Plan& plan) {
   t.bm = 1 << cp_log2;
   const long long tiles = u.A * ceil_div(u.B, t.bm);
   if (tiles > 0x7fffffffll) return TCB200_ERR_TOO_LARGE;
-  int S = t.bn > 0 ? t.bn : auto_segments(u, cp_log2);
+  int S = t.bn > 0 ? t.bn : auto_segments(u, cp_log2, plan.sms);
   if (S > kReduceMaxSegments) return TCB200_ERR_INVALID_ARGUMENT;
   const long long unroll = t.stages == 4 ? 4 : 8, TY = kThreads >> cp_log2;
   S = (int)std::min<long long>(S, ceil_div(u.C, unroll * TY));  // no segment without a block

@@ -304,7 +304,7 @@ int tensordot_plan(Plan& plan) {
     bulk_geometry(p, t.bm, t.stages, &R, &RY, &st, &sb);
     t.bm = R; t.stages = st; t.threads = kBulkThreads; t.bn = RY;
     const int64_t items = N * ceil_div(C1, R);
-    plan.launch.grid = dim3((unsigned)std::min<int64_t>(items, kNumSMs), 1, 1);
+    plan.launch.grid = dim3((unsigned)std::min<int64_t>(items, plan.sms), 1, 1);
     plan.launch.block = dim3(kBulkThreads, 1, 1);
     plan.launch.smem = (size_t)st * sb + 16 * st + 16;
     plan.kernel_id = 2;
@@ -327,7 +327,7 @@ int tensordot_plan(Plan& plan) {
     const int64_t total = N * C1 * P;
     plan.launch.block = dim3(t.threads, 1, 1);
     plan.launch.grid =
-        dim3((unsigned)std::min<int64_t>(ceil_div(total, t.threads), (int64_t)kNumSMs * 32), 1, 1);
+        dim3((unsigned)std::min<int64_t>(ceil_div(total, t.threads), (int64_t)plan.sms * 32), 1, 1);
     plan.kernel_id = 0;
   }
   plan.launch.smem = 0;
@@ -362,7 +362,7 @@ int tensordot_launch(const Plan& plan, const float* I0, const float* I1, float* 
     // Unaligned base pointers (a view into a larger buffer) take the scalar kernel.
     const int64_t total = p.td[0] * p.td[1] * p.td[4];
     dim3 block(256, 1, 1);
-    dim3 grid((unsigned)std::min<int64_t>(ceil_div(total, 256), (int64_t)kNumSMs * 32), 1, 1);
+    dim3 grid((unsigned)std::min<int64_t>(ceil_div(total, 256), (int64_t)plan.sms * 32), 1, 1);
     tensordot_generic_kernel<<<grid, block, 0, s>>>(I0, I1, O, p.td[0], (int)p.td[1],
                                                     (int)p.td[2], (int)p.td[3], (int)p.td[4]);
   }

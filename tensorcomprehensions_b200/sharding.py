@@ -39,21 +39,76 @@ def shard_shapes(shapes, shard_dims, world, rank):
     return out
 
 
+def _assemble(gathered, out, world, rows, total, inner):
+    """[world][rows][max_count * inner] -> [rows][total * inner]: trims the padding of uneven shards and, for a
+    shard dimension that is not the outermost one, interleaves the ranks' rows.  CUDA tensors go through the
+    kernel library (tcb200_assemble_shards) on the current stream; CPU tensors (the gloo runs that test this
+    module's host logic) are sliced with torch."""
+    if gathered.is_cuda:
+        import ctypes
+        from . import cabi
+        cabi.check(cabi.lib().tcb200_assemble_shards(
+            ctypes.c_void_p(gathered.data_ptr()), ctypes.c_void_p(out.data_ptr()), world, rows, total, inner,
+            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "tcb200_assemble_shards")
+        return out
+    g = gathered.view(world, rows, -1)
+    o = out.view(rows, total * inner)
+    for k in range(world):
+        start, count = shard_bounds(total, world, k)
+        o[:, start * inner:(start + count) * inner] = g[k, :, :count * inner]
+    return out
+
+
+class Gatherer:
+    """All-gather of one sharded output, with its buffers allocated once.
+
+    shard_shape: this rank's shard; dim: the sharded dimension; total: its unsharded extent.  gather(shard)
+    returns the full tensor on every rank: the shard is padded to the largest shard (only when the extent
+    does not divide), one all_gather_into_tensor of equal pieces (NCCL over NVLink on GPUs), then the pieces
+    are assembled into the row-major full tensor.  An evenly divided dimension-0 shard is gathered straight
+    into the result."""
+
+    def __init__(self, shard_shape, dim, total, device, dtype=torch.float32, group=None):
+        import torch.distributed as dist
+        self.group, self.dim, self.total = group, dim, total
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        shape = list(shard_shape)
+        self.count = shape[dim]
+        assert self.count == shard_bounds(total, self.world, self.rank)[1], "shard does not match the split"
+        self.max_count = max(shard_bounds(total, self.world, r)[1] for r in range(self.world))
+        self.rows = 1
+        for s in shape[:dim]:
+            self.rows *= s
+        self.inner = 1
+        for s in shape[dim + 1:]:
+            self.inner *= s
+        full_shape = shape[:dim] + [total] + shape[dim + 1:]
+        self.out = torch.empty(full_shape, dtype=dtype, device=device)
+        self.direct = self.rows == 1 and self.max_count * self.world == total
+        if not self.direct:
+            self.recv = torch.empty((self.world, self.rows, self.max_count * self.inner), dtype=dtype, device=device)
+            self.send = None
+            if self.count < self.max_count:
+                self.send = torch.zeros((self.rows, self.max_count * self.inner), dtype=dtype, device=device)
+
+    def gather(self, shard):
+        import torch.distributed as dist
+        shard = shard.contiguous()
+        if self.direct:
+            dist.all_gather_into_tensor(self.out.view(-1), shard.view(-1), group=self.group)
+            return self.out
+        piece = shard.view(self.rows, self.count * self.inner)
+        if self.send is not None:
+            self.send[:, :self.count * self.inner].copy_(piece)
+            piece = self.send
+        dist.all_gather_into_tensor(self.recv.view(-1), piece.reshape(-1), group=self.group)
+        return _assemble(self.recv, self.out, self.world, self.rows, self.total, self.inner)
+
+
 def all_gather_shards(shard, dim, total, group=None):
-    """All-gather of unevenly sized shards: every rank pads its shard to the largest count along
-    `dim`, one all_gather of equal buffers, then the padding is trimmed while concatenating."""
-    import torch.distributed as dist
-    world = dist.get_world_size(group)
-    max_count = max(shard_bounds(total, world, r)[1] for r in range(world))
-    moved = shard.movedim(dim, 0).contiguous()
-    if moved.shape[0] < max_count:
-        pad = torch.zeros((max_count - moved.shape[0],) + tuple(moved.shape[1:]), dtype=moved.dtype,
-                          device=moved.device)
-        moved = torch.cat([moved, pad], 0)
-    gathered = [torch.empty_like(moved) for _ in range(world)]
-    dist.all_gather(gathered, moved, group=group)
-    parts = [g[:shard_bounds(total, world, r)[1]] for r, g in enumerate(gathered)]
-    return torch.cat(parts, 0).movedim(0, dim).contiguous()
+    """One-off form of Gatherer: all-gather of (possibly unevenly sized) shards along `dim`."""
+    return Gatherer(tuple(shard.shape), dim, total, shard.device, shard.dtype, group).gather(shard)
 
 
 class ShardedProgram:
@@ -83,6 +138,9 @@ class ShardedProgram:
         return list(outs) if isinstance(outs, (tuple, list)) else [outs]
 
     def gather(self, shard_outputs, full_extents, group=None):
-        """full_extents[i]: size of output i along its shard dimension before sharding."""
-        return [all_gather_shards(o, d, n, group) for o, d, n in
-                zip(shard_outputs, self.w.shard_outputs, full_extents)]
+        """full_extents[i]: size of output i along its shard dimension before sharding.  The buffers of the
+        exchange are allocated at the first call and reused."""
+        if getattr(self, "_gatherers", None) is None:
+            self._gatherers = [Gatherer(tuple(o.shape), d, n, o.device, o.dtype, group)
+                               for o, d, n in zip(shard_outputs, self.w.shard_outputs, full_extents)]
+        return [g.gather(o) for g, o in zip(self._gatherers, shard_outputs)]

@@ -140,6 +140,22 @@ def colsum(M=16384, N=4096):
 
 
 EXTRA = {"sum1d": sum1d, "sum2d": sum2d, "colsum": colsum}
+
+# The size argument of each factory that is split across GPUs (the output index that also indexes the large
+# operand): a rank's shard of a comprehension is the same comprehension at a smaller extent.
+SHARD_ARG = {"tensordot": "N", "batchmatmul": "B", "tmm": "N", "group_conv": "N", "mlp3": "B"}
+
+
+def shard_of(name, world, rank):
+    """The Workload a rank of a `world`-GPU run compiles: extent / world of the sharded index, the remainder
+    on the first ranks (500 matrices over 8 GPUs -> 63, 63, 63, 63, 62, 62, 62, 62)."""
+    full = ALL[name]()
+    if world == 1:
+        return full
+    dim = next(d for d in full.shard_inputs if d is not None)
+    big = next(s for s, d in zip(full.shapes, full.shard_inputs) if d is not None)
+    base, rem = divmod(big[dim], world)
+    return ALL[name](**{SHARD_ARG[name]: base + (1 if rank < rem else 0)})
 BY_NAME = dict(ALL, **EXTRA)
 
 # Small instances of the same comprehensions for quick parity checks (odd sizes on purpose).
@@ -169,3 +185,20 @@ def make_inputs(w, seed=None, device="cpu"):
             t = t * scale
         out.append(t.to(device) if device != "cpu" else t)
     return out
+
+
+def make_shard_inputs(name, world, rank):
+    """Seeded inputs of one rank's shard.  Every tensor is drawn from its own generator: a replicated operand
+    (weights, the A of the transposed matmul) gets the same bits on every rank, a sharded operand a
+    rank-specific draw of its shard shape.  Returns (shard workload, tensors)."""
+    import torch
+    w = shard_of(name, world, rank)
+    out = []
+    for k, (shape, d, sd) in enumerate(zip(w.shapes, w.dist, w.shard_inputs)):
+        g = torch.Generator().manual_seed(20240 + 100 * w.index + k + (1000 * rank if sd is not None else 0))
+        scale = 1.0
+        if isinstance(d, tuple):
+            d, scale = d
+        t = torch.rand(shape, generator=g) if d == "uniform" else torch.randn(shape, generator=g)
+        out.append(t * scale if scale != 1.0 else t)
+    return w, out

@@ -23,7 +23,7 @@ def test_exports_every_declared_symbol():
     for n in names:
         assert hasattr(L, n), "libtcb200.so does not export " + n
     assert set(cabi.SYMBOLS) <= set(names)
-    assert L.tcb200_abi_version() == 2
+    assert L.tcb200_abi_version() == 3
 
 
 def test_strerror_and_argument_checks():

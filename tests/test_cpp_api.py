@@ -77,3 +77,13 @@ def test_cpp_library_cases_on_gpu(library_binary, cuda):
     r = _run(library_binary)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "library cases ok: 22 (gpu=1)" in r.stdout
+
+
+@pytest.mark.gpu
+def test_one_executor_on_several_devices(cuda):
+    """Compiled once, run from one host thread per device (needs two GPUs)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    r = _run(_build("multi_device"))
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "multi device ok" in r.stdout

@@ -212,6 +212,28 @@ def test_group_conv_accumulate(cuda, bias):
         assert_close(out, ref, C * KH * KW, what=plan.describe())
 
 
+def test_group_conv_views_at_a_4_byte_offset(cuda):
+    """Dense input / filter tensors that start 4 bytes into a larger buffer: the default (item) kernel
+    stages with 16-byte copies, so such a launch must run on a kernel that does not need the alignment."""
+    dims = (2, 3, 16, 16, 16, 16, 3, 3)
+    N, G, C, F, H, W, KH, KW = dims
+    I, W1, B = _rand((N, G, C, H, W), 45, "uniform"), _rand((G, F, C, KH, KW), 46, "uniform"), _rand((G, F), 47)
+    ref = orc.loop_group_conv(I, W1, B)
+
+    def offset_view(t):
+        buf = torch.empty(t.numel() + 1, device=cuda)
+        v = buf[1:].view(t.shape)
+        v.copy_(t)
+        assert v.data_ptr() % 16 == 4
+        return v
+
+    p = cabi.group_conv_problem(*dims)
+    for views in ((True, False), (False, True), (True, True)):
+        ins = [offset_view(I) if views[0] else I.to(cuda), offset_view(W1) if views[1] else W1.to(cuda), B.to(cuda)]
+        out, plan = run_plan(p, ins, ref.shape)
+        assert_close(out, ref, C * KH * KW, [I, W1], STRICT["group_conv"], plan.describe())
+
+
 def test_group_conv_full_size(cuda):
     w = wl.group_conv()
     I, W1, B = wl.make_inputs(w)

@@ -158,14 +158,15 @@ def test_compile_time_input_checks():
 def test_mapping_options_roundtrip_and_tile_encoding():
     naive = tc.MappingOptions("naive")
     assert naive.to_tile() is None and "tiling" in str(naive)
-    o = tc.MappingOptions.from_tile(3, 128, 256, 32, 2, 192, 3)
-    assert o.to_tile() == (3, 128, 256, 32, 2, 192, 3)
+    o = tc.MappingOptions.from_tile(3, 128, 128, 32, 2, 192, 3)
+    assert o.to_tile() == (3, 128, 128, 32, 2, 192, 3, 0)
+    assert tc.MappingOptions.from_tile(5, 256, 128, 32, 8, 608, 3, 4).to_tile() == (5, 256, 128, 32, 8, 608, 3, 4)
     assert tc.MappingOptions(o.serialize()) == o and tc.MappingOptions(naive.serialize()) == naive
     assert naive != o
     # a tuned tile is honoured where a launch accepts it and ignored elsewhere
     w = wl.tmm()
     exe = tc.compile(w.tc, w.entry, o, *[torch.empty(s) for s in w.shapes])
-    assert exe.tiles() == [(3, 128, 256, 32, 2, 448, 3)]
+    assert exe.tiles()[0][:4] == (3, 128, 128, 32) and exe.tiles()[0][5:] == (448, 3, 1)
     w = wl.tensordot()
     exe = tc.compile(w.tc, w.entry, o, *[torch.empty(s) for s in w.shapes])
     assert exe.tiles()[0][0] == 1  # tensordot has no tcgen05 variant: family default

@@ -94,7 +94,7 @@ def test_tile_encoding_survives_the_proto(msgs):
     p = msgs["CudaMappingOptionsProto"]()
     p.ParseFromString(o.serialize())
     assert (p.private_depth, p.shared_depth) == (5, 3) and list(p.generic_mapping_options.tiling.sizes) == [256, 128, 32]
-    assert tc.MappingOptions(p.SerializeToString()).to_tile() == (5, 256, 128, 32, 8, 608, 3)
+    assert tc.MappingOptions(p.SerializeToString()).to_tile() == (5, 256, 128, 32, 8, 608, 3, 0)
 
 
 def test_cache_file_is_a_cuda_options_cache_proto(tmp_path, msgs):

@@ -57,6 +57,25 @@ def test_reduce_explicit_segments_and_reuse_of_the_scratch(cuda):
         assert_close(out, orc.loop_reduce(I.cpu(), double=True), C, [I.cpu()], PREC, plan.describe())
 
 
+def test_first_launch_of_a_split_plan_on_a_fresh_stream(cuda):
+    """The ticket counters of a plan's scratch are zeroed on the launch stream: a first launch on a
+    non-blocking stream (every torch.cuda.Stream) must see them zero."""
+    A, C, B = 2, 300000, 3
+    I = _rand((A, C, B), 91).to(cuda)
+    ref = orc.loop_reduce(I.cpu(), double=True)
+    for _ in range(3):
+        plan = cabi.Plan(cabi.reduction_problem(A, C, B))
+        assert plan.geometry()[0][1] > 1, "the case must split the reduced range"
+        stream = torch.cuda.Stream()
+        out = torch.full((A, B), float("nan"), device=cuda)
+        torch.cuda.synchronize()
+        with torch.cuda.stream(stream):
+            plan.launch([I], [out])
+            plan.launch([I], [out])
+        stream.synchronize()
+        assert_close(out, ref, C, [I.cpu()], PREC, plan.describe())
+
+
 def test_reduce_accumulates_into_the_output(cuda):
     for dims in ((5, 300, 1), (1, 200000, 1), (2, 9000, 40)):
         I = _rand(dims, 90)

@@ -33,6 +33,11 @@ def ref64(A, B):
 @pytest.mark.parametrize("shape", [(1, 128, 256, 128), (1, 256, 384, 512), (1, 70, 200, 132), (3, 130, 96, 256)])
 def test_tcgen05_tiles(cuda, bn, split, shape):
     b, M, N, K = shape
+    if bn == 256 and split == 3:
+        # one accumulation over the whole K: offered as a one-pass TF32 tile only
+        with pytest.raises(cabi.Tcb200Error):
+            cabi.Plan(cabi.contraction_problem(b, M, N, K, True, True), tc_tile(bn, split))
+        return
     A, B = _rand((b, M, K), 21), _rand((b, N, K), 22)
     ref = ref64(A, B)
     p = cabi.contraction_problem(b, M, N, K, True, True)
@@ -192,3 +197,82 @@ def test_mlp3_full_size_tcgen05(cuda):
         out, plan = run_plan(p, [x, Wt, Bt], (x.shape[0], Wt.shape[0]), tc_tile(128, 3))
         assert_close(out, ref, L, ins, STRICT["mlp3"], plan.describe(), strict_is_gate=False)
         x = out
+
+
+def split_tile(bn, split_k, pair=False):
+    t = tc_tile(bn, 3, ts=not pair, pair=pair)
+    t.split_k = split_k
+    return t
+
+
+@pytest.mark.parametrize("case", [
+    # (M, N, K, tile width, pair, split_k)
+    (128, 2048, 4096, 128, False, 9),    # a 1/8 shard of the transposed matmul: 16 tiles x 9 splits, ragged last split
+    (128, 2048, 4096, 112, False, 7),    # 19 tiles x 7 splits
+    (2048, 512, 1024, 128, True, 2),     # MLP layer 2 on a 2048-row shard, CTA pairs
+    (2048, 256, 512, 128, True, 4),      # MLP layer 3 on a 2048-row shard
+    (300, 200, 1000, 64, False, 5),      # ragged everything, K not a multiple of the k-block
+    (130, 130, 132, 128, False, 5),      # more splits than k-blocks that hold data: the last splits add zeros
+])
+@pytest.mark.parametrize("epi", [cabi.EPI_NONE, cabi.EPI_BIAS_RELU])
+def test_split_k_tiles(cuda, case, epi):
+    """The reduction split over several CTAs per output tile: partial sums in the plan's scratch, added in a
+    fixed order by the second-pass kernel together with bias / ReLU.  Same criterion as the unsplit tiles, the
+    same bits on every run, and the scratch is reused by later launches of the plan."""
+    M, N, K, bn, pair, S = case
+    A, B, bias = _rand((M, K), 61), _rand((N, K), 62), _rand((N,), 63)
+    has_bias = epi == cabi.EPI_BIAS_RELU
+    ref = orc.loop_fcrelu(A, B, bias if has_bias else None, relu=has_bias, double=True) if M * N * K < 2 ** 28 else None
+    if ref is None:
+        r = A.double() @ B.double().t()
+        ref = (torch.clamp_min(r + bias.double(), 0) if has_bias else r).float()
+    p = cabi.contraction_problem(1, M, N, K, True, True, epilogue=epi)
+    ins = [A.to(cuda), B.to(cuda)] + ([bias.to(cuda)] if has_bias else [])
+    out, plan = run_plan(p, ins, (M, N), split_tile(bn, S, pair))
+    assert plan.tile().split_k == S
+    assert_close(out, ref, K, [A, B], 3e-7, plan.describe())
+    outs = []
+    for _ in range(2):  # one plan, launched again: same scratch, same bits
+        o = torch.full((M, N), float("nan"), device=cuda)
+        plan.launch(ins, [o])
+        torch.cuda.synchronize()
+        outs.append(o)
+    assert torch.equal(outs[0], out) and torch.equal(outs[1], out)
+
+
+def test_split_k_accumulates_and_takes_odd_outputs(cuda):
+    """`+=` through the second pass, and an output view at a 4-byte offset (scalar second pass)."""
+    M, N, K, S = 128, 384, 2048, 4
+    A, B = _rand((M, K), 64), _rand((N, K), 65)
+    init = _rand((M, N), 66)
+    ref = (A.double() @ B.double().t() + init.double()).float()
+    p = cabi.contraction_problem(1, M, N, K, True, True, accumulate=True)
+    out, plan = run_plan(p, [A.to(cuda), B.to(cuda)], (M, N), split_tile(128, S), out_init=init.to(cuda))
+    assert_close(out, ref, K, what=plan.describe())
+    p = cabi.contraction_problem(1, M, N, K, True, True)
+    buf = torch.full((M * N + 1,), float("nan"), device=cuda)
+    view = buf[1:].view(M, N)
+    plan = cabi.Plan(p, split_tile(128, S))
+    plan.launch([A.to(cuda), B.to(cuda)], [view])
+    torch.cuda.synchronize()
+    assert_close(view, (A.double() @ B.double().t()).float(), K, [A, B], 3e-7, plan.describe())
+
+
+def test_shard_shapes_get_a_split_by_default(cuda):
+    """What the family default is on the 1/8 shards of the benchmark contractions: the transposed matmul's
+    2048-column shard and the last two MLP layers on 2048 rows split their reductions, the full-size
+    problems do not."""
+    full = cabi.Plan(cabi.contraction_problem(1, 128, 16384, 4096, True, True))
+    assert full.tile().split_k <= 1
+    shard = cabi.Plan(cabi.contraction_problem(1, 128, 2048, 4096, True, True))
+    assert shard.tile().split_k > 1, shard.describe()
+    g = shard.geometry()[0][0]
+    assert 120 <= g <= 148, shard.describe()
+    l3 = cabi.Plan(cabi.contraction_problem(1, 2048, 256, 512, True, True, epilogue=cabi.EPI_BIAS_RELU))
+    assert l3.tile().split_k > 1, l3.describe()
+    A, B, bias = _rand((2048, 512), 67), _rand((256, 512), 68), _rand((256,), 69)
+    out = torch.full((2048, 256), float("nan"), device=cuda)
+    l3.launch([A.to(cuda), B.to(cuda), bias.to(cuda)], [out])
+    torch.cuda.synchronize()
+    ref = torch.clamp_min(A.double() @ B.double().t() + bias.double(), 0).float()
+    assert_close(out, ref, 512, [A, B], 3e-7, l3.describe())
