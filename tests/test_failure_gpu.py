@@ -39,7 +39,8 @@ def test_a_wait_that_runs_out_is_reported_and_the_context_survives(cuda):
         I1 = torch.rand((2, 8, 2, 4, 8), generator=torch.Generator().manual_seed(4))
         out = torch.full((2, 16, 2, 4, 8), float("nan"), device=cuda)
         plan = cabi.Plan(cabi.tensordot_problem(2, 16, 8, 2, 32))
-        plan.launch_ptrs([I0.to(cuda).data_ptr(), I1.to(cuda).data_ptr()], [out.data_ptr()], stream, status.value)
+        d0, d1 = I0.to(cuda), I1.to(cuda)
+        plan.launch_ptrs([d0.data_ptr(), d1.data_ptr()], [out.data_ptr()], stream, status.value)
         assert L.tcb200_status_check(status, stream, ctypes.byref(code)) == cabi.OK and code.value == 0
         assert_close(out, orc.loop_tensordot(I0, I1), 8, [I0, I1], STRICT["tensordot"])
     finally:

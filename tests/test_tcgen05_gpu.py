@@ -173,7 +173,7 @@ def test_tcgen05_rejects_what_it_cannot_take(cuda):
         cabi.Plan(p, tc_tile(128, 3))
 
 
-@pytest.mark.parametrize("bn,split,ts", [(128, 3, True), (112, 3, True), (128, 3, False), (256, 3, False), (128, 1, False)])
+@pytest.mark.parametrize("bn,split,ts", [(128, 3, True), (112, 3, True), (128, 3, False), (256, 1, False), (128, 1, False)])
 def test_tmm_full_size_tcgen05(cuda, bn, split, ts):
     w = wl.tmm()
     A, B = wl.make_inputs(w)
