@@ -263,10 +263,22 @@ def run_product(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        # NCCL_DEBUG=VERSION makes NCCL print its version banner on stdout, ahead of the JSON line
+        # NCCL prints its version banner on stdout when the communicator comes up (NCCL_DEBUG=VERSION, which
+        # some launchers export): stdout carries the one JSON line only, so file descriptor 1 points at
+        # stderr until the first collective has run
         if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
             os.environ["NCCL_DEBUG"] = "WARN"
-        dist.init_process_group("nccl", device_id=dev)
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=dev)
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
     peaks = load_peaks()
 
     names = suite_names(args)

@@ -33,8 +33,10 @@ enum {
   TCB200_FAMILY_CONTRACTION = 1, /* C(b,m,n) (+)= sum_k A(b,m,k) * B(b,n,k)  [+bias] [relu] */
   TCB200_FAMILY_TENSORDOT = 2,   /* O(n,c1,c3,p) = sum_c2 I0(n,c1,c2,p) * I1(n,c2,c3,p), tiny C2,C3 */
   TCB200_FAMILY_GROUP_CONV = 3,  /* O(n,g,f,h,w) = sum_{c,kh,kw} I(n,g,c,h+kh,w+kw) * W(g,f,c,kh,kw) [+B(g,f)] */
-  TCB200_FAMILY_REDUCTION = 4    /* O(a,b) (+)= sum_c I(a,c,b): one input, sum over a contiguous group of its indices
+  TCB200_FAMILY_REDUCTION = 4,   /* O(a,b) (+)= sum_c I(a,c,b): one input, sum over a contiguous group of its indices
                                     (sum1D / sum2D of test/test_tc_mapper_harness-inl.h:60-146) */
+  TCB200_FAMILY_COPY = 5         /* O(i...) = I(i...): a whole-tensor copy (red[0] = number of elements), what a
+                                    statement such as d_Bias(m) = Bias(m) is (python/tests/test_tc.py:403-407) */
 };
 
 /* Elementwise statements fused after the reduction (how the reference's TCs
@@ -88,7 +90,10 @@ typedef struct tcb200_problem {
                                            0 reads as 1.  Output extent: (H - KH) / SH + 1 by (W - KW) / SW + 1 */
   int64_t red[3];                       /* reduction: A, C, B of the [A][C][B] view of the input (C is reduced) */
   int32_t reduce_op;                    /* reduction: TCB200_REDUCE_SUM (+=), _MAX (max=), _MIN (min=), _PROD (*=) */
-  int32_t reserved;
+  int32_t batch_reduce;                 /* contraction: 1 = the batch index is reduced too,
+                                           C(m,n) (+)= sum_b sum_k A(b,m,k) * B(b,n,k)  (stride_c is ignored).  Runs as a
+                                           batched contraction into one plane of partial sums per batch entry (scratch
+                                           memory owned by the plan) and a second pass that adds the planes in order. */
 } tcb200_problem_t;
 
 /* One point of a family's tile sweep.  Fields a variant does not use are 0. */
@@ -134,7 +139,7 @@ int tcb200_plan_tile(const tcb200_plan_t* plan, tcb200_tile_t* tile);
 /* Enqueues the plan on `stream` of the CURRENT device (which must be the plan's
  * device) and returns without synchronising.  Replaces CudaRTCFunction::Launch
  * (tc/core/cuda/cuda_rtc.cc:299-387).
- *   inputs : contraction {A, B[, bias]}; tensordot {I0, I1}; group conv {I, W[, bias]}; reduction {I}
+ *   inputs : contraction {A, B[, bias]}; tensordot {I0, I1}; group conv {I, W[, bias]}; reduction {I}; copy {I}
  *   outputs: {O}
  *   dev_status: optional device int; a kernel whose bounded wait gives up stores a
  *               nonzero code there instead of spinning (NULL: not reported).

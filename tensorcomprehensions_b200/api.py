@@ -325,8 +325,10 @@ def make_autograd(forward_fun: Callable, backward_fun: Callable) -> Autograd:
     """A callable with torch.autograd support from a forward and a backward function, both usually entry
     points of a tc.define()d object (tensor_comprehensions/__init__.py:513-601): the backward function
     receives the forward inputs followed by the gradients of the outputs and returns one gradient per
-    input.  The backward comprehensions must themselves match a kernel family (the matmul gradients are
-    contractions; gradients written with `where` windows are not matched and raise at first use)."""
+    input.  The backward comprehensions must themselves match a kernel family: the matmul gradients are
+    contractions, and so are the convolution gradients of the reference's example for the 1 x 1 filters it uses
+    (index differences over 1-wide ranges); convolution gradients of wider filters, which need `where` windows,
+    are not matched and raise at first use."""
     return Autograd(forward_fun, backward_fun)
 
 

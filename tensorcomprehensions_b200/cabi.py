@@ -11,7 +11,7 @@ import os
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libtcb200.so")
 
-FAMILY_CONTRACTION, FAMILY_TENSORDOT, FAMILY_GROUP_CONV, FAMILY_REDUCTION = 1, 2, 3, 4
+FAMILY_CONTRACTION, FAMILY_TENSORDOT, FAMILY_GROUP_CONV, FAMILY_REDUCTION, FAMILY_COPY = 1, 2, 3, 4, 5
 EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_RELU = 0, 1, 2, 3
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_SIMT_SMALL, VARIANT_TCGEN05, VARIANT_TCGEN05_TS, VARIANT_TCGEN05_PAIR = 0, 1, 2, 3, 4, 5
 OK = 0
@@ -36,7 +36,7 @@ class Problem(ctypes.Structure):
         ("lda", ctypes.c_int64), ("ldb", ctypes.c_int64), ("ldc", ctypes.c_int64),
         ("stride_a", ctypes.c_int64), ("stride_b", ctypes.c_int64), ("stride_c", ctypes.c_int64),
         ("conv", ctypes.c_int64 * 8), ("td", ctypes.c_int64 * 5), ("conv_stride", ctypes.c_int64 * 2), ("red", ctypes.c_int64 * 3),
-        ("reduce_op", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("reduce_op", ctypes.c_int32), ("batch_reduce", ctypes.c_int32),
     ]
 
 
@@ -118,7 +118,7 @@ def tensordot_problem(N, C1, C2, C3, P):
 
 def contraction_problem(batch, M, N, K, a_k_major=True, b_k_major=True, epilogue=EPI_NONE,
                         accumulate=False, lda=None, ldb=None, ldc=None, stride_a=None,
-                        stride_b=None, stride_c=None, bias_on_m=False):
+                        stride_b=None, stride_c=None, bias_on_m=False, batch_reduce=False):
     p = Problem()
     p.family = FAMILY_CONTRACTION
     p.epilogue, p.accumulate = epilogue, int(accumulate)
@@ -130,6 +130,7 @@ def contraction_problem(batch, M, N, K, a_k_major=True, b_k_major=True, epilogue
     p.stride_a = stride_a if stride_a is not None else M * K
     p.stride_b = stride_b if stride_b is not None else N * K
     p.stride_c = stride_c if stride_c is not None else M * N
+    p.batch_reduce = int(batch_reduce)
     return p
 
 

@@ -19,6 +19,7 @@ std::string MatchedLaunch::family() const {
     case TCB200_FAMILY_TENSORDOT: return "tensordot";
     case TCB200_FAMILY_GROUP_CONV: return "group_conv";
     case TCB200_FAMILY_REDUCTION: return "reduction";
+    case TCB200_FAMILY_COPY: return "copy";
     default: return "?";
   }
 }
@@ -48,25 +49,51 @@ int valueIndex(const DefAnalysis& def, const std::string& tensor) {
   return -1;
 }
 
-const TreeRef& stripParens(const TreeRef& t) { return t; }
-
 bool isFloat32(const TensorSymbol* t) {
   return t && (t->scalarKind == lang::TK_FLOAT || t->scalarKind == lang::TK_FLOAT32);
 }
 
 // Every index of the access is a plain variable, no variable twice.
-bool plainOperand(const DefAnalysis& def, const TensorAccess& a, Operand* op) {
+// With `ranges` (the lenient form): index variables whose range is the single value 0 count as the constant 0,
+// so `h - r_kh` with a 1-wide r_kh is the plain index h (how the reference's convolution gradients are written,
+// tensor_comprehensions/__init__.py:563-574, for the 1 x 1 filters its example uses); a dimension of extent 1
+// that is indexed by such variables only is dropped from the operand (it does not change any stride).
+bool plainOperand(const DefAnalysis& def, const TensorAccess& a, Operand* op,
+                  const std::map<std::string, IndexRange>* ranges = nullptr) {
   const TensorSymbol* sym = def.find(a.tensor);
   if (!sym || sym->shape.size() != a.indices.size()) return false;
   op->tensor = a.tensor;
-  op->shape = sym->shape;
-  op->strides = makeStridesFromSizes(sym->shape);
   op->value = valueIndex(def, a.tensor);
+  const std::vector<int64_t> strides = makeStridesFromSizes(sym->shape);
+  auto unit = [&](const std::string& v) {
+    auto it = ranges->find(v);
+    return it != ranges->end() && it->second.min == 0 && it->second.max == 0;
+  };
   std::set<std::string> seen;
-  for (const auto& idx : a.indices) {
+  for (size_t d = 0; d < a.indices.size(); ++d) {
+    const AffineIndex& idx = a.indices[d];
     std::string v;
-    if (!idx.isSingleVar(&v) || !seen.insert(v).second) return false;
+    if (!ranges) {
+      if (!idx.isSingleVar(&v) || !seen.insert(v).second) return false;
+    } else {
+      if (!idx.affine || idx.constant != 0) return false;
+      int live = 0;
+      for (const auto& kv : idx.coeff) {
+        if (unit(kv.first)) continue;
+        if (kv.second != 1) return false;
+        v = kv.first;
+        ++live;
+      }
+      if (live > 1) return false;
+      if (live == 0) {  // the constant 0: only a dimension of extent 1 can be dropped
+        if (sym->shape[d] != 1) return false;
+        continue;
+      }
+      if (!seen.insert(v).second) return false;
+    }
     op->vars.push_back(v);
+    op->shape.push_back(sym->shape[d]);
+    op->strides.push_back(strides[d]);
   }
   return true;
 }
@@ -111,23 +138,41 @@ bool sameOrder(const std::vector<std::string>& a, const std::vector<std::string>
 // ----------------------------------------------------------------------------------------------
 bool matchProduct(const DefAnalysis& def, const StatementAnalysis& st, MatchedLaunch* out,
                   std::string* why) {
-  const TreeRef rhs = stripParens(lang::Comprehension(st.tree).rhs());
+  const TreeRef rhs = lang::Comprehension(st.tree).rhs();
   if (rhs->kind() != '*' || rhs->trees().size() != 2 || rhs->tree(0)->kind() != lang::TK_ACCESS ||
       rhs->tree(1)->kind() != lang::TK_ACCESS || st.reads.size() != 2) {
     *why = "the right-hand side is not a product of two tensor accesses";
     return false;
   }
   Operand A, B, O;
-  if (!plainOperand(def, st.reads[0], &A) || !plainOperand(def, st.reads[1], &B)) {
-    *why = "an operand index is not a plain index variable";
-    return false;
-  }
   const TensorSymbol* osym = def.find(st.lhs);
   O.tensor = st.lhs;
-  O.vars = st.lhsIndices;
-  O.shape = osym->shape;
-  O.strides = makeStridesFromSizes(O.shape);
   O.value = valueIndex(def, st.lhs);
+  std::vector<std::string> reductionVars = st.reductionVars;
+  if (plainOperand(def, st.reads[0], &A) && plainOperand(def, st.reads[1], &B)) {
+    O.vars = st.lhsIndices;
+    O.shape = osym->shape;
+    O.strides = makeStridesFromSizes(O.shape);
+  } else {
+    // second reading: variables that only take the value 0 are that constant
+    A = Operand();
+    B = Operand();
+    if (!plainOperand(def, st.reads[0], &A, &st.ranges) || !plainOperand(def, st.reads[1], &B, &st.ranges)) {
+      *why = "an operand index is not a plain index variable";
+      return false;
+    }
+    auto unit = [&](const std::string& v) { return st.ranges.at(v).min == 0 && st.ranges.at(v).max == 0; };
+    const std::vector<int64_t> ostrides = makeStridesFromSizes(osym->shape);
+    for (size_t d = 0; d < st.lhsIndices.size(); ++d) {
+      if (unit(st.lhsIndices[d]) && osym->shape[d] == 1) continue;
+      O.vars.push_back(st.lhsIndices[d]);
+      O.shape.push_back(osym->shape[d]);
+      O.strides.push_back(ostrides[d]);
+    }
+    reductionVars.clear();
+    for (const auto& v : st.reductionVars)
+      if (!unit(v)) reductionVars.push_back(v);
+  }
   {
     std::set<std::string> seen(O.vars.begin(), O.vars.end());
     if (seen.size() != O.vars.size()) {
@@ -163,7 +208,7 @@ bool matchProduct(const DefAnalysis& def, const StatementAnalysis& st, MatchedLa
     else if (b) nset.insert(v);
     else { *why = "output index " + v + " appears in no operand"; return false; }
   }
-  for (const auto& v : st.reductionVars) {
+  for (const auto& v : reductionVars) {
     if (posOf(A.vars, v) >= 0 && posOf(B.vars, v) >= 0) kset.insert(v);
     else { *why = "reduction index " + v + " does not appear in both operands"; return false; }
   }
@@ -173,6 +218,34 @@ bool matchProduct(const DefAnalysis& def, const StatementAnalysis& st, MatchedLa
   for (const auto& v : B.vars)
     if (!batch.count(v) && !nset.count(v) && !kset.count(v)) { *why = "unclassified index"; return false; }
 
+  // A free index that leads the output and one operand while the other free indices of that operand sit behind
+  // an index of the OTHER operand (d_I(n, c, hw) +=! d_O(n, r_m, hw) * W1(r_m, c): n, then c, then hw) is a batch
+  // index over which the other operand is shared (batch stride 0).
+  bool aLacksBatch = false, bLacksBatch = false;
+  {
+    auto contiguousIn = [&](const Operand& op, const std::set<std::string>& g) {
+      int64_t e, sd;
+      return flatten(op, orderedIn(op, g), &e, &sd);
+    };
+    if (batch.empty() && (!contiguousIn(O, mset) || !contiguousIn(O, nset))) {
+      for (size_t i = 0; i < O.vars.size(); ++i) {
+        const std::string v = O.vars[i];
+        if (mset.count(v) && !bLacksBatch && !aLacksBatch && i < A.vars.size() && A.vars[i] == v) {
+          mset.erase(v); batch.insert(v); bLacksBatch = true;
+        } else if (mset.count(v) && bLacksBatch && i < A.vars.size() && A.vars[i] == v) {
+          mset.erase(v); batch.insert(v);
+        } else if (nset.count(v) && !aLacksBatch && !bLacksBatch && i < B.vars.size() && B.vars[i] == v) {
+          nset.erase(v); batch.insert(v); aLacksBatch = true;
+        } else if (nset.count(v) && aLacksBatch && i < B.vars.size() && B.vars[i] == v) {
+          nset.erase(v); batch.insert(v);
+        } else {
+          break;
+        }
+        if (contiguousIn(O, mset) && contiguousIn(O, nset)) break;
+      }
+    }
+  }
+
   // The group that is outer in O plays "M" and its operand plays "A" (multiplication commutes).
   if (!mset.empty() && !nset.empty()) {
     const int firstM = posOf(O.vars, *orderedIn(O, mset).begin());
@@ -180,6 +253,7 @@ bool matchProduct(const DefAnalysis& def, const StatementAnalysis& st, MatchedLa
     if (firstN < firstM) {
       std::swap(A, B);
       std::swap(mset, nset);
+      std::swap(aLacksBatch, bLacksBatch);
     }
   }
 
@@ -192,7 +266,7 @@ bool matchProduct(const DefAnalysis& def, const StatementAnalysis& st, MatchedLa
   std::vector<std::string> inner;
   for (int i = (int)O.vars.size() - 1; i >= 0 && batch.count(O.vars[i]); --i)
     inner.insert(inner.begin(), O.vars[i]);
-  if (!inner.empty()) {
+  if (!inner.empty() && !aLacksBatch && !bLacksBatch) {
     auto tail = [&](const Operand& op) {
       if (op.vars.size() < inner.size()) return false;
       return std::equal(inner.begin(), inner.end(), op.vars.end() - inner.size());
@@ -238,22 +312,46 @@ bool matchProduct(const DefAnalysis& def, const StatementAnalysis& st, MatchedLa
   int64_t eB, eM, eN, eK, sBo, sBa, sBb, sMo, sMa, sNo, sNb, sKa, sKb;
   std::vector<std::string> bo = orderedIn(O, batch), mo = orderedIn(O, mset), no = orderedIn(O, nset),
                            ko = orderedIn(A, kset);
-  if (!sameOrder(orderedIn(A, batch), bo) || !sameOrder(orderedIn(B, batch), bo) ||
+  if ((!aLacksBatch && !sameOrder(orderedIn(A, batch), bo)) || (!bLacksBatch && !sameOrder(orderedIn(B, batch), bo)) ||
       !sameOrder(orderedIn(A, mset), mo) || !sameOrder(orderedIn(B, nset), no) ||
       !sameOrder(orderedIn(B, kset), ko)) {
     *why = "index groups are ordered differently in the operands";
     return false;
   }
   int64_t e2;
-  if (!flatten(O, bo, &eB, &sBo) || !flatten(A, bo, &e2, &sBa) || !flatten(B, bo, &e2, &sBb) ||
-      !flatten(O, mo, &eM, &sMo) || !flatten(A, mo, &e2, &sMa) || !flatten(O, no, &eN, &sNo) ||
+  // Reduction indices that lead both operands but are separated from the rest of the reduction by a free index
+  // (d_W1(m, c) +=! d_O(r_n, m, r_hw) * I(r_n, c, r_hw): r_n in front, r_hw behind m / c) act as a batch index
+  // that is reduced as well: the launch runs one contraction per value of them and adds the results.
+  std::vector<std::string> rb;
+  if (bo.empty() && (!flatten(A, ko, &eK, &sKa) || !flatten(B, ko, &e2, &sKb))) {
+    while (rb.size() < ko.size() && rb.size() < A.vars.size() && rb.size() < B.vars.size() &&
+           A.vars[rb.size()] == ko[rb.size()] && B.vars[rb.size()] == ko[rb.size()])
+      rb.push_back(ko[rb.size()]);
+    if (rb.empty() || rb.size() == ko.size()) {
+      *why = "the reduction indices are not contiguous in a tensor, so they do not flatten to one dimension";
+      return false;
+    }
+    ko.erase(ko.begin(), ko.begin() + rb.size());
+  }
+  sBa = sBb = 0;
+  if (!flatten(O, bo, &eB, &sBo) || (!aLacksBatch && !flatten(A, bo, &e2, &sBa)) ||
+      (!bLacksBatch && !flatten(B, bo, &e2, &sBb)) || !flatten(O, mo, &eM, &sMo) || !flatten(A, mo, &e2, &sMa) || !flatten(O, no, &eN, &sNo) ||
       !flatten(B, no, &e2, &sNb) || !flatten(A, ko, &eK, &sKa) || !flatten(B, ko, &e2, &sKb)) {
     *why = "an index group is not contiguous in a tensor, so it does not flatten to one dimension";
     return false;
   }
+  if (!rb.empty()) {
+    int64_t eRa, eRb;
+    if (!flatten(A, rb, &eRa, &sBa) || !flatten(B, rb, &eRb, &sBb) || eRa != eRb) {
+      *why = "the leading reduction indices do not flatten to one dimension";
+      return false;
+    }
+    eB = eRa;
+    sBo = 0;
+  }
   // batch indices must be the leading dimensions (uniform batch stride)
   for (size_t i = 0; i < bo.size(); ++i)
-    if (O.vars[i] != bo[i] || A.vars[i] != bo[i] || B.vars[i] != bo[i]) {
+    if (O.vars[i] != bo[i] || (!aLacksBatch && A.vars[i] != bo[i]) || (!bLacksBatch && B.vars[i] != bo[i])) {
       *why = "batch indices are not the leading dimensions of all three tensors";
       return false;
     }
@@ -262,9 +360,10 @@ bool matchProduct(const DefAnalysis& def, const StatementAnalysis& st, MatchedLa
   if (no.empty() && !mo.empty() && sMo != 1) { *why = "output is not dense"; return false; }
   p.family = TCB200_FAMILY_CONTRACTION;
   p.batch = eB; p.M = eM; p.N = eN; p.K = eK;
-  p.stride_a = bo.empty() ? 0 : sBa;
-  p.stride_b = bo.empty() ? 0 : sBb;
+  p.stride_a = bo.empty() && rb.empty() ? 0 : sBa;
+  p.stride_b = bo.empty() && rb.empty() ? 0 : sBb;
   p.stride_c = bo.empty() ? 0 : sBo;
+  p.batch_reduce = rb.empty() ? 0 : 1;
   p.ldc = no.empty() ? 1 : (mo.empty() ? eN : sMo);
   // A: k innermost -> k-major with row pitch = stride of m; else m innermost with pitch = stride of k
   if (sKa == 1) { p.a_k_major = 1; p.lda = mo.empty() ? eK : sMa; }
@@ -357,7 +456,7 @@ bool matchConv(const DefAnalysis& def, const StatementAnalysis& st, MatchedLaunc
 // (C +=! A(r_m), C(m) +=! A(m, r_n): test/test_tc_mapper_harness-inl.h:60-146)
 // ----------------------------------------------------------------------------------------------
 bool matchReduction(const DefAnalysis& def, const StatementAnalysis& st, MatchedLaunch* out, std::string* why) {
-  const TreeRef rhs = stripParens(lang::Comprehension(st.tree).rhs());
+  const TreeRef rhs = lang::Comprehension(st.tree).rhs();
   if (rhs->kind() != lang::TK_ACCESS || st.reads.size() != 1) return false;
   const TensorAccess& I = st.reads[0];
   const TensorSymbol* isym = def.find(I.tensor), *osym = def.find(st.lhs);
@@ -507,6 +606,33 @@ bool matchRelu(const StatementAnalysis& st, MatchedLaunch* launch) {
   return true;
 }
 
+// O(i, j, ...) = I(i, j, ...): the same plain indices in the same order over the whole of both tensors.
+bool matchCopy(const DefAnalysis& def, const StatementAnalysis& st, MatchedLaunch* out) {
+  if (st.assignment != '=' || !st.reductionVars.empty() || st.reads.size() != 1) return false;
+  const TreeRef rhs = lang::Comprehension(st.tree).rhs();
+  if (rhs->kind() != lang::TK_ACCESS) return false;
+  const TensorAccess& I = st.reads[0];
+  const TensorSymbol* isym = def.find(I.tensor), *osym = def.find(st.lhs);
+  if (!isym || !osym || I.tensor == st.lhs || !isFloat32(isym) || !isFloat32(osym)) return false;
+  if (I.indices.size() != st.lhsIndices.size() || isym->shape != osym->shape) return false;
+  int64_t elements = 1;
+  for (size_t d = 0; d < I.indices.size(); ++d) {
+    std::string v;
+    if (!I.indices[d].isSingleVar(&v) || v != st.lhsIndices[d]) return false;
+    const IndexRange& r = st.ranges.at(v);
+    if (r.min != 0 || r.extent() != isym->shape[d]) return false;
+    elements *= isym->shape[d];
+  }
+  if (elements <= 0) return false;
+  tcb200_problem_t& p = out->problem;
+  memset(&p, 0, sizeof(p));
+  p.family = TCB200_FAMILY_COPY;
+  p.red[0] = elements;
+  out->inputs = {valueIndex(def, I.tensor)};
+  out->output = valueIndex(def, st.lhs);
+  return true;
+}
+
 }  // namespace
 
 std::vector<MatchedLaunch> matchKernels(const DefAnalysis& def) {
@@ -529,11 +655,20 @@ std::vector<MatchedLaunch> matchKernels(const DefAnalysis& def) {
       launches.push_back(std::move(l));
       continue;
     }
-    // elementwise statement: must extend the launch that produced the same tensor just before
+    // elementwise statement: a whole-tensor copy is a launch of its own, anything else must extend the launch
+    // that produced the same tensor just before
+    {
+      MatchedLaunch copy;
+      if (matchCopy(def, st, &copy)) {
+        copy.statements.push_back((int)s);
+        launches.push_back(std::move(copy));
+        continue;
+      }
+    }
     if (launches.empty() || def.outputs.empty() ||
         launches.back().output != valueIndex(def, st.lhs))
       unmatched(st, "an elementwise statement is only supported as the epilogue of the reduction "
-                    "that produced the same tensor");
+                    "that produced the same tensor, or as a copy of a whole tensor");
     MatchedLaunch& l = launches.back();
     const StatementAnalysis& producer = def.statements[l.statements.front()];
     if (producer.lhsIndices.size() != st.lhsIndices.size())

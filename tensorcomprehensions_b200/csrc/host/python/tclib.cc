@@ -55,6 +55,9 @@ py::dict problemDict(const tc::MatchedLaunch& l) {
     d["a_k_major"] = p.a_k_major; d["b_k_major"] = p.b_k_major; d["bias_on_m"] = p.bias_on_m;
     d["lda"] = p.lda; d["ldb"] = p.ldb; d["ldc"] = p.ldc;
     d["stride_a"] = p.stride_a; d["stride_b"] = p.stride_b; d["stride_c"] = p.stride_c;
+    d["batch_reduce"] = p.batch_reduce;
+  } else if (p.family == TCB200_FAMILY_COPY) {
+    d["elements"] = p.red[0];
   } else if (p.family == TCB200_FAMILY_REDUCTION) {
     d["red"] = std::vector<int64_t>(p.red, p.red + 3);
     d["reduce_op"] = p.reduce_op;

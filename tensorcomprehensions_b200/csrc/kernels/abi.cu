@@ -55,7 +55,7 @@ __global__ void selftest_wait_kernel(long long limit, int* dev_status) {
 }
 
 int n_inputs_expected(const tcb200_problem_t& p) {
-  if (p.family == TCB200_FAMILY_REDUCTION) return 1;
+  if (p.family == TCB200_FAMILY_REDUCTION || p.family == TCB200_FAMILY_COPY) return 1;
   const bool has_bias = p.epilogue == TCB200_EPI_BIAS || p.epilogue == TCB200_EPI_BIAS_RELU;
   return 2 + (has_bias ? 1 : 0);
 }
@@ -93,6 +93,10 @@ struct tcb200_plan {
   std::atomic<void*> scratch{nullptr};
   // tensor-core contraction plans: tensor maps of the last few sets of base pointers
   void* map_cache = nullptr;
+  // a contraction that also reduces over its batch index: `impl` is the batched contraction into planes of
+  // partial sums, `outer` the problem as the caller stated it (its epilogue runs in the second pass)
+  bool batch_reduce = false;
+  tcb200_problem_t outer;
 };
 
 namespace tcb200 {
@@ -152,7 +156,20 @@ int tcb200_query(const tcb200_problem_t* problem, tcb200_tile_t* out, int max, i
       return group_conv_query(*problem, out, max, n);
     case TCB200_FAMILY_REDUCTION:
       return reduce_query(*problem, out, max, n);
+    case TCB200_FAMILY_COPY:
+      if (max > 0 && out) out[0] = tcb200_tile_t{TCB200_VARIANT_SIMT, 0, 0, 0, 0, 0, 0, 0};
+      *n = 1;
+      return problem->red[0] > 0 ? TCB200_OK : TCB200_ERR_INVALID_ARGUMENT;
     case TCB200_FAMILY_CONTRACTION: {
+      if (problem->batch_reduce && problem->batch > 1) {  // the candidates of the batched contraction into planes
+        tcb200_problem_t inner = *problem;
+        inner.batch_reduce = 0;
+        inner.epilogue = TCB200_EPI_NONE;
+        inner.accumulate = 0;
+        inner.ldc = inner.N;
+        inner.stride_c = inner.M * inner.N;
+        return tcb200_query(&inner, out, max, n);
+      }
       // The first candidate is the family default: the tensor-core tiles when the contraction is
       // large enough to prefer them, else the SIMT ones.
       int n_first = 0, n_second = 0;
@@ -185,8 +202,26 @@ int tcb200_plan_create(const tcb200_problem_t* problem, const tcb200_tile_t* til
   P.device = device;
   P.sms = sm_count(device);
   P.kernel_id = 0;
+  pl->outer = *problem;
+  if (problem->family == TCB200_FAMILY_CONTRACTION && problem->batch_reduce && problem->batch > 1) {
+    if (problem->M <= 0 || problem->N <= 0 || (double)problem->batch * problem->M * problem->N > 1e9) {
+      delete pl;
+      return TCB200_ERR_TOO_LARGE;
+    }
+    pl->batch_reduce = true;
+    P.p.batch_reduce = 0;
+    P.p.epilogue = TCB200_EPI_NONE;
+    P.p.accumulate = 0;
+    P.p.ldc = P.p.N;
+    P.p.stride_c = P.p.M * P.p.N;
+  }
+  problem = &P.p;
   int st = TCB200_ERR_INVALID_ARGUMENT;
   switch (problem->family) {
+    case TCB200_FAMILY_COPY:
+      st = problem->red[0] > 0 ? TCB200_OK : TCB200_ERR_INVALID_ARGUMENT;
+      P.tile.variant = TCB200_VARIANT_SIMT;
+      break;
     case TCB200_FAMILY_TENSORDOT:
       st = tensordot_plan(P);
       break;
@@ -218,8 +253,17 @@ int tcb200_plan_create(const tcb200_problem_t* problem, const tcb200_tile_t* til
       break;
   }
   if (st != TCB200_OK) {
+    if (pl->map_cache) tc_map_cache_delete(pl->map_cache);
     delete pl;
     return st;
+  }
+  if (pl->batch_reduce) {
+    if (P.scratch_floats != 0) {  // (a split-K tile never applies to a batched problem; keep the two scratch uses apart)
+      if (pl->map_cache) tc_map_cache_delete(pl->map_cache);
+      delete pl;
+      return TCB200_ERR_UNSUPPORTED;
+    }
+    P.scratch_floats = (size_t)P.p.batch * (size_t)P.p.M * (size_t)P.p.N;
   }
   *plan = pl;
   return TCB200_OK;
@@ -301,6 +345,9 @@ int tcb200_plan_describe(const tcb200_plan_t* plan, char* buf, size_t buflen) {
                : p.reduce_op == TCB200_REDUCE_PROD ? "prod" : "sum",
                (long long)p.red[0], (long long)p.red[1], (long long)p.red[2], p.accumulate ? " accumulate" : "");
       break;
+    case TCB200_FAMILY_COPY:
+      snprintf(head, sizeof(head), "tcb200::copy elements=%lld", (long long)p.red[0]);
+      break;
     case TCB200_FAMILY_GROUP_CONV:
       snprintf(head, sizeof(head),
                "tcb200::group_conv N=%lld G=%lld C=%lld F=%lld H=%lld W=%lld KH=%lld KW=%lld epilogue=%s",
@@ -314,10 +361,10 @@ int tcb200_plan_describe(const tcb200_plan_t* plan, char* buf, size_t buflen) {
       break;
     default:
       snprintf(head, sizeof(head),
-               "tcb200::contraction batch=%lld M=%lld N=%lld K=%lld A=%s B=%s epilogue=%s%s",
-               (long long)p.batch, (long long)p.M, (long long)p.N, (long long)p.K,
+               "tcb200::contraction batch=%lld%s M=%lld N=%lld K=%lld A=%s B=%s epilogue=%s%s",
+               (long long)p.batch, plan->batch_reduce ? " (reduced)" : "", (long long)p.M, (long long)p.N, (long long)p.K,
                p.a_k_major ? "k-major" : "m-major", p.b_k_major ? "k-major" : "n-major",
-               epilogue_name(p.epilogue), p.accumulate ? " accumulate" : "");
+               epilogue_name(plan->outer.epilogue), plan->outer.accumulate ? " accumulate" : "");
       break;
   }
   char split[32] = "";
@@ -334,7 +381,7 @@ int tcb200_launch(const tcb200_plan_t* plan, const void* const* inputs, int n_in
                   void* const* outputs, int n_outputs, tcb200_stream_t stream, int* dev_status) {
   if (!plan || !inputs || !outputs) return TCB200_ERR_INVALID_ARGUMENT;
   const Plan& P = plan->impl;
-  if (n_inputs != n_inputs_expected(P.p) || n_outputs != 1) return TCB200_ERR_INVALID_ARGUMENT;
+  if (n_inputs != n_inputs_expected(plan->outer) || n_outputs != 1) return TCB200_ERR_INVALID_ARGUMENT;
   for (int i = 0; i < n_inputs; ++i)
     if (!inputs[i]) return TCB200_ERR_INVALID_ARGUMENT;
   if (!outputs[0]) return TCB200_ERR_INVALID_ARGUMENT;
@@ -346,7 +393,26 @@ int tcb200_launch(const tcb200_plan_t* plan, const void* const* inputs, int n_in
   const float* in1 = n_inputs > 1 ? static_cast<const float*>(inputs[1]) : nullptr;
   const float* bias = n_inputs > 2 ? static_cast<const float*>(inputs[2]) : nullptr;
   float* out = static_cast<float*>(outputs[0]);
+  if (plan->batch_reduce) {
+    // batched contraction into one plane per batch entry, then the planes are added in order
+    float* planes;
+    unsigned* tickets;
+    int st = plan_scratch(plan, &planes, &tickets, s);
+    if (st != TCB200_OK) return st;
+    if (P.tile.variant == TCB200_VARIANT_TCGEN05 || P.tile.variant == TCB200_VARIANT_TCGEN05_TS ||
+        P.tile.variant == TCB200_VARIANT_TCGEN05_PAIR)
+      st = contraction_tc_launch(P, in0, in1, nullptr, planes, s, dev_status, nullptr, plan->map_cache);
+    else
+      st = contraction_simt_launch(P, in0, in1, nullptr, planes, s);
+    if (st != TCB200_OK) return st;
+    const tcb200_problem_t& o = plan->outer;
+    return partial_planes_reduce(planes, out, bias, (int)o.M, (int)o.N, (int)o.batch, o.ldc, o.epilogue, o.bias_on_m,
+                                 o.accumulate, P.sms, s);
+  }
   switch (P.p.family) {
+    case TCB200_FAMILY_COPY:
+      TCB200_CUDA_TRY(cudaMemcpyAsync(out, in0, (size_t)P.p.red[0] * sizeof(float), cudaMemcpyDeviceToDevice, s));
+      return TCB200_OK;
     case TCB200_FAMILY_TENSORDOT:
       return tensordot_launch(P, in0, in1, out, s, dev_status);
     case TCB200_FAMILY_GROUP_CONV:

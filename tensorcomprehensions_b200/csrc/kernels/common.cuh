@@ -120,6 +120,9 @@ int contraction_tc_plan(Plan& plan);
 // map_cache: a cache made by tc_map_cache_new() (may be null: the tensor maps are then encoded per launch)
 int contraction_tc_launch(const Plan& plan, const float* A, const float* B, const float* bias,
                           float* C, cudaStream_t s, int* dev_status, float* scratch, void* map_cache);
+// C = epilogue([C +] sum_s P[s]) over S dense planes P[s][M][N] of partial sums (splitk.cu)
+int partial_planes_reduce(const float* P, float* C, const float* bias, int M, int N, int S, int64_t ldc, int epi,
+                          int bias_on_m, int accumulate, int sms, cudaStream_t s);
 constexpr int kTcMapSlots = 8;
 void* tc_map_cache_new();
 void tc_map_cache_delete(void* cache);

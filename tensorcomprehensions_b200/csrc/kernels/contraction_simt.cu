@@ -253,6 +253,84 @@ __global__ void __launch_bounds__(256) simt_small_kernel(GemmArgs g, int ldas, i
   }
 }
 
+// ------------------------------------------------------------------------------------
+// simt_small, 4x4 register tiles (dense operands only).  The 2x2 form above moves one shared-memory word
+// per multiply-add into registers and is bound by that (shared memory returns 32 words per clock per SM
+// against 128 FMA lanes); a 4x4 tile moves half a word per multiply-add.  Per step of four k: four 128-bit
+// loads of A (rows tm, tm + TM, tm + 2 TM, tm + 3 TM: rows TM apart fall into different banks where
+// adjacent rows of a 72-float pitch would collide) and eight 64-bit loads of B (four consecutive columns of
+// four rows; a B row of 26 floats is only 8-byte aligned), then 64 FMAs.  Both slabs arrive by one bulk copy
+// each.  Threads past the edge of the tile grid read clamped rows / the next row's first columns and do not
+// store.
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) simt_small4_kernel(GemmArgs g) {
+  extern __shared__ __align__(16) float smem[];
+  pdl_sync();  // launched as a programmatic dependent: wait for the preceding kernel before any global access
+  const int M = g.M, N = g.N, K = g.K;
+  float* As = smem;                    // [M][K], dense
+  float* Bs = smem + (size_t)M * K;    // [K][N], dense, followed by 16 bytes of slack for the last row's overrun
+  uint64_t* bar = reinterpret_cast<uint64_t*>(Bs + (size_t)K * N + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar + 1);
+  const int64_t b = blockIdx.x;
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    mbar_init(bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const uint32_t bytes_a = (uint32_t)M * K * 4, bytes_b = (uint32_t)K * N * 4;
+    mbar_expect_tx(bar, bytes_a + bytes_b);
+    bulk_load(As, g.A + b * g.sa, bytes_a, bar);
+    bulk_load(Bs, g.B + b * g.sb, bytes_b, bar);
+  }
+  const int TM = (M + 3) >> 2, TN = (N + 3) >> 2;
+  const int tm = tid / TN, tn = tid - tm * TN;
+  const bool active = tm < TM;
+  const float* arow[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) arow[i] = As + (size_t)min(tm + TM * i, M - 1) * K;
+  const float* bcol = Bs + 4 * tn;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  __syncthreads();  // the barrier is initialised before anyone polls it
+  if (!mbar_wait(bar, 0, 9, nullptr, abort_flag)) return;
+  if (!active) return;
+#pragma unroll 2
+  for (int k = 0; k < K; k += 4) {
+    float a[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 v = *reinterpret_cast<const float4*>(arow[i] + k);
+      a[i][0] = v.x; a[i][1] = v.y; a[i][2] = v.z; a[i][3] = v.w;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 b0 = *reinterpret_cast<const float2*>(bcol + (size_t)(k + j) * N);
+      const float2 b1 = *reinterpret_cast<const float2*>(bcol + (size_t)(k + j) * N + 2);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[i][0] = fmaf(a[i][j], b0.x, acc[i][0]);
+        acc[i][1] = fmaf(a[i][j], b0.y, acc[i][1]);
+        acc[i][2] = fmaf(a[i][j], b1.x, acc[i][2]);
+        acc[i][3] = fmaf(a[i][j], b1.y, acc[i][3]);
+      }
+    }
+  }
+  float* C = g.C + b * g.sc;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = tm + TM * i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = 4 * tn + j;
+      if (n < N) store_out(g, C, m, n, acc[i][j]);
+    }
+  }
+}
+
 bool valid(const tcb200_problem_t& p) {
   return p.batch > 0 && p.M > 0 && p.N > 0 && p.K > 0 && p.M < (1ll << 31) &&
          p.N < (1ll << 31) && p.K < (1ll << 31) && p.batch <= 0x7fffffffll && p.lda > 0 &&
@@ -271,6 +349,14 @@ void small_pitches(const tcb200_problem_t& p, bool fast, int* ldas, int* ldbs) {
 size_t small_smem_bytes(const tcb200_problem_t& p) {
   return sizeof(float) * ((size_t)p.M * (p.K + 4) + (size_t)p.K * ((p.N + 1) / 2 * 2 + 2)) + 16;
 }
+// Shape part of the conditions of the bulk-copy forms: dense operands whose slabs are multiples of 16 bytes.
+bool small_dense_shape(const tcb200_problem_t& p) {
+  return small_fast_shape(p) && p.lda == p.K && p.ldb == p.N && p.N % 2 == 0 && (p.M * p.K) % 4 == 0 &&
+         (p.K * p.N) % 4 == 0 && p.stride_b % 4 == 0 && p.M * p.K * 4 < (1 << 20) && p.K * p.N * 4 < (1 << 20);
+}
+// The 4x4-tile form: one thread per 4x4 tile of the output.
+int small4_threads(const tcb200_problem_t& p) { return (int)round_up(((p.M + 3) / 4) * ((p.N + 3) / 4), 32); }
+bool small4_ok(const tcb200_problem_t& p) { return small_dense_shape(p) && small4_threads(p) <= 256; }
 
 // simt_small reads A as (m,k) row-major and B as (k,n) row-major: the batchmatmul form.
 bool small_ok(const tcb200_problem_t& p) {
@@ -289,6 +375,9 @@ int contraction_simt_query(const tcb200_problem_t& p, tcb200_tile_t* out, int ma
   };
   if (small_ok(p)) {
     push(TCB200_VARIANT_SIMT_SMALL, (int)p.M, (int)p.N, (int)p.K, 256);
+    // bk = 4: 4x4 register tiles.  Half the shared-memory words per multiply-add, but two warps per matrix instead
+    // of eight: 8.7 us against 7.5 us on the 500 x [26x72][72x26] benchmark, so it is a sweep point, not the default.
+    if (small4_ok(p)) push(TCB200_VARIANT_SIMT_SMALL, (int)p.M, (int)p.N, 4, small4_threads(p));
     push(TCB200_VARIANT_SIMT_SMALL, (int)p.M, (int)p.N, (int)p.K, 192);
     push(TCB200_VARIANT_SIMT_SMALL, (int)p.M, (int)p.N, (int)p.K, 128);
   }
@@ -303,6 +392,15 @@ int contraction_simt_plan(Plan& plan) {
   tcb200_tile_t& t = plan.tile;
   if (t.variant == TCB200_VARIANT_SIMT_SMALL) {
     if (!small_ok(p)) return TCB200_ERR_UNSUPPORTED;
+    if (t.bk == 4 && p.K != 4) {  // 4x4 register tiles, one thread per tile
+      if (!small4_ok(p)) return TCB200_ERR_UNSUPPORTED;
+      t.bm = (int)p.M; t.bn = (int)p.N; t.threads = small4_threads(p);
+      plan.launch.grid = dim3((unsigned)p.batch, 1, 1);
+      plan.launch.block = dim3(t.threads, 1, 1);
+      plan.launch.smem = sizeof(float) * ((size_t)p.M * p.K + (size_t)p.K * p.N + 4) + 16;
+      plan.kernel_id = 11;
+      return TCB200_OK;
+    }
     if (t.threads <= 0) t.threads = 256;
     if (t.threads > 256 || t.threads % 32) return TCB200_ERR_INVALID_ARGUMENT;
     t.bm = (int)p.M; t.bn = (int)p.N; t.bk = (int)p.K;
@@ -328,20 +426,23 @@ int contraction_simt_launch(const Plan& plan, const float* A, const float* B, co
   const tcb200_problem_t& p = plan.p;
   GemmArgs g{A, B, bias, C, (int)p.M, (int)p.N, (int)p.K, p.lda, p.ldb, p.ldc,
              p.stride_a, p.stride_b, p.stride_c, p.epilogue, p.bias_on_m, p.accumulate};
-  if (plan.kernel_id == 10) {
+  if (plan.kernel_id == 11 && (((uintptr_t)A | (uintptr_t)B) & 15) == 0) {
+    TCB200_CUDA_TRY(launch_pdl(simt_small4_kernel, plan.launch.grid, plan.launch.block, plan.launch.smem, s, g));
+  } else if (plan.kernel_id == 10 || plan.kernel_id == 11) {
+    // (a 4x4-tile plan whose operands are views at an odd offset runs the forms that take any alignment)
+    const dim3 block = plan.kernel_id == 11 ? dim3(256, 1, 1) : plan.launch.block;
+    const size_t smem_bytes = plan.kernel_id == 11 ? small_smem_bytes(p) : plan.launch.smem;
     const bool fast = small_fast_shape(p) && ((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 8 == 0);
     int ldas = 0, ldbs = 0;
     small_pitches(p, fast, &ldas, &ldbs);
-    const bool bulk = fast && p.lda == p.K && p.ldb == p.N && p.N % 2 == 0 && (p.M * p.K) % 4 == 0 &&
-                      (p.K * p.N) % 4 == 0 && p.stride_b % 4 == 0 && ((uintptr_t)B % 16 == 0) &&
-                      p.M * p.K * 4 < (1 << 20) && p.K * p.N * 4 < (1 << 20);
+    const bool bulk = fast && small_dense_shape(p) && ((uintptr_t)B % 16 == 0);
     if (bulk)
-      TCB200_CUDA_TRY(launch_pdl(simt_small_kernel<2>, plan.launch.grid, plan.launch.block, plan.launch.smem, s, g,
+      TCB200_CUDA_TRY(launch_pdl(simt_small_kernel<2>, plan.launch.grid, block, smem_bytes, s, g,
                                  (int)p.K, (int)p.N));
     else if (fast)
-      TCB200_CUDA_TRY(launch_pdl(simt_small_kernel<1>, plan.launch.grid, plan.launch.block, plan.launch.smem, s, g, ldas, ldbs));
+      TCB200_CUDA_TRY(launch_pdl(simt_small_kernel<1>, plan.launch.grid, block, smem_bytes, s, g, ldas, ldbs));
     else
-      TCB200_CUDA_TRY(launch_pdl(simt_small_kernel<0>, plan.launch.grid, plan.launch.block, plan.launch.smem, s, g, ldas, ldbs));
+      TCB200_CUDA_TRY(launch_pdl(simt_small_kernel<0>, plan.launch.grid, block, smem_bytes, s, g, ldas, ldbs));
   } else {
     // 128-bit loads need a 16-byte aligned base, leading dimension and batch stride.
     const int a_vec = ((uintptr_t)A % 16 == 0) && p.lda % 4 == 0 && p.stride_a % 4 == 0;

@@ -1162,66 +1162,6 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
 }
 
 
-// ---------------------------------------------------------------------------------- split-K, second pass
-// A contraction whose output has too few tiles for the SMs (a 128 x 2048 x 4096 shard of the transposed matmul:
-// 16 tiles for 148 SMs) splits its reduction over S CTAs per tile.  The tensor-core kernel runs as a "batch" of
-// S splits that write raw partial sums P[s][m][n] to scratch memory owned by the plan; this kernel adds the S
-// partials of every element in the fixed order s = 0 .. S-1 (the same bits on every run), then applies what the
-// single-pass kernel's epilogue would: the old output for "+=", bias, ReLU.
-struct SplitKArgs {
-  const float* P;
-  float* C;
-  const float* bias;
-  int M, N, S;
-  int64_t ldc;
-  int epi, bias_on_m, accumulate;
-};
-
-template <bool VEC>
-__global__ void __launch_bounds__(256) splitk_reduce_kernel(SplitKArgs a) {
-  pdl_sync();  // the partial sums come from the kernel launched just before this one
-  const bool has_bias = a.epi == TCB200_EPI_BIAS || a.epi == TCB200_EPI_BIAS_RELU;
-  const int64_t plane = (int64_t)a.M * a.N;
-  if (VEC) {
-    const int n4 = a.N >> 2;
-    const int64_t total = (int64_t)a.M * n4;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-      const int m = (int)(i / n4), n = (int)(i - (int64_t)m * n4) * 4;
-      const float4* src = reinterpret_cast<const float4*>(a.P + (int64_t)m * a.N + n);
-      float4 acc = src[0];
-      for (int s = 1; s < a.S; ++s) {
-        const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src) + s * plane);
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-      }
-      float4* dst = reinterpret_cast<float4*>(a.C + (int64_t)m * a.ldc + n);
-      if (a.accumulate) {
-        const float4 old = *dst;
-        acc.x += old.x; acc.y += old.y; acc.z += old.z; acc.w += old.w;
-      }
-      float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (has_bias) {
-        if (a.bias_on_m) b.x = b.y = b.z = b.w = __ldg(a.bias + m);
-        else b = make_float4(__ldg(a.bias + n), __ldg(a.bias + n + 1), __ldg(a.bias + n + 2), __ldg(a.bias + n + 3));
-      }
-      acc.x = apply_epilogue_rt(a.epi, acc.x, b.x);
-      acc.y = apply_epilogue_rt(a.epi, acc.y, b.y);
-      acc.z = apply_epilogue_rt(a.epi, acc.z, b.z);
-      acc.w = apply_epilogue_rt(a.epi, acc.w, b.w);
-      *dst = acc;
-    }
-  } else {
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < plane; i += (int64_t)gridDim.x * blockDim.x) {
-      const int m = (int)(i / a.N), n = (int)(i - (int64_t)m * a.N);
-      float acc = a.P[i];
-      for (int s = 1; s < a.S; ++s) acc += a.P[i + s * plane];
-      float* dst = a.C + (int64_t)m * a.ldc + n;
-      if (a.accumulate) acc += *dst;
-      const float b = has_bias ? __ldg(a.bias + (a.bias_on_m ? m : n)) : 0.f;
-      *dst = apply_epilogue_rt(a.epi, acc, b);
-    }
-  }
-}
-
 // ---------------------------------------------------------------------------------- host
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -1554,17 +1494,8 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
   if (st != TCB200_OK || S == 1) return st;
 
   // second pass: C = epilogue([C +] sum_s P[s])
-  SplitKArgs r;
-  r.P = scratch; r.C = C; r.bias = bias;
-  r.M = (int)p.M; r.N = (int)p.N; r.S = S;
-  r.ldc = p.ldc;
-  r.epi = p.epilogue; r.bias_on_m = p.bias_on_m; r.accumulate = p.accumulate;
-  const bool vec = p.N % 4 == 0 && p.ldc % 4 == 0 && (((uintptr_t)C | (uintptr_t)scratch) & 15) == 0;
-  const int64_t work = vec ? p.M * p.N / 4 : p.M * p.N;
-  const dim3 grid((unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div(work, 256), (int64_t)plan.sms * 8)), 1, 1);
-  if (vec) TCB200_CUDA_TRY(launch_pdl(splitk_reduce_kernel<true>, grid, dim3(256, 1, 1), (size_t)0, s, r));
-  else TCB200_CUDA_TRY(launch_pdl(splitk_reduce_kernel<false>, grid, dim3(256, 1, 1), (size_t)0, s, r));
-  return TCB200_OK;
+  return partial_planes_reduce(scratch, C, bias, (int)p.M, (int)p.N, S, p.ldc, p.epilogue, p.bias_on_m, p.accumulate,
+                               plan.sms, s);
 }
 
 }  // namespace tcb200

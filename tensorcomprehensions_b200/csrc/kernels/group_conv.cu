@@ -19,6 +19,7 @@
 // filters are re-laid out as Ws[c][kh][kw][f] so one 128-bit shared load feeds four
 // output channels.  Consecutive threads take consecutive output pixels, so the halo
 // reads are bank-conflict free and the output stores are coalesced along w.
+#include "async.cuh"
 #include "common.cuh"
 
 namespace tcb200 {
@@ -357,6 +358,178 @@ __global__ void __launch_bounds__(256 / FPT) group_conv_item_kernel(ConvArgs a) 
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// multi-item kernel: one CTA per SM-sized run of items, W = 16 in registers, OW <= 14, KW <= 3
+// ------------------------------------------------------------------------------------------------
+// What the item kernel's profile asked for (FMA pipe 63 % busy; shared memory at 60 % of its wavefront rate, i.e.
+// the two co-limit; two of sixteen lanes idle because 14 output rows are padded to 16 thread slots; a single
+// wave of 1024 small CTAs that loads, computes and stores in lock-step):
+//  * a thread owns one output row of FOUR output channels (56 accumulators as 28 packed pairs): per input
+//    row it loads 16 + 12 words from shared memory for 168 multiply-adds, half the words per multiply-add of
+//    the two-channel tile, so the FMA pipe, not shared memory, is the limit;
+//  * a CTA owns `ipc` consecutive items of the (g, n) order (1024 items / 148 SMs -> 7): every SM gets the same
+//    amount of work in ONE CTA, threads are numbered densely over (item, channel quad, row) so that no lane
+//    idles, and the filters of the (at most two) groups the run touches are staged once per CTA, transposed
+//    to [tap][f] so that a thread's four channels are one 128-bit load;
+//  * the input planes of all items arrive in four cp.async groups of C/4 channels; the channel loop starts
+//    when the first has landed, the other three land under the multiply-adds;
+//  * the output tiles go back through shared memory (each item's own input slab) and leave as one bulk copy
+//    per item (cp.async.bulk shared -> global), issued by one thread.
+constexpr int kMultiMaxThreads = 512;
+constexpr int kMultiWPitch = 20;  // floats per tap row of the transposed filters: F <= 16, conflict-free writes
+
+// PACKED: accumulate pairs of output channels with the packed fp32x2 FMA (half the FMA instructions, one
+// register move per input word to duplicate it); else plain FMAs (no moves, twice the FMA instructions).
+template <int KHT, bool PACKED>
+__global__ void __launch_bounds__(kMultiMaxThreads, 1) group_conv_multi_kernel(ConvArgs a, int ipc, int N, int total) {
+  extern __shared__ __align__(16) float smem[];
+  pdl_sync();  // launched as a programmatic dependent: wait for the preceding kernel before any global access
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const int taps = a.C * a.KH * a.KW;
+  const int F = a.F;
+  const int w0 = blockIdx.x * ipc;                 // first work index of this CTA; work w -> (g = w / N, n = w % N)
+  const int mine = min(ipc, total - w0);           // items of this CTA
+  const int g0 = w0 / N;                           // first group the run touches (it touches g0 and maybe g0 + 1)
+  const int groups = (w0 + mine - 1) / N - g0 + 1; // 1 or 2 (ipc <= N, checked by the plan)
+  float* Ws = smem;                                // [2][taps][kMultiWPitch]
+  float* Is = smem + 2 * (size_t)taps * kMultiWPitch;  // [ipc][C][H][kRowsPitch]
+  const int slab = a.C * a.H * kRowsPitch;         // floats per item in shared memory
+  const int in_elems = a.C * a.H * 16;             // floats per item in global memory
+  auto item_of = [&](int j) { const int w = w0 + j; return (w % N) * a.G + w / N; };
+
+  // input planes: quarter q of every item, 16-byte pieces, one commit group per quarter
+  const int rows_q = (a.C / 4) * a.H;
+#pragma unroll 1
+  for (int q = 0; q < 4; ++q) {
+    const int pieces = mine * rows_q * 4;
+    for (int i = tid; i < pieces; i += nt) {
+      const int j = i / (rows_q * 4), rem = i - j * rows_q * 4;
+      const int r = q * rows_q + (rem >> 2), piece = rem & 3;
+      cp_async_16(Is + (size_t)j * slab + (size_t)r * kRowsPitch + 4 * piece,
+                  a.I + (size_t)item_of(j) * in_elems + (size_t)r * 16 + 4 * piece);
+    }
+    cp_async_commit();
+  }
+  // filters of the run's groups, transposed on the way: thread -> (f = i % F, four consecutive taps).  The
+  // 16 threads of one piece index write 16 consecutive words of a tap row, the next piece index lands 80
+  // words further: no bank is hit twice.
+  {
+    const int tq = taps >> 2;  // taps % 4 == 0 because C % 4 == 0
+    for (int i = tid; i < groups * F * tq; i += nt) {
+      const int s = i / (F * tq), rem = i - s * F * tq;
+      const int piece = rem / F, f = rem - piece * F;
+      const float4 v = __ldg(reinterpret_cast<const float4*>(a.W + ((size_t)(g0 + s) * F + f) * taps) + piece);
+      float* dst = Ws + ((size_t)s * taps + 4 * piece) * kMultiWPitch + f;
+      dst[0] = v.x; dst[kMultiWPitch] = v.y; dst[2 * kMultiWPitch] = v.z; dst[3 * kMultiWPitch] = v.w;
+    }
+  }
+
+  // thread -> (item j, channel quad fq, output row h), densely numbered
+  const int FQ = F >> 2;
+  const int tpi = FQ * a.OH;  // threads per item
+  const int j = tid / tpi, rem = tid - j * tpi;
+  const bool active = j < mine;
+  const int fq = active ? rem / a.OH : 0, h = active ? rem - (rem / a.OH) * a.OH : 0;
+  const int jj = active ? j : 0;
+  const int gslot = (w0 + jj) / N - g0;
+
+  float2 acc[2][kItemOW];
+#pragma unroll
+  for (int p = 0; p < 2; ++p)
+#pragma unroll
+    for (int w = 0; w < kItemOW; ++w) acc[p][w] = make_float2(0.f, 0.f);
+
+  const int KH = KHT > 0 ? KHT : a.KH;
+  const int KW = KHT > 0 ? kItemKW : a.KW;
+  const int plane_step = (a.H - KH) * kRowsPitch;
+  const float* in = Is + (size_t)jj * slab;
+  const float* wt = Ws + (size_t)gslot * taps * kMultiWPitch + 4 * fq;
+  auto channels = [&](int c0, int c1) {
+    const float* rp = in + (c0 * a.H + h) * kRowsPitch;
+    const float* wrow = wt + (size_t)(c0 * KH * KW) * kMultiWPitch;
+    for (int c = c0; c < c1; ++c, rp += plane_step) {
+#pragma unroll
+      for (int kh = 0; kh < KH; ++kh, rp += kRowsPitch) {
+        const float4* row = reinterpret_cast<const float4*>(rp);
+        float x[16];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float4 v = row[q];
+          x[4 * q] = v.x; x[4 * q + 1] = v.y; x[4 * q + 2] = v.z; x[4 * q + 3] = v.w;
+        }
+#pragma unroll
+        for (int kw = 0; kw < kItemKW; ++kw) {
+          if (kw < KW) {
+            const float4 wv = *reinterpret_cast<const float4*>(wrow);
+            wrow += kMultiWPitch;
+            const float2 w01 = make_float2(wv.x, wv.y), w23 = make_float2(wv.z, wv.w);
+#pragma unroll
+            for (int w = 0; w < kItemOW; ++w) {
+              if (PACKED) {
+                const float2 xx = make_float2(x[w + kw], x[w + kw]);
+                acc[0][w] = __ffma2_rn(xx, w01, acc[0][w]);
+                acc[1][w] = __ffma2_rn(xx, w23, acc[1][w]);
+              } else {
+                const float xv = x[w + kw];
+                acc[0][w].x = fmaf(xv, wv.x, acc[0][w].x);
+                acc[0][w].y = fmaf(xv, wv.y, acc[0][w].y);
+                acc[1][w].x = fmaf(xv, wv.z, acc[1][w].x);
+                acc[1][w].y = fmaf(xv, wv.w, acc[1][w].y);
+              }
+            }
+          }
+        }
+      }
+    }
+  };
+  const int cq = a.C / 4;
+  cp_async_wait_group<3>(); __syncthreads(); if (active) channels(0, cq);   // (the sync also publishes the filters)
+  cp_async_wait_group<2>(); __syncthreads(); if (active) channels(cq, 2 * cq);
+  cp_async_wait_group<1>(); __syncthreads(); if (active) channels(2 * cq, 3 * cq);
+  cp_async_wait_group<0>(); __syncthreads(); if (active) channels(3 * cq, a.C);
+  __syncthreads();  // every thread is done with the input planes: each item's slab now takes its output tile
+
+  const bool has_bias = a.epi == TCB200_EPI_BIAS || a.epi == TCB200_EPI_BIAS_RELU;
+  const int out_elems = F * a.OH * a.OW;
+  if (active) {
+    float* Os = Is + (size_t)j * slab;
+    const int g = (w0 + j) / N;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int f = fq * 4 + k;
+      const float bias = has_bias ? __ldg(a.bias + g * F + f) : 0.f;
+      float* o = Os + ((size_t)f * a.OH + h) * a.OW;
+#pragma unroll
+      for (int w = 0; w < kItemOW; ++w) {
+        const float v = (k & 1) ? acc[k >> 1][w].y : acc[k >> 1][w].x;
+        if (w < a.OW) o[w] = apply_epilogue_rt(a.epi, v, bias);
+      }
+    }
+  }
+  // the output tiles are read by the bulk copies (async proxy): order the generic writes before them
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncthreads();
+  if ((out_elems & 3) == 0 && (((uintptr_t)a.O) & 15) == 0) {
+    if (tid == 0) {
+      for (int k = 0; k < mine; ++k)
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(
+                         a.O + (size_t)item_of(k) * out_elems),
+                     "r"(smem_u32(Is + (size_t)k * slab)), "r"((uint32_t)out_elems * 4)
+                     : "memory");
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // written before the CTA (and its memory) goes away
+    }
+  } else {
+    for (int i = tid; i < mine * out_elems; i += nt) {
+      const int k = i / out_elems, e = i - k * out_elems;
+      a.O[(size_t)item_of(k) * out_elems + e] = Is[(size_t)k * slab + e];
+    }
+  }
+}
+
+// Items per CTA of the multi-item kernel for this problem on `sms` multiprocessors (0: the kernel does not apply).
+int multi_ipc(const tcb200_problem_t& p, int sms);
+
 // Threads the two-channels-per-thread form of the item kernel would use (it takes up to 128).
 int item_two_threads(const tcb200_problem_t& p) {
   return (int)((p.conv[3] / 2) * ((p.conv[4] - p.conv[6] + 1 + 7) / 8 * 8));
@@ -372,6 +545,23 @@ bool item_ok(const tcb200_problem_t& p) {
          (F / 4) * ((OH + 7) / 8 * 8) <= kItemThreads &&
          F * OH * OW <= C * H * kRowsPitch &&
          sizeof(float) * (size_t)((C * KH * KW + 4) * F + C * H * kRowsPitch) <= 48 * 1024;
+}
+
+int multi_threads(const tcb200_problem_t& p, int ipc) {
+  return (int)round_up((int64_t)ipc * (p.conv[3] / 4) * (p.conv[4] - p.conv[6] + 1), 32);
+}
+size_t multi_smem(const tcb200_problem_t& p, int ipc) {
+  return sizeof(float) * (2 * (size_t)(p.conv[2] * p.conv[6] * p.conv[7]) * kMultiWPitch +
+                          (size_t)ipc * p.conv[2] * p.conv[4] * kRowsPitch);
+}
+int multi_ipc(const tcb200_problem_t& p, int sms) {
+  if (!item_ok(p) || p.accumulate || p.conv[3] > 16) return 0;
+  const int64_t items = p.conv[0] * p.conv[1];
+  // worth it from about four items per SM on; below that the one-item CTAs fill the SMs better
+  if (items < 4 * (int64_t)sms) return 0;
+  int ipc = (int)ceil_div(items, sms);
+  while (ipc > 1 && (ipc > p.conv[0] || multi_threads(p, ipc) > kMultiMaxThreads || multi_smem(p, ipc) > 200 * 1024)) --ipc;
+  return ipc >= 2 ? ipc : 0;
 }
 
 bool rows_ok(const tcb200_problem_t& p) {
@@ -435,6 +625,15 @@ int group_conv_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int
       ++cnt;
     }
   }
+  // stages = 5: a run of items per CTA (bk = items per CTA, chosen by the plan; bm = 1: plain FMAs).  Measured
+  // on the benchmark shape: 29.9 us (packed FMAs) / 32.7 us (plain) against 26.0 us for the one-item CTAs: its
+  // 13 warps per SM run in lock-step between CTA-wide barriers, where seven independent small CTAs drift apart.
+  if (multi_ipc(p, sm_count(-1)) > 0) {
+    if (cnt < max && out) out[cnt] = tcb200_tile_t{TCB200_VARIANT_SIMT, 0, 4, 0, 5, 0, 0};
+    ++cnt;
+    if (cnt < max && out) out[cnt] = tcb200_tile_t{TCB200_VARIANT_SIMT, 1, 4, 0, 5, 0, 0};
+    ++cnt;
+  }
   if (rows_ok(p)) {
     // bk = n per CTA of the rows kernel
     const int ns[] = {2, 1, 4};
@@ -478,6 +677,17 @@ int group_conv_plan(Plan& plan) {
     }
   }
   if (t.variant != TCB200_VARIANT_SIMT) return TCB200_ERR_UNSUPPORTED;
+  if (t.stages == 5) {  // multi-item kernel
+    const int ipc = multi_ipc(p, plan.sms);
+    if (ipc == 0) return TCB200_ERR_UNSUPPORTED;
+    t.bm = t.bm ? 1 : 0; t.bn = 4; t.bk = ipc;
+    t.threads = multi_threads(p, ipc);
+    plan.launch.grid = dim3((unsigned)ceil_div(p.conv[0] * p.conv[1], ipc), 1, 1);
+    plan.launch.block = dim3(t.threads, 1, 1);
+    plan.launch.smem = multi_smem(p, ipc);
+    plan.kernel_id = t.bm ? 104 : 103;
+    return TCB200_OK;
+  }
   if (t.bk == 1 && t.stages == 4) {  // item kernel
     if (!item_ok(p)) return TCB200_ERR_UNSUPPORTED;
     if (p.conv[0] * p.conv[1] > 0x7fffffffll) return TCB200_ERR_TOO_LARGE;
@@ -539,8 +749,19 @@ int group_conv_launch(const Plan& plan, const float* I, const float* W, const fl
   a.epi = p.epilogue; a.accumulate = p.accumulate;
   // The item kernel stages I and W with 16-byte asynchronous copies.  A dense tensor may still start at any
   // 4-byte offset of a larger buffer (a view): such a launch runs on the band kernel, which uses 4-byte loads.
-  const bool item_misaligned =
-      (plan.kernel_id == 101 || plan.kernel_id == 102) && ((((uintptr_t)I) | ((uintptr_t)W)) & 15) != 0;
+  const bool multi = plan.kernel_id == 103 || plan.kernel_id == 104;
+  const bool item_misaligned = (plan.kernel_id == 101 || plan.kernel_id == 102 || multi) &&
+                               ((((uintptr_t)I) | ((uintptr_t)W)) & 15) != 0;
+  if (multi && !item_misaligned) {
+    const bool k33 = a.KH == 3 && a.KW == 3, packed = plan.kernel_id == 103;
+    auto fn = k33 ? (packed ? group_conv_multi_kernel<3, true> : group_conv_multi_kernel<3, false>)
+                  : (packed ? group_conv_multi_kernel<0, true> : group_conv_multi_kernel<0, false>);
+    static std::atomic<uint64_t> multi_configured[4];
+    TCB200_CUDA_TRY(ensure_dynamic_smem(fn, 200 * 1024, plan.device, multi_configured[(k33 ? 2 : 0) + (packed ? 1 : 0)]));
+    TCB200_CUDA_TRY(launch_pdl(fn, plan.launch.grid, plan.launch.block, plan.launch.smem, s, a, plan.tile.bk,
+                               (int)p.conv[0], (int)(p.conv[0] * p.conv[1])));
+    return TCB200_OK;
+  }
   if ((plan.kernel_id == 101 || plan.kernel_id == 102) && !item_misaligned) {
     const bool k33 = a.KH == 3 && a.KW == 3;
     if (plan.kernel_id == 102) {

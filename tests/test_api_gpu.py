@@ -148,6 +148,79 @@ def matmul_bgrad(float(M, K) A, float(M, N) d_C) -> (d_B) { d_B(k, n) +=! d_C(r_
     assert tc.debug_tc_mapper(True) is True and tc.dump_cuda(False) is False  # accepted, no effect
 
 
+def test_make_autograd_with_the_convolution_example(cuda):
+    """The reference's own make_autograd example (tensor_comprehensions/__init__.py:558-601,
+    python/tests/test_tc.py:383-443): a 1x1 convolution with bias and its gradients, written with index
+    differences (h - r_kh, r_h - kh) that are the plain index for 1-wide filter ranges.  The input gradient is a
+    contraction over which the filter is shared by all images, the weight gradient a contraction that also reduces
+    over the image index, the bias "gradient" of the example a whole-tensor copy.  Forward and both real gradients
+    are compared with torch.autograd on conv2d."""
+    conv = """
+def convolution(float(N,C,H,W) I, float(M,C,KH,KW) W1, float(M) Bias) -> (O) {
+    O(n, m, h, w) +=! I(n, r_c, h + r_kh, w + r_kw) * W1(m, r_c, r_kh, r_kw)
+    O(n, m, h, w)  = O(n, m, h, w) + Bias(m)
+}
+def convolution_igrad(float(M,C,KH,KW) W1, float(N,M,H,W) d_O) -> (d_I) {
+    d_I(n, c, h, w) +=! d_O(  n, r_m, h - r_kh, w - r_kw) * W1(r_m, c, r_kh, r_kw)
+}
+def convolution_wgrad(float(N,C,H,W) I, float(N,M,H,W) d_O) -> (d_W1) {
+    d_W1(m, c, kh, kw) +=! d_O(r_n,   m, r_h - kh, r_w - kw) *  I(r_n, c,  r_h,  r_w)
+}
+def convolution_biasgrad(float(M) Bias) -> (d_Bias) {
+    d_Bias(m) = Bias(m)
+}
+"""
+    N, C, H, W, O, kH, kW = 32, 4, 56, 56, 16, 1, 1
+    T = tc.define(conv, tc.make_naive_options_factory())
+    g = torch.Generator().manual_seed(11)
+    I = torch.randn(N, C, H, W, generator=g).to(cuda).requires_grad_()
+    Wt = torch.randn(O, C, kH, kW, generator=g).to(cuda).requires_grad_()
+    Bias = torch.randn(O, generator=g).to(cuda).requires_grad_()
+    weight = torch.randn(N, O, H, W, generator=g).to(cuda)
+
+    def convolution_backward(I, W1, Bias, d_O):
+        return T.convolution_igrad(W1, d_O), T.convolution_wgrad(I, d_O), T.convolution_biasgrad(Bias)
+
+    fn = tc.make_autograd(T.convolution, convolution_backward)
+    out = fn(I, Wt, Bias)
+    (out * weight).sum().backward()
+    out2 = fn(I, Wt, Bias)          # the second call reuses the compiled executors
+    assert torch.equal(out, out2)
+
+    I2, W2, B2 = (t.detach().clone().double().requires_grad_() for t in (I, Wt, Bias))
+    ref = torch.nn.functional.conv2d(I2, W2, B2)
+    (ref * weight.double()).sum().backward()
+    assert_close(out.detach(), ref.detach().float().cpu(), C * kH * kW, what="forward")
+    assert_close(I.grad, I2.grad.float().cpu(), O, what="d_I")
+    assert_close(Wt.grad, W2.grad.float().cpu(), N * H * W, what="d_W1")
+    assert torch.equal(Bias.grad, Bias.detach())  # what the example's biasgrad comprehension computes: a copy
+
+
+def test_batch_reduced_contraction_and_copy_through_the_c_abi(cuda):
+    """C(m,n) = sum_b sum_k A(b,m,k) B(b,n,k) for every contraction tile, against float64; the copy family."""
+    b, M, N, K = 5, 130, 96, 256
+    g = torch.Generator().manual_seed(12)
+    A, B = torch.randn(b, M, K, generator=g), torch.randn(b, N, K, generator=g)
+    ref = torch.einsum("bmk,bnk->mn", A.double(), B.double()).float()
+    from tensorcomprehensions_b200 import cabi
+    from helpers import run_plan
+    p = cabi.contraction_problem(b, M, N, K, True, True, batch_reduce=True)
+    for tile in [None] + cabi.query(p):
+        out, plan = run_plan(p, [A.to(cuda), B.to(cuda)], (M, N), tile)
+        assert "(reduced)" in plan.describe()
+        assert_close(out, ref, b * K, what=plan.describe())
+    init = torch.randn(M, N, generator=g)
+    p = cabi.contraction_problem(b, M, N, K, True, True, batch_reduce=True, accumulate=True, epilogue=cabi.EPI_RELU)
+    out, plan = run_plan(p, [A.to(cuda), B.to(cuda)], (M, N), None, out_init=init.to(cuda))
+    assert_close(out, torch.clamp_min(ref + init, 0), b * K, what=plan.describe())
+    pc = cabi.Problem()
+    pc.family = cabi.FAMILY_COPY
+    pc.red[0] = 1001
+    src = torch.randn(1001, generator=g).to(cuda)
+    out, plan = run_plan(pc, [src], (1001,))
+    assert torch.equal(out, src) and "copy" in plan.describe()
+
+
 def test_accumulating_reduction_keeps_output(cuda):
     """'+=' without '!' adds to what the output holds (test/cuda/test_compile_and_run.cc:181-200)."""
     tcs = "def mm(float(M,K) A, float(K,N) B) -> (C) { C(m,n) += A(m,k) * B(k,n) }"

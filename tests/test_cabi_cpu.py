@@ -69,7 +69,7 @@ def test_query_and_plan_without_gpu():
     tcv = [t for t in cabi.query(c) if t.variant == cabi.VARIANT_TCGEN05_TS][0]
     pt = cabi.Plan(c, tcv)
     assert pt.geometry() == ((148, 1, 1), (448, 1, 1)) and "tcgen05_ts" in pt.describe()  # implicit GEMM
-    band = [t for t in cabi.query(c) if t.variant == cabi.VARIANT_SIMT and t.bk == 0][0]
+    band = [t for t in cabi.query(c) if t.variant == cabi.VARIANT_SIMT and t.bk == 0 and t.stages == 0][0]
     assert cabi.Plan(c, band).geometry()[0][0] == 32 * 32
 
 

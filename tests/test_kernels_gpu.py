@@ -212,6 +212,32 @@ def test_group_conv_accumulate(cuda, bias):
         assert_close(out, ref, C * KH * KW, what=plan.describe())
 
 
+@pytest.mark.parametrize("dims", [
+    (40, 16, 8, 12, 16, 16, 3, 3),    # 640 items: five per CTA, three channel quads, ragged last CTA
+    (37, 17, 4, 4, 16, 16, 1, 3),     # filter height read at run time, 16 output rows, runs that cross a group
+    (32, 32, 16, 16, 16, 16, 3, 3),   # the benchmark shape: seven items per CTA
+])
+def test_group_conv_multi_item_kernel(cuda, dims):
+    """A run of items per CTA (a sweep tile from about four items per SM on): threads numbered densely over
+    (item, channel quad, row), filters of up to two groups per CTA, output through bulk copies."""
+    N, G, C, F, H, W, KH, KW = dims
+    I, W1, B = _rand((N, G, C, H, W), 55, "uniform"), _rand((G, F, C, KH, KW), 56, "uniform"), _rand((G, F), 57)
+    ref = orc.aten_group_conv(I, W1, B)
+    for bias in (True, False):
+        p = cabi.group_conv_problem(*dims, epilogue=cabi.EPI_BIAS if bias else cabi.EPI_NONE)
+        ins = [I.to(cuda), W1.to(cuda)] + ([B.to(cuda)] if bias else [])
+        tiles = [t for t in cabi.query(p) if t.stages == 5]
+        assert len(tiles) == 2, "the multi-item tiles are listed for this many items"
+        out, plan = run_plan(p, ins, ref.shape, tiles[0 if bias else 1])
+        assert "stages=5" in plan.describe(), plan.describe()
+        if bias:
+            assert_close(out, ref, C * KH * KW, [I, W1], STRICT["group_conv"], plan.describe())
+        else:
+            assert_close(out, orc.aten_group_conv(I, W1, None), C * KH * KW, [I, W1], STRICT["group_conv"], plan.describe())
+        out2, _ = run_plan(p, ins, ref.shape, tiles[0 if bias else 1])
+        assert torch.equal(out, out2)
+
+
 def test_group_conv_views_at_a_4_byte_offset(cuda):
     """Dense input / filter tensors that start 4 bytes into a larger buffer: the default (item) kernel
     stages with 16-byte copies, so such a launch must run on a kernel that does not need the alignment."""
