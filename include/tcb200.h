@@ -102,7 +102,9 @@ typedef struct tcb200_tile {
   int32_t bm, bn, bk;  /* CTA tile (contraction); bm = rows of C1 per CTA (tensordot) */
   int32_t stages;      /* TMA pipeline depth (tcgen05) */
   int32_t threads;     /* CTA size */
-  int32_t split_tf32;  /* tcgen05: 1 = one TF32 pass, 3 = 3xTF32 split keeping fp32 accuracy */
+  int32_t split_tf32;  /* tcgen05: 1 = one TF32 pass, 3 = 3xTF32 split keeping fp32 accuracy, 4 = the same with
+                          every accumulator drained after each of its k-blocks (strict accumulation: meets the
+                          reference's checkRtol on all-positive operands too; slower) */
   int32_t split_k;     /* tensor-memory contraction tiles: CTAs that share the reduction of one output tile
                           (0 or 1 = none).  A split contraction keeps S x M x N partial sums in scratch memory
                           owned by the plan and adds them in a fixed order in a second small kernel. */

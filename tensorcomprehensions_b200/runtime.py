@@ -14,7 +14,7 @@ class CompiledWorkload:
         self.options = options
         self.exe = api.compile(w.tc, w.entry, options, *probe)
         self.launches = self.exe.num_launches
-        self.split_tf32 = max(t[6] for t in self.exe.tiles())
+        self.split_tf32 = min(3, max(t[6] for t in self.exe.tiles()))  # 4 = 3xTF32 with strict accumulation
         self.out_shapes = self.exe.output_shapes()
 
     def prepare_outputs(self):

@@ -276,3 +276,30 @@ def test_shard_shapes_get_a_split_by_default(cuda):
     torch.cuda.synchronize()
     ref = torch.clamp_min(A.double() @ B.double().t() + bias.double(), 0).float()
     assert_close(out, ref, 512, [A, B], 3e-7, l3.describe())
+
+
+@pytest.mark.parametrize("case", [
+    # (M, N, K, tile width, pair)
+    (128, 2048, 4096, 112, False),   # the transposed matmul of tc/benchmarks/tmm.cc:63-64 on its own rand() data
+    (128, 2048, 4096, 128, False),
+    (1024, 1024, 2048, 128, True),   # a fully connected layer of tc/benchmarks/MLP_model.cc:524-530 on rand() data
+    (512, 256, 512, 128, True),
+])
+def test_strict_accumulation_tiles_meet_the_reference_bound_on_all_positive_data(cuda, case):
+    """split_tf32 = 4: the accumulators are drained after every k-block.  On U[0,1) operands, where the
+    truncating accumulation of the tensor core has a sign, the result is inside the reference's own
+    checkRtol bound 3e-7 * K * max|input| (test/test_harness_aten.h:36-54), which the default tiles miss at
+    K = 4096 (2.8e-3 against 1.2e-3); the default tiles' error is printed beside it."""
+    M, N, K, bn, pair = case
+    g = torch.Generator().manual_seed(71)
+    A, B = torch.rand((M, K), generator=g), torch.rand((N, K), generator=g)
+    ref = A.double() @ B.double().t()
+    p = cabi.contraction_problem(1, M, N, K, True, True)
+    errs = {}
+    for split in (4, 3):
+        out, plan = run_plan(p, [A.to(cuda), B.to(cuda)], (M, N), tc_tile(bn, split, ts=not pair, pair=pair))
+        assert plan.tile().split_tf32 == split
+        errs[split] = (out.cpu().double() - ref).abs().max().item()
+    bound = 3e-7 * K * 1.0
+    print("K=%d bound %.3e: strict tile %.3e, default tile %.3e" % (K, bound, errs[4], errs[3]))
+    assert errs[4] < bound, (errs, bound)
