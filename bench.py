@@ -118,7 +118,9 @@ def make_config(args):
     names = suite_names(args)
     return {"workload": "tc5_suite" if args.workload == "suite" else args.workload, "configs": names,
             "tiles": "autotuned" if args.tune else "family default", "shard": SHARD_NOTE,
-            "l2": "inputs larger than L2: every comprehension rotates over buffer sets that total >= 192 MB"}
+            "l2": "inputs larger than L2: every comprehension rotates over buffer sets that total >= 192 MB",
+            "launch": "the K timed steps are one CUDA-graph replay (device time); per_config.kernel_us comes from "
+                      "the same steps launched one by one with an event after each comprehension"}
 
 
 def suite_names(args):
@@ -262,23 +264,14 @@ def run_product(args):
         raise SystemExit("bench.py: no CUDA device (the product path has no CPU fallback)")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    # stdout carries the one JSON line and nothing else.  Libraries print there too (NCCL writes its version
+    # banner to stdout when a communicator comes up, at a moment of its choosing): file descriptor 1 points at
+    # stderr for the whole run and the line is written to the saved descriptor at the end.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     if world > 1:
-        # NCCL prints its version banner on stdout when the communicator comes up (NCCL_DEBUG=VERSION, which
-        # some launchers export): stdout carries the one JSON line only, so file descriptor 1 points at
-        # stderr until the first collective has run
-        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"
-        sys.stdout.flush()
-        saved = os.dup(1)
-        os.dup2(2, 1)
-        try:
-            dist.init_process_group("nccl", device_id=dev)
-            dist.barrier()
-            torch.cuda.synchronize()
-        finally:
-            sys.stdout.flush()
-            os.dup2(saved, 1)
-            os.close(saved)
+        dist.init_process_group("nccl", device_id=dev)
     peaks = load_peaks()
 
     names = suite_names(args)
@@ -306,26 +299,55 @@ def run_product(args):
         return over_ranks(values, dist.ReduceOp.SUM if world > 1 else None)
 
     # ---- timed region 1: device-resident inputs ----------------------------------------------
+    # The K timed steps are ONE CUDA-graph replay: the launches of K consecutive steps (each step takes the next
+    # buffer set of every comprehension) are captured once and replayed, so that the step time is device time.
+    # Launched one by one through Python the small shards of a multi-GPU run (kernels of 4-15 us) would be
+    # timed at the host's launch rate.  A first replay is the warm-up of the graph itself.
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()   # sampled from the warm-up to the end of the host-buffer region
     for _ in range(args.warmup):
         for p in progs:
             p.run()
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(progs) + 1)] for _ in range(args.steps)]
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for p in progs:
+            p.cursor = 0
+        graph = torch.cuda.CUDAGraph()
+        # thread-local capture mode: other threads of the process (NCCL's watchdog at N > 1) keep their CUDA calls
+        with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+            for _ in range(args.steps):
+                for p in progs:
+                    p.run()
+        graph.replay()
+        stream.synchronize()
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        graph.replay()
+        g1.record()
+        stream.synchronize()
+        barrier()
+    total_ms = max_over_ranks([g0.elapsed_time(g1)])[0]
+    ms_per_step = total_ms / args.steps
+    del graph
+
+    # ---- the same steps launched one by one, with an event after every comprehension: the per-comprehension
+    # split of a step (inflated by the host's launch rate where a kernel is shorter than a launch) ----------
+    eager_steps = max(3, min(args.steps, 20))
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(progs) + 1)] for _ in range(eager_steps)]
     barrier()
-    for s in range(args.steps):
+    for s in range(eager_steps):
         ev[s][0].record()
         for i, p in enumerate(progs):
             p.run()
             ev[s][i + 1].record()
     barrier()
-    total_ms = ev[0][0].elapsed_time(ev[-1][-1])
-    per_prog_us = [statistics.mean(ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(args.steps)) * 1e3
+    eager_ms_per_step = max_over_ranks([ev[0][0].elapsed_time(ev[-1][-1]) / eager_steps])[0]
+    per_prog_us = [statistics.mean(ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(eager_steps)) * 1e3
                    for i in range(len(progs))]
-    total_ms = max_over_ranks([total_ms])[0]
     per_prog_us = max_over_ranks(per_prog_us)
-    ms_per_step = total_ms / args.steps
 
     # ---- per-config windows: R back-to-back launches over the rotating sets in ONE event pair --------
     # (the reference's benchmark fixture times a kernel this way; a CUDA graph replays the launches so
@@ -459,6 +481,7 @@ def run_product(args):
     line = {
         "metric": METRIC, "value": round(flops_step / (ms_per_step * 1e-3) / 1e12, 3), "unit": UNIT,
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
+        "ms_per_step_launched_one_by_one": round(eager_ms_per_step, 4),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": make_config(args),
         "e2e": {"value": round(flops_step / (e2e_ms * 1e-3) / 1e12, 3), "unit": UNIT,
@@ -471,7 +494,7 @@ def run_product(args):
         line["reductions"] = reductions
     if cpu:
         line["cpu_baseline"] = cpu
-    print(json.dumps(line), flush=True)
+    os.write(json_fd, (json.dumps(line) + "\n").encode())
     if world > 1:
         dist.destroy_process_group()
 

@@ -58,7 +58,6 @@ struct TcArgs {
   int a_batched, b_batched;  // 0: operand shared by all batch entries
   int c_vec;                 // 128-bit stores allowed
   int tma_store;             // pair kernel: epilogue through the staging tile and tiled TMA stores
-  int chunk_kb;              // TS and pair kernels: own k-blocks of an issuer between two drains of its accumulator
   int ksplit_kb;             // split-K launch (TS and pair kernels): k-blocks per split, the "batch" index is the
                              // split and selects the k range, not an operand slab; 0 = the whole reduction
   int* dev_status;
@@ -406,7 +405,7 @@ __host__ __device__ constexpr int ts_smem_bytes(int bn) {
 // keeps the tensor pipe busy.
 constexpr int kTsThreads = 608;
 
-template <int BN>
+template <int BN, int CHUNK>
 __global__ void __launch_bounds__(kTsThreads, 1)
 contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
                       const __grid_constant__ CUtensorMap tmB, TcArgs a) {
@@ -428,6 +427,7 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
   static_assert(B_SLOTS >= 2 && B_SLOTS <= 8 && A_SLOTS <= 4 && P_SLOTS == 4, "barrier arrays / TMEM ring sizes");
   static_assert(A_SLOTS % 2 == 0 && B_SLOTS % 2 == 0 && P_SLOTS % 2 == 0, "a slot must stay with one set");
   static_assert(B_BYTES % 1024 == 0, "128-byte swizzle atoms must stay 1024-byte aligned");
+  static_assert((kTsChunkKB & (kTsChunkKB - 1)) == 0 && (kPairChunkKB & (kPairChunkKB - 1)) == 0, "chunk lengths are powers of two");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -483,9 +483,10 @@ contraction_ts_kernel(const __grid_constant__ CUtensorMap tmA,
     const int f = own_first(it0, i);
     return num_kb > f ? (num_kb - f + 1) / 2 : 0;
   };
-  const int chunk_kb = a.chunk_kb;  // kTsChunkKB, or 1 for the strict-accumulation tiles
-  auto closes_chunk = [chunk_kb](int j, int count, int i) {
-    return j == count - 1 || (j + 1 + (i ? chunk_kb / 2 : 0)) % chunk_kb == 0;
+  // chunk length CHUNK: kTsChunkKB, or 1 for the strict-accumulation tiles (a compile-time constant: the test sits
+  // on the single issuing thread's critical path)
+  auto closes_chunk = [](int j, int count, int i) {
+    return j == count - 1 || (j + 1 + (i ? CHUNK / 2 : 0)) % CHUNK == 0;
   };
 
   // Static persistent schedule: tile t -> (batch, m-tile, n-tile) with n fastest, so the CTAs that
@@ -763,6 +764,7 @@ __host__ __device__ constexpr int ts_pair_out_offset() { return (ts_pair_rings_b
 __host__ __device__ constexpr int ts_pair_smem_bytes() { return ts_pair_out_offset() + kPairOutBytes + 1024; }
 static_assert(ts_pair_smem_bytes() <= kTsSmemLimit, "rings + output staging tile exceed shared memory");
 
+template <int CHUNK>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTsThreads, 1)
 contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
                            const __grid_constant__ CUtensorMap tmB,
@@ -847,9 +849,10 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     const int f = own_first(it0, i);
     return num_kb > f ? (num_kb - f + 1) / 2 : 0;
   };
-  const int chunk_kb = a.chunk_kb;  // kPairChunkKB, or 1 for the strict-accumulation tiles
-  auto closes_chunk = [chunk_kb](int j, int count, int i) {
-    return j == count - 1 || (j + 1 + (i ? chunk_kb / 2 : 0)) % chunk_kb == 0;
+  // chunk length CHUNK: kPairChunkKB, or 1 for the strict-accumulation tiles (a compile-time constant: the test
+  // sits on the single issuing thread's critical path)
+  auto closes_chunk = [](int j, int count, int i) {
+    return j == count - 1 || (j + 1 + (i ? CHUNK / 2 : 0)) % CHUNK == 0;
   };
 
   // Static persistent schedule: tile t -> (batch, m-tile, n-tile) with n fastest, so the CTAs that
@@ -1233,35 +1236,47 @@ int launch_inst(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, 
   return TCB200_OK;
 }
 
-template <int BN>
+template <int BN, int CHUNK>
 int launch_ts(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const TcArgs& args,
               cudaStream_t s) {
   static std::atomic<uint64_t> configured{0};  // bit per device
   const uint64_t bit = 1ull << (plan.device & 63);
   if (!(configured.load(std::memory_order_acquire) & bit)) {
-    TCB200_CUDA_TRY(cudaFuncSetAttribute(contraction_ts_kernel<BN>,
+    TCB200_CUDA_TRY(cudaFuncSetAttribute(contraction_ts_kernel<BN, CHUNK>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          ts_smem_bytes(BN)));
     configured.fetch_or(bit, std::memory_order_release);
   }
-  TCB200_CUDA_TRY(launch_pdl(contraction_ts_kernel<BN>, plan.launch.grid, dim3(kTsThreads, 1, 1),
+  TCB200_CUDA_TRY(launch_pdl(contraction_ts_kernel<BN, CHUNK>, plan.launch.grid, dim3(kTsThreads, 1, 1),
                              (size_t)ts_smem_bytes(BN), s, ta, tb, args));
   return TCB200_OK;
 }
+// strict: the accumulators are drained after every k-block (tile.split_tf32 == 4)
+template <int BN>
+int launch_ts(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const TcArgs& args, cudaStream_t s) {
+  return plan.tile.split_tf32 == 4 ? launch_ts<BN, 1>(plan, ta, tb, args, s)
+                                   : launch_ts<BN, kTsChunkKB>(plan, ta, tb, args, s);
+}
 
-int launch_pair(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
-                const TcArgs& args, cudaStream_t s) {
+template <int CHUNK>
+int launch_pair_chunk(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                      const TcArgs& args, cudaStream_t s) {
   static std::atomic<uint64_t> configured{0};  // bit per device
   const uint64_t bit = 1ull << (plan.device & 63);
   if (!(configured.load(std::memory_order_acquire) & bit)) {
-    TCB200_CUDA_TRY(cudaFuncSetAttribute(contraction_ts_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    TCB200_CUDA_TRY(cudaFuncSetAttribute(contraction_ts_pair_kernel<CHUNK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          ts_pair_smem_bytes()));
     configured.fetch_or(bit, std::memory_order_release);
   }
   // the kernel carries its cluster shape (2 CTAs); the grid is a multiple of 2
-  TCB200_CUDA_TRY(launch_pdl(contraction_ts_pair_kernel, plan.launch.grid, dim3(kTsThreads, 1, 1),
+  TCB200_CUDA_TRY(launch_pdl(contraction_ts_pair_kernel<CHUNK>, plan.launch.grid, dim3(kTsThreads, 1, 1),
                              (size_t)ts_pair_smem_bytes(), s, ta, tb, tc, args));
   return TCB200_OK;
+}
+int launch_pair(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                const TcArgs& args, cudaStream_t s) {
+  return plan.tile.split_tf32 == 4 ? launch_pair_chunk<1>(plan, ta, tb, tc, args, s)
+                                   : launch_pair_chunk<kPairChunkKB>(plan, ta, tb, tc, args, s);
 }
 
 }  // namespace
@@ -1455,7 +1470,6 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
   a.a_batched = S == 1 && p.batch > 1 && p.stride_a > 0;
   a.b_batched = S == 1 && p.batch > 1 && p.stride_b > 0;
   a.ksplit_kb = S > 1 ? (int)ceil_div(ceil_div(p.K, BK), S) : 0;
-  a.chunk_kb = plan.tile.split_tf32 == 4 ? 1 : (pair ? kPairChunkKB : kTsChunkKB);
   const bool bias_vec = !a.bias || p.bias_on_m || ((uintptr_t)a.bias & 15) == 0;
   a.c_vec = ((uintptr_t)Ck & 15) == 0 && ldck % 4 == 0 && stride_ck % 4 == 0 && bias_vec;
   a.dev_status = dev_status;
