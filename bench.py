@@ -277,7 +277,12 @@ def run_product(args):
     names = suite_names(args)
     if world > 1 and any(n not in wl.ALL for n in names):
         raise SystemExit("bench.py: %s is a single-GPU workload" % args.workload)
-    progs = [Program(n, world, rank, dev, rotate_bytes=192 << 20, tune=args.tune) for n in names]
+    # --shard-of W (one GPU only): run rank 0's shard of a W-GPU run, e.g. to profile the kernels a shard uses
+    shard_world = args.shard_of if (world == 1 and args.shard_of > 1) else world
+    progs = [Program(n, shard_world, rank, dev, rotate_bytes=192 << 20, tune=args.tune) for n in names]
+    if shard_world != world:
+        for p in progs:
+            p.full = p.w   # the shard is the whole job of this run
     launches_per_step = sum(p.launches_per_run for p in progs)
 
     def barrier():
@@ -483,7 +488,7 @@ def run_product(args):
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
         "ms_per_step_launched_one_by_one": round(eager_ms_per_step, 4),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": make_config(args),
+        "data": "synthetic", "config": dict(make_config(args), **({"shard_of": shard_world} if shard_world != world else {})),
         "e2e": {"value": round(flops_step / (e2e_ms * 1e-3) / 1e12, 3), "unit": UNIT,
                 "ms_per_step": round(e2e_ms, 3),
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
@@ -582,6 +587,8 @@ def main():
                     choices=["suite", "tensordot", "batchmatmul", "tmm", "group_conv", "mlp3", "sum1d", "sum2d", "colsum"])
     ap.add_argument("--cpu-seconds", type=float, default=20.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--shard-of", type=int, default=1,
+                    help="on one GPU: run rank 0's shard of a run on this many GPUs (profiling aid; not a bench line)")
     ap.add_argument("--no-reductions", action="store_true",
                     help="skip the stand-alone timing of the three reduction workloads (one GPU, suite only)")
     ap.add_argument("--tune", action="store_true",

@@ -66,10 +66,19 @@ def build_reference_lang(reference, verbose=False):
     return out
 
 
+def reference_checkout():
+    """Where the reference's sources lie: $TC_REFERENCE, else a directory `reference` next to this repository.
+    None when neither exists (then only the golden files pin the front-end)."""
+    for cand in (os.environ.get("TC_REFERENCE"), os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "tc", "lang")):
+            return cand
+    return None
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", action="store_true")
-    ap.add_argument("--reference", default=os.environ.get("TC_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=reference_checkout() or "")
     a = ap.parse_args()
     build_oracle(verbose=True)
     if a.ref:

@@ -20,11 +20,12 @@
  * double (used only to budget the rounding error of the float flavours).
  *
  * Parity status: the reference holds no numeric golden vector for this path
- * (its numeric tests are randomised comparisons against ATen); the structural
- * known answers above pin the loop order, and tests/golden holds outputs of
- * ATen-CPU (the library the reference's own harness compares against,
- * tc/benchmarks/batchmatmul.cc:67, tmm.cc:66, MLP_model.cc:537-541,
- * group_convolution.cc:83-101) that this file is checked against.
+ * (its numeric tests are randomised comparisons against ATen), so none is stored
+ * here either: tests/golden holds only front-end trees.  The structural known
+ * answers above pin the loop order, and tests/test_oracle_cpu.py compares these
+ * nests, live, with ATen-CPU (the library the reference's own harness compares
+ * against: tc/benchmarks/batchmatmul.cc:67, tmm.cc:66, MLP_model.cc:537-541,
+ * group_convolution.cc:83-101) on the seeded inputs of every benchmark.
  */
 #include <stddef.h>
 #include <stdint.h>

@@ -87,3 +87,25 @@ def test_static_scratch_refuses_what_does_not_fit(cuda):
     assert e.value.status == -1
     torch.cuda.synchronize()
     assert bool((out == 7.0).all())
+
+
+def test_static_scratch_launch_takes_no_device_memory(cuda):
+    """The reason the entry point exists: a plan that has never gone through the allocating launch runs
+    through the static one without the device's free memory moving.  (One earlier call of the entry point,
+    with another plan, has loaded the kernels and looked the array up: what the driver takes for code when a
+    module is first used is not this call's doing.)"""
+    warm_dims = (1, 300000, 1)
+    warm = cabi.Plan(cabi.reduction_problem(*warm_dims))
+    warm.launch_static(_rand(warm_dims, 599).to(cuda), torch.empty((1, 1), device=cuda))
+    dims = (1, 2500000, 1)
+    I = _rand(dims, 600).to(cuda)
+    out = torch.full((1, 1), float("nan"), device=cuda)
+    plan = cabi.Plan(cabi.reduction_problem(*dims))
+    assert plan.geometry()[0][1] > 1
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(2):
+        plan.launch_static(I, out)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert_close(out, orc.loop_reduce(I.cpu(), double=True), dims[1], [I.cpu()], 5e-7, plan.describe())
