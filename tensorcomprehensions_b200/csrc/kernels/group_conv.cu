@@ -359,6 +359,128 @@ __global__ void __launch_bounds__(256 / FPT) group_conv_item_kernel(ConvArgs a) 
 }
 
 // ------------------------------------------------------------------------------------------------
+// item kernel, channels split over four thread groups: for launches with about one item per SM or fewer
+// ------------------------------------------------------------------------------------------------
+// With few items (the 4-image shard of an 8-GPU run has 128) every SM holds one CTA of the item kernel: four
+// warps that each run the 48 (channel, filter row) steps of their thread tile one after the other, with nothing
+// to hide the shared-memory latency of a step behind: 12.9 us for 128 items, against 26 us for 1024.  Here an
+// item gets 512 threads: four groups of 128 with the item kernel's thread tile (one output row x two output
+// channels), group q taking channels [q C/4, (q+1) C/4) -- exactly the quarter of the input planes that the q-th
+// cp.async group brings in.  The four partial tiles are added through shared memory in the fixed order
+// q = 0, 1, 2, 3 (the same bits on every run), with bias, and leave in 128-bit coalesced stores.
+constexpr int kSplitGroups = 4;
+template <int KHT>
+__global__ void __launch_bounds__(128 * kSplitGroups) group_conv_item_split_kernel(ConvArgs a) {
+  extern __shared__ __align__(16) float smem[];
+  pdl_sync();  // launched as a programmatic dependent: wait for the preceding kernel before any global access
+  const int item = blockIdx.x;  // n * G + g
+  const int g = item % a.G;
+  const int taps = a.C * a.KH * a.KW;
+  const int F = a.F;
+  const int wp = taps + 4;                // filters in their global (f, tap) order, rows padded (see the item kernel)
+  float* Ws = smem;                       // [F][wp]
+  float* Is = smem + (size_t)F * wp;      // [C][H][kRowsPitch]
+  const int out_elems = F * a.OH * a.OW;
+  float* Ps = Is + (size_t)a.C * a.H * kRowsPitch;  // [kSplitGroups][out_elems] partial tiles
+  const int tid = threadIdx.x, nt = 128 * kSplitGroups;
+  const int q = tid >> 7, t = tid & 127;  // channel quarter of this thread's group, thread within the group
+
+  const float* Wg = a.W + (size_t)g * F * taps;
+  const int tq = taps >> 2;
+  for (int i = tid; i < F * tq; i += nt) {
+    const int f = i / tq, piece = i - f * tq;
+    cp_async_16(Ws + (size_t)f * wp + 4 * piece, Wg + (size_t)f * taps + 4 * piece);
+  }
+  const float* Ig = a.I + (size_t)item * a.C * a.H * a.Wd;
+  const int rows = a.C * a.H;
+  for (int i = tid; i < rows * 4; i += nt)  // four 16-byte pieces per row of 16 floats
+    cp_async_16(Is + (size_t)(i >> 2) * kRowsPitch + 4 * (i & 3), Ig + (size_t)(i >> 2) * 16 + 4 * (i & 3));
+
+  const int FQ = F / 2;
+  const int hslots = (a.OH + 7) & ~7;
+  const int fq_t = t / hslots, h_t = t - fq_t * hslots;
+  const bool active = fq_t < FQ && h_t < a.OH;
+  const int fq = active ? fq_t : 0, h = active ? h_t : 0;
+  float2 acc[kItemOW];
+#pragma unroll
+  for (int w = 0; w < kItemOW; ++w) acc[w] = make_float2(0.f, 0.f);
+  const int KH = KHT > 0 ? KHT : a.KH;
+  const int KW = KHT > 0 ? kItemKW : a.KW;
+  const int plane_step = (a.H - KH) * kRowsPitch;
+  cp_async_wait_all();
+  __syncthreads();
+  if (active) {
+    const int cq = a.C / kSplitGroups, c0 = q * cq;
+    const float* rp = Is + (c0 * a.H + h) * kRowsPitch;
+    const float* wrow = Ws + (size_t)(fq * 2) * wp + c0 * KH * KW;
+    for (int c = c0; c < c0 + cq; ++c, rp += plane_step) {
+#pragma unroll
+      for (int kh = 0; kh < KH; ++kh, rp += kRowsPitch, wrow += KW) {
+        const float4* row = reinterpret_cast<const float4*>(rp);
+        float x[16];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float4 v = row[k];
+          x[4 * k] = v.x; x[4 * k + 1] = v.y; x[4 * k + 2] = v.z; x[4 * k + 3] = v.w;
+        }
+#pragma unroll
+        for (int kw = 0; kw < kItemKW; ++kw) {
+          if (kw < KW) {
+            const float2 wv = make_float2(wrow[kw], wrow[wp + kw]);
+#pragma unroll
+            for (int w = 0; w < kItemOW; ++w) acc[w] = __ffma2_rn(make_float2(x[w + kw], x[w + kw]), wv, acc[w]);
+          }
+        }
+      }
+    }
+    // this group's partial tile, dense (f, oh, ow)
+    float* o0 = Ps + (size_t)q * out_elems + ((size_t)(fq * 2) * a.OH + h) * a.OW;
+    float* o1 = o0 + (size_t)a.OH * a.OW;
+#pragma unroll
+    for (int w = 0; w < kItemOW; ++w)
+      if (w < a.OW) { o0[w] = acc[w].x; o1[w] = acc[w].y; }
+  }
+  __syncthreads();
+  const bool has_bias = a.epi == TCB200_EPI_BIAS || a.epi == TCB200_EPI_BIAS_RELU;
+  const int per_f = a.OH * a.OW;
+  float* Og = a.O + (size_t)item * out_elems;
+  if ((out_elems & 3) == 0 && (per_f & 3) == 0 && (((uintptr_t)a.O) & 15) == 0) {
+    for (int i = tid; i < out_elems / 4; i += nt) {
+      float4 v = reinterpret_cast<const float4*>(Ps)[i];
+#pragma unroll
+      for (int k = 1; k < kSplitGroups; ++k) {
+        const float4 u = reinterpret_cast<const float4*>(Ps + (size_t)k * out_elems)[i];
+        v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+      }
+      const float bias = has_bias ? __ldg(a.bias + g * F + (4 * i) / per_f) : 0.f;  // four outputs of one channel
+      float4* dst = reinterpret_cast<float4*>(Og) + i;
+      if (a.accumulate) {
+        const float4 old = *dst;
+        v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+      }
+      v.x = apply_epilogue_rt(a.epi, v.x, bias); v.y = apply_epilogue_rt(a.epi, v.y, bias);
+      v.z = apply_epilogue_rt(a.epi, v.z, bias); v.w = apply_epilogue_rt(a.epi, v.w, bias);
+      *dst = v;
+    }
+  } else {
+    for (int i = tid; i < out_elems; i += nt) {
+      float v = Ps[i];
+#pragma unroll
+      for (int k = 1; k < kSplitGroups; ++k) v += Ps[(size_t)k * out_elems + i];
+      const float bias = has_bias ? __ldg(a.bias + g * F + i / per_f) : 0.f;
+      if (a.accumulate) v += Og[i];
+      Og[i] = apply_epilogue_rt(a.epi, v, bias);
+    }
+  }
+}
+
+size_t item_split_smem(const tcb200_problem_t& p) {
+  const int64_t C = p.conv[2], F = p.conv[3], H = p.conv[4], KH = p.conv[6], KW = p.conv[7];
+  const int64_t OH = H - KH + 1, OW = p.conv[5] - KW + 1;
+  return sizeof(float) * (size_t)((C * KH * KW + 4) * F + C * H * kRowsPitch + kSplitGroups * F * OH * OW);
+}
+
+// ------------------------------------------------------------------------------------------------
 // multi-item kernel: one CTA per SM-sized run of items, W = 16 in registers, OW <= 14, KW <= 3
 // ------------------------------------------------------------------------------------------------
 // What the item kernel's profile asked for (FMA pipe 63 % busy; shared memory at 60 % of its wavefront rate, i.e.
@@ -547,6 +669,12 @@ bool item_ok(const tcb200_problem_t& p) {
          sizeof(float) * (size_t)((C * KH * KW + 4) * F + C * H * kRowsPitch) <= 48 * 1024;
 }
 
+// the channel-split form of the item kernel: the item kernel's two-channel tile must fit 128 threads
+bool item_split_ok(const tcb200_problem_t& p) {
+  return item_ok(p) && item_two_threads(p) <= 128 && p.conv[2] % (4 * kSplitGroups) == 0 &&
+         item_split_smem(p) <= 160 * 1024;
+}
+
 int multi_threads(const tcb200_problem_t& p, int ipc) {
   return (int)round_up((int64_t)ipc * (p.conv[3] / 4) * (p.conv[4] - p.conv[6] + 1), 32);
 }
@@ -634,6 +762,11 @@ int group_conv_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int
     if (cnt < max && out) out[cnt] = tcb200_tile_t{TCB200_VARIANT_SIMT, 1, 4, 0, 5, 0, 0};
     ++cnt;
   }
+  // stages = 6: one item per CTA of 512 threads, the channels split over four thread groups (few items)
+  if (item_split_ok(p)) {
+    if (cnt < max && out) out[cnt] = tcb200_tile_t{TCB200_VARIANT_SIMT, 0, 2, 1, 6, 128 * kSplitGroups, 0};
+    ++cnt;
+  }
   if (rows_ok(p)) {
     // bk = n per CTA of the rows kernel
     const int ns[] = {2, 1, 4};
@@ -674,9 +807,20 @@ int group_conv_plan(Plan& plan) {
       t.bk = 1; t.stages = 4;
       // more warps in flight per item when the item has the work for them
       t.threads = item_two_threads(p) > kItemThreads && item_two_threads(p) <= 128 ? 128 : kItemThreads;
+      // about one item per SM or fewer: more threads per item (channel split) instead of more items per SM
+      if (item_split_ok(p) && p.conv[0] * p.conv[1] <= 2 * (int64_t)plan.sms) { t.stages = 6; t.threads = 128 * kSplitGroups; }
     }
   }
   if (t.variant != TCB200_VARIANT_SIMT) return TCB200_ERR_UNSUPPORTED;
+  if (t.stages == 6) {  // item kernel, channels split over four thread groups
+    if (!item_split_ok(p)) return TCB200_ERR_UNSUPPORTED;
+    t.bm = 0; t.bn = 2; t.bk = 1; t.threads = 128 * kSplitGroups;
+    plan.launch.grid = dim3((unsigned)(p.conv[0] * p.conv[1]), 1, 1);
+    plan.launch.block = dim3(t.threads, 1, 1);
+    plan.launch.smem = item_split_smem(p);
+    plan.kernel_id = 105;
+    return TCB200_OK;
+  }
   if (t.stages == 5) {  // multi-item kernel
     const int ipc = multi_ipc(p, plan.sms);
     if (ipc == 0) return TCB200_ERR_UNSUPPORTED;
@@ -750,8 +894,16 @@ int group_conv_launch(const Plan& plan, const float* I, const float* W, const fl
   // The item kernel stages I and W with 16-byte asynchronous copies.  A dense tensor may still start at any
   // 4-byte offset of a larger buffer (a view): such a launch runs on the band kernel, which uses 4-byte loads.
   const bool multi = plan.kernel_id == 103 || plan.kernel_id == 104;
-  const bool item_misaligned = (plan.kernel_id == 101 || plan.kernel_id == 102 || multi) &&
+  const bool item_misaligned = (plan.kernel_id == 101 || plan.kernel_id == 102 || plan.kernel_id == 105 || multi) &&
                                ((((uintptr_t)I) | ((uintptr_t)W)) & 15) != 0;
+  if (plan.kernel_id == 105 && !item_misaligned) {
+    const bool k33 = a.KH == 3 && a.KW == 3;
+    auto fn = k33 ? group_conv_item_split_kernel<3> : group_conv_item_split_kernel<0>;
+    static std::atomic<uint64_t> split_configured[2];
+    TCB200_CUDA_TRY(ensure_dynamic_smem(fn, 160 * 1024, plan.device, split_configured[k33]));
+    TCB200_CUDA_TRY(launch_pdl(fn, plan.launch.grid, plan.launch.block, plan.launch.smem, s, a));
+    return TCB200_OK;
+  }
   if (multi && !item_misaligned) {
     const bool k33 = a.KH == 3 && a.KW == 3, packed = plan.kernel_id == 103;
     auto fn = k33 ? (packed ? group_conv_multi_kernel<3, true> : group_conv_multi_kernel<3, false>)
