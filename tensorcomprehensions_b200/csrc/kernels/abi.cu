@@ -368,7 +368,8 @@ int tcb200_plan_describe(const tcb200_plan_t* plan, char* buf, size_t buflen) {
       break;
   }
   char split[32] = "";
-  if (t.split_k > 1) snprintf(split, sizeof(split), " split_k=%d", t.split_k);
+  if (t.split_k > 100) snprintf(split, sizeof(split), " tail_split=%d", t.split_k - 100);
+  else if (t.split_k > 1) snprintf(split, sizeof(split), " split_k=%d", t.split_k);
   snprintf(buf, buflen,
            "%s | variant=%s tile=%dx%dx%d stages=%d threads=%d split_tf32=%d%s | grid=(%u,%u,%u) "
            "block=(%u,%u,%u) smem=%zu",

@@ -123,6 +123,10 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
 // C = epilogue([C +] sum_s P[s]) over S dense planes P[s][M][N] of partial sums (splitk.cu)
 int partial_planes_reduce(const float* P, float* C, const float* bias, int M, int N, int S, int64_t ldc, int epi,
                           int bias_on_m, int accumulate, int sms, cudaStream_t s);
+// the same for the split tail of a CTA-pair launch: tail tile j = output tile tile0 + j (256 x 128, column tiles
+// fastest), its S partial tiles dense at P[(s * tail_tiles + j) * 256 * 128]
+int tail_tiles_reduce(const float* P, float* C, const float* bias, int M, int N, int S, int tail_tiles, int tile0,
+                      int64_t ldc, int epi, int bias_on_m, int accumulate, cudaStream_t s);
 constexpr int kTcMapSlots = 8;
 void* tc_map_cache_new();
 void tc_map_cache_delete(void* cache);

@@ -58,6 +58,8 @@ struct TcArgs {
   int a_batched, b_batched;  // 0: operand shared by all batch entries
   int c_vec;                 // 128-bit stores allowed
   int tma_store;             // pair kernel: epilogue through the staging tile and tiled TMA stores
+  int tail_S, tail_tiles, tail_kb;  // pair kernel: the last tail_tiles tiles split tail_S ways, tail_kb k-blocks each
+                                    // (tail_S = 0: none)
   int ksplit_kb;             // split-K launch (TS and pair kernels): k-blocks per split, the "batch" index is the
                              // split and selects the k range, not an operand slab; 0 = the whole reduction
   int* dev_status;
@@ -768,7 +770,8 @@ template <int CHUNK>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTsThreads, 1)
 contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
                            const __grid_constant__ CUtensorMap tmB,
-                           const __grid_constant__ CUtensorMap tmC, TcArgs a) {
+                           const __grid_constant__ CUtensorMap tmC,
+                           const __grid_constant__ CUtensorMap tmP, TcArgs a) {
   constexpr int BN = kPairBN;
   constexpr int A_SLOTS = kTsASlots, P_SLOTS = kTsPSlots, B_SLOTS = kPairBSlots;
   constexpr int A_BYTES = BM * BK * 4;
@@ -810,7 +813,17 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   // split-K: every split runs the same number of k-blocks; those past the end of K read zeros (TMA fill)
   const int num_kb = a.ksplit_kb > 0 ? a.ksplit_kb : (a.K + BK - 1) / BK;
   const int tiles_n = (a.N + BN - 1) / BN, tiles_m = (a.M + 2 * BM - 1) / (2 * BM);
-  const int64_t num_tiles = (int64_t)tiles_n * tiles_m * a.batch;  // tiles of 256 x BN, one per pair
+  // Work units, one per pair at a time.  Units [0, main_units) are whole tiles (in a split-K launch: (tile, split)
+  // pairs, the split being the "batch" index).  A launch whose tiles do not fill its last wave ends with a TAIL:
+  // the last tail_tiles tiles have their reduction split tail_S ways, unit main_units + s * tail_tiles + j being
+  // split s of tail tile j.  A tail unit runs tail_kb k-blocks and leaves a raw partial tile in scratch memory
+  // (tile number = its index in the tail, through the map tmP); a second kernel adds the splits and applies the
+  // epilogue.  256 tiles on 74 pairs are then 3 rounds of whole tiles and one round of half-length units
+  // instead of 4 rounds.
+  const int64_t all_tiles = (int64_t)tiles_n * tiles_m * a.batch;  // tiles of 256 x BN
+  const int64_t main_units = a.tail_S > 0 ? all_tiles - a.tail_tiles : all_tiles;
+  const int64_t num_tiles = main_units + (a.tail_S > 0 ? (int64_t)a.tail_tiles * a.tail_S : 0);  // units
+  auto unit_kb = [&](int64_t t) { return t < main_units ? num_kb : a.tail_kb; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < 4; ++s) {
@@ -845,9 +858,9 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   // j = 0 .. count-1; own k-block j closes a chunk when (j + 1 + skew) % kPairChunkKB == 0 (skew 0 for
   // issuer 0, kPairChunkKB / 2 for issuer 1) or when it is the issuer's last k-block of the tile.
   auto own_first = [](uint32_t it0, int i) { return (int)((it0 ^ (uint32_t)i) & 1u); };
-  auto own_count = [&](uint32_t it0, int i) {
+  auto own_count = [&](uint32_t it0, int i, int nkb) {
     const int f = own_first(it0, i);
-    return num_kb > f ? (num_kb - f + 1) / 2 : 0;
+    return nkb > f ? (nkb - f + 1) / 2 : 0;
   };
   // chunk length CHUNK: kPairChunkKB, or 1 for the strict-accumulation tiles (a compile-time constant: the test
   // sits on the single issuing thread's critical path)
@@ -857,10 +870,22 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
 
   // Static persistent schedule: tile t -> (batch, m-tile, n-tile) with n fastest, so the CTAs that
   // run at the same time share rows of A (L2 hits) while B tiles differ.
-  auto tile_coords = [&](int64_t t, int* m0, int* n0, int* bz) {
-    *n0 = (int)(t % tiles_n) * BN;
-    *m0 = (int)((t / tiles_n) % tiles_m) * (2 * BM) + (int)rank * BM;  // this CTA's 128 rows
-    *bz = (int)(t / ((int64_t)tiles_n * tiles_m));
+  // slot: -1 for a unit that writes the output, else the number of the partial tile a tail unit writes;
+  // k0: first k of the unit
+  auto tile_coords = [&](int64_t t, int* m0, int* n0, int* bz, int* k0, int* slot) {
+    int64_t tile = t;
+    *slot = -1;
+    *k0 = 0;
+    if (t >= main_units) {
+      const int64_t r = t - main_units;
+      tile = main_units + r % a.tail_tiles;
+      *k0 = (int)(r / a.tail_tiles) * a.tail_kb * BK;
+      *slot = (int)r;
+    }
+    *n0 = (int)(tile % tiles_n) * BN;
+    *m0 = (int)((tile / tiles_n) % tiles_m) * (2 * BM) + (int)rank * BM;  // this CTA's 128 rows
+    *bz = (int)(tile / ((int64_t)tiles_n * tiles_m));
+    if (*slot < 0 && a.ksplit_kb > 0) *k0 = *bz * a.ksplit_kb * BK;  // split-K launch: the batch index is the split
   };
 
   if (warp == 0) {
@@ -868,12 +893,12 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     if (lane == 0) {
       uint32_t it = 0;
       for (int64_t t = pair; t < num_tiles; t += num_pairs) {
-        int m0, n0, bz;
-        tile_coords(t, &m0, &n0, &bz);
+        int m0, n0, bz, k0, slot;
+        tile_coords(t, &m0, &n0, &bz, &k0, &slot);
         const int za = a.a_batched ? bz : 0, zb = a.b_batched ? bz : 0;
-        const int k0 = a.ksplit_kb > 0 ? bz * a.ksplit_kb * BK : 0;  // first k of this split
+        const int nkb = unit_kb(t);
         bool ok = true;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int sa = it % A_SLOTS, sb = it % B_SLOTS;
           ok = mbar_wait(&empty_a[sa], ((it / A_SLOTS) & 1) ^ 1, 1, a.dev_status, abort_flag);
           if (!ok) break;
@@ -894,8 +919,10 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       uint32_t it0 = 0, cc = 0;  // running k-block number at the start of the tile; chunks of this issuer
       bool ok = true;
       const uint32_t tmem_d = tmem_base + issuer * ACC_STRIDE;
-      for (int64_t t = pair; t < num_tiles && ok; t += num_pairs, it0 += (uint32_t)num_kb) {
-        const int first = own_first(it0, issuer), count = own_count(it0, issuer);
+      int nkb = 0;
+      for (int64_t t = pair; t < num_tiles && ok; t += num_pairs, it0 += (uint32_t)nkb) {
+        nkb = unit_kb(t);
+        const int first = own_first(it0, issuer), count = own_count(it0, issuer, nkb);
         bool opens = true;
         for (int j = 0; j < count; ++j) {
           const uint32_t it = it0 + (uint32_t)(first + 2 * j);
@@ -940,7 +967,8 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     uint32_t it = 0;
     bool ok = true;
     for (int64_t t = pair; t < num_tiles && ok; t += num_pairs) {
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+      const int nkb = unit_kb(t);
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
         if ((int)(it & 1) != set) continue;
         const int sa = it % A_SLOTS, sp = it % P_SLOTS, s = it % B_SLOTS;
         ok = mbar_wait(&pfree[sp], ((it / P_SLOTS) & 1) ^ 1, 6, a.dev_status, abort_flag) &&
@@ -1002,9 +1030,13 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     uint32_t it0 = 0, dc[2] = {0, 0};  // running k-block number of the tile; chunks drained per issuer
     uint32_t staged = 0;               // tiles that went through the staging tile
     bool ok = true;
-    for (int64_t t = pair; t < num_tiles && ok; t += num_pairs, it0 += (uint32_t)num_kb) {
-      int m0, n0, bz;
-      tile_coords(t, &m0, &n0, &bz);
+    int nkb = 0;
+    for (int64_t t = pair; t < num_tiles && ok; t += num_pairs, it0 += (uint32_t)nkb) {
+      nkb = unit_kb(t);
+      int m0, n0, bz, k0, slot;
+      tile_coords(t, &m0, &n0, &bz, &k0, &slot);
+      const bool tail = slot >= 0;               // raw partial tile to scratch, no epilogue
+      const int epi = tail ? (int)TCB200_EPI_NONE : a.epi;
       const int row = m0 + q * 32 + lane;
       float* crow = a.C + (int64_t)bz * a.stride_c + (int64_t)row * a.ldc;
       const float bias_m = (has_bias && a.bias_on_m && row < a.M) ? __ldg(a.bias + row) : 0.f;
@@ -1014,7 +1046,7 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       // move a load across a store that could alias it): ~9000 cycles per tile, measured, during
       // which the drain warps could not serve the next tile's first chunks.
       float2 bias_n = make_float2(0.f, 0.f);
-      if (has_bias && !a.bias_on_m && 2 * lane < mycols) {
+      if (has_bias && !tail && !a.bias_on_m && 2 * lane < mycols) {
         const int c = n0 + col0 + 2 * lane;
         if (c < a.N) bias_n.x = __ldg(a.bias + c);
         if (c + 1 < a.N) bias_n.y = __ldg(a.bias + c + 1);
@@ -1067,7 +1099,7 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       // Chunks of both issuers in the order of the k-block that closes them (the same order on
       // every run; the two can never tie because their k-blocks differ in parity).
       const int first0 = own_first(it0, 0), first1 = own_first(it0, 1);
-      const int count0 = own_count(it0, 0), count1 = own_count(it0, 1);
+      const int count0 = own_count(it0, 0, nkb), count1 = own_count(it0, 1, nkb);
       int j0 = 0, j1 = 0;  // own k-block index from which the next chunk of each issuer is searched
       while (j0 < count0 || j1 < count1) {
         int e0 = j0, e1 = j1;  // own index that closes the next chunk
@@ -1104,7 +1136,7 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         }
       }
       if (!ok) break;
-      if (!a.tma_store) {
+      if (!a.tma_store && !tail) {
 #pragma unroll
         for (int g = 0; g < PIECES; ++g)
           if (g * 16 < mycols) store16(acc[g], col0 + g * 16);
@@ -1129,10 +1161,10 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
             b4.z = a.bias_on_m ? bias_m : __shfl_sync(0xffffffffu, bias_n.x, src + 1);
             b4.w = a.bias_on_m ? bias_m : __shfl_sync(0xffffffffu, bias_n.y, src + 1);
             float4 o;
-            o.x = apply_epilogue_rt(a.epi, acc[g][j + 0], b4.x);
-            o.y = apply_epilogue_rt(a.epi, acc[g][j + 1], b4.y);
-            o.z = apply_epilogue_rt(a.epi, acc[g][j + 2], b4.z);
-            o.w = apply_epilogue_rt(a.epi, acc[g][j + 3], b4.w);
+            o.x = apply_epilogue_rt(epi, acc[g][j + 0], b4.x);
+            o.y = apply_epilogue_rt(epi, acc[g][j + 1], b4.y);
+            o.z = apply_epilogue_rt(epi, acc[g][j + 2], b4.z);
+            o.w = apply_epilogue_rt(epi, acc[g][j + 3], b4.w);
             const int chunk = ((c0 & 31) + j) >> 2;
             *reinterpret_cast<float4*>(box_row + ((chunk ^ (r & 7)) << 4)) = o;
           }
@@ -1145,8 +1177,12 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         if (ok) {
           const uint8_t* out_tile = smem + ts_pair_out_offset();
 #pragma unroll
-          for (int bx = 0; bx < BN / 32; ++bx)
-            if (n0 + bx * 32 < a.N && m0 < a.M) tma_store_3d(&tmC, out_tile + bx * (BM * 128), n0 + bx * 32, m0, bz);
+          for (int bx = 0; bx < BN / 32; ++bx) {
+            if (tail)  // partial tile `slot`, this CTA's 128 rows of it: a dense [tiles * 256][128] matrix
+              tma_store_3d(&tmP, out_tile + bx * (BM * 128), bx * 32, slot * (2 * BM) + (int)rank * BM, 0);
+            else if (n0 + bx * 32 < a.N && m0 < a.M)
+              tma_store_3d(&tmC, out_tile + bx * (BM * 128), n0 + bx * 32, m0, bz);
+          }
           tma_store_commit();
           tma_store_wait_read();  // the stores have read the tile: it may be overwritten
           mbar_arrive(out_free);
@@ -1260,7 +1296,7 @@ int launch_ts(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, co
 
 template <int CHUNK>
 int launch_pair_chunk(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
-                      const TcArgs& args, cudaStream_t s) {
+                      const CUtensorMap& tp, const TcArgs& args, cudaStream_t s) {
   static std::atomic<uint64_t> configured{0};  // bit per device
   const uint64_t bit = 1ull << (plan.device & 63);
   if (!(configured.load(std::memory_order_acquire) & bit)) {
@@ -1270,13 +1306,13 @@ int launch_pair_chunk(const Plan& plan, const CUtensorMap& ta, const CUtensorMap
   }
   // the kernel carries its cluster shape (2 CTAs); the grid is a multiple of 2
   TCB200_CUDA_TRY(launch_pdl(contraction_ts_pair_kernel<CHUNK>, plan.launch.grid, dim3(kTsThreads, 1, 1),
-                             (size_t)ts_pair_smem_bytes(), s, ta, tb, tc, args));
+                             (size_t)ts_pair_smem_bytes(), s, ta, tb, tc, tp, args));
   return TCB200_OK;
 }
 int launch_pair(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
-                const TcArgs& args, cudaStream_t s) {
-  return plan.tile.split_tf32 == 4 ? launch_pair_chunk<1>(plan, ta, tb, tc, args, s)
-                                   : launch_pair_chunk<kPairChunkKB>(plan, ta, tb, tc, args, s);
+                const CUtensorMap& tp, const TcArgs& args, cudaStream_t s) {
+  return plan.tile.split_tf32 == 4 ? launch_pair_chunk<1>(plan, ta, tb, tc, tp, args, s)
+                                   : launch_pair_chunk<kPairChunkKB>(plan, ta, tb, tc, tp, args, s);
 }
 
 }  // namespace
@@ -1316,6 +1352,20 @@ int pick_split_k(const tcb200_problem_t& p, int64_t tiles, int slots, double kb_
   return best;
 }
 
+// Tail split of the CTA-pair tiles (tile.split_k = kTailSplitBase + S).  When the tiles do not fill the last round
+// of the persistent pairs (256 tiles on 74 pairs: three full rounds and 34 tiles), the last r = tiles % pairs
+// tiles have their reduction split S ways so that the last round lasts 1 / S of a round.  S is the largest
+// split, up to 4, whose r * S units still fit one round and leave every unit at least 8 k-blocks.
+constexpr int kTailSplitBase = 100;
+int tail_split_factor(const tcb200_problem_t& p, int64_t tiles, int pairs) {
+  if (p.batch != 1 || tiles <= pairs) return 0;
+  const int64_t r = tiles % pairs;
+  if (r == 0) return 0;
+  const int64_t kbs = ceil_div(p.K, BK);
+  int64_t S = std::min<int64_t>({(int64_t)pairs / r, 4, kbs / 8});
+  return S >= 2 ? (int)S : 0;
+}
+
 int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n) {
   *n = 0;
   if (!shape_ok(p) || !worth_it(p)) return TCB200_OK;
@@ -1345,7 +1395,15 @@ int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max,
   if (p.M > BM && p.N >= kPairBN) {
     const int64_t tiles = ceil_div(p.N, kPairBN) * ceil_div(p.M, 2 * BM) * p.batch;
     Cand c{TCB200_VARIANT_TCGEN05_PAIR, 2 * BM, kPairBN, kPairBSlots, 1, 0.0};
-    c.split_k = pick_split_k(p, tiles, std::max(1, sms / 2), 0.56, &c.t);
+    const int pairs = std::max(1, sms / 2);
+    c.split_k = pick_split_k(p, tiles, pairs, 0.56, &c.t);
+    const int tailS = c.split_k == 1 ? tail_split_factor(p, tiles, pairs) : 0;
+    if (tailS) {
+      // full rounds + a round of 1 / S length + the second pass over the tail tiles
+      const int64_t kbs = ceil_div(p.K, BK);
+      const double t = (double)(tiles / pairs) * ((double)kbs * 0.56 + 3.0) + ((double)ceil_div(kbs, tailS) * 0.56 + 3.0) + 3.0;
+      if (t < c.t * 0.98) { c.t = t; c.split_k = kTailSplitBase + tailS; }
+    }
     c.t *= 0.999;  // ties go to the pair tile
     cands[nc++] = c;
   }
@@ -1389,7 +1447,15 @@ int contraction_tc_plan(Plan& plan) {
   if (!shape_ok(p)) return TCB200_ERR_UNSUPPORTED;
   tcb200_tile_t& t = plan.tile;
   if (t.split_k <= 0) t.split_k = 1;
-  if (t.split_k > 1) {
+  const bool tail_split = t.split_k > kTailSplitBase;
+  if (tail_split) {
+    // tail split: CTA-pair tiles only; the factor must be the one this problem and device call for
+    const int64_t tiles = ceil_div(p.N, kPairBN) * ceil_div(p.M, 2 * BM) * p.batch;
+    const int S = t.split_k - kTailSplitBase;
+    if (t.variant != TCB200_VARIANT_TCGEN05_PAIR || S != tail_split_factor(p, tiles, std::max(1, plan.sms / 2)))
+      return TCB200_ERR_UNSUPPORTED;
+    plan.scratch_floats = (size_t)S * (size_t)(tiles % std::max(1, plan.sms / 2)) * 2 * BM * kPairBN;
+  } else if (t.split_k > 1) {
     // split-K: tensor-memory tiles only, one unbatched contraction, every split at least one k-block
     if (t.variant == TCB200_VARIANT_TCGEN05 || p.batch != 1 || t.split_k > kMaxSplitK ||
         ceil_div(p.K, BK) < t.split_k || p.M * p.N > (1ll << 40))
@@ -1402,7 +1468,7 @@ int contraction_tc_plan(Plan& plan) {
     if (t.bn != kPairBN || (t.split_tf32 != 3 && t.split_tf32 != 4)) return TCB200_ERR_UNSUPPORTED;
     if (ceil_div(p.M, 2 * BM) > 65535) return TCB200_ERR_UNSUPPORTED;
     t.bm = 2 * BM; t.bk = BK; t.stages = kPairBSlots; t.threads = kTsThreads;
-    const int64_t tiles = ceil_div(p.N, kPairBN) * ceil_div(p.M, 2 * BM) * p.batch * t.split_k;
+    const int64_t tiles = ceil_div(p.N, kPairBN) * ceil_div(p.M, 2 * BM) * p.batch * (tail_split ? 1 : t.split_k);
     plan.launch.grid = dim3(2u * (unsigned)std::min<int64_t>(tiles, std::max(1, plan.sms / 2)), 1, 1);
     plan.launch.block = dim3(kTsThreads, 1, 1);
     plan.launch.smem = ts_pair_smem_bytes();
@@ -1438,7 +1504,7 @@ int contraction_tc_plan(Plan& plan) {
 // over buffer sets) takes them from this small per-plan cache instead.
 struct TcMaps {
   const void* key[3] = {nullptr, nullptr, nullptr};
-  CUtensorMap ta, tb, tc;
+  CUtensorMap ta, tb, tc, tp;
   bool valid = false, has_tc = false;
 };
 struct TcMapCache {
@@ -1454,9 +1520,12 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
                           float* C, cudaStream_t s, int* dev_status, float* scratch, void* map_cache) {
   const tcb200_problem_t& p = plan.p;
   if (((uintptr_t)A | (uintptr_t)B) & 15) return TCB200_ERR_ALIGNMENT;
-  const int S = plan.tile.split_k > 1 ? plan.tile.split_k : 1;
-  if (S > 1 && !scratch) return TCB200_ERR_INVALID_ARGUMENT;
   const bool pair = plan.kernel_id == 301283;
+  const int tailS = plan.tile.split_k > kTailSplitBase ? plan.tile.split_k - kTailSplitBase : 0;
+  const int S = !tailS && plan.tile.split_k > 1 ? plan.tile.split_k : 1;
+  if ((S > 1 || tailS) && !scratch) return TCB200_ERR_INVALID_ARGUMENT;
+  const int64_t pair_tiles = ceil_div(p.N, kPairBN) * ceil_div(p.M, 2 * BM) * p.batch;
+  const int tail_tiles = tailS ? (int)(pair_tiles % std::max(1, plan.sms / 2)) : 0;
   // where the tensor-core kernel writes: the output, or the partial planes [S][M][N] of a split-K launch
   float* Ck = S > 1 ? scratch : C;
   const int64_t ldck = S > 1 ? p.N : p.ldc, stride_ck = S > 1 ? p.M * p.N : p.stride_c;
@@ -1470,6 +1539,9 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
   a.a_batched = S == 1 && p.batch > 1 && p.stride_a > 0;
   a.b_batched = S == 1 && p.batch > 1 && p.stride_b > 0;
   a.ksplit_kb = S > 1 ? (int)ceil_div(ceil_div(p.K, BK), S) : 0;
+  a.tail_S = tailS;
+  a.tail_tiles = tail_tiles;
+  a.tail_kb = tailS ? (int)ceil_div(ceil_div(p.K, BK), tailS) : 0;
   const bool bias_vec = !a.bias || p.bias_on_m || ((uintptr_t)a.bias & 15) == 0;
   a.c_vec = ((uintptr_t)Ck & 15) == 0 && ldck % 4 == 0 && stride_ck % 4 == 0 && bias_vec;
   a.dev_status = dev_status;
@@ -1500,16 +1572,22 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
     m->tc = m->tb;  // unused by the kernel unless the staged epilogue is on
     // output map for the staged epilogue: {N, M, batch}, boxes of 32 columns x 128 rows
     m->has_tc = a.tma_store && make_operand_map(&m->tc, Ck, p.N, p.M, ldck, batch_k, stride_ck, BM) == TCB200_OK;
+    m->tp = m->tb;  // unused by the kernel unless the launch has a split tail
+    if (tailS) {
+      // the partial tiles of the tail: a dense matrix of [tailS * tail_tiles * 256] rows of 128 floats
+      st = make_operand_map(&m->tp, scratch, kPairBN, (int64_t)tailS * tail_tiles * 2 * BM, kPairBN, 1, 0, BM);
+      if (st != TCB200_OK) return st;
+    }
     m->key[0] = A; m->key[1] = B; m->key[2] = Ck;
     m->valid = true;
   }
   a.tma_store = a.tma_store && m->has_tc;
-  const CUtensorMap ta = m->ta, tb = m->tb, tc = m->tc;
+  const CUtensorMap ta = m->ta, tb = m->tb, tc = m->tc, tp = m->tp;
   if (cache) lock.unlock();
 
   int st;
   switch (plan.kernel_id) {
-    case 301283: st = launch_pair(plan, ta, tb, tc, a, s); break;
+    case 301283: st = launch_pair(plan, ta, tb, tc, tp, a, s); break;
     case 100643: st = launch_ts<64>(plan, ta, tb, a, s); break;
     case 101283: st = launch_ts<128>(plan, ta, tb, a, s); break;
     case 101123: st = launch_ts<112>(plan, ta, tb, a, s); break;
@@ -1520,7 +1598,11 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
     case 2561: st = launch_inst<256, 1>(plan, ta, tb, a, s); break;
     default: st = TCB200_ERR_UNSUPPORTED; break;
   }
-  if (st != TCB200_OK || S == 1) return st;
+  if (st != TCB200_OK) return st;
+  if (tailS)  // second pass over the tail tiles only: C = epilogue([C +] sum of their tailS partial tiles)
+    return tail_tiles_reduce(scratch, C, bias, (int)p.M, (int)p.N, tailS, tail_tiles, (int)(pair_tiles - tail_tiles),
+                             p.ldc, p.epilogue, p.bias_on_m, p.accumulate, s);
+  if (S == 1) return st;
 
   // second pass: C = epilogue([C +] sum_s P[s])
   return partial_planes_reduce(scratch, C, bias, (int)p.M, (int)p.N, S, p.ldc, p.epilogue, p.bias_on_m, p.accumulate,

@@ -66,7 +66,76 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(SplitKArgs a) {
   }
 }
 
+// Tail tiles of a CTA-pair launch: partial tile (s * tail_tiles + j) is a dense 256 x 128 block; output tile
+// tile0 + j covers rows ((tile0 + j) / tiles_n) * 256 .. and columns ((tile0 + j) % tiles_n) * 128 ..
+struct TailArgs {
+  const float* P;
+  float* C;
+  const float* bias;
+  int M, N, S, tail_tiles, tile0, tiles_n;
+  int64_t ldc;
+  int epi, bias_on_m, accumulate, vec;
+};
+
+__global__ void __launch_bounds__(256) tail_tiles_reduce_kernel(TailArgs a) {
+  pdl_sync();  // the partial tiles come from the kernel launched just before this one
+  const bool has_bias = a.epi == TCB200_EPI_BIAS || a.epi == TCB200_EPI_BIAS_RELU;
+  const int j = blockIdx.y, tile = a.tile0 + j;
+  const int m0 = (tile / a.tiles_n) * 256, n0 = (tile % a.tiles_n) * 128;
+  const int64_t tile_elems = 256 * 128;
+  const float* P0 = a.P + (int64_t)j * tile_elems;
+  const int64_t split_stride = (int64_t)a.tail_tiles * tile_elems;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < 256 * 32; i += gridDim.x * blockDim.x) {
+    const int r = i >> 5, c = (i & 31) << 2;
+    const int m = m0 + r, n = n0 + c;
+    if (m >= a.M || n >= a.N) continue;
+    float4 acc = *reinterpret_cast<const float4*>(P0 + r * 128 + c);
+    for (int s = 1; s < a.S; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(P0 + s * split_stride + r * 128 + c);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    float v[4] = {acc.x, acc.y, acc.z, acc.w};
+    float* dst = a.C + (int64_t)m * a.ldc + n;
+    if (a.vec && n + 3 < a.N) {
+      float4 o = make_float4(v[0], v[1], v[2], v[3]);
+      if (a.accumulate) {
+        const float4 old = *reinterpret_cast<const float4*>(dst);
+        o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+      }
+      float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (has_bias) {
+        if (a.bias_on_m) b.x = b.y = b.z = b.w = __ldg(a.bias + m);
+        else b = make_float4(__ldg(a.bias + n), __ldg(a.bias + n + 1), __ldg(a.bias + n + 2), __ldg(a.bias + n + 3));
+      }
+      o.x = apply_epilogue_rt(a.epi, o.x, b.x); o.y = apply_epilogue_rt(a.epi, o.y, b.y);
+      o.z = apply_epilogue_rt(a.epi, o.z, b.z); o.w = apply_epilogue_rt(a.epi, o.w, b.w);
+      *reinterpret_cast<float4*>(dst) = o;
+    } else {
+      for (int k = 0; k < 4 && n + k < a.N; ++k) {
+        float o = v[k];
+        if (a.accumulate) o += dst[k];
+        const float b = has_bias ? __ldg(a.bias + (a.bias_on_m ? m : n + k)) : 0.f;
+        dst[k] = apply_epilogue_rt(a.epi, o, b);
+      }
+    }
+  }
+}
+
 }  // namespace
+
+int tail_tiles_reduce(const float* P, float* C, const float* bias, int M, int N, int S, int tail_tiles, int tile0,
+                      int64_t ldc, int epi, int bias_on_m, int accumulate, cudaStream_t s) {
+  TailArgs a;
+  a.P = P; a.C = C; a.bias = bias;
+  a.M = M; a.N = N; a.S = S; a.tail_tiles = tail_tiles; a.tile0 = tile0;
+  a.tiles_n = (int)ceil_div(N, 128);
+  a.ldc = ldc;
+  a.epi = epi; a.bias_on_m = bias_on_m; a.accumulate = accumulate;
+  a.vec = ldc % 4 == 0 && (((uintptr_t)C) & 15) == 0;
+  const dim3 grid(8, (unsigned)tail_tiles, 1);
+  TCB200_CUDA_TRY(launch_pdl(tail_tiles_reduce_kernel, grid, dim3(256, 1, 1), (size_t)0, s, a));
+  return TCB200_OK;
+}
 
 int partial_planes_reduce(const float* P, float* C, const float* bias, int M, int N, int S, int64_t ldc, int epi,
                           int bias_on_m, int accumulate, int sms, cudaStream_t s) {

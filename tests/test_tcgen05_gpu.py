@@ -303,3 +303,54 @@ def test_strict_accumulation_tiles_meet_the_reference_bound_on_all_positive_data
     bound = 3e-7 * K * 1.0
     print("K=%d bound %.3e: strict tile %.3e, default tile %.3e" % (K, bound, errs[4], errs[3]))
     assert errs[4] < bound, (errs, bound)
+
+
+@pytest.mark.parametrize("case", [
+    # (M, N, K): CTA-pair tiles that do not fill the last round of the 74 pairs
+    (5120, 512, 1024),     # 80 tiles: one full round and 6 tail tiles split 4 ways
+    (5000, 500, 1000),     # the same with ragged rows, columns and k-blocks
+    (8192, 1024, 2048),    # MLP layer 1 on an 8192-row shard: 256 tiles, 34 tail tiles split in two
+])
+@pytest.mark.parametrize("epi", [cabi.EPI_NONE, cabi.EPI_BIAS_RELU])
+def test_pair_tiles_with_a_split_tail(cuda, case, epi):
+    """The last, partly filled round of the persistent CTA pairs runs as units of 1 / S of the reduction whose
+    partial tiles a second kernel adds: same criterion as the plain pair tiles, same bits on every run, and
+    the default for these shapes."""
+    M, N, K = case
+    A, B, bias = _rand((M, K), 81), _rand((N, K), 82), _rand((N,), 83)
+    has_bias = epi == cabi.EPI_BIAS_RELU
+    r = A.double() @ B.double().t()
+    ref = (torch.clamp_min(r + bias.double(), 0) if has_bias else r).float()
+    p = cabi.contraction_problem(1, M, N, K, True, True, epilogue=epi)
+    ins = [A.to(cuda), B.to(cuda)] + ([bias.to(cuda)] if has_bias else [])
+    out, plan = run_plan(p, ins, (M, N))
+    assert plan.tile().variant == cabi.VARIANT_TCGEN05_PAIR and "tail_split" in plan.describe(), plan.describe()
+    assert_close(out, ref, K, [A, B], 3e-7, plan.describe())
+    out2 = torch.full((M, N), float("nan"), device=cuda)
+    plan.launch(ins, [out2])
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2)
+    # the plain pair tile gives the same values up to the order of the additions in the tail
+    plain = tc_tile(128, 3, pair=True)
+    plain.split_k = 1
+    out3, plan3 = run_plan(p, ins, (M, N), plain)
+    assert "tail_split" not in plan3.describe()
+    assert_close(out3, ref, K, [A, B], 3e-7, plan3.describe())
+
+
+def test_pair_tail_split_accumulates_and_takes_odd_outputs(cuda):
+    M, N, K = 5120, 512, 1024
+    A, B, init = _rand((M, K), 84), _rand((N, K), 85), _rand((M, N), 86)
+    ref = (A.double() @ B.double().t() + init.double()).float()
+    p = cabi.contraction_problem(1, M, N, K, True, True, accumulate=True)
+    out, plan = run_plan(p, [A.to(cuda), B.to(cuda)], (M, N), out_init=init.to(cuda))
+    assert "tail_split" in plan.describe()
+    assert_close(out, ref, K, what=plan.describe())
+    # an output view at a 4-byte offset: direct stores for the whole tiles, scalar second pass for the tail
+    p = cabi.contraction_problem(1, M, N, K, True, True)
+    buf = torch.full((M * N + 1,), float("nan"), device=cuda)
+    view = buf[1:].view(M, N)
+    plan = cabi.Plan(p)
+    plan.launch([A.to(cuda), B.to(cuda)], [view])
+    torch.cuda.synchronize()
+    assert_close(view, (A.double() @ B.double().t()).float(), K, [A, B], 3e-7, plan.describe())
