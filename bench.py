@@ -458,9 +458,10 @@ def run_product(args):
         if ga:
             entry["gather"] = ga
         per_config.append(entry)
-    # dominant kernel = largest share of the step
-    dom = max(range(len(progs)), key=lambda i: per_prog_us[i])
-    dp, dus, dc = progs[dom], per_prog_us[dom], per_config[dom]
+    # dominant kernel = largest share of the step at the device's pace: the graph-replayed windows (the one-by-one
+    # event times of the smallest kernels hold the host's launch rate, above all on the shards of a multi-GPU run)
+    dom = max(range(len(progs)), key=lambda i: windows[i]["p50"])
+    dp, dus, dc = progs[dom], windows[dom]["p50"], per_config[dom]
     if dc["bound"] == "tensor":
         split = dp.exe.split_tf32
         peak = (peaks["tf32_tflops_burst"] if burst else peaks["tf32_tflops"]) * world
@@ -476,6 +477,7 @@ def run_product(args):
                 "unit": "GB/s", "frac": round(dp.full.bytes / dus / 1e3 / (peaks["hbm_gbs"] * world), 3),
                 "note": "of %s" % peaks["source"]}
     roof["kernel"] = dp.name
+    roof["timed"] = "p50 of %d windows of graph-replayed launches, CUDA events on the launching stream" % 20
     roof["traffic"] = NCU_TRAFFIC_BYTES.get(dp.name) if world == 1 else None
     if dp.name == "mlp3" and world == 1:
         roof["traffic_note"] = ("ncu capture of the first of the three launches (layer 1: 209.7 MB algorithmic, "
