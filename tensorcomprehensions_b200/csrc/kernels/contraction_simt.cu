@@ -262,8 +262,13 @@ __global__ void __launch_bounds__(256) simt_small_kernel(GemmArgs g, int ldas, i
 // four rows; a B row of 26 floats is only 8-byte aligned), then 64 FMAs.  Both slabs arrive by one bulk copy
 // each.  Threads past the edge of the tile grid read clamped rows / the next row's first columns and do not
 // store.
+// A 26 x 26 output has only 49 such tiles, two warps where the 2x2 form runs eight, and with a few matrices per
+// SM nothing then hides the latency of a step (measured: 8.7 us against 7.5 us).  So the reduction is split over
+// `ks` thread groups as well (72 = 3 x 24): group q runs k in [q K/ks, (q+1) K/ks), the ks partial tiles meet in
+// shared memory and are added in the fixed order q = 0 .. ks-1 by the threads that store the output, one element
+// per thread, consecutive threads on consecutive addresses.
 // ------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) simt_small4_kernel(GemmArgs g) {
+__global__ void __launch_bounds__(256) simt_small4_kernel(GemmArgs g, int ks) {
   extern __shared__ __align__(16) float smem[];
   pdl_sync();  // launched as a programmatic dependent: wait for the preceding kernel before any global access
   const int M = g.M, N = g.N, K = g.K;
@@ -271,8 +276,9 @@ __global__ void __launch_bounds__(256) simt_small4_kernel(GemmArgs g) {
   float* Bs = smem + (size_t)M * K;    // [K][N], dense, followed by 16 bytes of slack for the last row's overrun
   uint64_t* bar = reinterpret_cast<uint64_t*>(Bs + (size_t)K * N + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar + 1);
+  float* Ps = Bs + (size_t)K * N + 8;  // [ks][4 TM][4 TN] partial tiles (ks > 1)
   const int64_t b = blockIdx.x;
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, nt = blockDim.x;
   if (tid == 0) {
     mbar_init(bar, 1);
     *abort_flag = 0;
@@ -282,9 +288,10 @@ __global__ void __launch_bounds__(256) simt_small4_kernel(GemmArgs g) {
     bulk_load(As, g.A + b * g.sa, bytes_a, bar);
     bulk_load(Bs, g.B + b * g.sb, bytes_b, bar);
   }
-  const int TM = (M + 3) >> 2, TN = (N + 3) >> 2;
-  const int tm = tid / TN, tn = tid - tm * TN;
-  const bool active = tm < TM;
+  const int TM = (M + 3) >> 2, TN = (N + 3) >> 2, tasks = TM * TN;
+  const int q = tid / tasks, task = tid - q * tasks;
+  const int tm = task / TN, tn = task - tm * TN;
+  const bool active = q < ks;
   const float* arow[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) arow[i] = As + (size_t)min(tm + TM * i, M - 1) * K;
@@ -295,39 +302,60 @@ __global__ void __launch_bounds__(256) simt_small4_kernel(GemmArgs g) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
   __syncthreads();  // the barrier is initialised before anyone polls it
-  if (!mbar_wait(bar, 0, 9, nullptr, abort_flag)) return;
-  if (!active) return;
+  const bool loaded = mbar_wait(bar, 0, 9, nullptr, abort_flag);
+  if (loaded && active) {
+    const int kq = K / ks;  // a multiple of 4 (checked by the plan)
 #pragma unroll 2
-  for (int k = 0; k < K; k += 4) {
-    float a[4][4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float4 v = *reinterpret_cast<const float4*>(arow[i] + k);
-      a[i][0] = v.x; a[i][1] = v.y; a[i][2] = v.z; a[i][3] = v.w;
-    }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 b0 = *reinterpret_cast<const float2*>(bcol + (size_t)(k + j) * N);
-      const float2 b1 = *reinterpret_cast<const float2*>(bcol + (size_t)(k + j) * N + 2);
+    for (int k = q * kq; k < (q + 1) * kq; k += 4) {
+      float a[4][4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        acc[i][0] = fmaf(a[i][j], b0.x, acc[i][0]);
-        acc[i][1] = fmaf(a[i][j], b0.y, acc[i][1]);
-        acc[i][2] = fmaf(a[i][j], b1.x, acc[i][2]);
-        acc[i][3] = fmaf(a[i][j], b1.y, acc[i][3]);
+        const float4 v = *reinterpret_cast<const float4*>(arow[i] + k);
+        a[i][0] = v.x; a[i][1] = v.y; a[i][2] = v.z; a[i][3] = v.w;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 b0 = *reinterpret_cast<const float2*>(bcol + (size_t)(k + j) * N);
+        const float2 b1 = *reinterpret_cast<const float2*>(bcol + (size_t)(k + j) * N + 2);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          acc[i][0] = fmaf(a[i][j], b0.x, acc[i][0]);
+          acc[i][1] = fmaf(a[i][j], b0.y, acc[i][1]);
+          acc[i][2] = fmaf(a[i][j], b1.x, acc[i][2]);
+          acc[i][3] = fmaf(a[i][j], b1.y, acc[i][3]);
+        }
       }
     }
   }
   float* C = g.C + b * g.sc;
+  if (ks == 1) {
+    if (!(loaded && active)) return;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int m = tm + TM * i;
-    if (m >= M) continue;
+    for (int i = 0; i < 4; ++i) {
+      const int m = tm + TM * i;
+      if (m >= M) continue;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int n = 4 * tn + j;
-      if (n < N) store_out(g, C, m, n, acc[i][j]);
+      for (int j = 0; j < 4; ++j) {
+        const int n = 4 * tn + j;
+        if (n < N) store_out(g, C, m, n, acc[i][j]);
+      }
     }
+    return;
+  }
+  const int MP = 4 * TM, NP = 4 * TN;
+  if (loaded && active) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      *reinterpret_cast<float4*>(Ps + ((size_t)q * MP + tm + TM * i) * NP + 4 * tn) =
+          make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+  }
+  __syncthreads();
+  if (!loaded) return;
+  for (int i = tid; i < M * N; i += nt) {
+    const int m = i / N, n = i - m * N;
+    float v = Ps[(size_t)m * NP + n];
+    for (int s2 = 1; s2 < ks; ++s2) v += Ps[((size_t)s2 * MP + m) * NP + n];
+    store_out(g, C, m, n, v);
   }
 }
 
@@ -354,9 +382,22 @@ bool small_dense_shape(const tcb200_problem_t& p) {
   return small_fast_shape(p) && p.lda == p.K && p.ldb == p.N && p.N % 2 == 0 && (p.M * p.K) % 4 == 0 &&
          (p.K * p.N) % 4 == 0 && p.stride_b % 4 == 0 && p.M * p.K * 4 < (1 << 20) && p.K * p.N * 4 < (1 << 20);
 }
-// The 4x4-tile form: one thread per 4x4 tile of the output.
-int small4_threads(const tcb200_problem_t& p) { return (int)round_up(((p.M + 3) / 4) * ((p.N + 3) / 4), 32); }
-bool small4_ok(const tcb200_problem_t& p) { return small_dense_shape(p) && small4_threads(p) <= 256; }
+// The 4x4-tile form: one thread per (4x4 tile of the output, share of the reduction).
+int small4_tasks(const tcb200_problem_t& p) { return (int)(((p.M + 3) / 4) * ((p.N + 3) / 4)); }
+// Shares of the reduction: as many as keep every share a multiple of four k and the CTA within 256 threads.
+int small4_ksplit(const tcb200_problem_t& p) {
+  for (int ks = 4; ks > 1; --ks)
+    if (p.K % (4 * ks) == 0 && small4_tasks(p) * ks <= 256) return ks;
+  return 1;
+}
+int small4_threads(const tcb200_problem_t& p, int ks) { return (int)round_up((int64_t)small4_tasks(p) * ks, 32); }
+size_t small4_smem(const tcb200_problem_t& p, int ks) {
+  const size_t partial = ks > 1 ? (size_t)ks * 16 * small4_tasks(p) : 0;
+  return sizeof(float) * ((size_t)p.M * p.K + (size_t)p.K * p.N + 8 + partial) + 16;
+}
+bool small4_ok(const tcb200_problem_t& p) {
+  return small_dense_shape(p) && small4_tasks(p) <= 256 && small4_smem(p, small4_ksplit(p)) <= 48 * 1024;
+}
 
 // simt_small reads A as (m,k) row-major and B as (k,n) row-major: the batchmatmul form.
 bool small_ok(const tcb200_problem_t& p) {
@@ -375,9 +416,17 @@ int contraction_simt_query(const tcb200_problem_t& p, tcb200_tile_t* out, int ma
   };
   if (small_ok(p)) {
     push(TCB200_VARIANT_SIMT_SMALL, (int)p.M, (int)p.N, (int)p.K, 256);
-    // bk = 4: 4x4 register tiles.  Half the shared-memory words per multiply-add, but two warps per matrix instead
-    // of eight: 8.7 us against 7.5 us on the 500 x [26x72][72x26] benchmark, so it is a sweep point, not the default.
-    if (small4_ok(p)) push(TCB200_VARIANT_SIMT_SMALL, (int)p.M, (int)p.N, 4, small4_threads(p));
+    // bk = 4: 4x4 register tiles with the reduction shared by up to four thread groups (stages = groups);
+    // stages = 1 is the unsplit form (two warps per 26 x 26 matrix: 8.7 us against 7.5 us for the 2x2 form)
+    if (small4_ok(p)) {
+      const int ks = small4_ksplit(p);
+      if (cnt < max && out) out[cnt] = tcb200_tile_t{TCB200_VARIANT_SIMT_SMALL, (int)p.M, (int)p.N, 4, ks, small4_threads(p, ks), 0};
+      ++cnt;
+      if (ks > 1) {
+        if (cnt < max && out) out[cnt] = tcb200_tile_t{TCB200_VARIANT_SIMT_SMALL, (int)p.M, (int)p.N, 4, 1, small4_threads(p, 1), 0};
+        ++cnt;
+      }
+    }
     push(TCB200_VARIANT_SIMT_SMALL, (int)p.M, (int)p.N, (int)p.K, 192);
     push(TCB200_VARIANT_SIMT_SMALL, (int)p.M, (int)p.N, (int)p.K, 128);
   }
@@ -392,12 +441,15 @@ int contraction_simt_plan(Plan& plan) {
   tcb200_tile_t& t = plan.tile;
   if (t.variant == TCB200_VARIANT_SIMT_SMALL) {
     if (!small_ok(p)) return TCB200_ERR_UNSUPPORTED;
-    if (t.bk == 4 && p.K != 4) {  // 4x4 register tiles, one thread per tile
+    if (t.bk == 4 && p.K != 4) {  // 4x4 register tiles; stages = thread groups that share the reduction
       if (!small4_ok(p)) return TCB200_ERR_UNSUPPORTED;
-      t.bm = (int)p.M; t.bn = (int)p.N; t.threads = small4_threads(p);
+      int ks = t.stages > 0 ? t.stages : small4_ksplit(p);
+      if (ks > 4 || p.K % (4 * ks) != 0 || small4_tasks(p) * ks > 256 || small4_smem(p, ks) > 48 * 1024)
+        return TCB200_ERR_UNSUPPORTED;
+      t.bm = (int)p.M; t.bn = (int)p.N; t.stages = ks; t.threads = small4_threads(p, ks);
       plan.launch.grid = dim3((unsigned)p.batch, 1, 1);
       plan.launch.block = dim3(t.threads, 1, 1);
-      plan.launch.smem = sizeof(float) * ((size_t)p.M * p.K + (size_t)p.K * p.N + 4) + 16;
+      plan.launch.smem = small4_smem(p, ks);
       plan.kernel_id = 11;
       return TCB200_OK;
     }
@@ -427,7 +479,8 @@ int contraction_simt_launch(const Plan& plan, const float* A, const float* B, co
   GemmArgs g{A, B, bias, C, (int)p.M, (int)p.N, (int)p.K, p.lda, p.ldb, p.ldc,
              p.stride_a, p.stride_b, p.stride_c, p.epilogue, p.bias_on_m, p.accumulate};
   if (plan.kernel_id == 11 && (((uintptr_t)A | (uintptr_t)B) & 15) == 0) {
-    TCB200_CUDA_TRY(launch_pdl(simt_small4_kernel, plan.launch.grid, plan.launch.block, plan.launch.smem, s, g));
+    TCB200_CUDA_TRY(launch_pdl(simt_small4_kernel, plan.launch.grid, plan.launch.block, plan.launch.smem, s, g,
+                               plan.tile.stages));
   } else if (plan.kernel_id == 10 || plan.kernel_id == 11) {
     // (a 4x4-tile plan whose operands are views at an odd offset runs the forms that take any alignment)
     const dim3 block = plan.kernel_id == 11 ? dim3(256, 1, 1) : plan.launch.block;
