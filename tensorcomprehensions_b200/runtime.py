@@ -13,7 +13,8 @@ class CompiledWorkload:
         options = api.autotune(w.tc, w.entry, *probe, starting_options="naive") if tune else "naive"
         self.options = options
         self.exe = api.compile(w.tc, w.entry, options, *probe)
-        self.launches = self.exe.num_launches
+        # kernels per run: one per matched launch, plus the second pass of a launch whose tile splits its reduction
+        self.launches = self.exe.num_launches + sum(1 for t in self.exe.tiles() if t[7] > 1)
         self.split_tf32 = min(3, max(t[6] for t in self.exe.tiles()))  # 4 = 3xTF32 with strict accumulation
         self.out_shapes = self.exe.output_shapes()
 
