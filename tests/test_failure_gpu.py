@@ -68,6 +68,6 @@ def test_profile_times_short_kernels_at_device_pace(cuda, name):
     outs = [torch.empty(s, device=cuda) for s in exe.output_shapes()]
     exe.profile(*ins, outputs=outs)
     t = sorted(exe.profile(*ins, outputs=outs)["kernel_runtime_us"] for _ in range(5))
-    assert t[0] > 0.5 and t[-1] / t[0] < 1.35, t
+    assert t[0] > 0.5 and t[-1] / t[0] < 1.5, t
     refs = orc.as_list(orc.ATEN[name](*wl.make_inputs(w)))
     assert_close(outs[0], refs[0], w.reduction[0], what=name)  # the replays leave the same output
