@@ -221,6 +221,17 @@ def test_batch_reduced_contraction_and_copy_through_the_c_abi(cuda):
     assert torch.equal(out, src) and "copy" in plan.describe()
 
 
+def test_trivial_copies_of_the_corner_case_suite_run(cuda):
+    """test/cuda/test_corner_cases.cc E2 and E4: a one-element copy and a zero-dimensional one."""
+    a = torch.randn(1, device=cuda)
+    assert torch.equal(tc.compile("def f(float(1) a) -> (b) { b(i) = a(i) }", "f", "naive", a)(a), a)
+    s = torch.randn((), device=cuda)
+    out = tc.compile("def f(float a) -> (b) { b = a }", "f", "naive", s)(s)
+    assert out.shape == s.shape and torch.equal(out, s)
+    m = torch.randn(37, 21, device=cuda)
+    assert torch.equal(tc.compile("def f(float(N, M) a) -> (b) { b(i, j) = a(i, j) }", "f", "naive", m)(m), m)
+
+
 def test_accumulating_reduction_keeps_output(cuda):
     """'+=' without '!' adds to what the output holds (test/cuda/test_compile_and_run.cc:181-200)."""
     tcs = "def mm(float(M,K) A, float(K,N) B) -> (C) { C(m,n) += A(m,k) * B(k,n) }"
