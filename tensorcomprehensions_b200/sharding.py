@@ -111,6 +111,31 @@ def all_gather_shards(shard, dim, total, group=None):
     return Gatherer(tuple(shard.shape), dim, total, shard.device, shard.dtype, group).gather(shard)
 
 
+class RankFailure(RuntimeError):
+    """Raised on EVERY rank when one or more ranks reported a failure before an exchange."""
+
+    def __init__(self, failed, own_error=None):
+        self.failed_ranks = failed
+        msg = "rank(s) %s failed before the exchange" % ", ".join(str(r) for r in failed)
+        if own_error is not None:
+            msg += "; this rank's error: %r" % (own_error,)
+        super().__init__(msg)
+
+
+def agree_all_ranks_ok(ok, group=None, device=None, own_error=None):
+    """Every rank says whether its part went well; if any did not, all ranks raise RankFailure naming them, instead
+    of the healthy ranks walking into a collective that the failed one never joins.  One tiny all_gather; call it
+    between steps, with no kernel's result pending on the answer (it synchronises the host with the flag copy)."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=device or "cpu")
+    flags = torch.empty(world, dtype=torch.int32, device=flag.device)
+    dist.all_gather_into_tensor(flags, flag, group=group)
+    failed = [r for r, v in enumerate(flags.tolist()) if v == 0]
+    if failed:
+        raise RankFailure(failed, own_error)
+
+
 class ShardedProgram:
     """This rank's shard of a workload: compiled for the shard shapes, run on the local GPU.
 
@@ -136,6 +161,19 @@ class ShardedProgram:
             self.exe = fn(self.w.tc, self.w.entry, self.options, *shard_inputs)
         outs = self.exe(*shard_inputs)
         return list(outs) if isinstance(outs, (tuple, list)) else [outs]
+
+    def run_and_gather(self, shard_inputs, full_extents, group=None):
+        """run() then gather(), with a vote in between: a rank whose compile or launch raised (a shape its kernels
+        refuse, a device status that is not clean) makes every rank raise RankFailure before any of them enters
+        the all-gather."""
+        error, outs = None, None
+        try:
+            outs = self.run(shard_inputs)
+        except Exception as e:  # reported to the other ranks, then re-raised as RankFailure on all of them
+            error = e
+        device = shard_inputs[0].device if shard_inputs[0].is_cuda else None
+        agree_all_ranks_ok(error is None, group, device, error)
+        return self.gather(outs, full_extents, group)
 
     def gather(self, shard_outputs, full_extents, group=None):
         """full_extents[i]: size of output i along its shard dimension before sharding.  The buffers of the

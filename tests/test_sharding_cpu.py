@@ -77,3 +77,51 @@ def test_two_rank_gloo_shard_run_gather(name):
     if name == "batchmatmul":
         shapes = dict((r, s) for r, _, s in results)
         assert shapes[0][0][0] == 4 and shapes[1][0][0] == 3
+
+
+def _failing_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    from oracle import oracle as orc
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        name = "tmm"
+        w = wl.ALL[name](**wl.SMALL[name])
+        full = wl.make_inputs(w)
+
+        def compile_fn(tc, entry, options, *ins):
+            if rank == 1:
+                raise ValueError("this rank's kernels refuse the shard")   # the failure is made on the host
+            return lambda *xs: orc.ATEN[name](*xs)
+
+        prog = sharding.ShardedProgram(w, world, rank, compile_fn=compile_fn)
+        try:
+            prog.run_and_gather(prog.shard_inputs(full), [full[1].shape[0]])
+            q.put((rank, "no error"))
+        except sharding.RankFailure as e:
+            q.put((rank, e.failed_ranks, "refuse the shard" in str(e)))
+        # the group is still usable: a healthy exchange afterwards goes through on both ranks
+        good = sharding.ShardedProgram(w, world, rank, compile_fn=lambda *a: (lambda *xs: orc.ATEN[name](*xs)))
+        out = good.run_and_gather(good.shard_inputs(full), [full[1].shape[0]])[0]
+        q.put((rank, "recovered", tuple(out.shape)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_a_failing_rank_is_reported_on_every_rank_before_the_exchange():
+    """One rank raises on the host while compiling its shard: both ranks get RankFailure naming it, nobody hangs
+    in the all-gather, and the next exchange on the same group works."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() + 977) % 2000
+    procs = [ctx.Process(target=_failing_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in range(4)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    first = sorted(r for r in results if r[1] != "recovered")
+    assert first == [(0, [1], False), (1, [1], True)], results   # rank 1 also carries its own error text
+    assert sorted(r for r in results if r[1] == "recovered") == [(0, "recovered", (70, 200)), (1, "recovered", (70, 200))]
