@@ -766,7 +766,9 @@ __host__ __device__ constexpr int ts_pair_out_offset() { return (ts_pair_rings_b
 __host__ __device__ constexpr int ts_pair_smem_bytes() { return ts_pair_out_offset() + kPairOutBytes + 1024; }
 static_assert(ts_pair_smem_bytes() <= kTsSmemLimit, "rings + output staging tile exceed shared memory");
 
-template <int CHUNK>
+// TAIL: the launch ends with split tail units (a compile-time switch: carried as run-time state the unit
+// bookkeeping cost the kernel 2 % on launches that have no tail).
+template <int CHUNK, bool TAIL>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTsThreads, 1)
 contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
                            const __grid_constant__ CUtensorMap tmB,
@@ -821,9 +823,9 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   // epilogue.  256 tiles on 74 pairs are then 3 rounds of whole tiles and one round of half-length units
   // instead of 4 rounds.
   const int64_t all_tiles = (int64_t)tiles_n * tiles_m * a.batch;  // tiles of 256 x BN
-  const int64_t main_units = a.tail_S > 0 ? all_tiles - a.tail_tiles : all_tiles;
-  const int64_t num_tiles = main_units + (a.tail_S > 0 ? (int64_t)a.tail_tiles * a.tail_S : 0);  // units
-  auto unit_kb = [&](int64_t t) { return t < main_units ? num_kb : a.tail_kb; };
+  const int64_t main_units = TAIL ? all_tiles - a.tail_tiles : all_tiles;
+  const int64_t num_tiles = main_units + (TAIL ? (int64_t)a.tail_tiles * a.tail_S : 0);  // units
+  auto unit_kb = [&](int64_t t) { return !TAIL || t < main_units ? num_kb : a.tail_kb; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < 4; ++s) {
@@ -876,7 +878,7 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     int64_t tile = t;
     *slot = -1;
     *k0 = 0;
-    if (t >= main_units) {
+    if (TAIL && t >= main_units) {
       const int64_t r = t - main_units;
       tile = main_units + r % a.tail_tiles;
       *k0 = (int)(r / a.tail_tiles) * a.tail_kb * BK;
@@ -1035,7 +1037,7 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       nkb = unit_kb(t);
       int m0, n0, bz, k0, slot;
       tile_coords(t, &m0, &n0, &bz, &k0, &slot);
-      const bool tail = slot >= 0;               // raw partial tile to scratch, no epilogue
+      const bool tail = TAIL && slot >= 0;       // raw partial tile to scratch, no epilogue
       const int epi = tail ? (int)TCB200_EPI_NONE : a.epi;
       const int row = m0 + q * 32 + lane;
       float* crow = a.C + (int64_t)bz * a.stride_c + (int64_t)row * a.ldc;
@@ -1294,25 +1296,28 @@ int launch_ts(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, co
                                    : launch_ts<BN, kTsChunkKB>(plan, ta, tb, args, s);
 }
 
-template <int CHUNK>
-int launch_pair_chunk(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
-                      const CUtensorMap& tp, const TcArgs& args, cudaStream_t s) {
+template <int CHUNK, bool TAIL>
+int launch_pair_inst(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                     const CUtensorMap& tp, const TcArgs& args, cudaStream_t s) {
   static std::atomic<uint64_t> configured{0};  // bit per device
   const uint64_t bit = 1ull << (plan.device & 63);
   if (!(configured.load(std::memory_order_acquire) & bit)) {
-    TCB200_CUDA_TRY(cudaFuncSetAttribute(contraction_ts_pair_kernel<CHUNK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         ts_pair_smem_bytes()));
+    TCB200_CUDA_TRY(cudaFuncSetAttribute(contraction_ts_pair_kernel<CHUNK, TAIL>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, ts_pair_smem_bytes()));
     configured.fetch_or(bit, std::memory_order_release);
   }
   // the kernel carries its cluster shape (2 CTAs); the grid is a multiple of 2
-  TCB200_CUDA_TRY(launch_pdl(contraction_ts_pair_kernel<CHUNK>, plan.launch.grid, dim3(kTsThreads, 1, 1),
+  TCB200_CUDA_TRY(launch_pdl(contraction_ts_pair_kernel<CHUNK, TAIL>, plan.launch.grid, dim3(kTsThreads, 1, 1),
                              (size_t)ts_pair_smem_bytes(), s, ta, tb, tc, tp, args));
   return TCB200_OK;
 }
 int launch_pair(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
                 const CUtensorMap& tp, const TcArgs& args, cudaStream_t s) {
-  return plan.tile.split_tf32 == 4 ? launch_pair_chunk<1>(plan, ta, tb, tc, tp, args, s)
-                                   : launch_pair_chunk<kPairChunkKB>(plan, ta, tb, tc, tp, args, s);
+  const bool strict = plan.tile.split_tf32 == 4, tail = args.tail_S > 0;
+  if (strict) return tail ? launch_pair_inst<1, true>(plan, ta, tb, tc, tp, args, s)
+                          : launch_pair_inst<1, false>(plan, ta, tb, tc, tp, args, s);
+  return tail ? launch_pair_inst<kPairChunkKB, true>(plan, ta, tb, tc, tp, args, s)
+              : launch_pair_inst<kPairChunkKB, false>(plan, ta, tb, tc, tp, args, s);
 }
 
 }  // namespace
@@ -1356,12 +1361,18 @@ int pick_split_k(const tcb200_problem_t& p, int64_t tiles, int slots, double kb_
 // of the persistent pairs (256 tiles on 74 pairs: three full rounds and 34 tiles), the last r = tiles % pairs
 // tiles have their reduction split S ways so that the last round lasts 1 / S of a round.  S is the largest
 // split, up to 4, whose r * S units still fit one round and leave every unit at least 8 k-blocks.
+// Offered only when a round is long (K >= 1792): the second pass and the extra launch cost ~3 us, and the board
+// runs these kernels at its power limit, so SMs that idle at the end of a launch are partly paid back in clock
+// to the busy ones.  Measured with the plain tile beside it: 8192 x 1024 x 2048 146.1 -> 141.8 us, but
+// 16384 x 512 x 1024 (K = 1024) 77.4 -> 79.8 us.
 constexpr int kTailSplitBase = 100;
+constexpr int64_t kTailSplitMinKB = 56;
 int tail_split_factor(const tcb200_problem_t& p, int64_t tiles, int pairs) {
   if (p.batch != 1 || tiles <= pairs) return 0;
   const int64_t r = tiles % pairs;
   if (r == 0) return 0;
   const int64_t kbs = ceil_div(p.K, BK);
+  if (kbs < kTailSplitMinKB) return 0;
   int64_t S = std::min<int64_t>({(int64_t)pairs / r, 4, kbs / 8});
   return S >= 2 ? (int)S : 0;
 }

@@ -50,7 +50,7 @@ CONTRACTIONS = [
     (1, 70, 230, 260, True, True, cabi.EPI_BIAS, tile(cabi.VARIANT_TCGEN05_TS, 112, 3)),
     (2, 300, 136, 96, True, True, cabi.EPI_NONE, tile(cabi.VARIANT_TCGEN05_PAIR, 128, 3)),
     (1, 300, 200, 1000, True, True, cabi.EPI_BIAS_RELU, tile(cabi.VARIANT_TCGEN05_TS, 64, 3, split_k=5)),
-    (1, 5000, 500, 1000, True, True, cabi.EPI_BIAS_RELU, None),   # pair tiles with a split tail
+    (1, 5000, 500, 1800, True, True, cabi.EPI_BIAS_RELU, None),   # pair tiles with a split tail
     (1, 130, 100, 132, True, True, cabi.EPI_NONE, tile(cabi.VARIANT_TCGEN05, 128, 3)),
     (3, 70, 45, 33, True, False, cabi.EPI_NONE, tile(cabi.VARIANT_SIMT)),
     (3, 70, 45, 33, False, True, cabi.EPI_RELU, tile(cabi.VARIANT_SIMT)),

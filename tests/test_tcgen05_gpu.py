@@ -307,8 +307,8 @@ def test_strict_accumulation_tiles_meet_the_reference_bound_on_all_positive_data
 
 @pytest.mark.parametrize("case", [
     # (M, N, K): CTA-pair tiles that do not fill the last round of the 74 pairs
-    (5120, 512, 1024),     # 80 tiles: one full round and 6 tail tiles split 4 ways
-    (5000, 500, 1000),     # the same with ragged rows, columns and k-blocks
+    (5120, 512, 2048),     # 80 tiles: one full round and 6 tail tiles split 4 ways
+    (5000, 500, 1800),     # the same with ragged rows, columns and k-blocks
     (8192, 1024, 2048),    # MLP layer 1 on an 8192-row shard: 256 tiles, 34 tail tiles split in two
 ])
 @pytest.mark.parametrize("epi", [cabi.EPI_NONE, cabi.EPI_BIAS_RELU])
@@ -339,7 +339,7 @@ def test_pair_tiles_with_a_split_tail(cuda, case, epi):
 
 
 def test_pair_tail_split_accumulates_and_takes_odd_outputs(cuda):
-    M, N, K = 5120, 512, 1024
+    M, N, K = 5120, 512, 1792
     A, B, init = _rand((M, K), 84), _rand((N, K), 85), _rand((M, N), 86)
     ref = (A.double() @ B.double().t() + init.double()).float()
     p = cabi.contraction_problem(1, M, N, K, True, True, accumulate=True)
