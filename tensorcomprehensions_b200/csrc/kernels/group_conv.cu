@@ -776,6 +776,11 @@ int group_conv_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int
       ++cnt;
     }
   }
+  // tensor-core form with the filters stationary in tensor memory (stages = 3: its accumulator ring)
+  if (group_conv_tap_rows_ok(p)) {
+    if (cnt < max && out) out[cnt] = tcb200_tile_t{TCB200_VARIANT_TCGEN05_TS, 128, 128, 8, 3, 512, 3};
+    ++cnt;
+  }
   // tensor-core implicit GEMM: correct and fp32-accurate, but hand-off latency bound on small
   // problems (see group_conv_tcgen05.cu); the sweep can still pick it where it wins
   if (group_conv_tc_ok(p)) {
@@ -798,6 +803,7 @@ int group_conv_plan(Plan& plan) {
   if (p.epilogue == TCB200_EPI_RELU) return TCB200_ERR_UNSUPPORTED;
   tcb200_tile_t& t = plan.tile;
   if (t.variant == TCB200_VARIANT_AUTO && !rows_ok(p) && group_conv_tc_ok(p)) t.variant = TCB200_VARIANT_TCGEN05_TS;
+  if (t.variant == TCB200_VARIANT_TCGEN05_TS && t.stages == 3) return group_conv_tap_rows_plan(plan);
   if (t.variant == TCB200_VARIANT_TCGEN05_TS) return group_conv_tc_plan(plan);
   if (t.variant == TCB200_VARIANT_AUTO) {
     t.variant = TCB200_VARIANT_SIMT;
@@ -894,8 +900,10 @@ int group_conv_launch(const Plan& plan, const float* I, const float* W, const fl
   // The item kernel stages I and W with 16-byte asynchronous copies.  A dense tensor may still start at any
   // 4-byte offset of a larger buffer (a view): such a launch runs on the band kernel, which uses 4-byte loads.
   const bool multi = plan.kernel_id == 103 || plan.kernel_id == 104;
-  const bool item_misaligned = (plan.kernel_id == 101 || plan.kernel_id == 102 || plan.kernel_id == 105 || multi) &&
-                               ((((uintptr_t)I) | ((uintptr_t)W)) & 15) != 0;
+  const bool item_misaligned = ((plan.kernel_id == 101 || plan.kernel_id == 102 || plan.kernel_id == 105 || multi) &&
+                                ((((uintptr_t)I) | ((uintptr_t)W)) & 15) != 0) ||
+                               (plan.kernel_id == 201 && !group_conv_tap_rows_aligned(I, O));
+  if (plan.kernel_id == 201 && !item_misaligned) return group_conv_tap_rows_launch(plan, I, W, bias, O, s, dev_status);
   if (plan.kernel_id == 105 && !item_misaligned) {
     const bool k33 = a.KH == 3 && a.KW == 3;
     auto fn = k33 ? group_conv_item_split_kernel<3> : group_conv_item_split_kernel<0>;

@@ -1,0 +1,494 @@
+// K3 (tensor-core variant, filter rows) — grouped valid convolution on tcgen05 with the FILTERS as the
+// stationary operand and the filter rows (kh) as rows of the accumulator, 3xTF32.
+//
+//   O(n,g,f,oh,ow) = sum_{c,kh,kw} I(n,g,c,oh+kh,ow+kw) * W(g,f,c,kh,kw)  [+ B(g,f)]
+//
+// With C = F = 16 an implicit GEMM whose accumulator is (pixels x F) issues MMAs of N = 16: an eighth of
+// the tensor pipe, two hundred of them per item.  Here the roles are turned round.  Per work item (n, g)
+//
+//   D[(kh, f), p] = sum_{kw, c}  A[(kh, f), (kw, c)] * B[p + kw, c]        p = flat pixel h * W + w
+//   A[(kh, f), (kw, c)] = W(g, f, c, kh, kw)          48 x 48, in TENSOR MEMORY, loaded once per group
+//   B[p, c]             = I(n, g, c, p)               the item's own 16 KB slab, never replicated
+//   O(f, oh, ow)        = D[(0,f), oh*W+ow] + D[(1,f), (oh+1)*W+ow] + D[(2,f), (oh+2)*W+ow]
+//
+// so an MMA is 128 x 128 x 8 (N = 128 pixels), 36 of them per item, and the only im2col left is the sum
+// over the three filter rows, done on the accumulator rows after the MMAs.
+//   * kw is a shift of B by kw pixels.  B sits in shared memory k-major WITHOUT swizzle as
+//     [chunk of 4 channels][pixel][4 floats]: pixel p of a chunk is 16 bytes at p * 16, i.e. the 8-row core
+//     matrices follow each other at 128 bytes and a descriptor may start at ANY pixel.  The shift is the
+//     descriptor's start address; nothing is copied per tap.
+//   * kh is a shift by W = 16 accumulator columns, i.e. a sum over accumulator ROWS at shifted columns.  It is
+//     done through shared memory: eight warps copy the 48 live rows of a finished accumulator to shared memory
+//     (one 32-column load and eight 128-bit stores per warp and unit: the accumulator is free again a few
+//     hundred cycles after its last MMA), then every thread forms four adjacent outputs from three 128-bit
+//     loads, always as (kh0 + kh1) + kh2, and stages them for the item's bulk store.
+// The slab arrives by one bulk copy (cp.async.bulk + mbarrier, 3 stages); four warps re-lay it into the
+// chunked layout and produce the low half of the 3xTF32 split (the tensor core truncates the raw fp32 to
+// its high half itself); two threads in different warps issue the MMAs of alternate 128-pixel units (a
+// thread that has just issued MMAs pays a few hundred cycles for its next barrier wait); one thread issues the
+// bulk store of each finished item.  A warp reads only the 32 tensor-memory lanes of its position in its warp
+// quad, so the filter rows are written twice, into lanes 0-63 and 64-127 (the MMA computes 128 rows whatever
+// it is given): the warps at positions 0/1 copy the first 64 columns of a unit, those at 2/3 the other 64.
+// CTAs are persistent (one per SM) over a contiguous run of items in group-major order, so the filters change
+// at most once or twice per CTA.
+// All mbarrier waits are bounded; on expiry a code is written to *dev_status and every role leaves its loop.
+#include <atomic>
+
+#include "async.cuh"
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace tcb200 {
+namespace {
+
+// Out of line: the waits sit in loops whose bodies should stay small in the instruction cache.
+static __device__ __noinline__ bool wait_bar(uint64_t* bar, uint32_t parity, unsigned ns, int code, int* dev_status,
+                                             volatile int* abort_flag) {
+  return mbar_wait_relaxed(bar, parity, ns, code, dev_status, abort_flag);
+}
+
+constexpr int kThreads = 512;
+constexpr int kW = 16;              // input row pitch = accumulator columns per input row
+constexpr int kRawStages = 3;
+constexpr int kAccRing = 3;         // 128-column accumulators, one per unit of 8 input rows
+constexpr int kDrainWarps = 8;
+constexpr int kDumpPitch = 260;     // floats per accumulator row in shared memory: 128-bit stores of 32 rows hit all banks
+// Barriers of the accumulator hand-off, indexed by unit mod 6 although there are three accumulators.  A parity
+// wait only tells two phases apart, so every waiter must see each phase of its barrier: every drain warp waits
+// for every unit, and issuer u mod 2 owns the even or the odd barriers.  6 is also a multiple of the ring length,
+// so the next unit on a barrier reuses the same accumulator and cannot complete a phase before the waiters of
+// the previous one have been through.
+constexpr int kAccBars = 6;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kACol = 128 * kAccRing;   // filters: hi at [384, 384 + KW*C), lo right behind
+constexpr int kPadPixels = 8;       // zeroed pixels behind the plane: the shifted reads of the last unit
+
+struct TapRowsArgs {
+  const float* I;
+  const float* W;
+  const float* bias;
+  float* O;
+  int N, G, F, H, KH, KW, OH, OW;
+  int items;
+  int units;            // 128-pixel units per item
+  int n_last;           // pixels of the last unit
+  int epi;
+  uint32_t in_bytes;    // one item's slab
+  uint32_t pitch_b;     // bytes between channel chunks of the re-laid operand
+  uint32_t half_out;    // bytes of 8 output channels of one item
+  int* dev_status;
+};
+
+__device__ __forceinline__ void bulk_store(void* gdst, const void* ssrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(ssrc)),
+               "r"(bytes)
+               : "memory");
+}
+
+// shared-memory map (offsets are multiples of 128):
+//   kRawStages x in_bytes                     raw slabs (c, h, w)
+//   2 x 2 x (C/4) x pitch_b                   re-laid operand, [buffer][hi | lo][chunk][pixel][4]
+//   3 x 16 x kDumpPitch floats                accumulator rows (kh, f) of the item being reduced
+//   2 x out_bytes                             output staging, by item parity
+//   barriers
+template <int C>
+__global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRowsArgs a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int PL = a.H * kW;
+  const int KC = a.KW * C;                        // reduction length of one accumulator row
+  const uint32_t b_half = (uint32_t)(C / 4) * a.pitch_b;
+  uint8_t* raw = smem;
+  uint8_t* bop = raw + (size_t)kRawStages * a.in_bytes;
+  float* dump = reinterpret_cast<float*>(bop + (size_t)4 * b_half);
+  uint8_t* ost = reinterpret_cast<uint8_t*>(dump + 48 * kDumpPitch);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ost + (size_t)4 * a.half_out);
+  uint64_t* raw_full = bars;                      // [kRawStages]
+  uint64_t* raw_empty = raw_full + kRawStages;    // [kRawStages]
+  uint64_t* b_ready = raw_empty + kRawStages;     // [2]
+  uint64_t* b_free = b_ready + 2;                 // [2]
+  uint64_t* acc_full = b_free + 2;                // [kAccBars]
+  uint64_t* acc_empty = acc_full + kAccBars;      // [kAccBars]
+  uint64_t* a_ready = acc_empty + kAccBars;       // [1]
+  uint64_t* a_free = a_ready + 1;                 // [1]
+  uint64_t* st_done = a_free + 1;                 // [2] staged outputs of an item complete (item parity)
+  uint64_t* st_free = st_done + 2;                // [2] its bulk store has read the staging region
+  uint64_t* dump_full = st_free + 2;              // [1] both units of the item are in shared memory
+  uint64_t* dump_free = dump_full + 1;            // [1] ... and have been reduced
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dump_free + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = a.F / 8;                         // warps (of a set) that own output channels
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kRawStages; ++s) {
+      mbar_init(&raw_full[s], 1);
+      mbar_init(&raw_empty[s], 4);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&b_ready[b], 4);
+      mbar_init(&b_free[b], a.units >= 2 ? 2 : 1);
+    }
+    for (int k = 0; k < kAccBars; ++k) {
+      mbar_init(&acc_full[k], 1);
+      mbar_init(&acc_empty[k], kDrainWarps);
+    }
+    for (int k = 0; k < 2; ++k) {
+      mbar_init(&st_done[k], kDrainWarps);
+      mbar_init(&st_free[k], 1);
+    }
+    mbar_init(dump_full, kDrainWarps);
+    mbar_init(dump_free, kDrainWarps);
+    mbar_init(a_ready, 4);
+    mbar_init(a_free, 2);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 12) tmem_alloc(tmem_slot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_sync();  // nothing above touches global memory
+
+  // contiguous run of work indices w = g * N + n for this CTA; the slab index of I and O is n * G + g
+  const int begin = (int)((int64_t)a.items * blockIdx.x / gridDim.x);
+  const int end = (int)((int64_t)a.items * (blockIdx.x + 1) / gridDim.x);
+  const int nitems = end - begin;
+  const int U = a.units;
+
+  if (warp == 12) {
+    // ------------------------------------------------ producer: one bulk copy per item
+    if (lane == 0) {
+      for (int j = 0; j < nitems; ++j) {
+        const int st = j % kRawStages;
+        const uint32_t ph = (uint32_t)(j / kRawStages) & 1;
+        if (!wait_bar(&raw_empty[st], ph ^ 1, 32, 22, a.dev_status, abort_flag)) break;
+        const int w = begin + j, g = w / a.N, n = w - g * a.N;
+        mbar_expect_tx(&raw_full[st], a.in_bytes);
+        bulk_load(raw + (size_t)st * a.in_bytes,
+                  reinterpret_cast<const uint8_t*>(a.I) + ((size_t)n * a.G + g) * a.in_bytes, a.in_bytes,
+                  &raw_full[st]);
+      }
+    }
+  } else if (warp == 13 || warp == 14) {
+    // ------------------------------------------------ MMA issuers: units of alternate parity
+    if (lane == 0) {
+      const uint32_t q = warp == 13 ? 0u : 1u;
+      int cur_g = -1;
+      uint32_t epoch = 0;
+      bool ok = true;
+      for (int j = 0; j < nitems && ok; ++j) {
+        const int g = (begin + j) / a.N;
+        if (g != cur_g) {
+          if (cur_g >= 0) umma_commit(a_free);   // my MMAs on the old filters are done when this arrives
+          ok = wait_bar(a_ready, epoch & 1, 32, 23, a.dev_status, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          ++epoch;
+          cur_g = g;
+        }
+        const uint32_t b = (uint32_t)j & 1, bph = ((uint32_t)j >> 1) & 1;
+        const uint32_t bhi = smem_u32(bop + (size_t)(b * 2 + 0) * b_half);
+        const uint32_t blo = smem_u32(bop + (size_t)(b * 2 + 1) * b_half);
+        bool mine = false;
+        for (int h = 0; h < U && ok; ++h) {
+          const uint32_t u = (uint32_t)(j * U + h);
+          if ((u & 1) != q) continue;
+          if (!mine) {
+            ok = wait_bar(&b_ready[b], bph, 32, 24, a.dev_status, abort_flag);
+            if (!ok) break;
+            mine = true;
+          }
+          const uint32_t k = u % kAccRing;
+          if (u >= kAccRing) {   // the accumulator's previous unit has been drained
+            const uint32_t v = u - kAccRing;
+            ok = wait_bar(&acc_empty[v % kAccBars], (v / kAccBars) & 1, 32, 25, a.dev_status, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          const uint32_t idesc = make_idesc_tf32(128, h == U - 1 ? a.n_last : 128);
+          const uint32_t acc = tmem_base + k * 128;
+          uint32_t accumulate = 0;
+          for (int kw = 0; kw < a.KW; ++kw) {
+#pragma unroll
+            for (int c8 = 0; c8 < C / 8; ++c8) {
+              const uint32_t boff = (uint32_t)(2 * c8) * a.pitch_b + (uint32_t)(h * 128 + kw) * 16;
+              const uint64_t d_hi = make_desc_noswizzle(bhi + boff, a.pitch_b, 128);
+              const uint64_t d_lo = make_desc_noswizzle(blo + boff, a.pitch_b, 128);
+              const uint32_t a_hi = tmem_base + kACol + kw * C + c8 * 8, a_lo = a_hi + KC;
+              umma_tf32_ts(acc, a_lo, d_hi, idesc, accumulate);   // small terms first
+              umma_tf32_ts(acc, a_hi, d_lo, idesc, 1u);
+              umma_tf32_ts(acc, a_hi, d_hi, idesc, 1u);
+              accumulate = 1u;
+            }
+          }
+          umma_commit(&acc_full[u % kAccBars]);
+        }
+        if (ok && mine) umma_commit(&b_free[b]);
+      }
+    }
+  } else if (warp < 4) {
+    // ------------------------------------------------ re-lay + split (and the filters, once per group): warps 0-3
+    const int t = threadIdx.x;   // 0..127
+    // filters: lane 8 kh + j of warp q holds filter row kh of output channel 8 (q mod 2) + j, columns (kw, c)
+    const int wkh = lane >> 3, wf = (warp & 1) * 8 + (lane & 7);
+    const bool wlive = wkh < a.KH && wf < a.F;
+    const uint32_t ta = tmem_base + kACol + ((uint32_t)(warp * 32) << 16);
+    int cur_g = -1;
+    uint32_t epoch = 0;
+    // pixels behind the plane, read by the shifted descriptors of the last unit: zero, once
+    for (int e = t; e < 4 * (C / 4) * kPadPixels; e += 128) {
+      const int buf = e / ((C / 4) * kPadPixels), r = e - buf * (C / 4) * kPadPixels;
+      const int ch = r / kPadPixels, px = r - ch * kPadPixels;
+      *reinterpret_cast<float4*>(bop + (size_t)buf * b_half + (size_t)ch * a.pitch_b + (size_t)(PL + px) * 16) =
+          make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    // Filters of group g into tensor memory.  They are fetched before the wait for the MMAs of the previous group
+    // (which still read the old ones) and written after it.
+    auto filters = [&](const int g) -> bool {
+      const float* wg = a.W + ((size_t)g * a.F + wf) * C * a.KH * a.KW + wkh * a.KW;
+      float wv[3 * C];
+#pragma unroll
+      for (int col = 0; col < 3 * C; ++col) {
+        const int kw = col / C, c = col - kw * C;
+        wv[col] = wlive && kw < a.KW ? __ldg(wg + (size_t)c * a.KH * a.KW + kw) : 0.f;
+      }
+      if (cur_g >= 0) {
+        if (!wait_bar(a_free, (epoch - 1) & 1, 64, 21, a.dev_status, abort_flag)) return false;
+        tc_fence_after();
+      }
+#pragma unroll
+      for (int k8 = 0; k8 < 3 * C / 8; ++k8) {
+        if (k8 * 8 < KC) {
+          float lo[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) lo[i] = tf32_lo(wv[k8 * 8 + i]);
+          tmem_st8(ta + k8 * 8, &wv[k8 * 8]);
+          tmem_st8(ta + KC + k8 * 8, lo);
+        }
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive_warp(a_ready);
+      cur_g = g;
+      ++epoch;
+      return true;
+    };
+    // the first group's filters while the first slab is on its way; later groups after their first item's
+    // operand has been handed over (the MMAs of that item wait for both)
+    if (nitems > 0) filters(begin / a.N);   // nothing to wait for the first time
+    for (int j = 0; j < nitems; ++j) {
+      const int st = j % kRawStages;
+      const uint32_t ph = (uint32_t)(j / kRawStages) & 1;
+      const uint32_t b = (uint32_t)j & 1, bph = ((uint32_t)j >> 1) & 1;
+      if (!wait_bar(&raw_full[st], ph, 64, 26, a.dev_status, abort_flag)) break;
+      if (!wait_bar(&b_free[b], bph ^ 1, 64, 27, a.dev_status, abort_flag)) break;
+      const float* src = reinterpret_cast<const float*>(raw + (size_t)st * a.in_bytes);
+      uint8_t* hi = bop + (size_t)(b * 2 + 0) * b_half;
+      uint8_t* lo = bop + (size_t)(b * 2 + 1) * b_half;
+      for (int p = t; p < PL; p += 128) {
+#pragma unroll
+        for (int ch = 0; ch < C / 4; ++ch) {
+          float4 v;
+          v.x = src[(ch * 4 + 0) * PL + p];
+          v.y = src[(ch * 4 + 1) * PL + p];
+          v.z = src[(ch * 4 + 2) * PL + p];
+          v.w = src[(ch * 4 + 3) * PL + p];
+          *reinterpret_cast<float4*>(hi + (size_t)ch * a.pitch_b + (size_t)p * 16) = v;
+          *reinterpret_cast<float4*>(lo + (size_t)ch * a.pitch_b + (size_t)p * 16) =
+              make_float4(tf32_lo(v.x), tf32_lo(v.y), tf32_lo(v.z), tf32_lo(v.w));
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive_warp(&raw_empty[st]);
+      mbar_arrive_warp(&b_ready[b]);
+      const int g = (begin + j) / a.N;
+      if (g != cur_g && !filters(g)) break;
+    }
+  } else if (warp < 12) {
+    // ------------------------------------------------ drain: warps 4-11, all of them on every item
+    // Copy: position in the quad = 2 * (column half of the unit) + (half of the output channels); the two
+    // warps of a position take 32 columns each.  Lane 8 kh + j holds filter row kh of channel 8 q + j.
+    const int q = warp & 1;
+    const int col0 = (warp & 2) * 32 + (warp >= 8 ? 32 : 0);            // first of my 32 columns of a unit
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const int kh = lane >> 3, f_mine = q * 8 + (lane & 7);
+    const bool live_row = kh < 3 && f_mine < a.F;
+    float* my_row = dump + (size_t)(kh * 16 + f_mine) * kDumpPitch;
+    // Reduce: a warp task = one output channel x eight output rows; lane = (row, group of four columns).
+    const int dw = warp - 4;
+    const int orow = lane >> 2, oc4 = (lane & 3) * 4;
+    const bool has_bias = a.epi == TCB200_EPI_BIAS || a.epi == TCB200_EPI_BIAS_RELU;
+    const bool relu = a.epi == TCB200_EPI_BIAS_RELU;
+    const int plane_out = a.OH * a.OW;
+    const bool even_ow = (a.OW & 1) == 0;
+    const int row_blocks = (a.OH + 7) >> 3;
+    bool ok = true;
+    for (int j = 0; j < nitems && ok; ++j) {
+      const int g = (begin + j) / a.N;
+      const uint32_t sb = (uint32_t)j & 1, sph = ((uint32_t)j >> 1) & 1;
+      float* stage = reinterpret_cast<float*>(ost + (size_t)sb * 2 * a.half_out);
+      // the previous item has been reduced out of the copy area
+      if (j >= 1) ok = wait_bar(dump_free, (uint32_t)(j - 1) & 1, 32, 32, a.dev_status, abort_flag);
+      for (int h = 0; h < U && ok; ++h) {
+        const uint32_t u = (uint32_t)(j * U + h);
+        ok = wait_bar(&acc_full[u % kAccBars], (u / kAccBars) & 1, 32, 28, a.dev_status, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const int ncols = h == U - 1 ? a.n_last : 128;
+        float v[32];
+        const uint32_t ta = tmem_base + (u % kAccRing) * 128 + (uint32_t)col0 + lane_addr;
+        if (col0 < ncols) tmem_ld16_nowait(ta, v);
+        if (col0 + 16 < ncols) tmem_ld16_nowait(ta + 16, v + 16);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive_warp(&acc_empty[u % kAccBars]);          // the accumulator goes back to the issuers
+        if (live_row) {
+          float4* dst = reinterpret_cast<float4*>(my_row + h * 128 + col0);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (col0 + 4 * i < ncols) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        }
+      }
+      if (!ok) break;
+      mbar_arrive_warp(dump_full);
+      ok = wait_bar(dump_full, (uint32_t)j & 1, 20, 33, a.dev_status, abort_flag);
+      if (!ok) break;
+      if (j >= 2) {   // the staging region was last used by item j - 2: its bulk store has read it
+        ok = wait_bar(&st_free[sb], sph ^ 1, 32, 30, a.dev_status, abort_flag);
+        if (!ok) break;
+      }
+      for (int task = dw; task < a.F * row_blocks; task += kDrainWarps) {
+        const int f = task / row_blocks, oh = (task - f * row_blocks) * 8 + orow;
+        if (oh < a.OH) {
+          const float* src = dump + (size_t)f * kDumpPitch + oh * kW + oc4;
+          const float4 x0 = *reinterpret_cast<const float4*>(src);
+          const float4 x1 = *reinterpret_cast<const float4*>(src + 16 * kDumpPitch + kW);
+          const float4 x2 = *reinterpret_cast<const float4*>(src + 32 * kDumpPitch + 2 * kW);
+          const float bias = has_bias ? __ldg(a.bias + g * a.F + f) : 0.f;
+          float r[4] = {((x0.x + x1.x) + x2.x) + bias, ((x0.y + x1.y) + x2.y) + bias,
+                        ((x0.z + x1.z) + x2.z) + bias, ((x0.w + x1.w) + x2.w) + bias};
+          if (relu) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) r[i] = fmaxf(r[i], 0.f);
+          }
+          float* dst = stage + (size_t)f * plane_out + oh * a.OW + oc4;
+          if (even_ow) {   // rows of an even length start on 8-byte boundaries
+            if (oc4 < a.OW) *reinterpret_cast<float2*>(dst) = make_float2(r[0], r[1]);
+            if (oc4 + 2 < a.OW) *reinterpret_cast<float2*>(dst + 2) = make_float2(r[2], r[3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              if (oc4 + i < a.OW) dst[i] = r[i];
+          }
+        }
+      }
+      mbar_arrive_warp(dump_free);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive_warp(&st_done[sb]);
+    }
+  } else if (warp == 15) {
+    // ------------------------------------------------ output: one bulk store per item
+    // (a thread of its own, so that no drain warp waits for the others or for the store)
+    if (lane == 0) {
+      for (int j = 0; j < nitems; ++j) {
+        const int w = begin + j, g = w / a.N, n = w - g * a.N;
+        const uint32_t sb = (uint32_t)j & 1, sph = ((uint32_t)j >> 1) & 1;
+        if (j >= 1) {   // the store of item j - 1 has read its region: free for item j + 1, well before it gets there
+          tma_store_wait_read();
+          mbar_arrive(&st_free[sb ^ 1]);
+        }
+        if (!wait_bar(&st_done[sb], sph, 32, 31, a.dev_status, abort_flag)) break;
+        const size_t out_bytes = (size_t)nq * a.half_out;
+        bulk_store(reinterpret_cast<uint8_t*>(a.O) + ((size_t)n * a.G + g) * out_bytes,
+                   ost + (size_t)sb * 2 * a.half_out, (uint32_t)out_bytes);
+        tma_store_commit();
+      }
+      tma_store_wait_all();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 12) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+struct Geometry {
+  int units, n_last;
+  uint32_t in_bytes, pitch_b, half_out;
+  size_t smem;
+};
+
+bool geometry(const tcb200_problem_t& p, Geometry* g) {
+  if (conv_sh(p) != 1 || conv_sw(p) != 1) return false;
+  const int64_t C = p.conv[2], F = p.conv[3], H = p.conv[4], W = p.conv[5], KH = p.conv[6], KW = p.conv[7];
+  if (W != kW || H < 3 || H > 16) return false;
+  if (KH != 3 || KW < 1 || KW > 3) return false;
+  if (!(C == 8 || C == 16) || !(F == 8 || F == 16)) return false;
+  const int64_t OH = H - KH + 1, OW = W - KW + 1;
+  const int64_t PL = H * W;
+  g->units = (int)ceil_div(PL, 128);
+  g->n_last = (int)(PL - 128 * (g->units - 1));
+  g->in_bytes = (uint32_t)(C * PL * 4);
+  g->pitch_b = (uint32_t)((PL + kPadPixels) * 16);
+  g->half_out = (uint32_t)(8 * OH * OW * 4);
+  g->smem = (size_t)kRawStages * g->in_bytes + (size_t)4 * (C / 4) * g->pitch_b +
+            (size_t)48 * kDumpPitch * 4 + (size_t)4 * g->half_out + 512;   // barriers, tensor-memory slot, abort flag
+  return g->in_bytes % 128 == 0 && g->half_out % 16 == 0 && g->smem <= 200 * 1024;
+}
+
+}  // namespace
+
+bool group_conv_tap_rows_ok(const tcb200_problem_t& p) {
+  Geometry g;
+  return geometry(p, &g) && p.epilogue != TCB200_EPI_RELU && !p.accumulate;
+}
+
+int group_conv_tap_rows_plan(Plan& plan) {
+  Geometry g;
+  if (!group_conv_tap_rows_ok(plan.p) || !geometry(plan.p, &g)) return TCB200_ERR_UNSUPPORTED;
+  tcb200_tile_t& t = plan.tile;
+  t.variant = TCB200_VARIANT_TCGEN05_TS;
+  t.bm = 128; t.bn = 128; t.bk = 8; t.stages = kAccRing; t.threads = kThreads; t.split_tf32 = 3;
+  const int64_t items = plan.p.conv[0] * plan.p.conv[1];
+  if (items > 0x7fffffffll) return TCB200_ERR_TOO_LARGE;
+  plan.launch.grid = dim3((unsigned)std::min<int64_t>(items, plan.sms), 1, 1);
+  plan.launch.block = dim3(kThreads, 1, 1);
+  plan.launch.smem = g.smem;
+  plan.kernel_id = 201;
+  return TCB200_OK;
+}
+
+// false: the pointers do not allow the bulk copies (16-byte alignment); the caller takes another kernel
+bool group_conv_tap_rows_aligned(const float* I, const float* O) {
+  return ((((uintptr_t)I) | ((uintptr_t)O)) & 15) == 0;
+}
+
+int group_conv_tap_rows_launch(const Plan& plan, const float* I, const float* W, const float* bias, float* O,
+                               cudaStream_t s, int* dev_status) {
+  const tcb200_problem_t& p = plan.p;
+  Geometry g;
+  if (!geometry(p, &g)) return TCB200_ERR_UNSUPPORTED;
+  if (!group_conv_tap_rows_aligned(I, O)) return TCB200_ERR_ALIGNMENT;
+  TapRowsArgs a;
+  a.I = I; a.W = W; a.bias = bias; a.O = O;
+  a.N = (int)p.conv[0]; a.G = (int)p.conv[1]; a.F = (int)p.conv[3];
+  a.H = (int)p.conv[4]; a.KH = (int)p.conv[6]; a.KW = (int)p.conv[7];
+  a.OH = a.H - a.KH + 1; a.OW = kW - a.KW + 1;
+  a.items = a.N * a.G;
+  a.units = g.units; a.n_last = g.n_last;
+  a.epi = p.epilogue;
+  a.in_bytes = g.in_bytes; a.pitch_b = g.pitch_b; a.half_out = g.half_out;
+  a.dev_status = dev_status;
+  const bool c16 = p.conv[2] == 16;
+  auto fn = c16 ? group_conv_tap_rows_kernel<16> : group_conv_tap_rows_kernel<8>;
+  static std::atomic<uint64_t> configured[2];
+  TCB200_CUDA_TRY(ensure_dynamic_smem(fn, 200 * 1024, plan.device, configured[c16]));
+  TCB200_CUDA_TRY(launch_pdl(fn, plan.launch.grid, plan.launch.block, g.smem, s, a));
+  return TCB200_OK;
+}
+
+}  // namespace tcb200

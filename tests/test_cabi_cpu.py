@@ -66,9 +66,12 @@ def test_query_and_plan_without_gpu():
     assert grid == (1024, 1, 1) and block == (128, 1, 1)  # item kernel: one CTA per (n, g), 2 channels per thread
     rows = [t for t in cabi.query(c) if t.variant == cabi.VARIANT_SIMT and t.bk == 2][0]
     assert cabi.Plan(c, rows).geometry()[0][:2] == (32, 16)  # rows kernel: one CTA per (g, pair of n)
-    tcv = [t for t in cabi.query(c) if t.variant == cabi.VARIANT_TCGEN05_TS][0]
+    tcv = [t for t in cabi.query(c) if t.variant == cabi.VARIANT_TCGEN05_TS and t.stages == 4][0]
     pt = cabi.Plan(c, tcv)
-    assert pt.geometry() == ((148, 1, 1), (448, 1, 1)) and "tcgen05_ts" in pt.describe()  # implicit GEMM
+    assert pt.geometry() == ((148, 1, 1), (448, 1, 1)) and "tcgen05_ts" in pt.describe()  # implicit GEMM, pixels x F
+    rows = [t for t in cabi.query(c) if t.variant == cabi.VARIANT_TCGEN05_TS and t.stages == 3][0]
+    pr = cabi.Plan(c, rows)   # filters stationary in tensor memory, filter rows as accumulator rows
+    assert pr.geometry() == ((148, 1, 1), (512, 1, 1)) and "tile=128x128x8" in pr.describe()
     band = [t for t in cabi.query(c) if t.variant == cabi.VARIANT_SIMT and t.bk == 0 and t.stages == 0][0]
     assert cabi.Plan(c, band).geometry()[0][0] == 32 * 32
 

@@ -161,6 +161,10 @@ def test_contraction_shared_operand_and_padded_ld(cuda):
     (2, 2, 16, 32, 10, 8, 5, 2),    # tensor-core form: F=32, non-square filter
     (5, 3, 16, 16, 9, 12, 1, 1),    # tensor-core form: 1x1 filter, odd item count
     (1, 1, 16, 16, 24, 20, 3, 3),   # tensor-core form: four pixel tiles
+    (3, 2, 8, 8, 16, 16, 3, 3),     # filter-row tensor-core form: C = F = 8
+    (5, 3, 16, 8, 11, 16, 3, 2),    # ... 11 input rows (two units, the second short), 15 output columns
+    (4, 2, 8, 16, 8, 16, 3, 1),     # ... one unit per item, one filter column
+    (9, 50, 16, 8, 12, 16, 3, 2),   # ... three items per CTA, group changes inside a CTA's run
 ])
 @pytest.mark.parametrize("bias", [True, False])
 def test_group_conv_small(cuda, dims, bias):
