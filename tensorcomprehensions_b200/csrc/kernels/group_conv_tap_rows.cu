@@ -42,9 +42,15 @@ namespace tcb200 {
 namespace {
 
 // Out of line: the waits sit in loops whose bodies should stay small in the instruction cache.
-static __device__ __noinline__ bool wait_bar(uint64_t* bar, uint32_t parity, unsigned ns, int code, int* dev_status,
-                                             volatile int* abort_flag) {
+static __device__ __noinline__ bool wait_bar_poll(uint64_t* bar, uint32_t parity, unsigned ns, int code,
+                                                  int* dev_status, volatile int* abort_flag) {
   return mbar_wait_relaxed(bar, parity, ns, code, dev_status, abort_flag);
+}
+// ... but a wait that is already over must not pay for a call (measured: ~230 cycles each)
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, unsigned ns, int code, int* dev_status,
+                                         volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return wait_bar_poll(bar, parity, ns, code, dev_status, abort_flag);
 }
 
 constexpr int kThreads = 512;
@@ -75,21 +81,13 @@ struct TapRowsArgs {
   int epi;
   uint32_t in_bytes;    // one item's slab
   uint32_t pitch_b;     // bytes between channel chunks of the re-laid operand
-  uint32_t half_out;    // bytes of 8 output channels of one item
   int* dev_status;
 };
-
-__device__ __forceinline__ void bulk_store(void* gdst, const void* ssrc, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(ssrc)),
-               "r"(bytes)
-               : "memory");
-}
 
 // shared-memory map (offsets are multiples of 128):
 //   kRawStages x in_bytes                     raw slabs (c, h, w)
 //   2 x 2 x (C/4) x pitch_b                   re-laid operand, [buffer][hi | lo][chunk][pixel][4]
 //   3 x 16 x kDumpPitch floats                accumulator rows (kh, f) of the item being reduced
-//   2 x out_bytes                             output staging, by item parity
 //   barriers
 template <int C>
 __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRowsArgs a) {
@@ -100,8 +98,7 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
   uint8_t* raw = smem;
   uint8_t* bop = raw + (size_t)kRawStages * a.in_bytes;
   float* dump = reinterpret_cast<float*>(bop + (size_t)4 * b_half);
-  uint8_t* ost = reinterpret_cast<uint8_t*>(dump + 48 * kDumpPitch);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ost + (size_t)4 * a.half_out);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(dump + 48 * kDumpPitch);
   uint64_t* raw_full = bars;                      // [kRawStages]
   uint64_t* raw_empty = raw_full + kRawStages;    // [kRawStages]
   uint64_t* b_ready = raw_empty + kRawStages;     // [2]
@@ -110,15 +107,10 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
   uint64_t* acc_empty = acc_full + kAccBars;      // [kAccBars]
   uint64_t* a_ready = acc_empty + kAccBars;       // [1]
   uint64_t* a_free = a_ready + 1;                 // [1]
-  uint64_t* st_done = a_free + 1;                 // [2] staged outputs of an item complete (item parity)
-  uint64_t* st_free = st_done + 2;                // [2] its bulk store has read the staging region
-  uint64_t* dump_full = st_free + 2;              // [1] both units of the item are in shared memory
-  uint64_t* dump_free = dump_full + 1;            // [1] ... and have been reduced
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dump_free + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(a_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nq = a.F / 8;                         // warps (of a set) that own output channels
   if (threadIdx.x == 0) {
     for (int s = 0; s < kRawStages; ++s) {
       mbar_init(&raw_full[s], 1);
@@ -132,12 +124,6 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
       mbar_init(&acc_full[k], 1);
       mbar_init(&acc_empty[k], kDrainWarps);
     }
-    for (int k = 0; k < 2; ++k) {
-      mbar_init(&st_done[k], kDrainWarps);
-      mbar_init(&st_free[k], 1);
-    }
-    mbar_init(dump_full, kDrainWarps);
-    mbar_init(dump_free, kDrainWarps);
     mbar_init(a_ready, 4);
     mbar_init(a_free, 2);
     *abort_flag = 0;
@@ -323,16 +309,29 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
     const int plane_out = a.OH * a.OW;
     const bool even_ow = (a.OW & 1) == 0;
     const int row_blocks = (a.OH + 7) >> 3;
+    const int ntasks = a.F * row_blocks;               // at most 32: four per warp
+    int tf[4], toh[4];                                 // my tasks: channel and output row of this lane
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int task = dw + k * kDrainWarps;
+      tf[k] = task / row_blocks;
+      toh[k] = (task - tf[k] * row_blocks) * 8 + orow;
+      if (task >= ntasks || toh[k] >= a.OH) tf[k] = -1;
+    }
+    // The eight warps meet twice per item on a hardware barrier (the copy is complete / has been reduced).
+    // A warp whose wait ran out keeps meeting the others there and skips the work in between, so that
+    // nobody is left waiting at a barrier.
     bool ok = true;
-    for (int j = 0; j < nitems && ok; ++j) {
+    for (int j = 0; j < nitems; ++j) {
       const int g = (begin + j) / a.N;
-      const uint32_t sb = (uint32_t)j & 1, sph = ((uint32_t)j >> 1) & 1;
-      float* stage = reinterpret_cast<float*>(ost + (size_t)sb * 2 * a.half_out);
-      // the previous item has been reduced out of the copy area
-      if (j >= 1) ok = wait_bar(dump_free, (uint32_t)(j - 1) & 1, 32, 32, a.dev_status, abort_flag);
+      const int w = begin + j, n = w - g * a.N;
+      float* out = a.O + ((size_t)n * a.G + g) * (size_t)a.F * plane_out;
+      float bias[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) bias[k] = has_bias && tf[k] >= 0 ? __ldg(a.bias + g * a.F + tf[k]) : 0.f;
       for (int h = 0; h < U && ok; ++h) {
         const uint32_t u = (uint32_t)(j * U + h);
-        ok = wait_bar(&acc_full[u % kAccBars], (u / kAccBars) & 1, 32, 28, a.dev_status, abort_flag);
+        ok = wait_bar(&acc_full[u % kAccBars], (u / kAccBars) & 1, 20, 28, a.dev_status, abort_flag);
         if (!ok) break;
         tc_fence_after();
         const int ncols = h == U - 1 ? a.n_last : 128;
@@ -350,61 +349,43 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
             if (col0 + 4 * i < ncols) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
         }
       }
-      if (!ok) break;
-      mbar_arrive_warp(dump_full);
-      ok = wait_bar(dump_full, (uint32_t)j & 1, 20, 33, a.dev_status, abort_flag);
-      if (!ok) break;
-      if (j >= 2) {   // the staging region was last used by item j - 2: its bulk store has read it
-        ok = wait_bar(&st_free[sb], sph ^ 1, 32, 30, a.dev_status, abort_flag);
-        if (!ok) break;
-      }
-      for (int task = dw; task < a.F * row_blocks; task += kDrainWarps) {
-        const int f = task / row_blocks, oh = (task - f * row_blocks) * 8 + orow;
-        if (oh < a.OH) {
-          const float* src = dump + (size_t)f * kDumpPitch + oh * kW + oc4;
-          const float4 x0 = *reinterpret_cast<const float4*>(src);
-          const float4 x1 = *reinterpret_cast<const float4*>(src + 16 * kDumpPitch + kW);
-          const float4 x2 = *reinterpret_cast<const float4*>(src + 32 * kDumpPitch + 2 * kW);
-          const float bias = has_bias ? __ldg(a.bias + g * a.F + f) : 0.f;
-          float r[4] = {((x0.x + x1.x) + x2.x) + bias, ((x0.y + x1.y) + x2.y) + bias,
-                        ((x0.z + x1.z) + x2.z) + bias, ((x0.w + x1.w) + x2.w) + bias};
-          if (relu) {
+      asm volatile("bar.sync 1, 256;" ::: "memory");           // all 48 rows of the item are in shared memory
+      if (ok) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) r[i] = fmaxf(r[i], 0.f);
-          }
-          float* dst = stage + (size_t)f * plane_out + oh * a.OW + oc4;
-          if (even_ow) {   // rows of an even length start on 8-byte boundaries
-            if (oc4 < a.OW) *reinterpret_cast<float2*>(dst) = make_float2(r[0], r[1]);
-            if (oc4 + 2 < a.OW) *reinterpret_cast<float2*>(dst + 2) = make_float2(r[2], r[3]);
-          } else {
+        for (int k0 = 0; k0 < 4; k0 += 2) {   // two tasks' loads in flight together
+        float4 x[4][3];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              if (oc4 + i < a.OW) dst[i] = r[i];
+        for (int k = k0; k < k0 + 2; ++k) {
+          if (tf[k] >= 0) {
+            const float* src = dump + (size_t)tf[k] * kDumpPitch + toh[k] * kW + oc4;
+            x[k][0] = *reinterpret_cast<const float4*>(src);
+            x[k][1] = *reinterpret_cast<const float4*>(src + 16 * kDumpPitch + kW);
+            x[k][2] = *reinterpret_cast<const float4*>(src + 32 * kDumpPitch + 2 * kW);
           }
         }
-      }
-      mbar_arrive_warp(dump_free);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      mbar_arrive_warp(&st_done[sb]);
-    }
-  } else if (warp == 15) {
-    // ------------------------------------------------ output: one bulk store per item
-    // (a thread of its own, so that no drain warp waits for the others or for the store)
-    if (lane == 0) {
-      for (int j = 0; j < nitems; ++j) {
-        const int w = begin + j, g = w / a.N, n = w - g * a.N;
-        const uint32_t sb = (uint32_t)j & 1, sph = ((uint32_t)j >> 1) & 1;
-        if (j >= 1) {   // the store of item j - 1 has read its region: free for item j + 1, well before it gets there
-          tma_store_wait_read();
-          mbar_arrive(&st_free[sb ^ 1]);
+#pragma unroll
+        for (int k = k0; k < k0 + 2; ++k) {
+          if (tf[k] >= 0) {
+            float r[4] = {((x[k][0].x + x[k][1].x) + x[k][2].x) + bias[k], ((x[k][0].y + x[k][1].y) + x[k][2].y) + bias[k],
+                          ((x[k][0].z + x[k][1].z) + x[k][2].z) + bias[k], ((x[k][0].w + x[k][1].w) + x[k][2].w) + bias[k]};
+            if (relu) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) r[i] = fmaxf(r[i], 0.f);
+            }
+            float* dst = out + (size_t)tf[k] * plane_out + toh[k] * a.OW + oc4;
+            if (even_ow) {   // rows of an even length start on 8-byte boundaries
+              if (oc4 < a.OW) *reinterpret_cast<float2*>(dst) = make_float2(r[0], r[1]);
+              if (oc4 + 2 < a.OW) *reinterpret_cast<float2*>(dst + 2) = make_float2(r[2], r[3]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                if (oc4 + i < a.OW) dst[i] = r[i];
+            }
+          }
         }
-        if (!wait_bar(&st_done[sb], sph, 32, 31, a.dev_status, abort_flag)) break;
-        const size_t out_bytes = (size_t)nq * a.half_out;
-        bulk_store(reinterpret_cast<uint8_t*>(a.O) + ((size_t)n * a.G + g) * out_bytes,
-                   ost + (size_t)sb * 2 * a.half_out, (uint32_t)out_bytes);
-        tma_store_commit();
+        }
       }
-      tma_store_wait_all();
+      asm volatile("bar.sync 1, 256;" ::: "memory");           // ... and have been reduced
     }
   }
 
@@ -418,7 +399,7 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
 
 struct Geometry {
   int units, n_last;
-  uint32_t in_bytes, pitch_b, half_out;
+  uint32_t in_bytes, pitch_b;
   size_t smem;
 };
 
@@ -428,16 +409,14 @@ bool geometry(const tcb200_problem_t& p, Geometry* g) {
   if (W != kW || H < 3 || H > 16) return false;
   if (KH != 3 || KW < 1 || KW > 3) return false;
   if (!(C == 8 || C == 16) || !(F == 8 || F == 16)) return false;
-  const int64_t OH = H - KH + 1, OW = W - KW + 1;
   const int64_t PL = H * W;
   g->units = (int)ceil_div(PL, 128);
   g->n_last = (int)(PL - 128 * (g->units - 1));
   g->in_bytes = (uint32_t)(C * PL * 4);
   g->pitch_b = (uint32_t)((PL + kPadPixels) * 16);
-  g->half_out = (uint32_t)(8 * OH * OW * 4);
   g->smem = (size_t)kRawStages * g->in_bytes + (size_t)4 * (C / 4) * g->pitch_b +
-            (size_t)48 * kDumpPitch * 4 + (size_t)4 * g->half_out + 512;   // barriers, tensor-memory slot, abort flag
-  return g->in_bytes % 128 == 0 && g->half_out % 16 == 0 && g->smem <= 200 * 1024;
+            (size_t)48 * kDumpPitch * 4 + 512;   // barriers, tensor-memory slot, abort flag
+  return g->in_bytes % 128 == 0 && g->smem <= 200 * 1024;
 }
 
 }  // namespace
@@ -464,7 +443,7 @@ int group_conv_tap_rows_plan(Plan& plan) {
 
 // false: the pointers do not allow the bulk copies (16-byte alignment); the caller takes another kernel
 bool group_conv_tap_rows_aligned(const float* I, const float* O) {
-  return ((((uintptr_t)I) | ((uintptr_t)O)) & 15) == 0;
+  return (((uintptr_t)I) & 15) == 0 && (((uintptr_t)O) & 7) == 0;   // bulk copies of I, 8-byte stores to O
 }
 
 int group_conv_tap_rows_launch(const Plan& plan, const float* I, const float* W, const float* bias, float* O,
@@ -481,7 +460,7 @@ int group_conv_tap_rows_launch(const Plan& plan, const float* I, const float* W,
   a.items = a.N * a.G;
   a.units = g.units; a.n_last = g.n_last;
   a.epi = p.epilogue;
-  a.in_bytes = g.in_bytes; a.pitch_b = g.pitch_b; a.half_out = g.half_out;
+  a.in_bytes = g.in_bytes; a.pitch_b = g.pitch_b;
   a.dev_status = dev_status;
   const bool c16 = p.conv[2] == 16;
   auto fn = c16 ? group_conv_tap_rows_kernel<16> : group_conv_tap_rows_kernel<8>;
