@@ -457,11 +457,21 @@ def run_product(args):
             "window_us": win, "roofline_frac_window": round(troof / win["p50"], 3),
             "bound": "tensor" if split and t_tensor > t_hbm else "hbm",
             "kernel": p.exe.describe(), "rotating_sets": p.sets, "shard_shapes": [list(s) for s in p.w.shapes]}
-        if p.name == "group_conv":
-            # C = F = 16: an MMA would be 128 x 16 x 8 and the fp32 path is bound by the FMA pipe, not by HBM
+        if p.name == "group_conv" and not split:
+            # the fp32 kernels of this family are bound by the FMA pipe, not by HBM
             fma_us = (p.full.flops / 2.0) / (FMA_PEAK_TFMA * 1e6 * world)
             entry.update({"bound": "fma", "fma_floor_us": round(fma_us, 2),
                           "fma_frac": round(fma_us / us, 3), "fma_frac_window": round(fma_us / win["p50"], 3)})
+        elif p.name == "group_conv":
+            # Tensor-core kernel with the filter rows as accumulator rows: KH * F = 48 of an MMA's 128 rows carry work
+            # and all H * W pixels of an item are computed for its OH * OW outputs, so the tensor pipe ISSUES
+            # 3 (3xTF32) x 128/48 x 256/196 x the algorithmic flops; at the pipe's measured 4096 flop per clock and SM
+            # that is the floor this formulation can reach.
+            (_, _, _, H, W), (_, F, _, KH, KW) = p.full.shapes[0], p.full.shapes[1]
+            factor = 3.0 * 128.0 / (KH * F) * (H * W) / ((H - KH + 1) * (W - KW + 1))
+            pipe_us = p.full.flops * factor / (4096.0 * 148 * 1965.0 * world)
+            entry.update({"pipe_floor_us": round(pipe_us, 2), "pipe_frac_window": round(pipe_us / win["p50"], 3),
+                          "pipe_note": "MMA flops issued = %.2f x algorithmic; 4096 flop/clk/SM at 1965 MHz" % factor})
         if ga:
             entry["gather"] = ga
         per_config.append(entry)

@@ -147,7 +147,7 @@ const Plan* plan_of(const tcb200_plan_t* handle);
 // tensor-core variant with the filter rows as accumulator rows (group_conv_tap_rows.cu)
 bool group_conv_tap_rows_ok(const tcb200_problem_t& p);
 int group_conv_tap_rows_plan(Plan& plan);
-bool group_conv_tap_rows_aligned(const float* I, const float* O);
+bool group_conv_tap_rows_aligned(const float* I, const float* W, const float* O);
 int group_conv_tap_rows_launch(const Plan& plan, const float* I, const float* W, const float* bias, float* O,
                                cudaStream_t s, int* dev_status);
 // tensor-core variant (group_conv_tcgen05.cu)

@@ -745,6 +745,11 @@ int pick_band(const tcb200_problem_t& p, int ft, size_t* bytes) {
 int group_conv_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n) {
   if (!valid(p)) return TCB200_ERR_INVALID_ARGUMENT;
   int cnt = 0;
+  // tensor-core form with the filters stationary in tensor memory (stages = 3: its accumulator ring)
+  if (group_conv_tap_rows_ok(p)) {
+    if (cnt < max && out) out[cnt] = tcb200_tile_t{TCB200_VARIANT_TCGEN05_TS, 128, 128, 8, 3, 512, 3};
+    ++cnt;
+  }
   if (item_ok(p)) {  // stages = 4: one item per CTA, input staged in four cp.async groups
     if (cnt < max && out) out[cnt] = tcb200_tile_t{TCB200_VARIANT_SIMT, 0, 4, 1, 4, kItemThreads, 0};
     ++cnt;
@@ -776,11 +781,6 @@ int group_conv_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int
       ++cnt;
     }
   }
-  // tensor-core form with the filters stationary in tensor memory (stages = 3: its accumulator ring)
-  if (group_conv_tap_rows_ok(p)) {
-    if (cnt < max && out) out[cnt] = tcb200_tile_t{TCB200_VARIANT_TCGEN05_TS, 128, 128, 8, 3, 512, 3};
-    ++cnt;
-  }
   // tensor-core implicit GEMM: correct and fp32-accurate, but hand-off latency bound on small
   // problems (see group_conv_tcgen05.cu); the sweep can still pick it where it wins
   if (group_conv_tc_ok(p)) {
@@ -802,6 +802,10 @@ int group_conv_plan(Plan& plan) {
   if (!valid(p)) return TCB200_ERR_INVALID_ARGUMENT;
   if (p.epilogue == TCB200_EPI_RELU) return TCB200_ERR_UNSUPPORTED;
   tcb200_tile_t& t = plan.tile;
+  // default where it applies: the tensor-core kernel with the filters stationary in tensor memory (measured
+  // against the one-item SIMT kernels on 1024 / 512 / 256 / 128 items: 20.7 / 14.1 / 9.7 / 7.3 us against
+  // 26.1 / 16.8 / 10.6 / 9.9 us)
+  if (t.variant == TCB200_VARIANT_AUTO && group_conv_tap_rows_ok(p)) { t.variant = TCB200_VARIANT_TCGEN05_TS; t.stages = 3; }
   if (t.variant == TCB200_VARIANT_AUTO && !rows_ok(p) && group_conv_tc_ok(p)) t.variant = TCB200_VARIANT_TCGEN05_TS;
   if (t.variant == TCB200_VARIANT_TCGEN05_TS && t.stages == 3) return group_conv_tap_rows_plan(plan);
   if (t.variant == TCB200_VARIANT_TCGEN05_TS) return group_conv_tc_plan(plan);
@@ -902,7 +906,7 @@ int group_conv_launch(const Plan& plan, const float* I, const float* W, const fl
   const bool multi = plan.kernel_id == 103 || plan.kernel_id == 104;
   const bool item_misaligned = ((plan.kernel_id == 101 || plan.kernel_id == 102 || plan.kernel_id == 105 || multi) &&
                                 ((((uintptr_t)I) | ((uintptr_t)W)) & 15) != 0) ||
-                               (plan.kernel_id == 201 && !group_conv_tap_rows_aligned(I, O));
+                               (plan.kernel_id == 201 && !group_conv_tap_rows_aligned(I, W, O));
   if (plan.kernel_id == 201 && !item_misaligned) return group_conv_tap_rows_launch(plan, I, W, bias, O, s, dev_status);
   if (plan.kernel_id == 105 && !item_misaligned) {
     const bool k33 = a.KH == 3 && a.KW == 3;

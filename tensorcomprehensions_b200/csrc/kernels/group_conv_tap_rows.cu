@@ -81,13 +81,15 @@ struct TapRowsArgs {
   int epi;
   uint32_t in_bytes;    // one item's slab
   uint32_t pitch_b;     // bytes between channel chunks of the re-laid operand
+  uint32_t w_bytes;     // one group's filters
   int* dev_status;
 };
 
 // shared-memory map (offsets are multiples of 128):
 //   kRawStages x in_bytes                     raw slabs (c, h, w)
 //   2 x 2 x (C/4) x pitch_b                   re-laid operand, [buffer][hi | lo][chunk][pixel][4]
-//   3 x 16 x kDumpPitch floats                accumulator rows (kh, f) of the item being reduced
+//   w_bytes                                   raw filters of the current group (f, c, kh, kw)
+//   2 x 3 x 16 x kDumpPitch floats            accumulator rows (kh, f) of the items being copied / reduced
 //   barriers
 template <int C>
 __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRowsArgs a) {
@@ -97,8 +99,9 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
   const uint32_t b_half = (uint32_t)(C / 4) * a.pitch_b;
   uint8_t* raw = smem;
   uint8_t* bop = raw + (size_t)kRawStages * a.in_bytes;
-  float* dump = reinterpret_cast<float*>(bop + (size_t)4 * b_half);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(dump + 48 * kDumpPitch);
+  const float* wraw = reinterpret_cast<const float*>(bop + (size_t)4 * b_half);
+  float* dump = reinterpret_cast<float*>(bop + (size_t)4 * b_half + a.w_bytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(dump + 2 * 48 * kDumpPitch);
   uint64_t* raw_full = bars;                      // [kRawStages]
   uint64_t* raw_empty = raw_full + kRawStages;    // [kRawStages]
   uint64_t* b_ready = raw_empty + kRawStages;     // [2]
@@ -107,7 +110,9 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
   uint64_t* acc_empty = acc_full + kAccBars;      // [kAccBars]
   uint64_t* a_ready = acc_empty + kAccBars;       // [1]
   uint64_t* a_free = a_ready + 1;                 // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(a_free + 1);
+  uint64_t* w_full = a_free + 1;                  // [1] a group's raw filters have landed
+  uint64_t* w_free = w_full + 1;                  // [1] ... and have been read into registers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(w_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -126,6 +131,8 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
     }
     mbar_init(a_ready, 4);
     mbar_init(a_free, 2);
+    mbar_init(w_full, 1);
+    mbar_init(w_free, 4);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -145,11 +152,21 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
   if (warp == 12) {
     // ------------------------------------------------ producer: one bulk copy per item
     if (lane == 0) {
+      int cur_g = -1;
+      uint32_t epoch = 0;
       for (int j = 0; j < nitems; ++j) {
         const int st = j % kRawStages;
         const uint32_t ph = (uint32_t)(j / kRawStages) & 1;
-        if (!wait_bar(&raw_empty[st], ph ^ 1, 32, 22, a.dev_status, abort_flag)) break;
         const int w = begin + j, g = w / a.N, n = w - g * a.N;
+        if (g != cur_g) {   // first item of a group: its filters, one contiguous block, ahead of the slab
+          if (epoch > 0 && !wait_bar(w_free, (epoch - 1) & 1, 32, 34, a.dev_status, abort_flag)) break;
+          mbar_expect_tx(w_full, a.w_bytes);
+          bulk_load(const_cast<float*>(wraw), reinterpret_cast<const uint8_t*>(a.W) + (size_t)g * a.w_bytes, a.w_bytes,
+                    w_full);
+          cur_g = g;
+          ++epoch;
+        }
+        if (!wait_bar(&raw_empty[st], ph ^ 1, 32, 22, a.dev_status, abort_flag)) break;
         mbar_expect_tx(&raw_full[st], a.in_bytes);
         bulk_load(raw + (size_t)st * a.in_bytes,
                   reinterpret_cast<const uint8_t*>(a.I) + ((size_t)n * a.G + g) * a.in_bytes, a.in_bytes,
@@ -229,16 +246,18 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
       *reinterpret_cast<float4*>(bop + (size_t)buf * b_half + (size_t)ch * a.pitch_b + (size_t)(PL + px) * 16) =
           make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    // Filters of group g into tensor memory.  They are fetched before the wait for the MMAs of the previous group
-    // (which still read the old ones) and written after it.
+    // Filters of the next group into tensor memory.  They are read from the staged block before the wait for the
+    // MMAs of the previous group (which still read the old ones) and written after it.
     auto filters = [&](const int g) -> bool {
-      const float* wg = a.W + ((size_t)g * a.F + wf) * C * a.KH * a.KW + wkh * a.KW;
+      if (!wait_bar(w_full, epoch & 1, 32, 35, a.dev_status, abort_flag)) return false;
+      const float* wg = wraw + (size_t)wf * C * a.KH * a.KW + wkh * a.KW;
       float wv[3 * C];
 #pragma unroll
       for (int col = 0; col < 3 * C; ++col) {
         const int kw = col / C, c = col - kw * C;
-        wv[col] = wlive && kw < a.KW ? __ldg(wg + (size_t)c * a.KH * a.KW + kw) : 0.f;
+        wv[col] = wlive && kw < a.KW ? wg[c * a.KH * a.KW + kw] : 0.f;
       }
+      mbar_arrive_warp(w_free);   // the values are in registers: the next group's block may land
       if (cur_g >= 0) {
         if (!wait_bar(a_free, (epoch - 1) & 1, 64, 21, a.dev_status, abort_flag)) return false;
         tc_fence_after();
@@ -300,7 +319,7 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const int kh = lane >> 3, f_mine = q * 8 + (lane & 7);
     const bool live_row = kh < 3 && f_mine < a.F;
-    float* my_row = dump + (size_t)(kh * 16 + f_mine) * kDumpPitch;
+    const int my_row = (kh * 16 + f_mine) * kDumpPitch;
     // Reduce: a warp task = one output channel x eight output rows; lane = (row, group of four columns).
     const int dw = warp - 4;
     const int orow = lane >> 2, oc4 = (lane & 3) * 4;
@@ -318,14 +337,16 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
       toh[k] = (task - tf[k] * row_blocks) * 8 + orow;
       if (task >= ntasks || toh[k] >= a.OH) tf[k] = -1;
     }
-    // The eight warps meet twice per item on a hardware barrier (the copy is complete / has been reduced).
-    // A warp whose wait ran out keeps meeting the others there and skips the work in between, so that
-    // nobody is left waiting at a barrier.
+    // The eight warps meet once per item on a hardware barrier: the copy is complete.  Items alternate between
+    // two copy areas, so the barrier of item j + 1 (which a warp reaches after its reduction of item j) is also
+    // what lets the copy of item j + 2 overwrite item j.  A warp whose wait ran out keeps meeting the others
+    // there and skips the work in between, so that nobody is left waiting at a barrier.
     bool ok = true;
     for (int j = 0; j < nitems; ++j) {
       const int g = (begin + j) / a.N;
       const int w = begin + j, n = w - g * a.N;
       float* out = a.O + ((size_t)n * a.G + g) * (size_t)a.F * plane_out;
+      float* area = dump + (size_t)(j & 1) * 48 * kDumpPitch;
       float bias[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) bias[k] = has_bias && tf[k] >= 0 ? __ldg(a.bias + g * a.F + tf[k]) : 0.f;
@@ -343,7 +364,7 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
         tc_fence_before();
         mbar_arrive_warp(&acc_empty[u % kAccBars]);          // the accumulator goes back to the issuers
         if (live_row) {
-          float4* dst = reinterpret_cast<float4*>(my_row + h * 128 + col0);
+          float4* dst = reinterpret_cast<float4*>(area + my_row + h * 128 + col0);
 #pragma unroll
           for (int i = 0; i < 8; ++i)
             if (col0 + 4 * i < ncols) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
@@ -357,7 +378,7 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
 #pragma unroll
         for (int k = k0; k < k0 + 2; ++k) {
           if (tf[k] >= 0) {
-            const float* src = dump + (size_t)tf[k] * kDumpPitch + toh[k] * kW + oc4;
+            const float* src = area + (size_t)tf[k] * kDumpPitch + toh[k] * kW + oc4;
             x[k][0] = *reinterpret_cast<const float4*>(src);
             x[k][1] = *reinterpret_cast<const float4*>(src + 16 * kDumpPitch + kW);
             x[k][2] = *reinterpret_cast<const float4*>(src + 32 * kDumpPitch + 2 * kW);
@@ -385,7 +406,6 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
         }
         }
       }
-      asm volatile("bar.sync 1, 256;" ::: "memory");           // ... and have been reduced
     }
   }
 
@@ -399,7 +419,7 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
 
 struct Geometry {
   int units, n_last;
-  uint32_t in_bytes, pitch_b;
+  uint32_t in_bytes, pitch_b, w_bytes;
   size_t smem;
 };
 
@@ -414,9 +434,10 @@ bool geometry(const tcb200_problem_t& p, Geometry* g) {
   g->n_last = (int)(PL - 128 * (g->units - 1));
   g->in_bytes = (uint32_t)(C * PL * 4);
   g->pitch_b = (uint32_t)((PL + kPadPixels) * 16);
+  g->w_bytes = (uint32_t)(F * C * KH * KW * 4);
   g->smem = (size_t)kRawStages * g->in_bytes + (size_t)4 * (C / 4) * g->pitch_b +
-            (size_t)48 * kDumpPitch * 4 + 512;   // barriers, tensor-memory slot, abort flag
-  return g->in_bytes % 128 == 0 && g->smem <= 200 * 1024;
+            g->w_bytes + (size_t)2 * 48 * kDumpPitch * 4 + 512;   // barriers, tensor-memory slot, abort flag
+  return g->in_bytes % 128 == 0 && g->w_bytes % 128 == 0 && g->smem <= 226 * 1024;
 }
 
 }  // namespace
@@ -442,8 +463,8 @@ int group_conv_tap_rows_plan(Plan& plan) {
 }
 
 // false: the pointers do not allow the bulk copies (16-byte alignment); the caller takes another kernel
-bool group_conv_tap_rows_aligned(const float* I, const float* O) {
-  return (((uintptr_t)I) & 15) == 0 && (((uintptr_t)O) & 7) == 0;   // bulk copies of I, 8-byte stores to O
+bool group_conv_tap_rows_aligned(const float* I, const float* W, const float* O) {
+  return ((((uintptr_t)I) | ((uintptr_t)W)) & 15) == 0 && (((uintptr_t)O) & 7) == 0;   // bulk copies in, 8-byte stores out
 }
 
 int group_conv_tap_rows_launch(const Plan& plan, const float* I, const float* W, const float* bias, float* O,
@@ -451,7 +472,7 @@ int group_conv_tap_rows_launch(const Plan& plan, const float* I, const float* W,
   const tcb200_problem_t& p = plan.p;
   Geometry g;
   if (!geometry(p, &g)) return TCB200_ERR_UNSUPPORTED;
-  if (!group_conv_tap_rows_aligned(I, O)) return TCB200_ERR_ALIGNMENT;
+  if (!group_conv_tap_rows_aligned(I, W, O)) return TCB200_ERR_ALIGNMENT;
   TapRowsArgs a;
   a.I = I; a.W = W; a.bias = bias; a.O = O;
   a.N = (int)p.conv[0]; a.G = (int)p.conv[1]; a.F = (int)p.conv[3];
@@ -460,12 +481,12 @@ int group_conv_tap_rows_launch(const Plan& plan, const float* I, const float* W,
   a.items = a.N * a.G;
   a.units = g.units; a.n_last = g.n_last;
   a.epi = p.epilogue;
-  a.in_bytes = g.in_bytes; a.pitch_b = g.pitch_b;
+  a.in_bytes = g.in_bytes; a.pitch_b = g.pitch_b; a.w_bytes = g.w_bytes;
   a.dev_status = dev_status;
   const bool c16 = p.conv[2] == 16;
   auto fn = c16 ? group_conv_tap_rows_kernel<16> : group_conv_tap_rows_kernel<8>;
   static std::atomic<uint64_t> configured[2];
-  TCB200_CUDA_TRY(ensure_dynamic_smem(fn, 200 * 1024, plan.device, configured[c16]));
+  TCB200_CUDA_TRY(ensure_dynamic_smem(fn, 226 * 1024, plan.device, configured[c16]));
   TCB200_CUDA_TRY(launch_pdl(fn, plan.launch.grid, plan.launch.block, g.smem, s, a));
   return TCB200_OK;
 }

@@ -63,6 +63,10 @@ def test_query_and_plan_without_gpu():
     c = cabi.group_conv_problem(32, 32, 16, 16, 16, 16, 3, 3)
     plan = cabi.Plan(c)
     grid, block = plan.geometry()
+    assert grid == (148, 1, 1) and block == (512, 1, 1)   # default: persistent tensor-core kernel, filter rows as accumulator rows
+    assert "variant=tcgen05_ts tile=128x128x8 stages=3" in plan.describe()
+    item = [t for t in cabi.query(c) if t.variant == cabi.VARIANT_SIMT and t.stages == 4 and t.threads == 128][0]
+    grid, block = cabi.Plan(c, item).geometry()
     assert grid == (1024, 1, 1) and block == (128, 1, 1)  # item kernel: one CTA per (n, g), 2 channels per thread
     rows = [t for t in cabi.query(c) if t.variant == cabi.VARIANT_SIMT and t.bk == 2][0]
     assert cabi.Plan(c, rows).geometry()[0][:2] == (32, 16)  # rows kernel: one CTA per (g, pair of n)

@@ -86,6 +86,8 @@ def test_contraction_outputs_stay_inside(cuda, case, offset):
 
 @pytest.mark.parametrize("offset", [0, 1])
 @pytest.mark.parametrize("dims,stages", [
+    ((3, 5, 16, 16, 16, 16, 3, 3), 3),     # tensor-core kernel, filter rows as accumulator rows (8-byte stores)
+    ((9, 20, 16, 8, 11, 16, 3, 2), 3),     # ... odd row length (scalar stores), a short second unit, runs of items
     ((3, 5, 16, 16, 16, 16, 3, 3), 4),     # item kernel
     ((3, 5, 16, 16, 16, 16, 3, 3), 6),     # channel-split item kernel
     ((40, 16, 8, 12, 16, 16, 3, 3), 5),    # multi-item kernel, ragged last CTA
@@ -100,7 +102,8 @@ def test_group_conv_outputs_stay_inside(cuda, dims, stages, offset):
     p = cabi.group_conv_problem(*dims)
     t = None
     if stages is not None:
-        cands = [c for c in cabi.query(p) if c.variant == cabi.VARIANT_SIMT and c.stages == stages and (stages or c.bk == 0)]
+        variant = cabi.VARIANT_TCGEN05_TS if stages == 3 else cabi.VARIANT_SIMT
+        cands = [c for c in cabi.query(p) if c.variant == variant and c.stages == stages and (stages or c.bk == 0)]
         assert cands, "the tile this case is about is not listed"
         t = cands[0]
     plan = cabi.Plan(p, t)
