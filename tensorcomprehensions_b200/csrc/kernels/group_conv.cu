@@ -5,7 +5,7 @@
 // (library twins tc/library/group_convolution.h:26-44 and tc/library/convolution.h:26-31, whose
 // strides are template parameters; strides other than 1 run on the band kernel only).
 //
-// SIMT kernels (a tensor-core implicit-GEMM variant lives in group_conv_tcgen05.cu):
+// SIMT kernels (the tensor-core forms live in group_conv_tap_rows.cu, the default where it applies, and group_conv_tcgen05.cu):
 //  * rows kernel (default when W <= 16 and F % 4 == 0): one CTA per (g, pair of n).  A thread owns
 //    one output row h of four output channels: 4 x OW accumulators in registers.  Per (c, kh) it
 //    reads one input row (four 128-bit shared loads, row pitch padded to 20 floats so the eight
