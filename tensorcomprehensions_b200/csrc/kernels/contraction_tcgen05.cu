@@ -58,6 +58,7 @@ struct TcArgs {
   int a_batched, b_batched;  // 0: operand shared by all batch entries
   int c_vec;                 // 128-bit stores allowed
   int tma_store;             // pair kernel: epilogue through the staging tile and tiled TMA stores
+  int c_transposed;          // pair kernel: the kernel's (row, column) is C's (column, row): C = (B A^T)^T, operands swapped
   int tail_S, tail_tiles, tail_kb;  // pair kernel: the last tail_tiles tiles split tail_S ways, tail_kb k-blocks each
                                     // (tail_S = 0: none)
   int ksplit_kb;             // split-K launch (TS and pair kernels): k-blocks per split, the "batch" index is the
@@ -1064,6 +1065,12 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
           bb[j + 1] = a.bias_on_m ? bias_m : __shfl_sync(0xffffffffu, bias_n.y, src);
         }
         if (row >= a.M || nb >= a.N) return;
+        if (a.c_transposed) {   // (only when the staged path is not available: strided 4-byte stores)
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (nb + j < a.N) a.C[(int64_t)bz * a.stride_c + (int64_t)(nb + j) * a.ldc + row] = v[j];
+          return;
+        }
         if (a.c_vec && nb + 16 <= a.N) {
 #pragma unroll
           for (int j = 0; j < 16; j += 4) {
@@ -1150,6 +1157,20 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       {
         const int r = q * 32 + lane;  // row of the CTA's tile
         uint8_t* out_tile = smem + ts_pair_out_offset();
+        if (a.c_transposed) {
+          // The tile leaves transposed: box q holds my warp's 32 rows as its 32 columns, my column c is its row
+          // c.  For one c the 32 lanes write the 32 words of one 128-byte row (its 16-byte chunks permuted by the
+          // swizzle): conflict-free 4-byte stores.
+#pragma unroll
+          for (int g = 0; g < PIECES; ++g) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int c = col0 + g * 16 + j;
+              *reinterpret_cast<float*>(out_tile + q * (BM * 128) + c * 128 + ((((lane >> 2) ^ (c & 7)) << 4) | ((lane & 3) << 2))) =
+                  acc[g][j];
+            }
+          }
+        } else
 #pragma unroll
         for (int g = 0; g < PIECES; ++g) {
           const int c0 = col0 + g * 16;  // 16 columns = 4 chunks of one 32-column box
@@ -1182,7 +1203,9 @@ contraction_ts_pair_kernel(const __grid_constant__ CUtensorMap tmA,
           for (int bx = 0; bx < BN / 32; ++bx) {
             if (tail)  // partial tile `slot`, this CTA's 128 rows of it: a dense [tiles * 256][128] matrix
               tma_store_3d(&tmP, out_tile + bx * (BM * 128), bx * 32, slot * (2 * BM) + (int)rank * BM, 0);
-            else if (n0 + bx * 32 < a.N && m0 < a.M)
+            else if (a.c_transposed) {
+              if (m0 + bx * 32 < a.M && n0 < a.N) tma_store_3d(&tmC, out_tile + bx * (BM * 128), m0 + bx * 32, n0, bz);
+            } else if (n0 + bx * 32 < a.N && m0 < a.M)
               tma_store_3d(&tmC, out_tile + bx * (BM * 128), n0 + bx * 32, m0, bz);
           }
           tma_store_commit();
@@ -1377,6 +1400,14 @@ int tail_split_factor(const tcb200_problem_t& p, int64_t tiles, int pairs) {
   return S >= 2 ? (int)S : 0;
 }
 
+// A contraction of at most 128 rows has no two row tiles to pair, but C^T = B A^T has: the CTA-pair kernel then
+// runs with the operands swapped and writes its tile transposed (transposed matmul 128 x 16384 x 4096: 64 pair
+// tiles of 256 x 128; per k-block a CTA moves 80 KB through shared memory instead of the 116 KB of the 128 x 112
+// single-CTA tile).  Plain "=" outputs without an epilogue only.
+bool pair_transposable(const tcb200_problem_t& p) {
+  return p.batch == 1 && p.M <= BM && p.N >= 2 * BM && p.epilogue == TCB200_EPI_NONE && !p.accumulate;
+}
+
 int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max, int* n) {
   *n = 0;
   if (!shape_ok(p) || !worth_it(p)) return TCB200_OK;
@@ -1416,6 +1447,13 @@ int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max,
       if (t < c.t * 0.98) { c.t = t; c.split_k = kTailSplitBase + tailS; }
     }
     c.t *= 0.999;  // ties go to the pair tile
+    cands[nc++] = c;
+  }
+  if (pair_transposable(p)) {
+    const int pairs = std::max(1, sms / 2);
+    const int64_t tiles = ceil_div(p.N, 2 * BM);
+    Cand c{TCB200_VARIANT_TCGEN05_PAIR, 2 * BM, kPairBN, kPairBSlots, 1, 0.0};
+    c.t = tc_time_estimate(p, tiles, pairs, 0.56, 1);
     cands[nc++] = c;
   }
   for (int i = 0; i < nc; ++i)
@@ -1479,6 +1517,14 @@ int contraction_tc_plan(Plan& plan) {
     if (t.bn != kPairBN || (t.split_tf32 != 3 && t.split_tf32 != 4)) return TCB200_ERR_UNSUPPORTED;
     if (ceil_div(p.M, 2 * BM) > 65535) return TCB200_ERR_UNSUPPORTED;
     t.bm = 2 * BM; t.bk = BK; t.stages = kPairBSlots; t.threads = kTsThreads;
+    if (pair_transposable(p) && t.split_k == 1) {   // operands swapped, tile written transposed
+      const int64_t tiles = ceil_div(p.N, 2 * BM) * ceil_div(p.M, kPairBN);
+      plan.launch.grid = dim3(2u * (unsigned)std::min<int64_t>(tiles, std::max(1, plan.sms / 2)), 1, 1);
+      plan.launch.block = dim3(kTsThreads, 1, 1);
+      plan.launch.smem = ts_pair_smem_bytes();
+      plan.kernel_id = 301284;
+      return TCB200_OK;
+    }
     const int64_t tiles = ceil_div(p.N, kPairBN) * ceil_div(p.M, 2 * BM) * p.batch * (tail_split ? 1 : t.split_k);
     plan.launch.grid = dim3(2u * (unsigned)std::min<int64_t>(tiles, std::max(1, plan.sms / 2)), 1, 1);
     plan.launch.block = dim3(kTsThreads, 1, 1);
@@ -1529,9 +1575,17 @@ void tc_map_cache_delete(void* c) { delete static_cast<TcMapCache*>(c); }
 
 int contraction_tc_launch(const Plan& plan, const float* A, const float* B, const float* bias,
                           float* C, cudaStream_t s, int* dev_status, float* scratch, void* map_cache) {
-  const tcb200_problem_t& p = plan.p;
+  const tcb200_problem_t& po = plan.p;                  // the problem as the caller states it (C's layout)
   if (((uintptr_t)A | (uintptr_t)B) & 15) return TCB200_ERR_ALIGNMENT;
-  const bool pair = plan.kernel_id == 301283;
+  const bool transposed = plan.kernel_id == 301284;     // C^T = B A^T on the pair kernel
+  tcb200_problem_t p = po;                              // the problem as the kernel runs it
+  if (transposed) {
+    std::swap(p.M, p.N);
+    std::swap(p.lda, p.ldb);
+    std::swap(p.stride_a, p.stride_b);
+    std::swap(A, B);
+  }
+  const bool pair = plan.kernel_id == 301283 || transposed;
   const int tailS = plan.tile.split_k > kTailSplitBase ? plan.tile.split_k - kTailSplitBase : 0;
   const int S = !tailS && plan.tile.split_k > 1 ? plan.tile.split_k : 1;
   if ((S > 1 || tailS) && !scratch) return TCB200_ERR_INVALID_ARGUMENT;
@@ -1539,7 +1593,7 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
   const int tail_tiles = tailS ? (int)(pair_tiles % std::max(1, plan.sms / 2)) : 0;
   // where the tensor-core kernel writes: the output, or the partial planes [S][M][N] of a split-K launch
   float* Ck = S > 1 ? scratch : C;
-  const int64_t ldck = S > 1 ? p.N : p.ldc, stride_ck = S > 1 ? p.M * p.N : p.stride_c;
+  const int64_t ldck = S > 1 ? p.N : po.ldc, stride_ck = S > 1 ? p.M * p.N : po.stride_c;
   const int64_t batch_k = S > 1 ? S : p.batch;
 
   TcArgs a;
@@ -1557,6 +1611,7 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
   a.c_vec = ((uintptr_t)Ck & 15) == 0 && ldck % 4 == 0 && stride_ck % 4 == 0 && bias_vec;
   a.dev_status = dev_status;
   a.tma_store = pair && a.c_vec && !a.accumulate;
+  a.c_transposed = transposed;
 
   TcMaps local;
   TcMaps* m = &local;
@@ -1582,7 +1637,9 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
     if (st != TCB200_OK) return st;
     m->tc = m->tb;  // unused by the kernel unless the staged epilogue is on
     // output map for the staged epilogue: {N, M, batch}, boxes of 32 columns x 128 rows
-    m->has_tc = a.tma_store && make_operand_map(&m->tc, Ck, p.N, p.M, ldck, batch_k, stride_ck, BM) == TCB200_OK;
+    // (C as the caller lays it out: in a transposed launch its rows are the kernel's columns)
+    m->has_tc = a.tma_store &&
+                make_operand_map(&m->tc, Ck, S > 1 ? p.N : po.N, S > 1 ? p.M : po.M, ldck, batch_k, stride_ck, BM) == TCB200_OK;
     m->tp = m->tb;  // unused by the kernel unless the launch has a split tail
     if (tailS) {
       // the partial tiles of the tail: a dense matrix of [tailS * tail_tiles * 256] rows of 128 floats
@@ -1598,7 +1655,8 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
 
   int st;
   switch (plan.kernel_id) {
-    case 301283: st = launch_pair(plan, ta, tb, tc, tp, a, s); break;
+    case 301283:
+    case 301284: st = launch_pair(plan, ta, tb, tc, tp, a, s); break;
     case 100643: st = launch_ts<64>(plan, ta, tb, a, s); break;
     case 101283: st = launch_ts<128>(plan, ta, tb, a, s); break;
     case 101123: st = launch_ts<112>(plan, ta, tb, a, s); break;

@@ -21,12 +21,12 @@
 //     done through shared memory: eight warps copy the 48 live rows of a finished accumulator to shared memory
 //     (one 32-column load and eight 128-bit stores per warp and unit: the accumulator is free again a few
 //     hundred cycles after its last MMA), then every thread forms four adjacent outputs from three 128-bit
-//     loads, always as (kh0 + kh1) + kh2, and stages them for the item's bulk store.
-// The slab arrives by one bulk copy (cp.async.bulk + mbarrier, 3 stages); four warps re-lay it into the
+//     loads, always as (kh0 + kh1) + kh2, adds the bias and stores them (8-byte stores; a warp covers 448
+//     contiguous bytes of one output channel).
+// The slab arrives by one bulk copy (cp.async.bulk + mbarrier, 3 stages), a group's filters by another; four warps re-lay it into the
 // chunked layout and produce the low half of the 3xTF32 split (the tensor core truncates the raw fp32 to
 // its high half itself); two threads in different warps issue the MMAs of alternate 128-pixel units (a
-// thread that has just issued MMAs pays a few hundred cycles for its next barrier wait); one thread issues the
-// bulk store of each finished item.  A warp reads only the 32 tensor-memory lanes of its position in its warp
+// thread that has just issued MMAs pays a few hundred cycles for its next barrier wait).  A warp reads only the 32 tensor-memory lanes of its position in its warp
 // quad, so the filter rows are written twice, into lanes 0-63 and 64-127 (the MMA computes 128 rows whatever
 // it is given): the warps at positions 0/1 copy the first 64 columns of a unit, those at 2/3 the other 64.
 // CTAs are persistent (one per SM) over a contiguous run of items in group-major order, so the filters change

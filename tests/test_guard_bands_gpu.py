@@ -49,6 +49,7 @@ CONTRACTIONS = [
     (1, 130, 100, 132, True, True, cabi.EPI_NONE, tile(cabi.VARIANT_TCGEN05_TS, 64, 3)),
     (1, 70, 230, 260, True, True, cabi.EPI_BIAS, tile(cabi.VARIANT_TCGEN05_TS, 112, 3)),
     (2, 300, 136, 96, True, True, cabi.EPI_NONE, tile(cabi.VARIANT_TCGEN05_PAIR, 128, 3)),
+    (1, 100, 1000, 520, True, True, cabi.EPI_NONE, tile(cabi.VARIANT_TCGEN05_PAIR, 128, 3)),   # pair tiles written transposed
     (1, 300, 200, 1000, True, True, cabi.EPI_BIAS_RELU, tile(cabi.VARIANT_TCGEN05_TS, 64, 3, split_k=5)),
     (1, 5000, 500, 1800, True, True, cabi.EPI_BIAS_RELU, None),   # pair tiles with a split tail
     (1, 130, 100, 132, True, True, cabi.EPI_NONE, tile(cabi.VARIANT_TCGEN05, 128, 3)),

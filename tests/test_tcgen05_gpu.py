@@ -354,3 +354,36 @@ def test_pair_tail_split_accumulates_and_takes_odd_outputs(cuda):
     plan.launch([A.to(cuda), B.to(cuda)], [view])
     torch.cuda.synchronize()
     assert_close(view, (A.double() @ B.double().t()).float(), K, [A, B], 3e-7, plan.describe())
+
+
+@pytest.mark.parametrize("case", [
+    # (M, N, K, ldc offset): at most 128 rows, so the CTA-pair kernel runs C^T = B A^T and writes its tiles transposed
+    (128, 1024, 512, 0),      # four pair tiles, everything aligned: staged tiles, TMA stores
+    (100, 1000, 520, 0),      # ragged rows, columns and k-blocks: the stores clip
+    (128, 16384, 4096, 0),    # the transposed matmul of the benchmark: 64 pair tiles
+    (77, 600, 256, 1),        # an output view at a 4-byte offset: strided direct stores
+])
+def test_pair_tiles_with_a_transposed_output(cuda, case):
+    M, N, K, off = case
+    A, B = _rand((M, K), 91), _rand((N, K), 92)
+    ref = (A.double() @ B.double().t()).float()
+    p = cabi.contraction_problem(1, M, N, K, True, True)
+    t = tc_tile(128, 3, pair=True)
+    plan = cabi.Plan(p, t)
+    assert plan.tile().variant == cabi.VARIANT_TCGEN05_PAIR and plan.geometry()[0][0] == 2 * min(74, -(-N // 256))
+    buf = torch.full((M * N + off,), float("nan"), device=cuda)
+    out = buf[off:].view(M, N)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda)
+    plan.launch([A.to(cuda), B.to(cuda)], [out], dev_status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert_close(out, ref, K, [A, B], 3e-7, plan.describe())
+    out2 = torch.full((M, N), float("nan"), device=cuda)
+    plan.launch([A.to(cuda), B.to(cuda)], [out2])
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2)
+    # an epilogue or "+=" keeps the kernel's own orientation (one CTA of each pair idles on these shapes)
+    pe = cabi.contraction_problem(1, M, N, K, True, True, accumulate=True)
+    init = _rand((M, N), 93)
+    out3, plan3 = run_plan(pe, [A.to(cuda), B.to(cuda)], (M, N), t, out_init=init.to(cuda))
+    assert_close(out3, (A.double() @ B.double().t() + init.double()).float(), K, what=plan3.describe())
