@@ -112,7 +112,8 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
   uint64_t* a_free = a_ready + 1;                 // [1]
   uint64_t* w_full = a_free + 1;                  // [1] a group's raw filters have landed
   uint64_t* w_free = w_full + 1;                  // [1] ... and have been read into registers
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(w_free + 1);
+  uint64_t* seq = w_free + 1;                     // [2] the first unit of an item has been issued (item parity)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(seq + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -133,6 +134,8 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
     mbar_init(a_free, 2);
     mbar_init(w_full, 1);
     mbar_init(w_free, 4);
+    mbar_init(&seq[0], 1);
+    mbar_init(&seq[1], 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -209,6 +212,12 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
             if (!ok) break;
             tc_fence_after();
           }
+          // The second unit of an item queues behind the first, which then completes earlier, is copied out and
+          // frees the accumulator that the second unit of the NEXT item needs (measured: 20.1 -> 19.8 us).
+          if (q == 1 && U == 2) {
+            ok = wait_bar(&seq[b], bph, 20, 36, a.dev_status, abort_flag);
+            if (!ok) break;
+          }
           const uint32_t idesc = make_idesc_tf32(128, h == U - 1 ? a.n_last : 128);
           const uint32_t acc = tmem_base + k * 128;
           uint32_t accumulate = 0;
@@ -226,6 +235,7 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
             }
           }
           umma_commit(&acc_full[u % kAccBars]);
+          if (q == 0 && U == 2) mbar_arrive(&seq[b]);
         }
         if (ok && mine) umma_commit(&b_free[b]);
       }
@@ -373,10 +383,10 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
       asm volatile("bar.sync 1, 256;" ::: "memory");           // all 48 rows of the item are in shared memory
       if (ok) {
 #pragma unroll
-        for (int k0 = 0; k0 < 4; k0 += 2) {   // two tasks' loads in flight together
+        for (int k0 = 0; k0 < 4; k0 += 4) {   // the loads of all four tasks in flight together
         float4 x[4][3];
 #pragma unroll
-        for (int k = k0; k < k0 + 2; ++k) {
+        for (int k = k0; k < k0 + 4; ++k) {
           if (tf[k] >= 0) {
             const float* src = area + (size_t)tf[k] * kDumpPitch + toh[k] * kW + oc4;
             x[k][0] = *reinterpret_cast<const float4*>(src);
@@ -385,7 +395,7 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
           }
         }
 #pragma unroll
-        for (int k = k0; k < k0 + 2; ++k) {
+        for (int k = k0; k < k0 + 4; ++k) {
           if (tf[k] >= 0) {
             float r[4] = {((x[k][0].x + x[k][1].x) + x[k][2].x) + bias[k], ((x[k][0].y + x[k][1].y) + x[k][2].y) + bias[k],
                           ((x[k][0].z + x[k][1].z) + x[k][2].z) + bias[k], ((x[k][0].w + x[k][1].w) + x[k][2].w) + bias[k]};
