@@ -382,11 +382,9 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
       }
       asm volatile("bar.sync 1, 256;" ::: "memory");           // all 48 rows of the item are in shared memory
       if (ok) {
+        float4 x[4][3];   // the loads of all four tasks in flight together
 #pragma unroll
-        for (int k0 = 0; k0 < 4; k0 += 4) {   // the loads of all four tasks in flight together
-        float4 x[4][3];
-#pragma unroll
-        for (int k = k0; k < k0 + 4; ++k) {
+        for (int k = 0; k < 4; ++k) {
           if (tf[k] >= 0) {
             const float* src = area + (size_t)tf[k] * kDumpPitch + toh[k] * kW + oc4;
             x[k][0] = *reinterpret_cast<const float4*>(src);
@@ -395,7 +393,7 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
           }
         }
 #pragma unroll
-        for (int k = k0; k < k0 + 4; ++k) {
+        for (int k = 0; k < 4; ++k) {
           if (tf[k] >= 0) {
             float r[4] = {((x[k][0].x + x[k][1].x) + x[k][2].x) + bias[k], ((x[k][0].y + x[k][1].y) + x[k][2].y) + bias[k],
                           ((x[k][0].z + x[k][1].z) + x[k][2].z) + bias[k], ((x[k][0].w + x[k][1].w) + x[k][2].w) + bias[k]};
@@ -413,7 +411,6 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
                 if (oc4 + i < a.OW) dst[i] = r[i];
             }
           }
-        }
         }
       }
     }
