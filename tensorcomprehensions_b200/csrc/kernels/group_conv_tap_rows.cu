@@ -152,6 +152,43 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
   const int nitems = end - begin;
   const int U = a.units;
 
+  // Filters of a group into tensor memory, by the four warps of one quad (every position writes its 32 lanes):
+  // lane 8 kh + j of position q holds filter row kh of output channel 8 (q mod 2) + j, columns (kw, c).  They are
+  // read from the staged block before the wait for the MMAs of the previous group (which still read the old
+  // ones) and written after it.  `epoch` = groups loaded before this one.
+  auto load_filters = [&](const uint32_t epoch) -> bool {
+    const int wkh = lane >> 3, wf = (warp & 1) * 8 + (lane & 7);
+    const bool wlive = wkh < a.KH && wf < a.F;
+    const uint32_t ta = tmem_base + kACol + ((uint32_t)((warp & 3) * 32) << 16);
+    if (!wait_bar(w_full, epoch & 1, 32, 35, a.dev_status, abort_flag)) return false;
+    const float* wg = wraw + (size_t)wf * C * a.KH * a.KW + wkh * a.KW;
+    float wv[3 * C];
+#pragma unroll
+    for (int col = 0; col < 3 * C; ++col) {
+      const int kw = col / C, c = col - kw * C;
+      wv[col] = wlive && kw < a.KW ? wg[c * a.KH * a.KW + kw] : 0.f;
+    }
+    mbar_arrive_warp(w_free);   // the values are in registers: the next group's block may land
+    if (epoch > 0) {
+      if (!wait_bar(a_free, (epoch - 1) & 1, 64, 21, a.dev_status, abort_flag)) return false;
+      tc_fence_after();
+    }
+#pragma unroll
+    for (int k8 = 0; k8 < 3 * C / 8; ++k8) {
+      if (k8 * 8 < KC) {
+        float lo[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) lo[i] = tf32_lo(wv[k8 * 8 + i]);
+        tmem_st8(ta + k8 * 8, &wv[k8 * 8]);
+        tmem_st8(ta + KC + k8 * 8, lo);
+      }
+    }
+    tmem_wait_st();
+    tc_fence_before();
+    mbar_arrive_warp(a_ready);
+    return true;
+  };
+
   if (warp == 12) {
     // ------------------------------------------------ producer: one bulk copy per item
     if (lane == 0) {
@@ -243,12 +280,10 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
   } else if (warp < 4) {
     // ------------------------------------------------ re-lay + split (and the filters, once per group): warps 0-3
     const int t = threadIdx.x;   // 0..127
-    // filters: lane 8 kh + j of warp q holds filter row kh of output channel 8 (q mod 2) + j, columns (kw, c)
-    const int wkh = lane >> 3, wf = (warp & 1) * 8 + (lane & 7);
-    const bool wlive = wkh < a.KH && wf < a.F;
-    const uint32_t ta = tmem_base + kACol + ((uint32_t)(warp * 32) << 16);
-    int cur_g = -1;
-    uint32_t epoch = 0;
+    // the first group's filters are loaded by the drain warps 4-7, which have nothing else to do yet; later
+    // groups here, after their first item's operand has been handed over (the MMAs of that item wait for both)
+    int cur_g = nitems > 0 ? begin / a.N : -1;
+    uint32_t epoch = 1;
     // pixels behind the plane, read by the shifted descriptors of the last unit: zero, once
     for (int e = t; e < 4 * (C / 4) * kPadPixels; e += 128) {
       const int buf = e / ((C / 4) * kPadPixels), r = e - buf * (C / 4) * kPadPixels;
@@ -256,42 +291,6 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
       *reinterpret_cast<float4*>(bop + (size_t)buf * b_half + (size_t)ch * a.pitch_b + (size_t)(PL + px) * 16) =
           make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    // Filters of the next group into tensor memory.  They are read from the staged block before the wait for the
-    // MMAs of the previous group (which still read the old ones) and written after it.
-    auto filters = [&](const int g) -> bool {
-      if (!wait_bar(w_full, epoch & 1, 32, 35, a.dev_status, abort_flag)) return false;
-      const float* wg = wraw + (size_t)wf * C * a.KH * a.KW + wkh * a.KW;
-      float wv[3 * C];
-#pragma unroll
-      for (int col = 0; col < 3 * C; ++col) {
-        const int kw = col / C, c = col - kw * C;
-        wv[col] = wlive && kw < a.KW ? wg[c * a.KH * a.KW + kw] : 0.f;
-      }
-      mbar_arrive_warp(w_free);   // the values are in registers: the next group's block may land
-      if (cur_g >= 0) {
-        if (!wait_bar(a_free, (epoch - 1) & 1, 64, 21, a.dev_status, abort_flag)) return false;
-        tc_fence_after();
-      }
-#pragma unroll
-      for (int k8 = 0; k8 < 3 * C / 8; ++k8) {
-        if (k8 * 8 < KC) {
-          float lo[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) lo[i] = tf32_lo(wv[k8 * 8 + i]);
-          tmem_st8(ta + k8 * 8, &wv[k8 * 8]);
-          tmem_st8(ta + KC + k8 * 8, lo);
-        }
-      }
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive_warp(a_ready);
-      cur_g = g;
-      ++epoch;
-      return true;
-    };
-    // the first group's filters while the first slab is on its way; later groups after their first item's
-    // operand has been handed over (the MMAs of that item wait for both)
-    if (nitems > 0) filters(begin / a.N);   // nothing to wait for the first time
     for (int j = 0; j < nitems; ++j) {
       const int st = j % kRawStages;
       const uint32_t ph = (uint32_t)(j / kRawStages) & 1;
@@ -318,7 +317,11 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
       mbar_arrive_warp(&raw_empty[st]);
       mbar_arrive_warp(&b_ready[b]);
       const int g = (begin + j) / a.N;
-      if (g != cur_g && !filters(g)) break;
+      if (g != cur_g) {
+        if (!load_filters(epoch)) break;
+        cur_g = g;
+        ++epoch;
+      }
     }
   } else if (warp < 12) {
     // ------------------------------------------------ drain: warps 4-11, all of them on every item
@@ -352,6 +355,7 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
     // what lets the copy of item j + 2 overwrite item j.  A warp whose wait ran out keeps meeting the others
     // there and skips the work in between, so that nobody is left waiting at a barrier.
     bool ok = true;
+    if (warp < 8 && nitems > 0) ok = load_filters(0);   // while the first slab is re-laid by warps 0-3
     for (int j = 0; j < nitems; ++j) {
       const int g = (begin + j) / a.N;
       const int w = begin + j, n = w - g * a.N;
