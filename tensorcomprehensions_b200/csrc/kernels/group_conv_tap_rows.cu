@@ -25,8 +25,8 @@
 //     contiguous bytes of one output channel).
 // The slab arrives by one bulk copy (cp.async.bulk + mbarrier, 3 stages), a group's filters by another; four warps re-lay it into the
 // chunked layout and produce the low half of the 3xTF32 split (the tensor core truncates the raw fp32 to
-// its high half itself); two threads in different warps issue the MMAs of alternate 128-pixel units (a
-// thread that has just issued MMAs pays a few hundred cycles for its next barrier wait).  A warp reads only the 32 tensor-memory lanes of its position in its warp
+// its high half itself); three threads in different warps issue the MMAs, each into its own accumulator (one
+// thread gets an MMA out every ~100 cycles, the pipe takes one every ~60).  A warp reads only the 32 tensor-memory lanes of its position in its warp
 // quad, so the filter rows are written twice, into lanes 0-63 and 64-127 (the MMA computes 128 rows whatever
 // it is given): the warps at positions 0/1 copy the first 64 columns of a unit, those at 2/3 the other 64.
 // CTAs are persistent (one per SM) over a contiguous run of items in group-major order, so the filters change
@@ -61,7 +61,7 @@ constexpr int kDrainWarps = 8;
 constexpr int kDumpPitch = 260;     // floats per accumulator row in shared memory: 128-bit stores of 32 rows hit all banks
 // Barriers of the accumulator hand-off, indexed by unit mod 6 although there are three accumulators.  A parity
 // wait only tells two phases apart, so every waiter must see each phase of its barrier: every drain warp waits
-// for every unit, and issuer u mod 2 owns the even or the odd barriers.  6 is also a multiple of the ring length,
+// for every unit, and issuer u mod 3 owns barriers u mod 3 and u mod 3 + 3.  6 is also a multiple of the ring length,
 // so the next unit on a barrier reuses the same accumulator and cannot complete a phase before the waiters of
 // the previous one have been through.
 constexpr int kAccBars = 6;
@@ -112,8 +112,7 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
   uint64_t* a_free = a_ready + 1;                 // [1]
   uint64_t* w_full = a_free + 1;                  // [1] a group's raw filters have landed
   uint64_t* w_free = w_full + 1;                  // [1] ... and have been read into registers
-  uint64_t* seq = w_free + 1;                     // [2] the first unit of an item has been issued (item parity)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(seq + 2);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(w_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -131,11 +130,9 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
       mbar_init(&acc_empty[k], kDrainWarps);
     }
     mbar_init(a_ready, 4);
-    mbar_init(a_free, 2);
+    mbar_init(a_free, 3);
     mbar_init(w_full, 1);
     mbar_init(w_free, 4);
-    mbar_init(&seq[0], 1);
-    mbar_init(&seq[1], 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -213,10 +210,12 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
                   &raw_full[st]);
       }
     }
-  } else if (warp == 13 || warp == 14) {
-    // ------------------------------------------------ MMA issuers: units of alternate parity
+  } else if (warp >= 13) {
+    // ------------------------------------------------ MMA issuers: issuer q owns accumulator q (units u = q mod 3)
+    // One thread feeds the tensor pipe an MMA every ~100 cycles, the pipe takes one every ~60: with three
+    // issuers, one per accumulator, two or three units are in flight whenever the accumulators allow it.
     if (lane == 0) {
-      const uint32_t q = warp == 13 ? 0u : 1u;
+      const uint32_t q = (uint32_t)(warp - 13);
       int cur_g = -1;
       uint32_t epoch = 0;
       bool ok = true;
@@ -233,27 +232,20 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
         const uint32_t b = (uint32_t)j & 1, bph = ((uint32_t)j >> 1) & 1;
         const uint32_t bhi = smem_u32(bop + (size_t)(b * 2 + 0) * b_half);
         const uint32_t blo = smem_u32(bop + (size_t)(b * 2 + 1) * b_half);
+        // every issuer sees every phase of the barrier, also for an item in which it has no unit
+        ok = wait_bar(&b_ready[b], bph, 32, 24, a.dev_status, abort_flag);
+        if (!ok) break;
         bool mine = false;
         for (int h = 0; h < U && ok; ++h) {
           const uint32_t u = (uint32_t)(j * U + h);
-          if ((u & 1) != q) continue;
-          if (!mine) {
-            ok = wait_bar(&b_ready[b], bph, 32, 24, a.dev_status, abort_flag);
-            if (!ok) break;
-            mine = true;
-          }
+          if (u % kAccRing != q) continue;
+          mine = true;
           const uint32_t k = u % kAccRing;
           if (u >= kAccRing) {   // the accumulator's previous unit has been drained
             const uint32_t v = u - kAccRing;
             ok = wait_bar(&acc_empty[v % kAccBars], (v / kAccBars) & 1, 32, 25, a.dev_status, abort_flag);
             if (!ok) break;
             tc_fence_after();
-          }
-          // The second unit of an item queues behind the first, which then completes earlier, is copied out and
-          // frees the accumulator that the second unit of the NEXT item needs (measured: 20.1 -> 19.8 us).
-          if (q == 1 && U == 2) {
-            ok = wait_bar(&seq[b], bph, 20, 36, a.dev_status, abort_flag);
-            if (!ok) break;
           }
           const uint32_t idesc = make_idesc_tf32(128, h == U - 1 ? a.n_last : 128);
           const uint32_t acc = tmem_base + k * 128;
@@ -272,7 +264,6 @@ __global__ void __launch_bounds__(kThreads, 1) group_conv_tap_rows_kernel(TapRow
             }
           }
           umma_commit(&acc_full[u % kAccBars]);
-          if (q == 0 && U == 2) mbar_arrive(&seq[b]);
         }
         if (ok && mine) umma_commit(&b_free[b]);
       }
