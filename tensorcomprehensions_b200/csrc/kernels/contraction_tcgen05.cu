@@ -1453,7 +1453,7 @@ int contraction_tc_query(const tcb200_problem_t& p, tcb200_tile_t* out, int max,
     const int pairs = std::max(1, sms / 2);
     const int64_t tiles = ceil_div(p.N, 2 * BM);
     Cand c{TCB200_VARIANT_TCGEN05_PAIR, 2 * BM, kPairBN, kPairBSlots, 1, 0.0};
-    c.t = tc_time_estimate(p, tiles, pairs, 0.56, 1);
+    c.split_k = pick_split_k(p, tiles, pairs, 0.56, &c.t);   // the shards of a multi-GPU run: 8-32 tiles for 74 pairs
     cands[nc++] = c;
   }
   for (int i = 0; i < nc; ++i)
@@ -1517,8 +1517,8 @@ int contraction_tc_plan(Plan& plan) {
     if (t.bn != kPairBN || (t.split_tf32 != 3 && t.split_tf32 != 4)) return TCB200_ERR_UNSUPPORTED;
     if (ceil_div(p.M, 2 * BM) > 65535) return TCB200_ERR_UNSUPPORTED;
     t.bm = 2 * BM; t.bk = BK; t.stages = kPairBSlots; t.threads = kTsThreads;
-    if (pair_transposable(p) && t.split_k == 1) {   // operands swapped, tile written transposed
-      const int64_t tiles = ceil_div(p.N, 2 * BM) * ceil_div(p.M, kPairBN);
+    if (pair_transposable(p) && !tail_split) {   // operands swapped, tile written transposed
+      const int64_t tiles = ceil_div(p.N, 2 * BM) * ceil_div(p.M, kPairBN) * t.split_k;
       plan.launch.grid = dim3(2u * (unsigned)std::min<int64_t>(tiles, std::max(1, plan.sms / 2)), 1, 1);
       plan.launch.block = dim3(kTsThreads, 1, 1);
       plan.launch.smem = ts_pair_smem_bytes();
@@ -1593,7 +1593,8 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
   const int tail_tiles = tailS ? (int)(pair_tiles % std::max(1, plan.sms / 2)) : 0;
   // where the tensor-core kernel writes: the output, or the partial planes [S][M][N] of a split-K launch
   float* Ck = S > 1 ? scratch : C;
-  const int64_t ldck = S > 1 ? p.N : po.ldc, stride_ck = S > 1 ? p.M * p.N : po.stride_c;
+  // (the partial planes of a split-K launch are dense [S][M][N] in the caller's orientation)
+  const int64_t ldck = S > 1 ? po.N : po.ldc, stride_ck = S > 1 ? po.M * po.N : po.stride_c;
   const int64_t batch_k = S > 1 ? S : p.batch;
 
   TcArgs a;
@@ -1639,7 +1640,7 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
     // output map for the staged epilogue: {N, M, batch}, boxes of 32 columns x 128 rows
     // (C as the caller lays it out: in a transposed launch its rows are the kernel's columns)
     m->has_tc = a.tma_store &&
-                make_operand_map(&m->tc, Ck, S > 1 ? p.N : po.N, S > 1 ? p.M : po.M, ldck, batch_k, stride_ck, BM) == TCB200_OK;
+                make_operand_map(&m->tc, Ck, po.N, po.M, ldck, batch_k, stride_ck, BM) == TCB200_OK;
     m->tp = m->tb;  // unused by the kernel unless the launch has a split tail
     if (tailS) {
       // the partial tiles of the tail: a dense matrix of [tailS * tail_tiles * 256] rows of 128 floats
@@ -1674,7 +1675,7 @@ int contraction_tc_launch(const Plan& plan, const float* A, const float* B, cons
   if (S == 1) return st;
 
   // second pass: C = epilogue([C +] sum_s P[s])
-  return partial_planes_reduce(scratch, C, bias, (int)p.M, (int)p.N, S, p.ldc, p.epilogue, p.bias_on_m, p.accumulate,
+  return partial_planes_reduce(scratch, C, bias, (int)po.M, (int)po.N, S, po.ldc, po.epilogue, po.bias_on_m, po.accumulate,
                                plan.sms, s);
 }
 

@@ -364,13 +364,33 @@ def test_pair_tail_split_accumulates_and_takes_odd_outputs(cuda):
     (77, 600, 256, 1),        # an output view at a 4-byte offset: strided direct stores
 ])
 def test_pair_tiles_with_a_transposed_output(cuda, case):
+    _transposed_case(cuda, case, 1)
+
+
+@pytest.mark.parametrize("case,split", [
+    ((128, 2048, 4096, 0), 8),    # the 1/8 shard of the transposed matmul: 8 pair tiles, the reduction split 8 ways
+    ((100, 1000, 520, 0), 3),     # ragged everything, k-blocks that do not divide by the split
+    ((128, 512, 1024, 1), 4),     # the second pass writes an output view at a 4-byte offset
+])
+def test_pair_tiles_with_a_transposed_output_and_a_split_reduction(cuda, case, split):
+    """The partial planes are written transposed as well, i.e. in the output's own orientation, and the same
+    second pass as for every other split adds them."""
+    _transposed_case(cuda, case, split)
+    M, N, K, _ = case
+    if (M, N, K) == (128, 2048, 4096):   # what the family lists first for that shard
+        first = cabi.query(cabi.contraction_problem(1, M, N, K, True, True))[0]
+        assert first.variant == cabi.VARIANT_TCGEN05_PAIR and first.split_k > 1
+
+
+def _transposed_case(cuda, case, split):
     M, N, K, off = case
     A, B = _rand((M, K), 91), _rand((N, K), 92)
     ref = (A.double() @ B.double().t()).float()
     p = cabi.contraction_problem(1, M, N, K, True, True)
     t = tc_tile(128, 3, pair=True)
+    t.split_k = split
     plan = cabi.Plan(p, t)
-    assert plan.tile().variant == cabi.VARIANT_TCGEN05_PAIR and plan.geometry()[0][0] == 2 * min(74, -(-N // 256))
+    assert plan.tile().variant == cabi.VARIANT_TCGEN05_PAIR and plan.geometry()[0][0] == 2 * min(74, -(-N // 256) * split)
     buf = torch.full((M * N + off,), float("nan"), device=cuda)
     out = buf[off:].view(M, N)
     status = torch.zeros(1, dtype=torch.int32, device=cuda)
