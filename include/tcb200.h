@@ -56,7 +56,8 @@ enum {
   TCB200_VARIANT_SIMT_SMALL = 2, /* fp32 FMA, one whole small matrix pair per CTA (batched)      */
   TCB200_VARIANT_TCGEN05 = 3,    /* tcgen05/TMEM tiles fed by TMA, TF32 with optional 3x split   */
   TCB200_VARIANT_TCGEN05_TS = 4, /* same, 3xTF32 with the A operand staged in tensor memory     */
-  TCB200_VARIANT_TCGEN05_PAIR = 5 /* same on CTA pairs (cta_group::2): 256-row tiles, B split over the pair */
+  TCB200_VARIANT_TCGEN05_PAIR = 5 /* same on CTA pairs (cta_group::2): 256-row tiles, B split over the pair; an output of
+                                     at most 128 rows runs as C^T = B A^T with its tiles written transposed */
 };
 
 /* Status codes (0 = success, negative = error). */
@@ -100,7 +101,9 @@ typedef struct tcb200_problem {
 typedef struct tcb200_tile {
   int32_t variant;
   int32_t bm, bn, bk;  /* CTA tile (contraction); bm = rows of C1 per CTA (tensordot) */
-  int32_t stages;      /* TMA pipeline depth (tcgen05) */
+  int32_t stages;      /* TMA pipeline depth (tcgen05 contraction).  Group convolution: which kernel of the family
+                          (SIMT: 0 band / rows, 4 item, 5 run of items, 6 channel-split item; tcgen05_ts: 3 = filters
+                          stationary in tensor memory with the filter rows as accumulator rows, 4 = pixels x F) */
   int32_t threads;     /* CTA size */
   int32_t split_tf32;  /* tcgen05: 1 = one TF32 pass, 3 = 3xTF32 split keeping fp32 accuracy, 4 = the same with
                           every accumulator drained after each of its k-blocks (strict accumulation: meets the
