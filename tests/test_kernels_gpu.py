@@ -165,6 +165,7 @@ def test_contraction_shared_operand_and_padded_ld(cuda):
     (5, 3, 16, 8, 11, 16, 3, 2),    # ... 11 input rows (two units, the second short), 15 output columns
     (4, 2, 8, 16, 8, 16, 3, 1),     # ... one unit per item, one filter column
     (9, 50, 16, 8, 12, 16, 3, 2),   # ... three items per CTA, group changes inside a CTA's run
+    (37, 32, 8, 8, 16, 16, 3, 3),   # ... eight items per CTA: every ring of the kernel wraps several times
 ])
 @pytest.mark.parametrize("bias", [True, False])
 def test_group_conv_small(cuda, dims, bias):
