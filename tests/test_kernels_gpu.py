@@ -272,6 +272,9 @@ def test_group_conv_full_size(cuda):
     out, plan = run_plan(p, [I.to(cuda), W1.to(cuda), B.to(cuda)], (32, 32, 16, 14, 14))
     assert_close(out, orc.loop_group_conv(I, W1, B), 144, [I, W1, B], STRICT["group_conv"], plan.describe())
     assert_close(out, orc.aten_group_conv(I, W1, B), 144, what="vs conv2d")
+    assert "tcgen05_ts" in plan.describe() and "stages=3" in plan.describe()   # the family default for this shape
+    out2, _ = run_plan(p, [I.to(cuda), W1.to(cuda), B.to(cuda)], (32, 32, 16, 14, 14))
+    assert torch.equal(out, out2)   # fixed order of additions: the same bits on every run
 
 
 # ---------------------------------------------------------------- TMM / MLP3 through whatever the default tile is
