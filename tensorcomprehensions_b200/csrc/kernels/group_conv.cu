@@ -803,7 +803,7 @@ int group_conv_plan(Plan& plan) {
   if (p.epilogue == TCB200_EPI_RELU) return TCB200_ERR_UNSUPPORTED;
   tcb200_tile_t& t = plan.tile;
   // default where it applies: the tensor-core kernel with the filters stationary in tensor memory (measured
-  // against the one-item SIMT kernels on 1024 / 512 / 256 / 128 items: 18.9 / 13.0 / 9.0 / 6.5 us against
+  // against the one-item SIMT kernels on 1024 / 512 / 256 / 128 items: 18.35 / 12.25 / 8.3 / 6.06 us against
   // 26.1 / 16.8 / 10.6 / 9.9 us)
   if (t.variant == TCB200_VARIANT_AUTO && group_conv_tap_rows_ok(p)) { t.variant = TCB200_VARIANT_TCGEN05_TS; t.stages = 3; }
   if (t.variant == TCB200_VARIANT_AUTO && !rows_ok(p) && group_conv_tc_ok(p)) t.variant = TCB200_VARIANT_TCGEN05_TS;

@@ -101,14 +101,25 @@ __global__ void __launch_bounds__(kBulkThreads, 1) tensordot_bulk_kernel(BulkArg
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  __syncthreads();
-  pdl_sync();  // nothing above touches global memory
-
   const int groups = (a.C1 + a.R - 1) / a.R;          // work items per n
   const int64_t items = (int64_t)a.N * groups;
   const int64_t begin = items * blockIdx.x / gridDim.x;
   const int64_t end = items * (blockIdx.x + 1) / gridDim.x;
   const uint32_t row_bytes = (uint32_t)C2 * a.P4 * 16;
+  if (threadIdx.x == 32) {
+    // The first stages of this CTA are asked into L2 before the wait for the preceding kernel: a prefetch uses
+    // no value, and L2 is where that kernel's writes land, so the bulk copies below read what it wrote.
+    int it = 0;
+    for (int64_t item = begin; item < end && it < a.stages; ++item, ++it) {
+      const int n = (int)(item / groups), c1 = (int)(item % groups) * a.R;
+      const uint32_t bytes = min(a.R, a.C1 - c1) * row_bytes;
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.I0 + ((size_t)n * a.C1 + c1) * C2 * a.P4 * 4),
+                   "r"(bytes)
+                   : "memory");
+    }
+  }
+  __syncthreads();
+  pdl_sync();  // nothing above uses a value from global memory
 
   if (threadIdx.x < 32) {
     if (threadIdx.x == 0) {
